@@ -1,0 +1,339 @@
+"""Transformer building blocks selected by the string names used in model configs.
+
+Parameter names (``norm_1..4.weight``, ``attn.Wqkv.weight``, ``attn.qk_bias``, ``attn.proj.weight``,
+``mlp.fc.weight``, ``mlp.proj.weight``) and fused layouts (``Wqkv`` rows ``[Q;K;V]``, gated ``fc`` rows
+``[gate;up]``) are the checkpoint contract of the reference (recpre/model_dynamic.py:150-412,745-780).
+All arithmetic goes through ``ops.functional`` so the same module runs the PyTorch statements on CPU
+and the sm_100a kernels on a GPU.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as ops
+
+
+# ------------------------------------------------------------------------------------------
+# primitives
+# ------------------------------------------------------------------------------------------
+class Linear(nn.Module):
+    """Bias-optional linear layer whose weight is initialised by a role-aware initialiser
+    (recpre/config_dynamic.py:450-467)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, init=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self._init = init
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        if self._init is not None:
+            self._init(self.weight)
+        else:
+            nn.init.trunc_normal_(self.weight, std=1 / math.sqrt(self.in_features))
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+
+    def forward(self, x):
+        y = ops.linear(x, self.weight)
+        return y if self.bias is None else y + self.bias.to(y.dtype)
+
+    def extra_repr(self) -> str:
+        return f"{self.in_features} -> {self.out_features}, bias={self.bias is not None}"
+
+
+class RMSNorm(nn.Module):
+    """RMS norm with a learned scale; statistics in fp32 (recpre/norms.py:19-75)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, add_unit_offset: bool = False, learnable: bool = True):
+        super().__init__()
+        self.eps, self.add_unit_offset = eps, add_unit_offset
+        self.weight = nn.Parameter(torch.ones(dim)) if learnable else None
+
+    def _w(self):
+        if self.weight is None:
+            return None
+        return 1 + self.weight if self.add_unit_offset else self.weight
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self._w(), self.eps)
+
+    def forward_add(self, a, x):
+        """norm(a + x) in one pass."""
+        return ops.add_rmsnorm(a, x, self._w(), self.eps)
+
+    def reset_parameters(self) -> None:
+        if self.weight is not None:
+            nn.init.ones_(self.weight)
+
+
+class _PlainNorm(nn.Module):
+    """Adapter giving torch norms (LayerNorm / Identity) the ``forward_add`` entry."""
+
+    def __init__(self, inner: nn.Module):
+        super().__init__()
+        self.inner = inner
+
+    def forward(self, x):
+        return self.inner(x)
+
+    def forward_add(self, a, x):
+        return self.inner(a + x)
+
+
+class LayerNorm(nn.LayerNorm):
+    def forward_add(self, a, x):
+        return self.forward(a + x)
+
+
+class Identity(nn.Identity):
+    def __init__(self, *a, **k):
+        super().__init__()
+
+    def forward_add(self, a, x):
+        return a + x
+
+
+def make_norm(config, dim: int | None = None) -> nn.Module:
+    dim = config.n_embd if dim is None else dim
+    name = config.norm_class_name
+    if name in ("RMSNorm", "RMSNorm_llama", "FusedRMSNorm"):
+        return RMSNorm(dim, eps=config.norm_eps, add_unit_offset="Gemma" in config.name)
+    if name == "UnparametrizedRMSNorm":
+        return RMSNorm(dim, eps=config.norm_eps, learnable=False)
+    if name == "LayerNorm":
+        return LayerNorm(dim, eps=config.norm_eps)
+    if name == "Identity":
+        return Identity()
+    raise ValueError(f"unknown norm class {name!r}")
+
+
+class Relu2(nn.Module):
+    def forward(self, x):
+        return F.relu(x).square()
+
+
+def make_nonlin(name: str) -> nn.Module:
+    if name == "ReLU2":
+        return Relu2()
+    if hasattr(nn, name):
+        return getattr(nn, name)()
+    raise ValueError(f"Could not identify nonlinearity {name}")
+
+
+# ------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------
+class CausalSelfAttention(nn.Module):
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config = config
+        self.n_head, self.n_kv = config.n_head, config.num_key_value_heads
+        self.head_dim = config.n_embd // self.n_head
+        width = (self.n_head + 2 * self.n_kv) * self.head_dim
+        init = config.init
+        self.Wqkv = Linear(config.n_embd, width, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "qkv", layer_id))
+        if config.qk_bias:
+            self.qk_bias = nn.Parameter(torch.zeros(2, 1, self.n_head, self.head_dim))
+        else:
+            self.qk_bias = None
+        self.proj = Linear(config.n_embd, config.n_embd, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "out_attn", layer_id))
+        self.layer_id = layer_id
+        self.monitoring = False
+        self.latest_metrics: dict = {}
+
+    def forward(self, x, rope, mask=None):
+        B, S, E = x.shape
+        cos, sin = rope
+        qkv = self.Wqkv(x)
+        if self.config.clip_qkv is not None:
+            qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
+        if self.config.rope_settings.use_rope:
+            q, k, v = ops.qk_bias_rope(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+        else:
+            one, zero = torch.ones_like(cos), torch.zeros_like(sin)
+            q, k, v = ops.qk_bias_rope(qkv, self.qk_bias, one, zero, self.n_head, self.n_kv, self.head_dim)
+        if self.config.qk_norm:
+            q = F.rms_norm(q, (q.shape[-1],))
+            k = F.rms_norm(k, (k.shape[-1],))
+        if self.config.attn_impl == "debug-skip":
+            y = q  # attention bypass for pure-GEMM sanity models
+        else:
+            y = ops.causal_attention(q, k, v)
+        if self.monitoring:
+            self._monitor(q, k)
+        return self.proj(y.reshape(B, S, E))
+
+    @torch.no_grad()
+    def _monitor(self, q, k):
+        """Attention-entropy / max-logit telemetry on a small slice (recpre/model_dynamic.py:389-412)."""
+        qs, ks = q[:1, :256].float().transpose(1, 2), k[:1, :256].float().transpose(1, 2)
+        if ks.shape[1] != qs.shape[1]:
+            ks = ks.repeat_interleave(qs.shape[1] // ks.shape[1], dim=1)
+        logits = qs @ ks.transpose(-1, -2) / math.sqrt(q.shape[-1])
+        S = logits.shape[-1]
+        logits = logits.masked_fill(torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+        p = torch.softmax(logits, dim=-1)
+        ent = -(p * torch.log(p.clamp_min(1e-30))).sum(-1).mean()
+        self.latest_metrics = {f"attn_entropy_{self.layer_id}": ent.item(),
+                               f"max_attn_logit_{self.layer_id}": logits[logits.isfinite()].max().item()}
+
+
+# ------------------------------------------------------------------------------------------
+# MLPs
+# ------------------------------------------------------------------------------------------
+class BaseMLP(nn.Module):
+    def __init__(self, config, layer_id: int = 0, in_features: int = 0):
+        super().__init__()
+        in_features = in_features or config.n_embd
+        init = config.init
+        self.fc = Linear(in_features, config.intermediate_size, bias=config.bias,
+                         init=lambda w: init.init_weight_(w, "in_proj", layer_id))
+        self.proj = Linear(config.intermediate_size, config.n_embd, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "out_proj", layer_id))
+        self.nonlin = make_nonlin(config.nonlin_name)
+
+    def forward(self, x):
+        return self.proj(self.nonlin(self.fc(x)))
+
+
+class GatedMLP(nn.Module):
+    """proj(nonlin(gate) * up) with a single fused ``fc`` producing [gate | up]."""
+
+    def __init__(self, config, layer_id: int = 0, in_features: int = 0):
+        super().__init__()
+        in_features = in_features or config.n_embd
+        init = config.init
+        self.fc = Linear(in_features, 2 * config.intermediate_size, bias=config.bias,
+                         init=lambda w: init.init_weight_(w, "glu", layer_id))
+        self.proj = Linear(config.intermediate_size, config.n_embd, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "out_proj", layer_id))
+        self.is_silu = config.nonlin_name == "SiLU"
+        self.nonlin = make_nonlin(config.nonlin_name)
+
+    def forward(self, x):
+        h = self.fc(x)
+        if self.is_silu:
+            return self.proj(ops.swiglu(h))
+        a, b = h.chunk(2, dim=-1)
+        return self.proj(self.nonlin(a) * b)
+
+
+class BrickLP(nn.Module):
+    def __init__(self, config, layer_id: int = 0, in_features: int = 0):
+        super().__init__()
+        in_features = in_features or config.n_embd
+        self.fc = Linear(in_features, in_features, bias=False)
+
+    def forward(self, x):
+        return self.fc(x)
+
+
+MLP_CLASSES = {"BaseMLP": BaseMLP, "GatedMLP": GatedMLP, "LLaMAMLP": GatedMLP, "BrickLP": BrickLP}
+
+
+def make_mlp(config, layer_id: int, in_features: int = 0) -> nn.Module:
+    try:
+        return MLP_CLASSES[config.mlp_class_name](config, layer_id, in_features)
+    except KeyError:
+        raise ValueError(f"unknown MLP class {config.mlp_class_name!r}") from None
+
+
+# ------------------------------------------------------------------------------------------
+# blocks
+# ------------------------------------------------------------------------------------------
+class _TwoNormBlock(nn.Module):
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.norm_1 = make_norm(config)
+        self.attn = CausalSelfAttention(config, layer_id)
+        self.norm_2 = make_norm(config)
+        self.mlp = make_mlp(config, layer_id)
+        res, skip = config.init.get_scales(layer_id)
+        self.register_buffer("res_scale", torch.as_tensor(res), persistent=True)
+        self.register_buffer("skip_scale", torch.as_tensor(skip), persistent=True)
+
+
+class TransformerScaledPreNormBlock(_TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.attn(self.norm_1(x), rope, mask) * self.res_scale + x * self.skip_scale
+        return self.mlp(self.norm_2(x)) * self.res_scale + x * self.skip_scale
+
+
+class TransformerPreNormBlock(_TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.attn(self.norm_1(x), rope, mask) + x
+        return self.mlp(self.norm_2(x)) + x
+
+
+class TransformerPostNormBlock(_TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.norm_1.forward_add(self.attn(x, rope, mask), x)
+        return self.norm_2.forward_add(self.mlp(x), x)
+
+
+class ScaledTransformerPostNormBlock(_TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.norm_1(self.attn(x, rope, mask) * self.res_scale + x * self.skip_scale)
+        return self.norm_2(self.mlp(x) * self.res_scale + x * self.skip_scale)
+
+
+class SwinBlock(_TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.norm_1(self.attn(x, rope, mask)) + x
+        return self.norm_2(self.mlp(x)) + x
+
+
+class SandwichBlock(nn.Module):
+    """x = n2(attn(n1(x)) + x); x = n4(mlp(n3(x)) + x)   (recpre/model_dynamic.py:265-288)."""
+
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.norm_1 = make_norm(config)
+        self.attn = CausalSelfAttention(config, layer_id)
+        self.norm_2 = make_norm(config)
+        self.norm_3 = make_norm(config)
+        self.mlp = make_mlp(config, layer_id)
+        self.norm_4 = make_norm(config)
+
+    def forward(self, x, rope, mask=None):
+        x = self.norm_2.forward_add(self.attn(self.norm_1(x), rope, mask), x)
+        return self.norm_4.forward_add(self.mlp(self.norm_3(x)), x)
+
+
+class Brick(nn.Module):
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.mlp = make_mlp(config, layer_id)
+        self.layer_id = layer_id
+
+    def forward(self, x, rope, mask=None):
+        return self.mlp(x)
+
+
+BLOCK_CLASSES = {c.__name__: c for c in (
+    TransformerScaledPreNormBlock, TransformerPreNormBlock, TransformerPostNormBlock,
+    ScaledTransformerPostNormBlock, SwinBlock, SandwichBlock, Brick)}
+
+
+def make_block(config, layer_id: int) -> nn.Module:
+    try:
+        return BLOCK_CLASSES[config.block_class_name](config, layer_id)
+    except KeyError:
+        raise ValueError(f"unknown block class {config.block_class_name!r}") from None

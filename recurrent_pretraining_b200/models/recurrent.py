@@ -1,0 +1,309 @@
+"""Training models: the depth-recurrent LM and the plain GPT baseline.
+
+Forward contract (recpre/model_dynamic.py:1075-1162): ``model(input_ids, position_ids=, labels=,
+attention_mask=, return_logits=, num_steps_pair=) -> {"loss", "logits", "log_ppl"}``.  The recurrent
+model embeds, runs the prelude, draws a state, iterates the core ``n`` times without a graph and
+``k`` times with one (input re-injected each time), then ``ln_f -> coda -> ln_f -> tied head``.
+State-dict keys are ``transformer.{wte,prelude.i,adapter,core_block.i,coda.i,ln_f}.*``,
+``lm_head.weight`` and the fp32 buffer ``freqs_cis`` of shape [1, S, 1, hd/2, 2].
+
+B200 design notes.  The residual stream is bf16 on the GPU; no activation checkpointing is needed at
+micro-batch 1 x 4096 tokens (about 33 GB of saved activations for k = 8 out of 180 GB), so the
+``gradient_checkpointing`` flag re-computes only when asked.  The loss uses the fused linear +
+cross-entropy op, which never materialises the [tokens, vocab] logits unless ``return_logits``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint
+
+from ..ops import functional as ops
+from ..ops import reference as ref
+from .blocks import Linear, make_block, make_mlp, make_norm
+from .sampler import sample_recurrence
+
+
+def _rank() -> int:
+    import torch.distributed as dist
+
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+class _LMBase(nn.Module):
+    def _setup_rope(self, config) -> None:
+        length = config.randomize_positions_from or config.block_size
+        cos, sin = ref.rope_tables(config.head_size, length, config.rope_settings.rope_base,
+                                   config.rope_settings.rope_condense_ratio)
+        self.register_buffer("freqs_cis", ref.freqs_cis_buffer(cos, sin), persistent=True)
+
+    def _rope(self, seq_len: int, position_ids: Optional[torch.Tensor]):
+        """cos/sin [S, hd/2] fp32 views of the buffer for this call."""
+        fc = self.freqs_cis
+        if position_ids is None:
+            fc = fc[0, :seq_len, 0]
+        else:
+            fc = fc[0].index_select(0, position_ids.reshape(-1))[:, 0]
+        return fc[..., 0].contiguous(), fc[..., 1].contiguous()
+
+    def _loss(self, x, labels, return_logits: bool):
+        cfg = self.config
+        scale = cfg.init.logit_scale
+        logits = None
+        if labels is not None:
+            ignore = -100
+            if return_logits:
+                logits = ops.linear(x, self.lm_head.weight).float() * scale
+                loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), labels.view(-1),
+                                                         ignore_index=ignore)
+                z = self.objective.get("z_regularization", 0.0)
+                if z:
+                    lse = torch.logsumexp(logits.view(-1, logits.shape[-1]), dim=-1)
+                    valid = labels.view(-1) != ignore
+                    loss = loss + z * (lse.pow(2) * valid).sum() / valid.sum().clamp(min=1)
+            else:
+                loss = ops.linear_cross_entropy(x, self.lm_head.weight, labels, scale, ignore,
+                                                self.objective.get("z_regularization", 0.0))
+            return loss, logits, loss.detach().clone()
+        logits = ops.linear(x, self.lm_head.weight).float() * scale
+        zero = torch.zeros((), device=x.device)
+        return zero, logits, zero
+
+
+class RecurrentGPT(_LMBase):
+    def __init__(self, config, objective: Optional[dict] = None, gradient_checkpointing: bool = False, **_):
+        super().__init__()
+        self.config = config
+        self.objective = objective or {"ignore_index": -100, "z_regularization": 0.0}
+        E = config.n_embd
+        P, R, C = config.n_layers_in_prelude, config.n_layers_in_recurrent_block, config.n_layers_in_coda
+        init = config.init
+        prelude = nn.ModuleList(make_block(config, i) for i in range(P))
+        if config.injection_type == "linear":
+            adapter = Linear(2 * E, E, bias=config.bias, init=lambda w: init.init_weight_(w, "in_proj", P))
+        elif config.injection_type == "ffn":
+            adapter = make_mlp(config, 0, in_features=2 * E)
+        else:
+            adapter = nn.Identity()
+        core = nn.ModuleList(make_block(config, i + P) for i in range(R))
+        off = P + R * config.mean_recurrence
+        coda = nn.ModuleList(make_block(config, i + off) for i in range(C))
+        self.transformer = nn.ModuleDict(dict(
+            wte=nn.Embedding(config.padded_vocab_size, E), prelude=prelude, adapter=adapter, core_block=core,
+            coda=coda, ln_f=make_norm(config)))
+        self.emb_scale = init.embedding_scale
+        self.lm_head = Linear(E, config.padded_vocab_size, bias=False,
+                              init=lambda w: init.init_weight_(w, "head"))
+        if config.tie_embeddings:
+            self.lm_head.weight = self.transformer.wte.weight
+        self.max_seq_length = config.block_size
+        self.gradient_checkpointing = gradient_checkpointing
+        self._setup_rope(config)
+        self.step = 0
+        self.monitoring = False
+        self.latest_metrics: dict = {}
+        self.last_depths = (0, 0)
+        init.init_weight_(self.transformer.wte.weight, "embedding")
+
+    # -- pieces ------------------------------------------------------------------------
+    def state_sigma(self) -> float:
+        return self.config.init.get_std("embedding") * self.emb_scale * self.config.state_init_scale
+
+    def initialize_state(self, e: torch.Tensor) -> torch.Tensor:
+        """Random start state (recpre/model_dynamic.py:1353-1372); ``like-init`` is a +-3 sigma truncated
+        normal with sigma = sqrt(2/(5E)) * sqrt(E) for the ``takase`` family."""
+        mode = self.config.state_init
+        if self.config.injection_type == "none":
+            return e
+        if mode == "like-init":
+            seed = (self.step * 7919 + 104729 * (_rank() + 1)) & 0x7FFFFFFF
+            if not self.training:
+                seed = 12345
+            return ops.trunc_normal_state(e, self.state_sigma(), seed)
+        if mode == "normal":
+            return torch.randn_like(e)
+        if mode == "embed":
+            return torch.randn_like(e) / math.sqrt(e.shape[-1])
+        if mode == "zero":
+            return torch.zeros_like(e)
+        if mode == "unit":
+            x = torch.randn_like(e)
+            std, mean = torch.std_mean(x, dim=-1, keepdim=True)
+            return (x - mean) / std
+        raise ValueError(f"unknown state_init {mode!r}")
+
+    def sample_depths(self) -> tuple[int, int]:
+        c = self.config
+        return sample_recurrence(c.sampling_scheme, c.mean_recurrence, c.mean_backprop_depth, self.step,
+                                 training=self.training, rank=_rank(), lockstep_n=c.lockstep_n,
+                                 lockstep_k=c.lockstep_k)
+
+    def randomized_iteration_sampler(self):
+        n, k = self.sample_depths()
+        return torch.as_tensor(n, dtype=torch.long), torch.as_tensor(k, dtype=torch.long)
+
+    def core_block_forward(self, x, e, rope, mask, step: int):
+        c = self.config
+        inj = c.injection_type
+        if inj == "add":
+            x = x + e
+        elif inj == "gate":
+            x = x * e
+        elif inj == "linear":
+            x = ops.adapter(x, e, self.transformer.adapter.weight)
+            if self.transformer.adapter.bias is not None:
+                x = x + self.transformer.adapter.bias.to(x.dtype)
+        elif inj == "ffn":
+            x = self.transformer.adapter(torch.cat([x, e], dim=-1))
+        elif inj != "none":
+            raise ValueError("Invalid injection type")
+        noise = c.intermediate_noise_injection
+        if noise > 0:
+            if c.geom_noise_injection == "geom":
+                f = noise / (step + 1)
+            elif c.geom_noise_injection == "sqrt":
+                f = noise / math.sqrt(step + 1)
+            else:
+                f = noise
+            x = x * (1 - f) + torch.randn_like(x) * f
+        per_block = self.gradient_checkpointing and "per-block" in c.activation_checkpoint_impl
+        for block in self.transformer.core_block:
+            if per_block and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(block, x, rope, mask, use_reentrant=False)
+            else:
+                x = block(x, rope, mask)
+        return x
+
+    def iterate_forward(self, e, rope, mask, num_steps_pair=None, input_states=None):
+        x = self.initialize_state(e) if input_states is None else input_states
+        if num_steps_pair is None:
+            n, k = self.sample_depths()
+        else:
+            pair = [int(v) for v in torch.as_tensor(num_steps_pair).reshape(-1).tolist()]
+            n, k = (pair[0], pair[1]) if len(pair) > 1 else (pair[0], 0)
+        self.last_depths = (n, k)
+        xk = x
+        with torch.no_grad():
+            for step in range(n):
+                xk = x
+                x = self.core_block_forward(x, e, rope, mask, step)
+        per_iter = self.gradient_checkpointing and "per-iteration" in self.config.activation_checkpoint_impl
+        for step in range(k):
+            xk = x
+            if per_iter and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(self.core_block_forward, x, e, rope, mask, n + step,
+                                                      use_reentrant=False)
+            else:
+                x = self.core_block_forward(x, e, rope, mask, n + step)
+        return self.transformer.ln_f(x), n, k, xk.detach()
+
+    def contributions_per_step(self, k: int) -> dict:
+        """How many gradient contributions each parameter receives in one backward pass with k grad
+        iterations: k for the core and the adapter, 2 for a tied embedding/head, 2 for ln_f, else 1."""
+        out = {}
+        for name, p in self.named_parameters():
+            if ".core_block." in name or ".adapter." in name:
+                out[name] = max(k, 0)
+            elif name.endswith("wte.weight") and self.config.tie_embeddings:
+                out[name] = 2
+            elif ".ln_f." in name:
+                out[name] = 2 if k > 0 else 1
+            else:
+                out[name] = 1
+        return out
+
+    # -- forward -----------------------------------------------------------------------
+    def forward(self, input_ids, attention_mask=None, position_ids=None, labels=None, return_logits: bool = False,
+                num_steps_pair=None, input_states=None):
+        cfg = self.config
+        S = input_ids.shape[1]
+        if cfg.randomize_positions_from is not None and self.training:
+            position_ids = torch.sort(torch.randint(0, cfg.randomize_positions_from, (S,),
+                                                    device=input_ids.device))[0]
+        rope = self._rope(S, position_ids)
+        e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+        for block in self.transformer.prelude:
+            e = block(e, rope, attention_mask)
+        x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
+        x_rec = x
+        in_coda = self.gradient_checkpointing and "in-coda" in cfg.activation_checkpoint_impl
+        for block in self.transformer.coda:
+            if in_coda and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(block, x, rope, attention_mask, use_reentrant=False)
+            else:
+                x = block(x, rope, attention_mask)
+        x = self.transformer.ln_f(x)
+        if self.monitoring:
+            self.monitor_module(x, x_rec, xk, e, n, k)
+        loss, logits, log_ppl = self._loss(x, labels, return_logits or labels is None)
+        if labels is not None and self.training:
+            if cfg.mcleish_throttle and k > 0:
+                loss = loss / k
+            if cfg.elbayad_weighing:
+                t = cfg.mean_recurrence
+                w = torch.arange(1, 16 * t, device=loss.device, dtype=torch.float32) ** cfg.elbayad_exponent
+                w = w / torch.sum(torch.arange(1, t + 1, device=loss.device, dtype=torch.float32)
+                                  ** cfg.elbayad_exponent)
+                loss = loss * (w[n + k] / w[t // 2])
+        return {"loss": loss, "logits": logits if (return_logits or labels is None) else None, "log_ppl": log_ppl}
+
+    @torch.no_grad()
+    def monitor_module(self, x_out, x_rec, xk, e, n, k):
+        """Model telemetry for one step (recpre/model_dynamic.py:1374-1405)."""
+        xf, rf, kf = x_out.float(), x_rec.float(), xk.float()
+        tok = torch.nn.functional.normalize(xf[0], dim=-1)
+        corr = (tok @ tok.T).mean()
+        self.latest_metrics = {
+            "last_hidden_token_corr": corr.item(),
+            "last_hidden_norm": xf.norm(dim=-1).mean().item(),
+            "rec_hidden_norm": rf.norm(dim=-1).mean().item(),
+            "embed_norm": e.float().norm(dim=-1).mean().item(),
+            "rec_residual": (rf - kf).norm(dim=-1).mean().item(),
+            "num_steps_no_grad": n,
+            "num_steps_with_grad": k,
+        }
+
+
+class GPT(_LMBase):
+    """Non-recurrent decoder (recpre/model_dynamic.py:22-144)."""
+
+    def __init__(self, config, objective: Optional[dict] = None, gradient_checkpointing: bool = False, **_):
+        super().__init__()
+        self.config = config
+        self.objective = objective or {"ignore_index": -100, "z_regularization": 0.0}
+        init = config.init
+        self.transformer = nn.ModuleDict(dict(
+            wte=nn.Embedding(config.padded_vocab_size, config.n_embd),
+            h=nn.ModuleList(make_block(config, i) for i in range(config.n_layer)),
+            ln_f=make_norm(config)))
+        self.lm_head = Linear(config.n_embd, config.padded_vocab_size, bias=config.lm_head_bias,
+                              init=lambda w: init.init_weight_(w, "head"))
+        self.emb_scale = math.sqrt(config.n_embd) if config.scale_embeddings else init.embedding_scale
+        self.gradient_checkpointing = gradient_checkpointing
+        self.max_seq_length = config.block_size
+        self._setup_rope(config)
+        self.step = 0
+        self.monitoring = False
+        self.latest_metrics: dict = {}
+        self.last_depths = (0, config.n_layer)
+        init.init_weight_(self.transformer.wte.weight, "embedding")
+
+    def contributions_per_step(self, k: int) -> dict:
+        return {name: 1 for name, _ in self.named_parameters()}
+
+    def forward(self, input_ids, attention_mask=None, position_ids=None, labels=None, return_logits: bool = False,
+                num_steps_pair=None, **_):
+        S = input_ids.shape[1]
+        rope = self._rope(S, position_ids)
+        x = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+        for block in self.transformer.h:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(block, x, rope, attention_mask, use_reentrant=False)
+            else:
+                x = block(x, rope, attention_mask)
+        x = self.transformer.ln_f(x)
+        loss, logits, log_ppl = self._loss(x, labels, return_logits or labels is None)
+        return {"loss": loss, "logits": logits if (return_logits or labels is None) else None, "log_ppl": log_ppl}

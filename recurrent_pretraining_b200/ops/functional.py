@@ -1,0 +1,332 @@
+"""Differentiable front end of the op set.
+
+CPU tensors take the plain PyTorch statements in ``reference`` (ordinary autograd).  CUDA
+tensors take ``torch.autograd.Function``s whose forward and backward launch the sm_100a
+kernels through ``ops.cuda``; there is no silent fallback on a GPU: if the native library
+is missing the import of ``ops.cuda`` raises.
+
+Weight gradients on the CUDA path can be accumulated straight into a persistent fp32
+gradient buffer by the wgrad GEMM epilogue: a parameter that carries ``_fused_grad = True``
+and a preallocated ``.grad`` gets ``grad += dy^T x`` in place and autograd sees ``None``.
+After each contribution the optional callback ``param._on_grad(param)`` is invoked; the data
+parallel fabric uses it to learn when a bucket is complete (the recurrent core receives k
+contributions per step, the tied embedding two).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import reference as ref
+
+_cuda = None
+
+
+def cuda_backend():
+    global _cuda
+    if _cuda is None:
+        from . import cuda as _c
+
+        _cuda = _c
+    return _cuda
+
+
+def _lp(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 compute copy of a parameter: the persistent shadow kept by the optimizer when present."""
+    lp = getattr(weight, "_lp", None)
+    if lp is not None:
+        return lp
+    return weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
+
+
+def _notify(p: torch.Tensor) -> None:
+    cb = getattr(p, "_on_grad", None)
+    if cb is not None:
+        cb(p)
+
+
+def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
+    """dW = dy2^T x2.  Returns the tensor for autograd, or None after fused accumulation."""
+    C = cuda_backend()
+    if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+        C.gemm_tn(dy2, x2, out=weight.grad, accumulate=True)
+        _notify(weight)
+        return None
+    return C.gemm_tn(dy2, x2, out_dtype=torch.float32).to(weight.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# linear / adapter
+# ------------------------------------------------------------------------------------------
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        C = cuda_backend()
+        x2 = x.reshape(-1, x.shape[-1])
+        y = C.gemm_nt(x2, _lp(weight))
+        ctx.save_for_backward(x2, weight)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = C.gemm_nn(dy2, _lp(weight)).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy2, x2, weight) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if x.is_cuda:
+        return _Linear.apply(x, weight)
+    return ref.linear(x, weight)
+
+
+class _Adapter(torch.autograd.Function):
+    """y = x Ws^T + e We^T with W = [Ws | We] (no concatenation is materialised)."""
+
+    @staticmethod
+    def forward(ctx, x, e, weight):
+        C = cuda_backend()
+        E = x.shape[-1]
+        x2, e2 = x.reshape(-1, E), e.reshape(-1, E)
+        w = _lp(weight)
+        y = C.gemm_nt(x2, w[:, :E])
+        C.gemm_nt(e2, w[:, E:], out=y, accumulate=True)
+        ctx.save_for_backward(x2, e2, weight)
+        ctx.xshape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        x2, e2, weight = ctx.saved_tensors
+        E = x2.shape[-1]
+        w = _lp(weight)
+        dy2 = dy.reshape(-1, E)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = C.gemm_nn(dy2, w[:, :E]).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        de = C.gemm_nn(dy2, w[:, E:]).view(ctx.xshape) if ctx.needs_input_grad[1] else None
+        dw = None
+        if ctx.needs_input_grad[2]:
+            if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+                C.gemm_tn(dy2, x2, out=weight.grad[:, :E], accumulate=True)
+                C.gemm_tn(dy2, e2, out=weight.grad[:, E:], accumulate=True)
+                _notify(weight)
+            else:
+                dw = torch.empty(weight.shape, dtype=torch.float32, device=dy.device)
+                C.gemm_tn(dy2, x2, out=dw[:, :E])
+                C.gemm_tn(dy2, e2, out=dw[:, E:])
+                dw = dw.to(weight.dtype)
+        return dx, de, dw
+
+
+def adapter(x: torch.Tensor, e: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if x.is_cuda:
+        return _Adapter.apply(x, e, weight)
+    return ref.adapter(x, e, weight)
+
+
+# ------------------------------------------------------------------------------------------
+# norms
+# ------------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        C = cuda_backend()
+        x2 = x.reshape(-1, x.shape[-1])
+        y, rstd = C.rmsnorm_fwd(x2, weight, eps)
+        ctx.save_for_backward(x2, weight, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        x2, weight, rstd = ctx.saved_tensors
+        dx, dw = C.rmsnorm_bwd(dy.reshape(x2.shape), x2, weight, rstd, need_dw=ctx.needs_input_grad[1])
+        return dx.view(dy.shape), (dw.to(weight.dtype) if dw is not None else None), None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, x, weight, eps):
+        C = cuda_backend()
+        a2, x2 = a.reshape(-1, a.shape[-1]), x.reshape(-1, x.shape[-1])
+        y, s, rstd = C.add_rmsnorm_fwd(a2, x2, weight, eps)
+        ctx.save_for_backward(s, weight, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        s, weight, rstd = ctx.saved_tensors
+        ds, dw = C.rmsnorm_bwd(dy.reshape(s.shape), s, weight, rstd, need_dw=ctx.needs_input_grad[2])
+        ds = ds.view(dy.shape)
+        return ds, ds, (dw.to(weight.dtype) if dw is not None else None), None
+
+
+def rmsnorm(x, weight, eps: float):
+    if x.is_cuda:
+        return _RMSNorm.apply(x, weight, eps)
+    return ref.rmsnorm(x, weight, eps)
+
+
+def add_rmsnorm(a, x, weight, eps: float):
+    if x.is_cuda:
+        return _AddRMSNorm.apply(a, x, weight, eps)
+    return ref.add_rmsnorm(a, x, weight, eps)
+
+
+# ------------------------------------------------------------------------------------------
+# qk-bias + RoPE, attention, SwiGLU
+# ------------------------------------------------------------------------------------------
+class _QKBiasRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, qk_bias, cos, sin, n_head, n_kv, head_dim):
+        C = cuda_backend()
+        q, k, v = C.qk_bias_rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+        ctx.save_for_backward(cos, sin)
+        ctx.meta = (n_head, n_kv, head_dim, qk_bias is not None)
+        ctx.mark_non_differentiable()
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        C = cuda_backend()
+        cos, sin = ctx.saved_tensors
+        n_head, n_kv, head_dim, has_bias = ctx.meta
+        dqkv, dbias = C.qk_bias_rope_bwd(dq, dk, dv, cos, sin, n_head, n_kv, head_dim, has_bias)
+        return dqkv, dbias, None, None, None, None, None
+
+
+def qk_bias_rope(qkv, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int):
+    if qkv.is_cuda:
+        return _QKBiasRope.apply(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+    return ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        C = cuda_backend()
+        o, lse = C.attention_fwd(q, k, v, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        C = cuda_backend()
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = C.attention_bwd(do.contiguous(), q, k, v, o, lse, ctx.scale)
+        return dq, dk, dv, None
+
+
+def causal_attention(q, k, v, scale: float | None = None):
+    """q,k,v: [B,S,H,hd] -> [B,S,H,hd], causal, softmax scale defaults to 1/sqrt(hd)."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if q.is_cuda:
+        return _Attention.apply(q, k, v, scale)
+    return ref.causal_attention(q, k, v, scale)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h):
+        C = cuda_backend()
+        ctx.save_for_backward(h)
+        return C.swiglu_fwd(h)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        (h,) = ctx.saved_tensors
+        return C.swiglu_bwd(dy.contiguous(), h)
+
+
+def swiglu(h):
+    if h.is_cuda:
+        return _SwiGLU.apply(h)
+    return ref.swiglu(h)
+
+
+# ------------------------------------------------------------------------------------------
+# embedding, fused linear + cross-entropy, state init
+# ------------------------------------------------------------------------------------------
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, scale):
+        C = cuda_backend()
+        ctx.save_for_backward(ids, weight)
+        ctx.scale = scale
+        return C.embedding_fwd(ids, _lp(weight), scale)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        ids, weight = ctx.saved_tensors
+        if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+            C.embedding_bwd(dy.contiguous(), ids, weight.grad, ctx.scale)
+            _notify(weight)
+            return None, None, None
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy.device)
+        C.embedding_bwd(dy.contiguous(), ids, dw, ctx.scale)
+        return None, dw.to(weight.dtype), None
+
+
+def embedding(ids, weight, scale: float = 1.0):
+    if weight.is_cuda:
+        return _Embedding.apply(ids, weight, scale)
+    return ref.embedding(ids, weight, scale)
+
+
+class _LinearCE(torch.autograd.Function):
+    """Loss = mean CE(x W^T * logit_scale) without keeping the logits: the forward walks the rows in
+    chunks, keeps (lse, target logit) per row, and already produces dX and dW for a unit loss gradient
+    (the scheme of recpre/ops.py:1034-1040); backward only scales them by the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, labels, logit_scale, ignore_index, z_reg):
+        C = cuda_backend()
+        x2 = x.reshape(-1, x.shape[-1])
+        lab = labels.reshape(-1)
+        need_grad = x.requires_grad or weight.requires_grad
+        loss, dx, dw = C.linear_ce(x2, _lp(weight), lab, logit_scale, ignore_index, z_reg, need_grad=need_grad)
+        ctx.weight = weight
+        if need_grad:
+            ctx.save_for_backward(dx, dw)
+        ctx.xshape = x.shape
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dx, dw = ctx.saved_tensors
+        weight = ctx.weight
+        dx = (dx * dloss.to(dx.dtype)).view(ctx.xshape)
+        if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+            weight.grad.addcmul_(dw, dloss.to(dw.dtype))
+            _notify(weight)
+            return dx, None, None, None, None, None
+        return dx, (dw * dloss).to(weight.dtype), None, None, None, None
+
+
+def linear_cross_entropy(x, weight, labels, logit_scale: float = 1.0, ignore_index: int = -100, z_reg: float = 0.0):
+    if x.is_cuda:
+        return _LinearCE.apply(x, weight, labels, logit_scale, ignore_index, z_reg)
+    return ref.linear_cross_entropy(x, weight, labels, logit_scale, ignore_index, z_reg)
+
+
+def trunc_normal_state(like: torch.Tensor, std: float, seed: int, generator: torch.Generator | None = None):
+    """Fresh recurrent state with the shape/dtype/device of ``like``."""
+    if like.is_cuda:
+        return cuda_backend().trunc_normal(like.shape, std, seed, like.dtype, like.device)
+    if generator is None:
+        generator = torch.Generator(device="cpu")
+        generator.manual_seed(seed)
+    return ref.trunc_normal_state(like.shape, std, generator, like.device, like.dtype)
