@@ -1,0 +1,338 @@
+"""Headline benchmark: training tokens/s of nebel-raven-3.5b (seq 4096, micro-batch 1 per GPU, recurrence sampled
+with mean 32, truncated backprop depth 8, AdamW with global-norm clip 1.0) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 8 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same metric/config
+
+Rank 0 prints ONE JSON line.  Timing: CUDA events on the launching stream around exactly K steps, bracketed by a
+barrier + device synchronise on both sides, max over ranks.  The per-step working set (7.1 GB of bf16 weights
+streamed per recurrence, ~30 GB of activations) is far larger than the 126 MB L2, so no explicit L2 flush is needed.
+SM clocks and throttle reasons are sampled with nvidia-smi during the timed region.  A second timed region measures
+the same steps end to end through the public API (``TrainEngine.train_step``) including a pinned host->device copy
+of every step's tokens and a device->host read of every step's loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "baseline"))
+
+MODEL = "nebel-raven-3.5b"
+SEQ = 4096
+BASELINE_PUBLISHED = None  # the reference publishes no tokens/s figure for this config
+
+
+# ------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while a region is being timed (read-only query)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                 str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    return rank, world, local
+
+
+def max_over_ranks(value: float, device) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return value
+
+
+def sync_all(device):
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.synchronize(device)
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier(device_ids=[device.index])
+    torch.cuda.synchronize(device)
+
+
+def make_batches(n: int, vocab: int, seed: int, rank: int):
+    """Synthetic uniform-random token rows of block_size+1, pinned in host memory (one row per step)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed + 1000 * rank)
+    rows = torch.randint(0, vocab, (n, 1, SEQ + 1), generator=g, dtype=torch.int64)
+    return rows.pin_memory()
+
+
+def timed_region(step_fn, steps: int, device, sampler: ClockSampler | None):
+    """Device time in ms for `steps` calls of step_fn(i), max over ranks."""
+    import torch
+
+    sync_all(device)
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step_fn(i)
+    e1.record()
+    sync_all(device)
+    clocks = sampler.stop() if sampler else None
+    return max_over_ranks(e0.elapsed_time(e1), device), clocks
+
+
+# ------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.ops import cuda as C
+    from recurrent_pretraining_b200.parallel.fabric import Fabric
+    from recurrent_pretraining_b200.runtime.engine import TrainEngine
+
+    rank, world, local = dist_env()
+    fabric = Fabric.from_env(grad_sync=os.environ.get("B200_GRAD_SYNC"))
+    device = fabric.device
+    cfg = ModelConfig.from_name(args.model, lockstep_n=True, lockstep_k=True)
+    torch.manual_seed(1337)
+    with torch.device(device):
+        model = cfg.construct_model()
+    engine = TrainEngine(model, fabric, lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8, grad_clip=1.0,
+                         grad_accum=1)
+    total = args.warmup + args.steps
+    host = make_batches(total, cfg.padded_vocab_size, 0, rank)
+    dev_rows = host.to(device)
+
+    def device_step(i, base):
+        row = dev_rows[base + i]
+        engine.train_step(row[:, :-1], row[:, 1:])
+
+    for i in range(args.warmup):
+        device_step(i, 0)
+    start_micro, start_opt = engine.micro_step, engine.optimizer_step
+    launches0 = C.launch_count()
+    ms, clocks = timed_region(lambda i: device_step(i, args.warmup), args.steps, device, ClockSampler(local))
+    launches = C.launch_count() - launches0
+    status = C.check_device_status()
+
+    # end-to-end region: same step indices (same sampled recurrence depths), inputs from pinned host memory
+    engine.micro_step, engine.optimizer_step = start_micro, start_opt
+    losses = []
+
+    def e2e_step(i):
+        row = host[args.warmup + i].to(device, non_blocking=True)
+        out = engine.train_step(row[:, :-1], row[:, 1:])
+        losses.append(float(out["loss"].item()))
+
+    ms_e2e, _ = timed_region(e2e_step, args.steps, device, None)
+    tokens = world * SEQ * args.steps
+    value = tokens / (ms / 1e3)
+    rec = {
+        "metric": "train tokens/sec (raven-3.5B, r=32 mean sampled, bptt 8)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
+        "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
+        "config": {"model": args.model, "global_batch": world, "seq_len": SEQ, "parallelism": f"dp{world}",
+                   "micro_batch": 1, "mean_recurrence": cfg.mean_recurrence, "backprop_depth": cfg.mean_backprop_depth,
+                   "sampling": cfg.sampling_scheme, "optimizer": "AdamW fused, clip 1.0",
+                   "grad_sync": fabric.grad_sync if world > 1 else "none",
+                   "l2": "working set (7.1 GB weights per recurrence) >> 126 MB L2; no explicit flush",
+                   "activation_checkpointing": False},
+        "clocks": clocks,
+        "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches, "device_status": status,
+        "final_loss": losses[-1] if losses else None,
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
+    }
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    fabric.shutdown()
+
+
+# ------------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The unmodified reference (baseline/_ref): its RecurrentGPT, SimpleFabric (bf16-mixed autocast wrapper,
+    chunked NCCL all-reduce inside ``fabric.backward``), its optimizer factory (torch AdamW, fused) and its
+    clip_gradients -- the train_step sequence of the reference's train.py:389-475."""
+    try:
+        import refload
+
+        if not refload.available():
+            raise ImportError("baseline/_ref is empty (reference not installed)")
+        import torch
+
+        rank, world, local = dist_env()
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("LOCAL_RANK", "0")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        utils = refload.module("utils")
+        optim = refload.module("optim")
+        fabric = utils.SimpleFabric(precision="bf16-mixed")
+        device = fabric.device
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
+        return
+
+    def build(checkpointing: bool):
+        torch.manual_seed(1337)
+        with torch.device(device):
+            model, cfg = refload.build_train_model(args.model, gradient_checkpointing=checkpointing,
+                                                   lockstep_n=True, lockstep_k=True, attn_impl="sdpa")
+        model = fabric.setup(model, compile=os.environ.get("REF_COMPILE", "0") == "1")
+        groups = optim.get_param_groups(model.named_parameters(), no_weight_decay_for_bias_and_norm_params=False)
+        opt = optim.get_optimizer("AdamW")(groups, lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8)
+        return model, cfg, opt
+
+    state = {"checkpointing": os.environ.get("REF_CHECKPOINT", "0") == "1"}
+    model, cfg, opt = build(state["checkpointing"])
+    total = args.warmup + args.steps
+    host = make_batches(total, cfg.padded_vocab_size, 0, rank)
+    dev_rows = host.to(device)
+    counters = {"micro": 0, "opt": 0}
+
+    def train_step(input_ids, labels):
+        counters["micro"] += 1
+        inner = model.module if hasattr(model, "module") else model
+        inner.step = counters["micro"]
+        out = model(input_ids, position_ids=None, labels=labels, attention_mask=None)
+        loss = out["loss"]
+        fabric.backward(loss, model=model)
+        for g in opt.param_groups:
+            g["lr"] = torch.tensor(4e-4 * g["base_lr"], device=device)
+        gn = fabric.clip_gradients(model, opt, max_norm=1.0)
+        if torch.isfinite(gn) and counters["opt"] > 0:
+            opt.step()
+        opt.zero_grad(set_to_none=False)
+        counters["opt"] += 1
+        return loss
+
+    def device_step(i, base):
+        row = dev_rows[base + i]
+        train_step(row[:, :-1], row[:, 1:])
+
+    try:
+        for i in range(args.warmup):
+            device_step(i, 0)
+    except torch.cuda.OutOfMemoryError:
+        del model, opt
+        torch.cuda.empty_cache()
+        state["checkpointing"] = True
+        model, cfg, opt = build(True)
+        counters.update(micro=0, opt=0)
+        for i in range(args.warmup):
+            device_step(i, 0)
+    start = dict(counters)
+    ms, clocks = timed_region(lambda i: device_step(i, args.warmup), args.steps, device, ClockSampler(local))
+    counters.update(start)
+    losses = []
+
+    def e2e_step(i):
+        row = host[args.warmup + i].to(device, non_blocking=True)
+        losses.append(float(train_step(row[:, :-1], row[:, 1:]).item()))
+
+    ms_e2e, _ = timed_region(e2e_step, args.steps, device, None)
+    tokens = world * SEQ * args.steps
+    rec = {
+        "metric": "train tokens/sec (raven-3.5B, r=32 mean sampled, bptt 8)", "value": round(tokens / (ms / 1e3), 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 autocast, fp32 master weights", "data": "synthetic uniform-random tokens, random-init weights",
+        "impl": "reference",
+        "config": {"model": args.model, "global_batch": world, "seq_len": SEQ, "parallelism": f"dp{world}",
+                   "micro_batch": 1, "attn_impl": "sdpa", "compile": os.environ.get("REF_COMPILE", "0") == "1",
+                   "activation_checkpointing": state["checkpointing"],
+                   "l2": "working set >> 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
+        "final_loss": losses[-1] if losses else None,
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
+    }
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    try:
+        torch.distributed.destroy_process_group()
+    except Exception:
+        pass
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default=MODEL)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.model == MODEL else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

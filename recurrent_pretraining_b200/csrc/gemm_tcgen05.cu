@@ -1,0 +1,421 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] (+)= A[M,K] * B[N,K]^T  with fp32 accumulation in
+// tensor memory.
+//
+//   warp 0      : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier complete_tx)
+//   warp 1      : MMA issuer    (one elected thread, tcgen05.mma 128 x BN x 16, tcgen05.commit frees smem stages)
+//   warps 2..5  : epilogue      (tcgen05.ld from the *other* TMEM accumulator while the next tile is multiplied)
+//
+// One CTA per SM walks a static tile list (m fastest so that the CTAs in flight share B tiles through L2).
+// Both operands may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major), which covers
+// forward (x W^T), dgrad (dy W) and wgrad (dy^T x) without transposed copies.  Ragged M/N/K are handled by
+// TMA zero fill on loads and by predicated stores.  An optional second A operand continues the K loop
+// (y = x Ws^T + e We^T against one [N, K1+K2] weight): the recurrent adapter without a concatenation.
+//
+// Epilogues: bf16 store, fp32 store, fp32 accumulate (weight gradients summed over recurrences), bf16 store of
+// acc + residual, and SwiGLU (B rows n and n + N are the gate and up rows; output silu(gate) * up).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+
+enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_RESID = 3, OUT_SWIGLU = 4 };
+
+struct GemmParams {
+  int M, N, K1, K2;
+  int ldc;        // elements
+  int ld_resid;   // elements (OUT_BF16_RESID)
+  int swiglu_n;   // row offset of the "up" half inside B (OUT_SWIGLU)
+  void* C;
+  const __nv_bfloat16* resid;
+  int* err;
+};
+
+template <int BN, int MODE>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int NB = (MODE == OUT_SWIGLU) ? 2 : 1;  // SwiGLU stages a gate tile and an up tile
+  static constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
+  static constexpr int STAGES = (STAGE_BYTES > 32768) ? 4 : 6;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 for manual alignment
+};
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+            const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN, MODE>;
+  constexpr int STAGES = L::STAGES;
+  // accumulator width in TMEM columns: SwiGLU keeps gate and up side by side
+  constexpr int ACC_COLS = (MODE == OUT_SWIGLU) ? 2 * BN : BN;
+  static_assert(ACC_COLS <= 256, "accumulator too wide");
+  constexpr int ACC_STRIDE = 256;
+  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int nk1 = (p.K1 + BK - 1) / BK;
+  const int nk2 = (p.K2 + BK - 1) / BK;
+  const int nk = nk1 + nk2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if (nk2 > 0) tma_prefetch_desc(&tmA2);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM;
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          const bool second = kb >= nk1;
+          const int ka = (second ? (kb - nk1) : kb) * BK;          // k offset inside the A operand
+          const int kbcol = second ? (p.K1 + ka) : ka;             // k offset inside B
+          const CUtensorMap* ta = second ? &tmA2 : &tmA;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, ta, &full_bar[s], ka, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), ta, &full_bar[s], m0 + c * 64, ka);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[s], kbcol, n0);
+            if constexpr (MODE == OUT_SWIGLU) tma_load_2d(sb + L::B_BYTES, &tmB, &full_bar[s], kbcol, n0 + p.swiglu_n);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, kbcol);
+          }
+        }
+      }
+      // drain: every issued load must have landed before the CTA may exit
+      const uint32_t issued = it;
+      for (uint32_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j) {
+        const int s = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1;
+        unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full_bar[s], ph)) {
+          if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_WAIT_TMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // K-major: 16 elements = 32 bytes inside the swizzle row.  MN-major: 16 k-rows of 128 bytes.
+            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                        : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                        : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb | k) ? 1u : 0u);
+            if constexpr (MODE == OUT_SWIGLU) {
+              const uint64_t b2 = make_smem_desc(sb + L::B_BYTES + k * 32, 16, 1024);
+              umma_bf16(d_tmem + BN, adesc, b2, IDESC, (kb | k) ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      const int m0 = (tile % tiles_m) * BM;
+      const int n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(taddr + c0, v);
+        uint32_t u[16];
+        if constexpr (MODE == OUT_SWIGLU) tmem_ld_32x16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        const int col = n0 + c0;
+        if (!row_ok || col >= p.N) continue;
+        const int nvalid = min(16, p.N - col);
+        if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_SWIGLU) {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+          float f[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+          if constexpr (MODE == OUT_SWIGLU) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g = f[i], up = __uint_as_float(u[i]);
+              f[i] = g / (1.f + __expf(-g)) * up;
+            }
+          }
+          if constexpr (MODE == OUT_BF16_RESID) {
+            const __nv_bfloat16* rrow = p.resid + static_cast<size_t>(row) * p.ld_resid + col;
+            if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(rrow) & 15) == 0)) {
+              uint4 r0 = *reinterpret_cast<const uint4*>(rrow), r1 = *reinterpret_cast<const uint4*>(rrow + 8);
+              const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float2 t = unpack_bf16x2(rr[i]);
+                f[2 * i] += t.x;
+                f[2 * i + 1] += t.y;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) f[i] += bf2f(rrow[i]);
+            }
+          }
+          if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+            uint4 o0, o1;
+            o0.x = pack_bf16x2(f[0], f[1]);   o0.y = pack_bf16x2(f[2], f[3]);
+            o0.z = pack_bf16x2(f[4], f[5]);   o0.w = pack_bf16x2(f[6], f[7]);
+            o1.x = pack_bf16x2(f[8], f[9]);   o1.y = pack_bf16x2(f[10], f[11]);
+            o1.z = pack_bf16x2(f[12], f[13]); o1.w = pack_bf16x2(f[14], f[15]);
+            *reinterpret_cast<uint4*>(crow) = o0;
+            *reinterpret_cast<uint4*>(crow + 8) = o1;
+          } else {
+            for (int i = 0; i < nvalid; ++i) crow[i] = f2bf(f[i]);
+          }
+        } else {
+          float* crow = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+          if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              if constexpr (MODE == OUT_F32_ACC) {
+                const float4 old = *reinterpret_cast<const float4*>(crow + 4 * i);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(crow + 4 * i) = o;
+            }
+          } else {
+            for (int i = 0; i < nvalid; ++i) {
+              float o = __uint_as_float(v[i]);
+              if constexpr (MODE == OUT_F32_ACC) o += crow[i];
+              crow[i] = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements); the box is
+// [box_rows, 64 columns] with 128-byte swizzle.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, const GemmParams& p,
+                  cudaStream_t stream, int max_ctas) {
+  using L = SmemLayout<BN, MODE>;
+  constexpr int SMEM = L::TOTAL;
+  static_assert(MODE != OUT_SWIGLU || BN == 128, "SwiGLU epilogue uses BN = 128");
+  auto kern = gemm_kernel<BN, A_MN, B_MN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grid <= 0) return 0;
+  kern<<<grid, 192, SMEM, stream>>>(ta, ta2, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// C[M,N] (+)= A * B^T.
+//   a_mn = 0: A is [M, K1] row-major (lda);  a_mn = 1: A is [K1, M] row-major (lda)
+//   b_mn = 0: B is [N, K]  row-major (ldb);  b_mn = 1: B is [K, N]  row-major (ldb),  K = K1 + K2
+//   A2 (optional, K-major only): second A operand [M, K2] multiplied against B columns K1..K1+K2
+//   out_mode: see OutMode.  For OUT_SWIGLU, N is the output width I and B holds 2I rows ([gate; up]).
+//   bn: tile width (256, 240 or 128); 0 picks one.  max_ctas > 0 caps the grid (used to leave SMs to a
+//   concurrent communication kernel).
+B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, const void* resid, int M, int N,
+                       int K1, int K2, int lda, int lda2, int ldb, int ldc, int ld_resid, int a_mn, int b_mn,
+                       int out_mode, int bn, int max_ctas, void* stream, int* err) {
+  if (M <= 0 || N <= 0 || K1 <= 0) return 0;
+  if (K2 > 0 && (a_mn || b_mn || (K1 & 7))) return -20;
+  const int K = K1 + K2;
+  if (bn == 0) {
+    if (out_mode == OUT_SWIGLU) bn = 128;
+    else if (b_mn) bn = (N <= 128) ? 128 : 256;
+    else if (N <= 128) bn = 128;
+    else bn = (N % 256 != 0 && N % 240 == 0) ? 240 : 256;
+  }
+  if (b_mn && bn == 240) return -21;
+  CUtensorMap ta, ta2, tb;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d_bf16(&ta, A, M, K1, lda, BM, BK);
+  else rc = make_tmap_2d_bf16(&ta, A, K1, M, lda, BK, 64);
+  if (rc) return rc;
+  ta2 = ta;
+  if (K2 > 0) {
+    rc = make_tmap_2d_bf16(&ta2, A2, M, K2, lda2, BM, BK);
+    if (rc) return rc;
+  }
+  const int brows = (out_mode == OUT_SWIGLU) ? 2 * N : N;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, brows, K, ldb, bn, BK);
+  else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N;
+  p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+#define DISPATCH_MODE(BN_, AMN_, BMN_)                                                            \
+  switch (out_mode) {                                                                             \
+    case OUT_BF16: return launch<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, p, st, max_ctas);        \
+    case OUT_F32: return launch<BN_, AMN_, BMN_, OUT_F32>(ta, ta2, tb, p, st, max_ctas);          \
+    case OUT_F32_ACC: return launch<BN_, AMN_, BMN_, OUT_F32_ACC>(ta, ta2, tb, p, st, max_ctas);  \
+    case OUT_BF16_RESID: return launch<BN_, AMN_, BMN_, OUT_BF16_RESID>(ta, ta2, tb, p, st, max_ctas); \
+    default: return -22;                                                                          \
+  }
+
+  if (out_mode == OUT_SWIGLU) {
+    if (a_mn || b_mn || bn != 128) return -23;
+    return launch<128, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  }
+  if (!a_mn && !b_mn) {
+    if (bn == 256) { DISPATCH_MODE(256, false, false) }
+    if (bn == 240) { DISPATCH_MODE(240, false, false) }
+    if (bn == 128) { DISPATCH_MODE(128, false, false) }
+  } else if (!a_mn && b_mn) {
+    if (bn == 256) { DISPATCH_MODE(256, false, true) }
+    if (bn == 128) { DISPATCH_MODE(128, false, true) }
+  } else if (a_mn && b_mn) {
+    if (bn == 256) { DISPATCH_MODE(256, true, true) }
+    if (bn == 128) { DISPATCH_MODE(128, true, true) }
+  } else {
+    if (bn == 256) { DISPATCH_MODE(256, true, false) }
+    if (bn == 128) { DISPATCH_MODE(128, true, false) }
+  }
+#undef DISPATCH_MODE
+  return -24;
+}

@@ -130,6 +130,19 @@ def make_nonlin(name: str) -> nn.Module:
 # ------------------------------------------------------------------------------------------
 # attention
 # ------------------------------------------------------------------------------------------
+def _split_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim):
+    """Differentiable unfused q/k/v path for the rarely used variants (qk_norm, telemetry, attention bypass)."""
+    from ..ops import reference as ref
+
+    return ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+
+
+def _dense_attention(q, k, v):
+    from ..ops import reference as ref
+
+    return ref.causal_attention(q, k, v)
+
+
 class CausalSelfAttention(nn.Module):
     def __init__(self, config, layer_id: int):
         super().__init__()
@@ -156,18 +169,20 @@ class CausalSelfAttention(nn.Module):
         qkv = self.Wqkv(x)
         if self.config.clip_qkv is not None:
             qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
-        if self.config.rope_settings.use_rope:
-            q, k, v = ops.qk_bias_rope(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
-        else:
-            one, zero = torch.ones_like(cos), torch.zeros_like(sin)
-            q, k, v = ops.qk_bias_rope(qkv, self.qk_bias, one, zero, self.n_head, self.n_kv, self.head_dim)
+        if not self.config.rope_settings.use_rope:
+            cos, sin = torch.ones_like(cos), torch.zeros_like(sin)
+        plain = not (self.config.qk_norm or self.monitoring or self.config.attn_impl == "debug-skip")
+        if plain:
+            y = ops.rope_attention(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+            return self.proj(y)
+        q, k, v = _split_rope(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
         if self.config.qk_norm:
             q = F.rms_norm(q, (q.shape[-1],))
             k = F.rms_norm(k, (k.shape[-1],))
         if self.config.attn_impl == "debug-skip":
             y = q  # attention bypass for pure-GEMM sanity models
         else:
-            y = ops.causal_attention(q, k, v)
+            y = _dense_attention(q, k, v)
         if self.monitoring:
             self._monitor(q, k)
         return self.proj(y.reshape(B, S, E))

@@ -96,8 +96,7 @@ class _Adapter(torch.autograd.Function):
         E = x.shape[-1]
         x2, e2 = x.reshape(-1, E), e.reshape(-1, E)
         w = _lp(weight)
-        y = C.gemm_nt(x2, w[:, :E])
-        C.gemm_nt(e2, w[:, E:], out=y, accumulate=True)
+        y = C.gemm_nt(x2, w, a2=e2)  # the K loop runs over x then e against the two column halves of W
         ctx.save_for_backward(x2, e2, weight)
         ctx.xshape = x.shape
         return y.view(x.shape)
@@ -186,54 +185,60 @@ def add_rmsnorm(a, x, weight, eps: float):
 # ------------------------------------------------------------------------------------------
 # qk-bias + RoPE, attention, SwiGLU
 # ------------------------------------------------------------------------------------------
-class _QKBiasRope(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, qkv, qk_bias, cos, sin, n_head, n_kv, head_dim):
-        C = cuda_backend()
-        q, k, v = C.qk_bias_rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
-        ctx.save_for_backward(cos, sin)
-        ctx.meta = (n_head, n_kv, head_dim, qk_bias is not None)
-        ctx.mark_non_differentiable()
-        return q, k, v
+class _RopeAttention(torch.autograd.Function):
+    """qkv [B,S,(H+2Hkv)D] -> causal attention output [B,S,H*D].
+
+    Forward: one pass adds the q/k bias and rotates q,k into a packed copy (the only tensor saved besides the
+    output and the row log-sum-exp); the attention kernel reads q, k, v as strided views of that copy.
+    Backward: the attention backward writes dq|dk|dv into one packed buffer, which is un-rotated in place and
+    handed to the Wqkv GEMMs without a concatenation."""
 
     @staticmethod
-    def backward(ctx, dq, dk, dv):
+    def forward(ctx, qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, scale):
         C = cuda_backend()
-        cos, sin = ctx.saved_tensors
-        n_head, n_kv, head_dim, has_bias = ctx.meta
-        dqkv, dbias = C.qk_bias_rope_bwd(dq, dk, dv, cos, sin, n_head, n_kv, head_dim, has_bias)
-        return dqkv, dbias, None, None, None, None, None
-
-
-def qk_bias_rope(qkv, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int):
-    if qkv.is_cuda:
-        return _QKBiasRope.apply(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
-    return ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
-
-
-class _Attention(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, scale):
-        C = cuda_backend()
-        o, lse = C.attention_fwd(q, k, v, scale)
-        ctx.save_for_backward(q, k, v, o, lse)
-        ctx.scale = scale
+        qkv_r = C.rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+        o, lse = C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale)
+        ctx.save_for_backward(qkv_r, o, lse, cos, sin)
+        ctx.meta = (n_head, n_kv, head_dim, scale, qk_bias is not None)
         return o
 
     @staticmethod
     def backward(ctx, do):
         C = cuda_backend()
-        q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = C.attention_bwd(do.contiguous(), q, k, v, o, lse, ctx.scale)
-        return dq, dk, dv, None
+        qkv_r, o, lse, cos, sin = ctx.saved_tensors
+        n_head, n_kv, head_dim, scale, has_bias = ctx.meta
+        dqkv = C.attention_bwd(do.contiguous(), qkv_r, o, lse, n_head, n_kv, head_dim, scale)
+        dqkv, dbias = C.rope_bwd_(dqkv, cos, sin, n_head, n_kv, head_dim, has_bias and ctx.needs_input_grad[1])
+        return dqkv, dbias, None, None, None, None, None, None
 
 
-def causal_attention(q, k, v, scale: float | None = None):
-    """q,k,v: [B,S,H,hd] -> [B,S,H,hd], causal, softmax scale defaults to 1/sqrt(hd)."""
+def rope_attention(qkv, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int, scale: float | None = None):
+    """Fused qk-bias + RoPE + causal attention on a packed qkv tensor; returns [B, S, n_head*head_dim]."""
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if qkv.is_cuda:
+        return _RopeAttention.apply(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, scale)
+    q, k, v = ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+    o = ref.causal_attention(q, k, v, scale)
+    return o.reshape(*qkv.shape[:2], n_head * head_dim)
+
+
+def qk_bias_rope(qkv, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int):
+    """Unfused form (used by the inference model, which caches k and v): returns q, k, v as [B,S,H,hd]."""
+    if qkv.is_cuda and not torch.is_grad_enabled():
+        r = cuda_backend().rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+        B, S, _ = r.shape
+        wq, wk = n_head * head_dim, n_kv * head_dim
+        return (r[..., :wq].view(B, S, n_head, head_dim), r[..., wq:wq + wk].view(B, S, n_kv, head_dim),
+                r[..., wq + wk:].view(B, S, n_kv, head_dim))
+    return ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
+
+
+def causal_attention(q, k, v, scale: float | None = None, q_offset: int = 0):
+    """q,k,v: [B,S,H,hd] -> [B,Sq,H,hd] (inference path; keys start at position 0, queries at q_offset)."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if q.is_cuda:
-        return _Attention.apply(q, k, v, scale)
-    return ref.causal_attention(q, k, v, scale)
+        return cuda_backend().attention_infer(q, k, v, scale, q_offset)
+    return ref.causal_attention(q, k, v, scale, q_offset)
 
 
 class _SwiGLU(torch.autograd.Function):

@@ -1,0 +1,191 @@
+"""Process-group fabric: one process per GPU, ``torch.distributed`` (NCCL on GPUs, gloo on CPU) for rendezvous
+and control traffic, and pluggable gradient synchronisation.
+
+Counterpart of the reference's ``SimpleFabric`` (recpre/utils.py:1072-1289): same responsibilities (device set-up,
+seeding, gradient all-reduce after the last micro-batch of an accumulation window, scalar reductions, barrier,
+broadcast, rank-0 printing, save/load helpers) with a different data path on GPUs:
+
+* ``grad_sync="chunked"``  -- the reference's semantics: sum-all-reduce of fp32 chunks of at most 64 MiB followed
+  by a division by the world size (recpre/utils.py:1004-1043).  Used on CPU/gloo and as the NCCL baseline.
+* ``grad_sync="flat"``     -- one NCCL all-reduce per flat optimizer-group buffer (no pack/unpack copies); the
+  1/world factor is folded into the fused optimizer kernel.
+* ``grad_sync="p2p"``      -- hand-written one-shot / two-shot all-reduce kernels over NVLink peer memory on
+  symmetric buffers, which also produce the squared gradient norm (``parallel.p2p``).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from contextlib import contextmanager
+
+import torch
+import torch.distributed as dist
+
+CHUNK_ELEMS = 64 * 1024 * 1024 // 4  # 64 MiB of fp32
+
+
+class Fabric:
+    def __init__(self, device: torch.device, rank: int = 0, world_size: int = 1, local_rank: int = 0,
+                 grad_sync: str = "flat", precision: str = "bf16-mixed"):
+        self.device, self.global_rank, self.world_size, self.local_rank = device, rank, world_size, local_rank
+        self.grad_sync = grad_sync
+        self.precision = precision
+        self.flat_groups = []
+        self._p2p = None
+        self.no_sync = False
+
+    # -- construction ----------------------------------------------------------------------
+    @classmethod
+    def single(cls, device) -> "Fabric":
+        return cls(torch.device(device))
+
+    @classmethod
+    def from_env(cls, backend: str | None = None, grad_sync: str | None = None, timeout_s: int = 900,
+                 precision: str = "bf16-mixed") -> "Fabric":
+        """Read RANK / WORLD_SIZE / LOCAL_RANK (or their SLURM equivalents) and join the process group."""
+        env = os.environ
+        rank = int(env.get("RANK", env.get("SLURM_PROCID", 0)))
+        world = int(env.get("WORLD_SIZE", env.get("SLURM_NTASKS", 1)))
+        local = int(env.get("LOCAL_RANK", env.get("SLURM_LOCALID", 0)))
+        use_cuda = torch.cuda.is_available() and backend != "gloo"
+        device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+        if use_cuda:
+            torch.cuda.set_device(device)
+        if world > 1 and not dist.is_initialized():
+            env.setdefault("MASTER_ADDR", "127.0.0.1")
+            env.setdefault("MASTER_PORT", "29500")
+            backend = backend or ("nccl" if use_cuda else "gloo")
+            kwargs = {"device_id": device} if backend == "nccl" else {}
+            dist.init_process_group(backend, rank=rank, world_size=world,
+                                    timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        sync = grad_sync or ("flat" if use_cuda else "chunked")
+        return cls(device, rank, world, local, sync, precision)
+
+    # -- basic collectives -----------------------------------------------------------------
+    @property
+    def is_distributed(self) -> bool:
+        return self.world_size > 1 and dist.is_initialized()
+
+    def barrier(self) -> None:
+        if self.is_distributed:
+            if self.device.type == "cuda":
+                dist.barrier(device_ids=[self.device.index])
+            else:
+                dist.barrier()
+
+    def all_reduce(self, t: torch.Tensor, reduce_op: str = "mean") -> torch.Tensor:
+        if not self.is_distributed:
+            return t
+        t = t.clone()
+        op = {"sum": dist.ReduceOp.SUM, "mean": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN,
+              "max": dist.ReduceOp.MAX}[reduce_op]
+        dist.all_reduce(t, op=op)
+        if reduce_op == "mean":
+            t = t / self.world_size
+        return t
+
+    def broadcast(self, obj, src: int = 0):
+        if not self.is_distributed:
+            return obj
+        if torch.is_tensor(obj):
+            dist.broadcast(obj, src)
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src)
+        return box[0]
+
+    def print(self, *a, **k) -> None:
+        if self.global_rank == 0:
+            print(*a, **k, flush=True)
+
+    def seed_everything(self, seed: int) -> None:
+        import random
+
+        import numpy as np
+
+        random.seed(seed)
+        np.random.seed(seed % (2**32))
+        torch.manual_seed(seed)
+        if torch.cuda.is_available():
+            torch.cuda.manual_seed_all(seed)
+
+    @contextmanager
+    def no_backward_sync(self, enabled: bool = True):
+        prev, self.no_sync = self.no_sync, enabled
+        try:
+            yield
+        finally:
+            self.no_sync = prev
+
+    # -- gradient synchronisation ----------------------------------------------------------
+    def register_flat_groups(self, groups, model=None) -> None:
+        self.flat_groups = groups
+        if self.grad_sync == "p2p" and self.is_distributed and self.device.type == "cuda":
+            from .p2p import P2PReducer
+
+            self._p2p = P2PReducer(self, groups)
+
+    def begin_backward(self, model, accumulating: bool) -> None:
+        """Hook point for overlap schedulers (bucket readiness counting); nothing to prepare for the flat path."""
+        if self._p2p is not None:
+            self._p2p.begin_backward(model, accumulating)
+
+    def reduce_gradients(self, optimizer) -> bool:
+        """Sum the flat gradient buffers over ranks.  Returns True when the squared norm of the reduced
+        gradients has already been written to ``optimizer.gnorm_sq`` by a fused path."""
+        if not self.is_distributed:
+            return False
+        if self._p2p is not None:
+            return self._p2p.reduce(optimizer)
+        for g in self.flat_groups:
+            if self.grad_sync == "chunked":
+                for s in range(0, g.grad.numel(), CHUNK_ELEMS):
+                    dist.all_reduce(g.grad[s:s + CHUNK_ELEMS])
+            else:
+                dist.all_reduce(g.grad)
+        return False
+
+    def all_reduce_gradients(self, params) -> None:
+        """Reference semantics for unflattened parameters: pack gradients into fp32 chunks of at most 64 MiB,
+        sum-all-reduce each chunk, divide by the world size, scatter back (recpre/utils.py:1004-1043)."""
+        if not self.is_distributed or self.no_sync:
+            return
+        grads = [p.grad for p in params if p.grad is not None]
+        if not grads:
+            return
+        batch, size = [], 0
+        for g in grads:
+            n = g.numel()
+            if batch and size + n > CHUNK_ELEMS:
+                self._reduce_batch(batch)
+                batch, size = [], 0
+            if n > CHUNK_ELEMS:
+                flat = g.view(-1)
+                for s in range(0, n, CHUNK_ELEMS):
+                    piece = flat[s:s + CHUNK_ELEMS]
+                    buf = piece.float()
+                    dist.all_reduce(buf)
+                    piece.copy_(buf / self.world_size)
+                continue
+            batch.append(g)
+            size += n
+        if batch:
+            self._reduce_batch(batch)
+
+    def _reduce_batch(self, batch) -> None:
+        flat = torch.cat([g.reshape(-1).float() for g in batch])
+        dist.all_reduce(flat)
+        flat /= self.world_size
+        off = 0
+        for g in batch:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+
+    # -- teardown --------------------------------------------------------------------------
+    def shutdown(self) -> None:
+        if self._p2p is not None:
+            self._p2p.close()
+            self._p2p = None
+        if dist.is_initialized():
+            dist.destroy_process_group()

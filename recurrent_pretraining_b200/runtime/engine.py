@@ -1,0 +1,144 @@
+"""Training engine: one object that owns the model, the flat parameter store, the optimizer and the gradient
+synchronisation, and exposes ``train_step(input_ids, labels)``.
+
+Step semantics follow the reference (train.py:389-475, recpre/utils.py:1196-1206): gradients of
+``grad_accum`` micro-batches are summed locally, then summed across ranks and divided by the world size,
+clipped by global L2 norm, and applied; the very first optimizer step of a run only clears the gradients
+(``skip_first_step``); a non-finite norm skips the update.
+
+Two execution modes:
+* ``fused`` (CUDA): bf16 compute copies + fp32 master weights in flat buffers; wgrad GEMMs accumulate into the
+  flat fp32 gradient buffer; the 1/(accum*world) scale and the clip factor are folded into the fused AdamW
+  kernel, so no host synchronisation happens inside a step.
+* ``torch`` (CPU or any ``torch.optim`` optimizer): conventional loss scaling, ``clip_grad_norm_`` and
+  ``optimizer.step()``; used for the gloo plumbing tests and the research optimizers.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..optim.fused import FusedAdamW
+from ..optim.groups import get_param_groups
+from ..parallel.flat import flatten_group
+
+
+class TrainEngine:
+    def __init__(self, model, fabric=None, *, lr: float = 4e-4, weight_decay: float = 0.1, betas=(0.9, 0.95),
+                 eps: float = 1e-8, grad_clip: float = 1.0, grad_accum: int = 1, skip_first_step: bool = True,
+                 no_weight_decay_for_bias_and_norm_params: bool = False, optimizer: Optional[object] = None,
+                 mode: Optional[str] = None, atan2: bool = False, lr_fn=None, allow_skip_nonfinite: bool = True):
+        from ..parallel.fabric import Fabric
+
+        self.fabric = fabric if fabric is not None else Fabric.single(next(model.parameters()).device)
+        self.model = model
+        self.device = self.fabric.device
+        self.grad_clip, self.grad_accum = grad_clip, max(int(grad_accum), 1)
+        self.skip_first_step = skip_first_step
+        self.micro_step = 0
+        self.optimizer_step = 0
+        self.lr_fn = lr_fn
+        self.base_lr = lr
+        self.last_grad_norm = None
+        self.mode = mode or ("fused" if self.device.type == "cuda" and optimizer is None else "torch")
+        model.to(self.device)
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        groups = get_param_groups(named, no_weight_decay_for_bias_and_norm_params, with_names=True)
+        self.flat_groups = []
+        if self.mode == "fused":
+            for g in groups:
+                hyper = {"lr": lr * g["base_lr"], "base_lr": g["base_lr"],
+                         "weight_decay": g.get("weight_decay", weight_decay)}
+                self.flat_groups.append(flatten_group(g["params"], g["names"], self.device, True, hyper))
+            self.optimizer = FusedAdamW(self.flat_groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                        atan2=atan2)
+            self.fabric.register_flat_groups(self.flat_groups, model)
+        else:
+            if optimizer is None:
+                for g in groups:
+                    g.pop("names", None)
+                    g.setdefault("weight_decay", weight_decay)
+                optimizer = torch.optim.AdamW(groups, lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+            for g in optimizer.param_groups:
+                g.setdefault("base_lr", 1.0)
+            self.optimizer = optimizer
+        self.params = [p for _, p in named]
+
+    # ------------------------------------------------------------------------------------------
+    def set_lr(self, lr: float) -> None:
+        for h in self.optimizer.param_groups:
+            h["lr"] = lr * h.get("base_lr", 1.0)
+
+    def is_accumulating(self) -> bool:
+        return self.micro_step % self.grad_accum != 0
+
+    def train_step(self, input_ids: torch.Tensor, labels: torch.Tensor, **fwd_kwargs) -> dict:
+        """One micro-batch: forward, backward, and -- on accumulation boundaries -- reduce, clip, update.
+        Returns ``{"loss": device tensor, "grad_norm": device tensor or None, "depths": (n, k)}``."""
+        model = self.model
+        model.train()
+        self.micro_step += 1
+        model.step = self.micro_step
+        accumulating = self.is_accumulating()
+        if self.mode == "fused":
+            self.fabric.begin_backward(model, accumulating)
+        out = model(input_ids, labels=labels, **fwd_kwargs)
+        loss = out["loss"]
+        if self.mode == "fused":
+            loss.backward()
+        else:
+            (loss / self.grad_accum).backward()
+        result = {"loss": loss.detach(), "log_ppl": out["log_ppl"], "grad_norm": None,
+                  "depths": getattr(model, "last_depths", (0, 0))}
+        if accumulating:
+            return result
+        if self.lr_fn is not None:
+            self.set_lr(self.lr_fn(self.micro_step))
+        do_update = not (self.skip_first_step and self.optimizer_step == 0)
+        if self.mode == "fused":
+            world = self.fabric.world_size
+            scale = 1.0 / (self.grad_accum * world)
+            norm_ready = self.fabric.reduce_gradients(self.optimizer)  # sum over ranks (+ squared norm if fused)
+            if do_update:
+                self.optimizer.step(max_norm=self.grad_clip, grad_scale=scale, zero_grad=True, norm_ready=norm_ready)
+            else:
+                if not norm_ready:
+                    self.optimizer.compute_grad_norm_sq()
+                self.optimizer.zero_grad()
+            result["grad_norm"] = self.optimizer.grad_norm(scale)
+        else:
+            self.fabric.all_reduce_gradients(self.params)
+            gn = torch.nn.utils.clip_grad_norm_(self.params, self.grad_clip if self.grad_clip > 0 else math.inf)
+            finite = bool(torch.isfinite(gn))
+            if do_update and finite:
+                self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=False)
+            result["grad_norm"] = gn
+        self.last_grad_norm = result["grad_norm"]
+        self.optimizer_step += 1
+        return result
+
+    @torch.no_grad()
+    def eval_loss(self, input_ids, labels, num_steps_pair=None):
+        self.model.eval()
+        out = self.model(input_ids, labels=labels, num_steps_pair=num_steps_pair)
+        self.model.train()
+        return out["loss"]
+
+    # ------------------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return {"micro_step": self.micro_step, "optimizer_step": self.optimizer_step,
+                "optimizer": self.optimizer.state_dict()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.micro_step = sd["micro_step"]
+        self.optimizer_step = sd["optimizer_step"]
+        self.optimizer.load_state_dict(sd["optimizer"])
+
+    def refresh_shadows(self) -> None:
+        """Re-derive the bf16 compute copies from the fp32 masters (after loading a checkpoint)."""
+        for g in self.flat_groups:
+            if g.shadow is not None:
+                g.shadow.copy_(g.master)

@@ -1,0 +1,203 @@
+"""Numerics of each sm_100a kernel against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from recurrent_pretraining_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from recurrent_pretraining_b200.ops import cuda
+
+    return cuda
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(got, want, rtol, atol):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g}, worst excess {(err - tol).max().item():.4g}"
+
+
+GEMM_SHAPES = [(128, 128, 64), (256, 512, 256), (300, 200, 136), (129, 240, 1320), (4096, 480, 528), (64, 96, 72)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nt(C, M, N, K):
+    a, b = _rand(M, K), _rand(N, K)
+    out = C.gemm_nt(a, b)
+    torch.cuda.synchronize()
+    assert C.check_device_status() == 0
+    _close(out, a.float() @ b.float().T, 2e-2, 2e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("bn", [128, 240, 256])
+def test_gemm_nt_tile_widths(C, bn):
+    a, b = _rand(384, 320), _rand(720, 320)
+    out = C.gemm(a, b, bn=bn)
+    _close(out, a.float() @ b.float().T, 2e-2, 0.4)
+    assert C.check_device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nn_dgrad(C, M, N, K):
+    dy, w = _rand(M, K), _rand(K, N)  # dy [M, K] @ w [K, N]
+    out = C.gemm_nn(dy, w)
+    _close(out, dy.float() @ w.float(), 2e-2, 2e-2 * math.sqrt(K))
+    assert C.check_device_status() == 0
+
+
+@pytest.mark.parametrize("T,N,K", [(128, 128, 128), (512, 256, 192), (1000, 200, 136), (4096, 480, 528)])
+def test_gemm_tn_wgrad_accumulate(C, T, N, K):
+    dy, x = _rand(T, N), _rand(T, K)
+    want = dy.float().T @ x.float()
+    out = C.gemm_tn(dy, x)
+    assert out.dtype == torch.float32
+    _close(out, want, 1e-2, 1e-2 * math.sqrt(T))
+    acc = torch.ones(N, K, device="cuda")
+    C.gemm_tn(dy, x, out=acc, accumulate=True)
+    _close(acc, want + 1.0, 1e-2, 1e-2 * math.sqrt(T))
+    assert C.check_device_status() == 0
+
+
+def test_gemm_strided_views_and_dual_a(C):
+    E, T = 136, 300
+    w = _rand(E, 2 * E)
+    x, e = _rand(T, E), _rand(T, E)
+    y = C.gemm_nt(x, w, a2=e)
+    _close(y, torch.cat([x, e], -1).float() @ w.float().T, 2e-2, 0.4)
+    dy = _rand(T, E)
+    dx = C.gemm_nn(dy, w[:, :E])
+    de = C.gemm_nn(dy, w[:, E:])
+    _close(dx, dy.float() @ w[:, :E].float(), 2e-2, 0.3)
+    _close(de, dy.float() @ w[:, E:].float(), 2e-2, 0.3)
+    g = torch.zeros(E, 2 * E, device="cuda")
+    C.gemm_tn(dy, x, out=g[:, :E], accumulate=True)
+    C.gemm_tn(dy, e, out=g[:, E:], accumulate=True)
+    _close(g, dy.float().T @ torch.cat([x, e], -1).float(), 1e-2, 0.3)
+    assert C.check_device_status() == 0
+
+
+def test_gemm_residual_and_swiglu_epilogues(C):
+    T, E, I = 260, 136, 256
+    x, w, r = _rand(T, E), _rand(E, E), _rand(T, E)
+    y = C.gemm(x, w, resid=r, out_mode=C.OUT_BF16_RESID)
+    _close(y, x.float() @ w.float().T + r.float(), 2e-2, 0.3)
+    fc = _rand(2 * I, E, scale=0.2)
+    h = C.gemm(x, fc, out_mode=C.OUT_SWIGLU)
+    full = x.float() @ fc.float().T
+    want = torch.nn.functional.silu(full[:, :I]) * full[:, I:]
+    _close(h, want, 3e-2, 0.05)
+    assert C.check_device_status() == 0
+
+
+@pytest.mark.parametrize("M,E", [(7, 256), (33, 480), (64, 5280), (5, 8200)])
+def test_rmsnorm_fwd_bwd(C, M, E):
+    x, a = _rand(M, E), _rand(M, E)
+    w = torch.rand(E, device="cuda") + 0.5
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-6)
+    _close(y, ref.rmsnorm(x.float(), w, 1e-6), 1e-2, 1e-2)
+    y2, s, rstd2 = C.add_rmsnorm_fwd(a, x, w, 1e-6)
+    s_ref = (a.float() + x.float()).bfloat16()
+    assert torch.equal(s, s_ref)
+    _close(y2, ref.rmsnorm(s_ref.float(), w, 1e-6), 1e-2, 1e-2)
+    dy = _rand(M, E)
+    dx, dw = C.rmsnorm_bwd(dy, x, w, rstd)
+    xr = x.float().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    x32 = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6)
+    (x32 * wr).backward(dy.float())
+    _close(dx, xr.grad, 2e-2, 2e-2)
+    _close(dw, wr.grad, 2e-2, 2e-2 * math.sqrt(M))
+
+
+def test_rope_fwd_bwd(C):
+    B, S, H, D = 2, 64, 5, 96
+    qkv = _rand(B, S, 3 * H * D)
+    bias = (torch.randn(2, 1, H, D, device="cuda") * 0.1)
+    cos, sin = (t.cuda() for t in ref.rope_tables(D, S))
+    out = C.rope_fwd(qkv, bias, cos, sin, H, H, D)
+    q, k, v = ref.qk_bias_rope(qkv, bias, cos, sin, H, H, D)
+    want = torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)], -1)
+    _close(out, want, 1e-2, 1e-2)
+    # backward of a rotation is the inverse rotation; bias grad is the column sum
+    d = _rand(B, S, 3 * H * D)
+    dq = d.clone()
+    dq, dbias = C.rope_bwd_(dq, cos, sin, H, H, D, True)
+    leaf = qkv.float().requires_grad_(True)
+    bl = bias.clone().requires_grad_(True)
+    q, k, v = ref.qk_bias_rope(leaf, bl, cos, sin, H, H, D)
+    torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)], -1).backward(d.float())
+    _close(dq, leaf.grad, 2e-2, 2e-2)
+    _close(dbias, bl.grad, 2e-2, 0.2)
+
+
+def test_swiglu_embedding_state(C):
+    T, I = 37, 264
+    h = _rand(T, 2 * I)
+    y = C.swiglu_fwd(h)
+    _close(y, ref.swiglu(h.float()), 1e-2, 1e-2)
+    dy = _rand(T, I)
+    dh = C.swiglu_bwd(dy, h)
+    hl = h.float().requires_grad_(True)
+    ref.swiglu(hl).backward(dy.float())
+    _close(dh, hl.grad, 2e-2, 2e-2)
+    V, E = 100, 136
+    w = _rand(V, E)
+    ids = torch.randint(0, V, (3, 11), device="cuda")
+    out = C.embedding_fwd(ids, w, 2.0)
+    _close(out, w[ids].float() * 2.0, 1e-2, 1e-3)
+    g = torch.zeros(V, E, device="cuda")
+    d = _rand(3, 11, E)
+    C.embedding_bwd(d, ids, g, 2.0)
+    want = torch.zeros(V, E, device="cuda").index_add_(0, ids.reshape(-1), d.reshape(-1, E).float() * 2.0)
+    _close(g, want, 1e-3, 1e-3)
+    s = C.trunc_normal((1024, 1024), 0.6325, 7).float()
+    assert abs(s.mean().item()) < 5e-3 and abs(s.std().item() - 0.6325 * 0.9866) < 1e-2
+    assert s.abs().max().item() <= 3 * 0.6325 * 1.01
+    s2 = C.trunc_normal((1024, 1024), 0.6325, 8).float()
+    assert not torch.equal(s, s2)
+
+
+def test_adamw_matches_torch(C):
+    n = 10007
+    p0 = torch.randn(n, device="cuda")
+    g0 = torch.randn(n, device="cuda") * 0.01
+    p = p0.clone(); g = g0.clone(); m = torch.zeros(n, device="cuda"); v = torch.zeros(n, device="cuda")
+    shadow = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pt = p0.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([pt], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    gn = torch.zeros(1, device="cuda")
+    for step in range(1, 4):
+        pt.grad = g0.clone() * step
+        torch.nn.utils.clip_grad_norm_([pt], 0.5)
+        opt.step()
+        g.copy_(g0 * step)
+        gn.zero_()
+        C.sumsq_(g, gn)
+        C.adamw_(p, g, m, v, shadow, gn, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, step=step, max_norm=0.5)
+        assert float(g.abs().max()) == 0.0  # gradient zeroed for the next step
+    _close(p, pt.detach(), 1e-4, 1e-5)
+    _close(shadow, pt.detach(), 1e-2, 1e-3)
+
+
+def test_linear_ce(C):
+    T, E, V = 300, 136, 1000
+    x, w = _rand(T, E), _rand(V, E, scale=0.2)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    loss, dx, dw = C.linear_ce(x, w, labels, chunk_rows=128)
+    xl, wl = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    want = ref.linear_cross_entropy(xl, wl, labels)
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-3 * max(1.0, abs(want.item()))
+    _close(dx, xl.grad, 5e-2, 2e-4)
+    _close(dw, wl.grad, 5e-2, 2e-4)
