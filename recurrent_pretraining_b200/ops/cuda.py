@@ -32,7 +32,7 @@ def _sig(name, argtypes):
     return fn
 
 
-_gemm = _sig("b200_gemm", [_vp] * 5 + [_i] * 15 + [_vp, _vp])
+_gemm = _sig("b200_gemm", [_vp] * 5 + [_i] * 14 + [_vp, _vp])
 _rms_fwd = _sig("b200_rmsnorm_fwd", [_vp] * 6 + [_i, _i, _f, _vp])
 _rms_bwd = _sig("b200_rmsnorm_bwd", [_vp] * 7 + [_i, _i, _vp])
 _rms_bwd_grid = _sig("b200_rmsnorm_bwd_grid", [_i])
@@ -267,6 +267,8 @@ def embedding_bwd(dy, ids, grad_f32, scale):
 
 
 def trunc_normal(shape, std, seed, dtype=BF16, device=None):
+    if device is None or torch.device(device).type != "cuda":
+        device = torch.device("cuda", torch.cuda.current_device())
     out = torch.empty(tuple(shape), dtype=BF16, device=device)
     _check(_trunc_normal(_ptr(out), out.numel(), float(std), int(seed) & 0xFFFFFFFFFFFFFFFF, _stream()), "trunc_normal")
     return out if dtype == BF16 else out.to(dtype)

@@ -1,0 +1,107 @@
+"""Micro-benchmarks of the hot kernels on the flagship shapes, reported against the library GEMM and the measured
+machine peaks.  ``python -m recurrent_pretraining_b200.utils.kernel_bench [gemm|norm|attn|all]``.
+
+Timing: CUDA events on the launching stream after warm-up, L2 flushed between timed launches by writing a 256 MB
+buffer, median of the repeats.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+import sys
+
+import torch
+
+
+def _flush(buf):
+    buf.zero_()
+
+
+def time_fn(fn, reps=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        if flush is not None:
+            _flush(flush)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def bench_gemm(M=4096):
+    from ..ops import cuda as C
+
+    E, I, V = 5280, 17920, 65536
+    shapes = [("qkv", 3 * E, E), ("attn.proj", E, E), ("mlp.fc", 2 * I, E), ("mlp.proj", E, I), ("adapter", E, 2 * E),
+              ("head(4096 rows)", V, E)]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    rows = []
+    for name, N, K in shapes:
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        dy = torch.randn(M, N, device="cuda").bfloat16()
+        g = torch.zeros(N, K, device="cuda")
+        fl = 2.0 * M * N * K
+        res = {"shape": name, "M": M, "N": N, "K": K}
+        for tag, ours, lib in (
+            ("fwd", lambda: C.gemm_nt(x, w), lambda: torch.matmul(x, w.t())),
+            ("dgrad", lambda: C.gemm_nn(dy, w), lambda: torch.matmul(dy, w)),
+            ("wgrad", lambda: C.gemm_tn(dy, x, out=g, accumulate=True), lambda: torch.matmul(dy.t(), x)),
+        ):
+            t_ours = time_fn(ours, flush=flush)
+            t_lib = time_fn(lib, flush=flush)
+            res[tag] = {"ours_ms": round(t_ours, 3), "ours_tflops": round(fl / t_ours / 1e9, 1),
+                        "cublas_ms": round(t_lib, 3), "cublas_tflops": round(fl / t_lib / 1e9, 1)}
+        rows.append(res)
+        print(json.dumps(res), flush=True)
+        del x, w, dy, g
+    assert C.check_device_status() == 0
+    return rows
+
+
+def bench_norm(M=4096, E=5280):
+    from ..ops import cuda as C
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    M = M * 8  # 346 MB per tensor: larger than L2
+    x = torch.randn(M, E, device="cuda").bfloat16()
+    a = torch.randn(M, E, device="cuda").bfloat16()
+    w = torch.ones(E, device="cuda")
+    t = time_fn(lambda: C.rmsnorm_fwd(x, w, 1e-6), flush=flush)
+    print(json.dumps({"kernel": "rmsnorm_fwd", "ms": round(t, 3), "GBps": round(2 * x.numel() * 2 / t / 1e6, 1)}))
+    t = time_fn(lambda: C.add_rmsnorm_fwd(a, x, w, 1e-6), flush=flush)
+    print(json.dumps({"kernel": "add_rmsnorm_fwd", "ms": round(t, 3), "GBps": round(4 * x.numel() * 2 / t / 1e6, 1)}))
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-6)
+    t = time_fn(lambda: C.rmsnorm_bwd(a, x, w, rstd), flush=flush)
+    print(json.dumps({"kernel": "rmsnorm_bwd", "ms": round(t, 3), "GBps": round(3 * x.numel() * 2 / t / 1e6, 1)}))
+
+
+def bench_attn(B=1, S=4096, H=55, D=96):
+    from ..ops import cuda as C
+
+    qkv = torch.randn(B, S, 3 * H * D, device="cuda").bfloat16()
+    fl = 4.0 * B * H * S * S * D / 2
+    scale = D ** -0.5
+    t = time_fn(lambda: C.attention_fwd(qkv, H, H, D, scale))
+    o, lse = C.attention_fwd(qkv, H, H, D, scale)
+    do = torch.randn_like(o)
+    tb = time_fn(lambda: C.attention_bwd(do, qkv, o, lse, H, H, D, scale))
+    print(json.dumps({"kernel": "attention", "native": bool(lse.numel()), "fwd_ms": round(t, 3),
+                      "fwd_tflops": round(fl / t / 1e9, 1), "bwd_ms": round(tb, 3),
+                      "bwd_tflops": round(2.5 * fl / tb / 1e9, 1)}))
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("norm", "all"):
+        bench_norm()
+    if what in ("attn", "all"):
+        bench_attn()
