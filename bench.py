@@ -176,12 +176,13 @@ def run_ours(args):
 
     # end-to-end region: same step indices (same sampled recurrence depths), inputs from pinned host memory
     engine.micro_step, engine.optimizer_step = start_micro, start_opt
-    losses = []
+    losses, norms = [], []
 
     def e2e_step(i):
         row = host[args.warmup + i].to(device, non_blocking=True)
         out = engine.train_step(row[:, :-1], row[:, 1:])
         losses.append(float(out["loss"].item()))
+        norms.append(out["grad_norm"])
 
     ms_e2e, _ = timed_region(e2e_step, args.steps, device, None)
     tokens = world * SEQ * args.steps
@@ -203,6 +204,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
         "gpu_launches": launches, "device_status": status,
         "final_loss": losses[-1] if losses else None,
+        "final_grad_norm": float(norms[-1]) if norms and norms[-1] is not None else None,
         "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
     }
     if rank == 0:
@@ -252,6 +254,7 @@ def run_reference(args):
     host = make_batches(total, cfg.padded_vocab_size, 0, rank)
     dev_rows = host.to(device)
     counters = {"micro": 0, "opt": 0}
+    last_norm = [None]
 
     def train_step(input_ids, labels):
         counters["micro"] += 1
@@ -263,6 +266,7 @@ def run_reference(args):
         for g in opt.param_groups:
             g["lr"] = torch.tensor(4e-4 * g["base_lr"], device=device)
         gn = fabric.clip_gradients(model, opt, max_norm=1.0)
+        last_norm[0] = gn
         if torch.isfinite(gn) and counters["opt"] > 0:
             opt.step()
         opt.zero_grad(set_to_none=False)
@@ -287,11 +291,12 @@ def run_reference(args):
     start = dict(counters)
     ms, clocks = timed_region(lambda i: device_step(i, args.warmup), args.steps, device, ClockSampler(local))
     counters.update(start)
-    losses = []
+    losses, norms = [], []
 
     def e2e_step(i):
         row = host[args.warmup + i].to(device, non_blocking=True)
         losses.append(float(train_step(row[:, :-1], row[:, 1:]).item()))
+        norms.append(last_norm[0])
 
     ms_e2e, _ = timed_region(e2e_step, args.steps, device, None)
     tokens = world * SEQ * args.steps
@@ -309,6 +314,7 @@ def run_reference(args):
         "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
         "final_loss": losses[-1] if losses else None,
+        "final_grad_norm": float(norms[-1]) if norms and norms[-1] is not None else None,
         "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
     }
     if rank == 0:

@@ -16,23 +16,12 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace b200 {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
-
-enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_RESID = 3, OUT_SWIGLU = 4 };
-
-struct GemmParams {
-  int M, N, K1, K2;
-  int ldc;        // elements
-  int ld_resid;   // elements (OUT_BF16_RESID)
-  int swiglu_n;   // row offset of the "up" half inside B (OUT_SWIGLU)
-  void* C;
-  const __nv_bfloat16* resid;
-  int* err;
-};
 
 template <int BN, int MODE>
 struct SmemLayout {
@@ -119,12 +108,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const bool second = kb >= nk1;
           const int ka = (second ? (kb - nk1) : kb) * BK;          // k offset inside the A operand
           const int kbcol = second ? (p.K1 + ka) : ka;             // k offset inside B
-          const CUtensorMap* ta = second ? &tmA2 : &tmA;
           if constexpr (!A_MN) {
-            tma_load_2d(sa, ta, &full_bar[s], ka, m0);
+            if (second) tma_load_2d(sa, &tmA2, &full_bar[s], ka, m0);
+            else tma_load_2d(sa, &tmA, &full_bar[s], ka, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), ta, &full_bar[s], m0 + c * 64, ka);
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, ka);
           }
           if constexpr (!B_MN) {
             tma_load_2d(sb, &tmB, &full_bar[s], kbcol, n0);
@@ -193,79 +182,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int n0 = (tile / tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld_32x16(taddr + c0, v);
-        uint32_t u[16];
-        if constexpr (MODE == OUT_SWIGLU) tmem_ld_32x16(taddr + BN + c0, u);
-        tmem_ld_wait();
-        const int col = n0 + c0;
-        if (!row_ok || col >= p.N) continue;
-        const int nvalid = min(16, p.N - col);
-        if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_SWIGLU) {
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-          float f[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-          if constexpr (MODE == OUT_SWIGLU) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float g = f[i], up = __uint_as_float(u[i]);
-              f[i] = g / (1.f + __expf(-g)) * up;
-            }
-          }
-          if constexpr (MODE == OUT_BF16_RESID) {
-            const __nv_bfloat16* rrow = p.resid + static_cast<size_t>(row) * p.ld_resid + col;
-            if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(rrow) & 15) == 0)) {
-              uint4 r0 = *reinterpret_cast<const uint4*>(rrow), r1 = *reinterpret_cast<const uint4*>(rrow + 8);
-              const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float2 t = unpack_bf16x2(rr[i]);
-                f[2 * i] += t.x;
-                f[2 * i + 1] += t.y;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) f[i] += bf2f(rrow[i]);
-            }
-          }
-          if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
-            uint4 o0, o1;
-            o0.x = pack_bf16x2(f[0], f[1]);   o0.y = pack_bf16x2(f[2], f[3]);
-            o0.z = pack_bf16x2(f[4], f[5]);   o0.w = pack_bf16x2(f[6], f[7]);
-            o1.x = pack_bf16x2(f[8], f[9]);   o1.y = pack_bf16x2(f[10], f[11]);
-            o1.z = pack_bf16x2(f[12], f[13]); o1.w = pack_bf16x2(f[14], f[15]);
-            *reinterpret_cast<uint4*>(crow) = o0;
-            *reinterpret_cast<uint4*>(crow + 8) = o1;
-          } else {
-            for (int i = 0; i < nvalid; ++i) crow[i] = f2bf(f[i]);
-          }
-        } else {
-          float* crow = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-          if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-              if constexpr (MODE == OUT_F32_ACC) {
-                const float4 old = *reinterpret_cast<const float4*>(crow + 4 * i);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(crow + 4 * i) = o;
-            }
-          } else {
-            for (int i = 0; i < nvalid; ++i) {
-              float o = __uint_as_float(v[i]);
-              if constexpr (MODE == OUT_F32_ACC) o += crow[i];
-              crow[i] = o;
-            }
-          }
-        }
-      }
+      epilogue_tile<BN, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -348,7 +266,20 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
 
 }  // namespace b200
 
+namespace b200 {
+int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,
+                       int a_mn, int b_mn, int out_mode, int bn, int max_ctas, cudaStream_t st);
+static int g_use_2cta = 1;
+}  // namespace b200
+
 using namespace b200;
+
+// 1: prefer the 2-CTA (cta_group::2) kernel where it applies (default); 0: always the 1-CTA kernel.
+B200_API int b200_gemm_set_2cta(int enable) {
+  const int old = g_use_2cta;
+  g_use_2cta = enable;
+  return old;
+}
 
 // C[M,N] (+)= A * B^T.
 //   a_mn = 0: A is [M, K1] row-major (lda);  a_mn = 1: A is [K1, M] row-major (lda)
@@ -370,6 +301,14 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
     else bn = (N % 256 != 0 && N % 240 == 0) ? 240 : 256;
   }
   if (b_mn && bn == 240) return -21;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  GemmParams p;
+  p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N;
+  p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
+  if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240) && out_mode != OUT_SWIGLU) {
+    const int rc2 = gemm_2cta_dispatch(A, A2, B, p, lda, lda2, ldb, a_mn, b_mn, out_mode, bn, max_ctas, st);
+    if (rc2 != -100) return rc2;
+  }
   CUtensorMap ta, ta2, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d_bf16(&ta, A, M, K1, lda, BM, BK);
@@ -384,10 +323,6 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, brows, K, ldb, bn, BK);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, 64);
   if (rc) return rc;
-  GemmParams p;
-  p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N;
-  p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
 #define DISPATCH_MODE(BN_, AMN_, BMN_)                                                            \
   switch (out_mode) {                                                                             \

@@ -1,0 +1,324 @@
+// 2-CTA (cta_group::2) variant of the persistent bf16 GEMM: a cluster of two CTAs on neighbouring SMs computes
+// one 256 x BN tile.  Each CTA stages its own 128 rows of A and only HALF of the B tile; the pair's tensor cores
+// read both halves, so shared-memory fill traffic from L2 per FLOP drops by a third against the 1-CTA 128 x 256
+// tile -- the L2 -> SM path, not the tensor pipe, is what limits the 1-CTA kernel on B200.
+//
+// Protocol (rank 0 of the pair is the leader):
+//   * both producers wait on their LOCAL empty barrier and issue their TMA loads with the .cta_group::2 form whose
+//     mbarrier operand is the LEADER's full barrier (cluster address from mapa); the leader arms that barrier with
+//     the byte count of both CTAs.  No load uses cluster multicast.
+//   * only the leader issues tcgen05.mma.cta_group::2 (M = 256); it releases a stage with two tcgen05.commit
+//     instructions, one on its own empty barrier and one on the peer's (plain cluster address, no multicast),
+//     and publishes a finished accumulator the same way.
+//   * each CTA's epilogue warps drain their own 128 TMEM lanes and arrive on the leader's accumulator-empty
+//     barrier (the peer through mbarrier.arrive on a cluster address).
+// All waits are bounded; a time-out sets the status word and every role falls through to the common exit, where
+// the pair synchronises with the cluster barrier before tensor memory is released.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+
+namespace b200 {
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols);
+int num_sms();
+
+constexpr int BM2 = 128;   // rows per CTA (256 per pair)
+constexpr int BK2 = 64;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's smem whose completion bytes are counted on a barrier given by cluster address.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (once the pair's prior MMAs are complete) on one mbarrier given by cluster address
+__device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+
+template <int BN>
+struct Smem2 {
+  static constexpr int A_BYTES = BM2 * BK2 * 2;        // 16 KB
+  static constexpr int B_BYTES = (BN / 2) * BK2 * 2;   // this CTA's half of the B tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+};
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+             const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = Smem2<BN>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int ACC_STRIDE = 256;
+  constexpr int BNH = BN / 2;
+  constexpr uint32_t IDESC = make_idesc_bf16(2 * BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+  static_assert(MODE != OUT_SWIGLU, "SwiGLU epilogue is provided by the 1-CTA kernel");
+  static_assert(!B_MN || (BNH % 64 == 0), "MN-major B needs 64-column chunks per CTA");
+
+  extern __shared__ uint8_t smem_raw[];
+  // identical offsets in both CTAs of the pair (the MMA descriptors are shared)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM2 - 1) / (2 * BM2);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int nk1 = (p.K1 + BK2 - 1) / BK2;
+  const int nk2 = (p.K2 + BK2 - 1) / BK2;
+  const int nk = nk1 + nk2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);   // 4 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before any remote arrive or remote complete_tx
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if (nk2 > 0) tma_prefetch_desc(&tmA2);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
+        const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * BNH;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
+          const bool second = kb >= nk1;
+          const int ka = (second ? (kb - nk1) : kb) * BK2;
+          const int kbcol = second ? (p.K1 + ka) : ka;
+          if constexpr (!A_MN) {
+            if (second) tma_load_2d_pair(sa, &tmA2, fb, ka, m0);
+            else tma_load_2d_pair(sa, &tmA, fb, ka, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM2 / 64; ++c) tma_load_2d_pair(sa + c * (BK2 * 128), &tmA, fb, m0 + c * 64, ka);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, fb, kbcol, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (BK2 * 128), &tmB, fb, n0 + c * 64, kbcol);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_WAIT_TMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK2 / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, BK2 * 128, 1024)
+                                        : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK2 * 128, 1024)
+                                        : make_smem_desc(sb + k * 32, 16, 1024);
+            umma2_bf16(d_tmem, adesc, bdesc, IDESC, (kb | k) ? 1u : 0u);
+          }
+          const uint32_t eb = smem_u32(&empty_bar[s]);
+          umma2_commit(mapa_shared(eb, 0));
+          umma2_commit(mapa_shared(eb, 1));
+        }
+        if (ok) {
+          const uint32_t tb = smem_u32(&tfull_bar[acc]);
+          umma2_commit(mapa_shared(tb, 0));
+          umma2_commit(mapa_shared(tb, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs, warps 2..5)
+    const int quad = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
+      const int n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
+      epilogue_tile<BN, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  // common exit: nobody leaves (and no tensor memory is released) while the partner may still touch this CTA
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, const GemmParams& p,
+                   cudaStream_t stream, int max_ctas) {
+  using L = Smem2<BN>;
+  auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE>;
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return -10;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_sms() & ~1, 1, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
+    max_clusters = n;
+  }
+  const int tiles = ((p.M + 2 * BM2 - 1) / (2 * BM2)) * ((p.N + BN - 1) / BN);
+  int clusters = tiles < max_clusters ? tiles : max_clusters;
+  if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2;
+  if (clusters <= 0) return 0;
+  kern<<<2 * clusters, 192, L::TOTAL, stream>>>(ta, ta2, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Entry used by b200_gemm: returns -100 when the 2-CTA kernel does not cover the request.
+int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,
+                       int a_mn, int b_mn, int out_mode, int bn, int max_ctas, cudaStream_t st) {
+  if (out_mode == OUT_SWIGLU) return -100;
+  if (bn == 240 && b_mn) return -100;
+  if (bn != 256 && bn != 240) return -100;
+  const int K = p.K1 + p.K2;
+  CUtensorMap ta, ta2, tb;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d_bf16(&ta, A, p.M, p.K1, lda, BM2, BK2);
+  else rc = make_tmap_2d_bf16(&ta, A, p.K1, p.M, lda, BK2, 64);
+  if (rc) return rc;
+  ta2 = ta;
+  if (p.K2 > 0) {
+    rc = make_tmap_2d_bf16(&ta2, A2, p.M, p.K2, lda2, BM2, BK2);
+    if (rc) return rc;
+  }
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, p.N, K, ldb, bn / 2, BK2);
+  else rc = make_tmap_2d_bf16(&tb, B, K, p.N, ldb, BK2, 64);
+  if (rc) return rc;
+
+#define DISPATCH2(BN_, AMN_, BMN_)                                                                  \
+  switch (out_mode) {                                                                               \
+    case OUT_BF16: return launch2<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, p, st, max_ctas);         \
+    case OUT_F32: return launch2<BN_, AMN_, BMN_, OUT_F32>(ta, ta2, tb, p, st, max_ctas);           \
+    case OUT_F32_ACC: return launch2<BN_, AMN_, BMN_, OUT_F32_ACC>(ta, ta2, tb, p, st, max_ctas);   \
+    case OUT_BF16_RESID: return launch2<BN_, AMN_, BMN_, OUT_BF16_RESID>(ta, ta2, tb, p, st, max_ctas); \
+    default: return -100;                                                                           \
+  }
+  if (!a_mn && !b_mn) {
+    if (bn == 256) { DISPATCH2(256, false, false) }
+    if (bn == 240) { DISPATCH2(240, false, false) }
+  } else if (!a_mn && b_mn) {
+    DISPATCH2(256, false, true)
+  } else if (a_mn && b_mn) {
+    DISPATCH2(256, true, true)
+  } else {
+    DISPATCH2(256, true, false)
+  }
+#undef DISPATCH2
+  return -100;
+}
+
+}  // namespace b200

@@ -48,7 +48,14 @@ _adamw = _sig("b200_adamw", [_vp] * 5 + [_ll, _vp] + [_f] * 9 + [_i, _i, _vp])
 _cast = _sig("b200_cast_f32_bf16", [_vp, _vp, _ll, _vp])
 _ce_rows = _sig("b200_ce_rows", [_vp] * 6 + [_i] * 4 + [_f, _i, _f, _vp])
 
+_set_2cta = _sig("b200_gemm_set_2cta", [_i])
+
 OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_BF16_RESID, OUT_SWIGLU = range(5)
+
+
+def set_gemm_2cta(enable: bool) -> bool:
+    """Select the 2-CTA (cta_group::2, 256-row tiles) GEMM where it applies; returns the previous setting."""
+    return bool(_set_2cta(int(enable)))
 
 BF16 = torch.bfloat16
 

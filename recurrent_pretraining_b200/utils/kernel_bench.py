@@ -54,9 +54,14 @@ def bench_gemm(M=4096):
             ("dgrad", lambda: C.gemm_nn(dy, w), lambda: torch.matmul(dy, w)),
             ("wgrad", lambda: C.gemm_tn(dy, x, out=g, accumulate=True), lambda: torch.matmul(dy.t(), x)),
         ):
+            C.set_gemm_2cta(True)
             t_ours = time_fn(ours, flush=flush)
+            C.set_gemm_2cta(False)
+            t_one = time_fn(ours, flush=flush)
+            C.set_gemm_2cta(True)
             t_lib = time_fn(lib, flush=flush)
-            res[tag] = {"ours_ms": round(t_ours, 3), "ours_tflops": round(fl / t_ours / 1e9, 1),
+            res[tag] = {"ours_2cta_ms": round(t_ours, 3), "ours_2cta_tflops": round(fl / t_ours / 1e9, 1),
+                        "ours_1cta_tflops": round(fl / t_one / 1e9, 1),
                         "cublas_ms": round(t_lib, 3), "cublas_tflops": round(fl / t_lib / 1e9, 1)}
         rows.append(res)
         print(json.dumps(res), flush=True)

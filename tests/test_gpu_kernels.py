@@ -9,11 +9,13 @@ from recurrent_pretraining_b200.ops import reference as ref
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def C():
+@pytest.fixture(scope="module", params=["2cta", "1cta"])
+def C(request):
     from recurrent_pretraining_b200.ops import cuda
 
-    return cuda
+    old = cuda.set_gemm_2cta(request.param == "2cta")
+    yield cuda
+    cuda.set_gemm_2cta(old)
 
 
 def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
@@ -27,7 +29,8 @@ def _close(got, want, rtol, atol):
     assert bool((err <= tol).all()), f"max err {err.max().item():.4g}, worst excess {(err - tol).max().item():.4g}"
 
 
-GEMM_SHAPES = [(128, 128, 64), (256, 512, 256), (300, 200, 136), (129, 240, 1320), (4096, 480, 528), (64, 96, 72)]
+GEMM_SHAPES = [(128, 128, 64), (256, 512, 256), (300, 200, 136), (129, 240, 1320), (4096, 480, 528), (64, 96, 72),
+               (1024, 1024, 2048), (700, 1304, 264)]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
