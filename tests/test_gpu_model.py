@@ -69,3 +69,30 @@ def test_sampled_depth_step_runs_and_reports_norm():
     assert r1["grad_norm"] is None  # still accumulating
     r2 = eng.train_step(ids[:, :-1], ids[:, 1:])
     assert torch.isfinite(r2["grad_norm"]).all() and r2["grad_norm"].item() > 0
+
+
+def test_training_dynamics_track_fp32_torch_engine():
+    """Six optimizer steps on distinct batches, then the first batch again: the fused bf16 engine must follow the
+    fp32 torch.optim.AdamW engine step by step (same clip, same skipped first step, same recurrent state)."""
+    torch.manual_seed(3)
+    cfg = ModelConfig.from_name("smoke-raven-96")
+    cpu_model = cfg.construct_model()
+    gpu_model = copy.deepcopy(cpu_model)
+    eng_c = TrainEngine(cpu_model, lr=1e-3, mode="torch")
+    eng_g = TrainEngine(gpu_model.cuda(), lr=1e-3)
+    B, S = 2, 128
+    batches = [torch.randint(0, cfg.padded_vocab_size, (B, S + 1)) for _ in range(6)]
+    batches.append(batches[0])
+    pair = torch.tensor([2, 2])
+    lc, lg = [], []
+    for i, ids in enumerate(batches):
+        state = torch.randn(B, S, cfg.n_embd, generator=torch.Generator().manual_seed(100 + i)) * 0.6
+        rc = eng_c.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=pair, input_states=state)
+        rg = eng_g.train_step(ids[:, :-1].cuda(), ids[:, 1:].cuda(), num_steps_pair=pair,
+                              input_states=state.cuda().bfloat16())
+        lc.append(rc["loss"].item())
+        lg.append(rg["loss"].item())
+        assert abs(rg["grad_norm"].item() - rc["grad_norm"].item()) < 0.1 * rc["grad_norm"].item() + 1e-3, (i, lc, lg)
+    for a, b in zip(lc, lg):
+        assert abs(a - b) < 0.05 * abs(a) + 0.05, (lc, lg)
+    assert lg[-1] < lg[0]  # the re-seen batch is (partly) memorised by both engines
