@@ -150,7 +150,7 @@ def run_ours(args):
     from recurrent_pretraining_b200.runtime.engine import TrainEngine
 
     rank, world, local = dist_env()
-    fabric = Fabric.from_env(grad_sync=os.environ.get("B200_GRAD_SYNC"))
+    fabric = Fabric.from_env(grad_sync=os.environ.get("B200_GRAD_SYNC", "p2p"))
     device = fabric.device
     cfg = ModelConfig.from_name(args.model, lockstep_n=True, lockstep_k=True)
     torch.manual_seed(1337)

@@ -28,8 +28,17 @@ class FusedAdamW:
             self.param_groups.append(h)
             g.state["m"] = torch.zeros_like(g.master)
             g.state["v"] = torch.zeros_like(g.master)
+            g.state["range"] = (0, g.numel)
         dev = flat_groups[0].master.device
         self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def shard(self, ranges) -> None:
+        """Keep optimizer state only for ``ranges[i] = (lo, hi)`` of group i (sharded data-parallel update)."""
+        for g, (lo, hi) in zip(self.groups, ranges):
+            dev = g.master.device
+            g.state["m"] = torch.zeros(max(hi - lo, 4), dtype=torch.float32, device=dev)
+            g.state["v"] = torch.zeros(max(hi - lo, 4), dtype=torch.float32, device=dev)
+            g.state["range"] = (lo, hi)
 
     # -- norm ------------------------------------------------------------------------------
     def compute_grad_norm_sq(self) -> torch.Tensor:
@@ -84,7 +93,8 @@ class FusedAdamW:
 
     def state_dict(self):
         return {"step": self.step_count,
-                "groups": [{"m": g.state["m"], "v": g.state["v"], "names": g.names, "offsets": g.offsets,
+                "groups": [{"m": g.state["m"], "v": g.state["v"], "range": g.state["range"], "names": g.names,
+                            "offsets": g.offsets,
                             "hyper": {k: v for k, v in h.items() if k != "params"}}
                            for g, h in zip(self.groups, self.param_groups)]}
 

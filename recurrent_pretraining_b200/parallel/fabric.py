@@ -32,6 +32,7 @@ class Fabric:
         self.precision = precision
         self.flat_groups = []
         self._p2p = None
+        self._p2p_alloc = None
         self.no_sync = False
 
     # -- construction ----------------------------------------------------------------------
@@ -118,12 +119,35 @@ class Fabric:
             self.no_sync = prev
 
     # -- gradient synchronisation ----------------------------------------------------------
-    def register_flat_groups(self, groups, model=None) -> None:
+    @property
+    def uses_p2p(self) -> bool:
+        return self.grad_sync == "p2p" and self.is_distributed and self.device.type == "cuda"
+
+    def buffer_allocator(self, group_index: int):
+        """Allocator for the flat buffers of optimizer group ``group_index`` (symmetric memory in p2p mode)."""
+        if not self.uses_p2p:
+            return None
+        if self._p2p_alloc is None:
+            from .p2p import P2PAllocator
+
+            self._p2p_alloc = P2PAllocator(self)
+        return lambda kind, numel, dtype: self._p2p_alloc(group_index, kind, numel, dtype)
+
+    def register_flat_groups(self, groups, model=None, optimizer=None) -> None:
         self.flat_groups = groups
-        if self.grad_sync == "p2p" and self.is_distributed and self.device.type == "cuda":
+        if self.uses_p2p:
             from .p2p import P2PReducer
 
-            self._p2p = P2PReducer(self, groups)
+            self._p2p = P2PReducer(self, groups, self._p2p_alloc)
+            if optimizer is not None:
+                optimizer.shard(self._p2p.ranges)
+
+    def fused_reduce_and_step(self, optimizer, max_norm: float, grad_scale: float, do_update: bool) -> bool:
+        """Run the fused reduce-scatter + sharded update + parameter push when available."""
+        if self._p2p is None:
+            return False
+        self._p2p.step(optimizer, max_norm, grad_scale, do_update)
+        return True
 
     def begin_backward(self, model, accumulating: bool) -> None:
         """Hook point for overlap schedulers (bucket readiness counting); nothing to prepare for the flat path."""
@@ -135,8 +159,6 @@ class Fabric:
         gradients has already been written to ``optimizer.gnorm_sq`` by a fused path."""
         if not self.is_distributed:
             return False
-        if self._p2p is not None:
-            return self._p2p.reduce(optimizer)
         for g in self.flat_groups:
             if self.grad_sync == "chunked":
                 for s in range(0, g.grad.numel(), CHUNK_ELEMS):

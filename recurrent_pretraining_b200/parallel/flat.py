@@ -32,15 +32,19 @@ def _aligned(n: int) -> int:
     return (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
 
 
-def flatten_group(params, names, device, with_shadow: bool, hyper: dict, grad_buffer=None) -> FlatGroup:
+def flatten_group(params, names, device, with_shadow: bool, hyper: dict, alloc=None) -> FlatGroup:
+    """``alloc(kind, numel, dtype)`` may supply the three buffers (e.g. from symmetric communication memory)."""
     offsets, total = [], 0
     for p in params:
         offsets.append(total)
         total += _aligned(p.numel())
     total = max(total, ALIGN_ELEMS)
-    master = torch.zeros(total, dtype=torch.float32, device=device)
-    grad = torch.zeros(total, dtype=torch.float32, device=device) if grad_buffer is None else grad_buffer
-    shadow = torch.zeros(total, dtype=torch.bfloat16, device=device) if with_shadow else None
+    if alloc is None:
+        def alloc(kind, numel, dtype):
+            return torch.zeros(numel, dtype=dtype, device=device)
+    master = alloc("master", total, torch.float32)
+    grad = alloc("grad", total, torch.float32)
+    shadow = alloc("shadow", total, torch.bfloat16) if with_shadow else None
     for p, off in zip(params, offsets):
         n = p.numel()
         view = master[off:off + n].view(p.shape)

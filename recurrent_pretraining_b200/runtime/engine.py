@@ -48,13 +48,14 @@ class TrainEngine:
         groups = get_param_groups(named, no_weight_decay_for_bias_and_norm_params, with_names=True)
         self.flat_groups = []
         if self.mode == "fused":
-            for g in groups:
+            for gi, g in enumerate(groups):
                 hyper = {"lr": lr * g["base_lr"], "base_lr": g["base_lr"],
                          "weight_decay": g.get("weight_decay", weight_decay)}
-                self.flat_groups.append(flatten_group(g["params"], g["names"], self.device, True, hyper))
+                self.flat_groups.append(flatten_group(g["params"], g["names"], self.device, True, hyper,
+                                                      alloc=self.fabric.buffer_allocator(gi)))
             self.optimizer = FusedAdamW(self.flat_groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                         atan2=atan2)
-            self.fabric.register_flat_groups(self.flat_groups, model)
+            self.fabric.register_flat_groups(self.flat_groups, model, self.optimizer)
         else:
             if optimizer is None:
                 for g in groups:
@@ -100,7 +101,12 @@ class TrainEngine:
         if self.mode == "fused":
             world = self.fabric.world_size
             scale = 1.0 / (self.grad_accum * world)
-            norm_ready = self.fabric.reduce_gradients(self.optimizer)  # sum over ranks (+ squared norm if fused)
+            if self.fabric.fused_reduce_and_step(self.optimizer, self.grad_clip, scale, do_update):
+                result["grad_norm"] = self.optimizer.grad_norm(scale)
+                self.last_grad_norm = result["grad_norm"]
+                self.optimizer_step += 1
+                return result
+            norm_ready = self.fabric.reduce_gradients(self.optimizer)  # sum over ranks
             if do_update:
                 self.optimizer.step(max_norm=self.grad_clip, grad_scale=scale, zero_grad=True, norm_ready=norm_ready)
             else:

@@ -1,0 +1,109 @@
+"""Communication sweep: fused NVLink kernels vs NCCL on bf16 / fp32 gradient buckets of 1 MB .. 1 GB.
+
+Run under ``python -m torch.distributed.run --nproc-per-node N -m recurrent_pretraining_b200.utils.comm_bench``.
+Device-timed with CUDA events, max over ranks.  Reports algorithm bandwidth, bus bandwidth (2 (N-1)/N x bytes / t for
+an all-reduce) and the fraction of the measured 770 GB/s per-direction peer-copy bandwidth.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.fabric import Fabric
+from ..parallel.symm import SymmetricBuffer
+
+LINK_GBS = 770.0
+
+
+def _time(fn, device, reps=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    ts = []
+    for _ in range(reps):
+        dist.barrier(device_ids=[device.index])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        t = torch.tensor([e0.elapsed_time(e1)], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ts.append(float(t))
+    return statistics.median(ts)
+
+
+def main():
+    from ..ops import cuda as K
+
+    fabric = Fabric.from_env(grad_sync="flat")
+    dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
+    sizes_mb = [1, 4, 16, 64, 256, 1024]
+    max_bytes = sizes_mb[-1] * 2**20
+    buf = SymmetricBuffer(fabric, max_bytes)
+    ctrl = SymmetricBuffer(fabric, 512)
+    out = torch.empty(max_bytes // 4, dtype=torch.float32, device=dev)
+    sumsq = torch.zeros(1, device=dev)
+    src_f32 = buf.tensor(torch.float32, max_bytes // 4)
+    src_f32.normal_(0, 1e-3)
+    epoch = [0]
+    flags = ctrl.ptr_array(0)
+    err = C.c_void_p(K.err_word(dev).data_ptr())
+
+    def barrier():
+        epoch[0] += 1
+        K._check(K.lib.b200_barrier(flags, rank, N, C.c_uint(epoch[0]), 20000, None, None, err,
+                                    C.c_void_p(K._stream())), "barrier")
+
+    for mb in sizes_mb:
+        nbytes = mb * 2**20
+        n32 = nbytes // 4
+        per = (n32 + N - 1) // N
+        per = (per + 127) // 128 * 128
+        lo, hi = min(rank * per, n32), min(rank * per + per, n32)
+        nccl_t = torch.empty(n32, dtype=torch.float32, device=dev).normal_(0, 1e-3)
+
+        def ours_two_shot():
+            st = C.c_void_p(K._stream())
+            barrier()
+            K._check(K.lib.b200_reduce_scatter_f32(buf.ptr_array(), rank, N, C.c_longlong(lo), C.c_longlong(hi - lo),
+                                                   C.c_void_p(sumsq.data_ptr()), 0, st), "rs")
+            barrier()
+            K._check(K.lib.b200_allgather_bytes(buf.ptr_array(), rank, N, C.c_longlong(per * 4), 0, st), "ag")
+            barrier()
+
+        def ours_one_shot():
+            st = C.c_void_p(K._stream())
+            barrier()
+            K._check(K.lib.b200_allreduce_oneshot_f32(buf.ptr_array(), rank, N, C.c_void_p(out.data_ptr()),
+                                                      C.c_longlong(n32), C.c_float(1.0 / N),
+                                                      C.c_void_p(sumsq.data_ptr()), 0, st), "oneshot")
+            barrier()
+
+        t_nccl = _time(lambda: dist.all_reduce(nccl_t), dev)
+        t_two = _time(ours_two_shot, dev) if n32 >= N * 128 else float("nan")
+        t_one = _time(ours_one_shot, dev) if mb <= 64 else float("nan")
+        bus = 2 * (N - 1) / N * nbytes
+        rec = {"bucket_MB": mb, "dtype": "fp32", "n_gpus": N,
+               "nccl_ms": round(t_nccl, 4), "nccl_bus_GBps": round(bus / t_nccl / 1e6, 1),
+               "two_shot_ms": round(t_two, 4), "two_shot_bus_GBps": round(bus / t_two / 1e6, 1),
+               "two_shot_frac_of_link": round(bus / t_two / 1e6 / LINK_GBS, 3),
+               "one_shot_ms": round(t_one, 4),
+               "one_shot_in_GBps": round((N - 1) * nbytes / t_one / 1e6, 1) if t_one == t_one else None}
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+    status = K.check_device_status()
+    if rank == 0:
+        print(json.dumps({"device_status": status}))
+    torch.cuda.synchronize(dev)
+    ctrl.close()
+    buf.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,100 @@
+"""Worker run under torch.distributed.run by tests/test_gpu_multi.py (one process per GPU)."""
+import copy
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from recurrent_pretraining_b200.config import ModelConfig  # noqa: E402
+from recurrent_pretraining_b200.parallel.fabric import Fabric  # noqa: E402
+from recurrent_pretraining_b200.runtime.engine import TrainEngine  # noqa: E402
+
+
+def run_training(sync: str, steps: int = 4):
+    fabric = Fabric.from_env(grad_sync=sync)
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("smoke-raven-96", lockstep_n=True, lockstep_k=True)
+    with torch.device(fabric.device):
+        model = cfg.construct_model()
+    eng = TrainEngine(model, fabric, lr=1e-3)
+    g = torch.Generator().manual_seed(100 + fabric.global_rank)
+    losses, norms = [], []
+    for i in range(steps):
+        ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), generator=g).to(fabric.device)
+        state = (torch.randn(2, 128, cfg.n_embd, generator=g) * 0.6).to(fabric.device).bfloat16()
+        out = eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]), input_states=state)
+        losses.append(out["loss"].item())
+        norms.append(out["grad_norm"].item())
+    torch.cuda.synchronize()
+    shadow = torch.cat([g_.shadow.float().cpu() for g_ in eng.flat_groups])
+    return fabric, eng, losses, norms, shadow
+
+
+def main():
+    mode = sys.argv[1]
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    if mode == "train":
+        fabric, eng, l1, n1, s1 = run_training("p2p")
+        status = K.check_device_status()
+        # all ranks must hold identical bf16 parameters after the pushes
+        mine = s1.to(fabric.device)
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        same = bool(torch.equal(mine, ref))
+        if fabric._p2p is not None:
+            fabric._p2p.close()
+            fabric._p2p = None
+        # same run with the NCCL flat all-reduce + replicated update as the oracle
+        fabric2 = Fabric(fabric.device, fabric.global_rank, fabric.world_size, fabric.local_rank, "flat")
+        torch.manual_seed(0)
+        cfg = ModelConfig.from_name("smoke-raven-96", lockstep_n=True, lockstep_k=True)
+        with torch.device(fabric.device):
+            model = cfg.construct_model()
+        eng2 = TrainEngine(model, fabric2, lr=1e-3)
+        g = torch.Generator().manual_seed(100 + fabric.global_rank)
+        l2, n2 = [], []
+        for i in range(4):
+            ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), generator=g).to(fabric.device)
+            state = (torch.randn(2, 128, cfg.n_embd, generator=g) * 0.6).to(fabric.device).bfloat16()
+            out = eng2.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]), input_states=state)
+            l2.append(out["loss"].item())
+            n2.append(out["grad_norm"].item())
+        s2 = torch.cat([g_.shadow.float().cpu() for g_ in eng2.flat_groups])
+        rel = ((s1 - s2).norm() / s2.norm()).item()
+        if fabric.global_rank == 0:
+            print("RESULT " + json.dumps({"p2p_losses": l1, "nccl_losses": l2, "p2p_norms": n1, "nccl_norms": n2,
+                                          "replicas_identical": same, "param_rel_diff": rel, "status": status}))
+        dist.barrier()
+        dist.destroy_process_group()
+    elif mode == "timeout":
+        # a barrier whose peer flag nobody sets must give up and report through the status word
+        import ctypes as C
+
+        from recurrent_pretraining_b200.parallel.symm import SymmetricBuffer
+
+        fabric = Fabric.from_env(grad_sync="flat")
+        ctrl = SymmetricBuffer(fabric, 512)
+        torch.cuda.synchronize()
+        dist.barrier()
+        code = 0
+        if fabric.global_rank == 0:  # only rank 0 enters: its peer never signals epoch 7
+            K._check(K.lib.b200_barrier(ctrl.ptr_array(0), 0, fabric.world_size, C.c_uint(7), 200, None, None,
+                                        C.c_void_p(K.err_word(fabric.device).data_ptr()), C.c_void_p(K._stream())),
+                     "barrier")
+            torch.cuda.synchronize()
+            code = K.check_device_status()
+            x = torch.ones(4, device=fabric.device) * 2  # the context is still usable
+            print("RESULT " + json.dumps({"status": code, "after": float(x.sum())}))
+        dist.barrier()
+        ctrl.close()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,44 @@
+"""Multi-GPU tests (skipped with fewer than two GPUs): child processes under torch.distributed.run, NVLS off."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(mode: str, nproc: int = 2, port: int = 29641):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), mode]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@needs2
+def test_p2p_sharded_step_matches_nccl_allreduce():
+    res = _run("train")
+    assert res["status"] == 0
+    assert res["replicas_identical"]
+    for a, b in zip(res["p2p_losses"], res["nccl_losses"]):
+        assert abs(a - b) < 0.02 * abs(b) + 0.02, res
+    for a, b in zip(res["p2p_norms"], res["nccl_norms"]):
+        assert abs(a - b) < 0.05 * abs(b) + 1e-3, res
+    assert res["param_rel_diff"] < 2e-2, res
+
+
+@needs2
+def test_barrier_wait_times_out_and_reports():
+    res = _run("timeout", port=29643)
+    assert res["status"] == 5  # ERR_WAIT_PEER_FLAG
+    assert res["after"] == 8.0
