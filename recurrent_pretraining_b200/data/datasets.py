@@ -1,0 +1,194 @@
+"""Token sources.  All yield 1-D int64 tensors of ``block_size + 1`` token ids (or dicts for text rows).
+
+* ``RandomTokens``  -- synthetic uniform ids (the ``rngds`` debug source of recpre/huggingface_dataset.py:484-507,
+  generated lazily per row instead of as a 10^6-row table).
+* ``ParquetStream`` -- pyarrow-only stateful stream over pre-tokenised parquet shards with the sharding, shuffling
+  and resume semantics of the reference's production loader (recpre/huggingface_dataset.py:124-294): files are
+  globbed on rank 0 and broadcast, shuffled with a seeded RNG, assigned ``rank::max(8, world)``; one row group at a
+  time is read, shuffled with a per-dataset ``random.Random`` and popped from the end; the state (file index, row
+  group, rows left, RNG state, fingerprint) is all-gathered on save and reloaded modulo the saved world size.
+* ``TextRows``      -- rows of a ``datasets.load_from_disk`` directory or a list of dicts (tokenised in collate).
+"""
+from __future__ import annotations
+
+import hashlib
+import random
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+from torch.utils.data import IterableDataset
+
+
+class RandomTokens(IterableDataset):
+    def __init__(self, vocab_size: int, block_size: int, seed: int = 233, process_rank: int = 0, length: int = 10**6):
+        self.vocab_size, self.block_size, self.seed, self.rank, self.length = vocab_size, block_size, seed, process_rank, length
+        self._pos = 0
+
+    def __iter__(self):
+        while self._pos < self.length:
+            g = torch.Generator().manual_seed(self.seed + 7919 * self.rank + self._pos)
+            self._pos += 1
+            yield torch.randint(0, self.vocab_size, (self.block_size,), generator=g, dtype=torch.int64)
+
+    def state_dict(self):
+        return {"pos": self._pos}
+
+    def load_state_dict(self, sd, **_):
+        self._pos = int(sd["pos"])
+
+
+class ParquetStream(IterableDataset):
+    def __init__(self, dataset_folder_path: str = "", seed: int = 12345, shuffle: bool = True, num_processes: int = 1,
+                 process_rank: int = 0, prefix: str = "", shuffle_filenames: bool = True, column: str = "input_ids",
+                 broadcast_glob: bool = True, stateful: bool = True, plan_for_later_rank_expansion_to: int = 8,
+                 return_data_id: bool = False, data_id=None):
+        files = None
+        distributed = dist.is_available() and dist.is_initialized()
+        if not (broadcast_glob and distributed) or process_rank == 0:
+            files = sorted(str(p) for p in Path(dataset_folder_path).glob(f"{prefix}*.parquet"))
+        if broadcast_glob and distributed:
+            box = [files]
+            dist.broadcast_object_list(box, 0)
+            files = box[0]
+        if shuffle_filenames:
+            random.Random(seed).shuffle(files)
+        stride = max(plan_for_later_rank_expansion_to, num_processes) if plan_for_later_rank_expansion_to > 0 \
+            else num_processes
+        self.parquet_files = files[process_rank::stride] if stride > 1 else files
+        if not self.parquet_files:
+            raise ValueError(f"Empty dataset on rank {process_rank}")
+        self.fingerprint = hashlib.shake_128(str(self.parquet_files).encode()).hexdigest(4)
+        self.shuffle, self.seed, self.rank, self.stateful, self.column = shuffle, seed, process_rank, stateful, column
+        self.return_data_id, self.data_id = return_data_id, data_id
+        self._reset()
+
+    def _reset(self):
+        self._rng = random.Random(self.seed)
+        self._rng_state = None
+        self._buffer: list = []
+        self._file_idx = 0
+        self._row_group_idx = 0
+
+    def _read_buffer(self, pf):
+        self._buffer = pf.read_row_group(self._row_group_idx).column(self.column).to_pylist()
+        if self.shuffle:
+            self._rng_state = self._rng.getstate()
+            self._rng.shuffle(self._buffer)
+
+    def __iter__(self):
+        import pyarrow.parquet as pq
+
+        if not self.stateful:
+            self._reset()
+        while self._file_idx < len(self.parquet_files):
+            if not self._buffer:
+                pf = pq.ParquetFile(self.parquet_files[self._file_idx])
+                if self._row_group_idx >= pf.num_row_groups:
+                    self._file_idx += 1
+                    self._row_group_idx = 0
+                    continue
+                self._read_buffer(pf)
+                self._row_group_idx += 1
+            while self._buffer:
+                row = torch.as_tensor(self._buffer.pop(), dtype=torch.long)
+                yield {"input_ids": row, "data_id": self.data_id} if self.return_data_id else row
+
+    # -- state ---------------------------------------------------------------------------------
+    def local_state(self) -> dict:
+        return {"file_idx": self._file_idx, "row_group_idx": self._row_group_idx - 1, "row_idx": len(self._buffer),
+                "fingerprint": self.fingerprint, "rng_state": self._rng_state}
+
+    def state_dict(self) -> dict:
+        """Per-rank states gathered into lists indexed by rank (a different world size can reload them)."""
+        local = self.local_state()
+        if dist.is_available() and dist.is_initialized():
+            states = [None] * dist.get_world_size()
+            dist.all_gather_object(states, local)
+        else:
+            states = [local]
+        return {k: [s[k] for s in states] for k in local}
+
+    def load_state_dict(self, sd: dict, offset_ranks: bool = False) -> None:
+        import pyarrow.parquet as pq
+
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        pick = lambda key: sd[key][rank % len(sd["fingerprint"])]  # noqa: E731
+        if pick("fingerprint") != self.fingerprint:
+            print(f"WARNING dataset fingerprint mismatch: expected {self.fingerprint}, got {pick('fingerprint')}")
+            self._file_idx, self._row_group_idx, row_idx = 0, 0, 0
+        else:
+            self._file_idx = max(pick("file_idx"), 0)
+            self._row_group_idx = max(pick("row_group_idx"), 0)
+            row_idx = max(pick("row_idx"), 0) + (rank % 1000 if offset_ranks else 0)
+        state = pick("rng_state")
+        if state is not None:
+            self._rng = random.Random()
+            self._rng.setstate(tuple(state) if not isinstance(state, tuple) else state)
+        self._read_buffer(pq.ParquetFile(self.parquet_files[self._file_idx]))
+        self._buffer = self._buffer[:row_idx]
+        self._row_group_idx += 1
+
+
+class TextRows(IterableDataset):
+    """Raw-text rows (dicts) sharded by rank; tokenisation happens in the collate function."""
+
+    def __init__(self, rows_or_path, data_signature: dict, num_processes: int = 1, process_rank: int = 0,
+                 shuffle: bool = False, seed: int = 0, data_id=None):
+        if isinstance(rows_or_path, (str, Path)):
+            import datasets
+
+            rows_or_path = datasets.load_from_disk(str(rows_or_path))
+        self.rows, self.sig = rows_or_path, data_signature
+        self.world, self.rank, self.shuffle, self.seed, self.data_id = num_processes, process_rank, shuffle, seed, data_id
+        self._pos = 0
+
+    def __iter__(self):
+        order = list(range(self.rank, len(self.rows), self.world))
+        if self.shuffle:
+            random.Random(self.seed).shuffle(order)
+        while self._pos < len(order):
+            row = dict(self.rows[order[self._pos]])
+            self._pos += 1
+            row["data_signature"] = self.sig
+            if self.data_id is not None:
+                row["data_id"] = self.data_id
+            yield row
+
+    def state_dict(self):
+        return {"pos": self._pos}
+
+    def load_state_dict(self, sd, **_):
+        self._pos = int(sd["pos"])
+
+
+class WeightedMixture(IterableDataset):
+    """Draws the next row from one of several sources according to (scheduled) weights."""
+
+    def __init__(self, sources: list, weights: list, seed: int = 0, scheduler=None):
+        self.sources, self.weights, self.scheduler = sources, list(weights), scheduler
+        self._rng = random.Random(seed)
+
+    def __iter__(self):
+        iters = [iter(s) for s in self.sources]
+        alive = [True] * len(iters)
+        while any(alive):
+            w = self.scheduler.get_data_weights() if self.scheduler is not None else self.weights
+            w = [wi if a else 0.0 for wi, a in zip(w, alive)]
+            if sum(w) <= 0:
+                return
+            i = self._rng.choices(range(len(iters)), weights=w)[0]
+            try:
+                yield next(iters[i])
+            except StopIteration:
+                alive[i] = False
+
+    def state_dict(self):
+        return {"sources": [s.state_dict() if hasattr(s, "state_dict") else None for s in self.sources],
+                "rng": self._rng.getstate()}
+
+    def load_state_dict(self, sd, **_):
+        for s, st in zip(self.sources, sd["sources"]):
+            if st is not None:
+                s.load_state_dict(st)
+        self._rng.setstate(sd["rng"])

@@ -1,0 +1,97 @@
+"""Per-source sampling-weight schedules for data mixtures (recpre/data_scheduler_utils.py:1-229).
+
+A source's ``scheduler`` entry is ``["const", w]``, ``["step", w0, every, gamma]``, ``["linear", w0, w1[, steps]]``,
+``["cosine", w_max, w_min, period]``, ``["base"]`` / ``["base-renorm"]`` (this source takes what is left of 100), or
+a piecewise list ``[[start_step, spec], ...]``.  A source whose ``max_epoch`` is exhausted gets weight 0.
+"""
+from __future__ import annotations
+
+import math
+
+
+def _make(spec, default_weight, max_steps):
+    if isinstance(spec[0], (list, tuple)):
+        pieces = [(int(start), _make(sub, default_weight, max_steps)) for start, sub in spec]
+
+        def piecewise(step):
+            for i, (start, fn) in enumerate(pieces):
+                end = pieces[i + 1][0] if i + 1 < len(pieces) else float("inf")
+                if start <= step < end:
+                    return fn(step - start)
+            return default_weight
+
+        return piecewise
+    kind = spec[0]
+    if kind == "const":
+        return lambda step: spec[1]
+    if kind == "step":
+        return lambda step: spec[1] * spec[3] ** (step // spec[2])
+    if kind == "linear":
+        total = spec[3] if len(spec) > 3 else max_steps
+        return lambda step: spec[1] + (spec[2] - spec[1]) * (min(step, total) / total)
+    if kind == "cosine":
+        return lambda step: spec[2] + (spec[1] - spec[2]) * (1 + math.cos(math.pi * (step % spec[3]) / spec[3])) / 2
+    if kind in ("base", "base-renorm"):
+        return lambda step: 0
+    raise NotImplementedError(f"unknown weight schedule {kind!r}")
+
+
+class DataSchedulerTracker:
+    def __init__(self, weights):
+        self.weights = list(weights)
+        self.sample_count = [0] * len(weights)
+        self.epoch_count = [0] * len(weights)
+        self.max_epochs = None
+        self.base_id = None
+
+    def reset(self):
+        self.sample_count = [0] * len(self.weights)
+        self.epoch_count = [0] * len(self.weights)
+
+    def get_data_weights(self):
+        return self.weights
+
+
+class DataScheduler:
+    def __init__(self, tracker: DataSchedulerTracker, data_config: list, max_steps: int):
+        self.tracker = tracker
+        self.base_id, self._renorm = None, False
+        self.max_epochs, self._fns = [], []
+        for i, entry in enumerate(data_config):
+            self.max_epochs.append(entry.max_epoch if entry.max_epoch is not None else float("inf"))
+            spec = entry.scheduler if entry.scheduler is not None else ["const", entry.weight]
+            if spec[0] in ("base", "base-renorm"):
+                self.base_id = i
+                tracker.base_id = i
+                self._renorm = spec[0] == "base-renorm"
+            self._fns.append(_make(spec, entry.weight, max_steps))
+        tracker.max_epochs = self.max_epochs
+
+    def step(self, curr_step: int) -> None:
+        w = [fn(curr_step) for fn in self._fns]
+        for i in range(len(w)):
+            if self.max_epochs[i] <= self.tracker.epoch_count[i]:
+                w[i] = 0
+        if self.base_id is not None:
+            explicit = sum(x for i, x in enumerate(w) if i != self.base_id)
+            if self._renorm and explicit != 0:
+                w = [x * 100.0 / explicit if i != self.base_id else 0 for i, x in enumerate(w)]
+            w[self.base_id] = 0
+            w[self.base_id] = 100.0 - sum(w)
+        self.tracker.weights[:] = w
+
+    def get_data_weights(self):
+        return self.tracker.weights
+
+    def set_one_hot_schedule(self, idx: int) -> None:
+        self._fns = [(lambda s: 0) for _ in self._fns]
+        self._fns[idx] = lambda s: 1
+
+    def state_dict(self):
+        return {"weights": list(self.tracker.weights), "sample_count": list(self.tracker.sample_count),
+                "epoch_count": list(self.tracker.epoch_count)}
+
+    def load_state_dict(self, sd):
+        self.tracker.weights[:] = sd["weights"]
+        self.tracker.sample_count = list(sd["sample_count"])
+        self.tracker.epoch_count = list(sd["epoch_count"])

@@ -81,9 +81,9 @@ def sample_recurrence(scheme: str, mean_recurrence: int, mean_backprop_depth: in
         n = max(total - k, 0)
     elif "gupta" in scheme:
         n = randint(0, t * 2, gn)
-        draw = float(torch.rand(size=(1,), generator=gk))
-        skew = randint(2 * t, t * 8, gk)
-        k = int(1 + (t - n) * draw**skew)
+        draw = torch.rand(size=(1,), generator=gk)
+        skew = torch.randint(low=2 * t, high=t * 8, size=(1,), generator=gk)
+        k = int((1 + (t - n) * draw**skew).to(torch.long))  # float32 arithmetic, truncated toward zero
     elif "simple" in scheme:
         n = randint(0, 2 * t, gn)
         k = randint(1, 2 * s + 1, gk)

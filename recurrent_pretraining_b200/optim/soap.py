@@ -1,0 +1,137 @@
+"""SOAP: Adam in the eigenbasis of Shampoo's preconditioners (recpre/soap.py:34-446, arXiv 2409.11321).
+
+Per 2-D parameter: accumulate ``L = E[G G^T]`` and ``R = E[G^T G]`` for every dimension not larger than
+``max_precond_dim`` (so the 15840/17920/35840/65536-wide sides of the flagship stay un-preconditioned), keep their
+eigenvectors ``Q_L, Q_R`` (``eigh`` at the first step, one power-iteration + QR refresh every ``precondition_frequency``
+steps), run Adam on the rotated gradient ``Q_L^T G Q_R`` and rotate the update back.  The first step only initialises
+the preconditioners.  The GG-accumulation and projection GEMMs go through ``torch.matmul``; they are not on a hot path
+named by the benchmark (one optimizer step per ~0.7 s training step).
+"""
+from __future__ import annotations
+
+import torch
+from torch.optim import Optimizer
+
+
+class SOAP(Optimizer):
+    def __init__(self, params, lr: float = 3e-3, betas=(0.95, 0.95), shampoo_beta: float = -1, eps: float = 1e-8,
+                 weight_decay: float = 0.01, precondition_frequency: int = 10, max_precond_dim: int = 10000,
+                 merge_dims: bool = False, precondition_1d: bool = False, correct_bias: bool = True):
+        defaults = dict(lr=lr, betas=tuple(betas), shampoo_beta=shampoo_beta, eps=eps, weight_decay=weight_decay,
+                        precondition_frequency=precondition_frequency, max_precond_dim=max_precond_dim,
+                        merge_dims=merge_dims, precondition_1d=precondition_1d, correct_bias=correct_bias)
+        super().__init__(params, defaults)
+
+    @staticmethod
+    def _merge(shape, max_dim):
+        out, cur = [], 1
+        for s in shape:
+            if cur * s > max_dim:
+                if cur > 1:
+                    out.append(cur)
+                    cur = s
+                else:
+                    out.append(s)
+                    cur = 1
+            else:
+                cur *= s
+        if cur > 1 or not out:
+            out.append(cur)
+        return out
+
+    def _init_precond(self, g, st, group):
+        st["GG"], st["Q"] = [], None
+        if g.dim() == 1 and (not group["precondition_1d"] or g.shape[0] > group["max_precond_dim"]):
+            st["GG"].append([])
+        else:
+            for s in g.shape:
+                st["GG"].append([] if s > group["max_precond_dim"] else torch.zeros(s, s, device=g.device))
+        st["shampoo_beta"] = group["shampoo_beta"] if group["shampoo_beta"] >= 0 else group["betas"][1]
+
+    @staticmethod
+    def _project(g, Q, back=False):
+        for mat in Q:
+            if len(mat) > 0:
+                g = torch.tensordot(g, mat, dims=[[0], [1 if back else 0]])
+            else:
+                g = g.permute(list(range(1, g.dim())) + [0])
+        return g
+
+    def _update_gg(self, g, st):
+        beta = st["shampoo_beta"]
+        for i, m in enumerate(st["GG"]):
+            if len(m) > 0:
+                dims = [j for j in range(g.dim()) if j != i]
+                outer = torch.tensordot(g, g, dims=[dims, dims])
+                m.lerp_(outer, 1 - beta)
+
+    @staticmethod
+    def _eigh_basis(mats):
+        out = []
+        for m in mats:
+            if len(m) == 0:
+                out.append([])
+                continue
+            try:
+                _, q = torch.linalg.eigh(m.float() + 1e-30 * torch.eye(m.shape[0], device=m.device))
+            except Exception:
+                _, q = torch.linalg.eigh(m.double() + 1e-30 * torch.eye(m.shape[0], device=m.device, dtype=torch.float64))
+                q = q.float()
+            out.append(torch.flip(q, [1]))
+        return out
+
+    def _refresh_basis(self, st):
+        exp_avg_sq = st["exp_avg_sq"]
+        new_q = []
+        for i, (m, q) in enumerate(zip(st["GG"], st["Q"])):
+            if len(m) == 0:
+                new_q.append([])
+                continue
+            est = torch.diag(q.T @ m @ q)
+            order = torch.argsort(est, descending=True)
+            exp_avg_sq = exp_avg_sq.index_select(i, order)
+            q = q[:, order]
+            power = m @ q
+            q_new, _ = torch.linalg.qr(power)
+            new_q.append(q_new)
+        st["exp_avg_sq"] = exp_avg_sq
+        st["Q"] = new_q
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                g = p.grad.float()
+                st = self.state[p]
+                shape = g.shape
+                if group["merge_dims"] and g.dim() > 1:
+                    g = g.reshape(self._merge(g.shape, group["max_precond_dim"]))
+                if "step" not in st:
+                    st["step"] = 0
+                    st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(g), torch.zeros_like(g)
+                    self._init_precond(g, st, group)
+                    self._update_gg(g, st)
+                    st["Q"] = self._eigh_basis(st["GG"])
+                    continue  # the first step only initialises the preconditioner
+                st["step"] += 1
+                gp = self._project(g, st["Q"])
+                m, v = st["exp_avg"], st["exp_avg_sq"]
+                m.mul_(b1).add_(g, alpha=1 - b1)
+                v.mul_(b2).addcmul_(gp, gp, value=1 - b2)
+                denom = v.sqrt().add_(group["eps"])
+                mp = self._project(m, st["Q"])
+                step_size = group["lr"]
+                if group["correct_bias"]:
+                    step_size = step_size * ((1 - b2 ** st["step"]) ** 0.5) / (1 - b1 ** st["step"])
+                upd = self._project(mp / denom, st["Q"], back=True)
+                p.add_(upd.reshape(shape).to(p.dtype), alpha=-float(step_size))
+                if group["weight_decay"] > 0:
+                    p.add_(p, alpha=-float(group["lr"]) * group["weight_decay"])
+                self._update_gg(g, st)
+                if st["step"] % group["precondition_frequency"] == 0:
+                    self._refresh_basis(st)
+        return loss

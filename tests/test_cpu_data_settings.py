@@ -1,0 +1,148 @@
+"""Data path, settings loader, schedules, goldfish masking."""
+import os
+import random
+
+import pytest
+import torch
+
+from recurrent_pretraining_b200.data import (DataScheduler, DataSchedulerTracker, ParquetStream, RandomTokens,
+                                             StatefulLoader, apply_tld, generic_collate_fn)
+from recurrent_pretraining_b200.data.goldfish import hashint
+from recurrent_pretraining_b200.optim.schedules import get_batch_size, get_lr
+from recurrent_pretraining_b200.settings import DataEntry, GoldfishConfig, parse_cli
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _write_shards(tmp_path, n_files=3, groups=2, rows=5, width=9):
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    counter = 0
+    for f in range(n_files):
+        tables = []
+        for _ in range(groups):
+            data = [[counter * 100 + j for j in range(width)] for counter in range(counter, counter + rows)]
+            counter += rows
+            tables.append(pa.table({"input_ids": data}))
+        with pq.ParquetWriter(str(tmp_path / f"shard_{f:03d}.parquet"), tables[0].schema) as w:
+            for t in tables:
+                w.write_table(t)
+    return n_files * groups * rows
+
+
+def test_parquet_stream_covers_everything_once_and_resumes(tmp_path):
+    total = _write_shards(tmp_path)
+    ds = ParquetStream(str(tmp_path), seed=1, plan_for_later_rank_expansion_to=0)
+    rows = [tuple(r.tolist()) for r in ds]
+    assert len(rows) == total and len(set(rows)) == total
+    # resume in the middle of a row group: the continuation equals the uninterrupted stream
+    ds1 = ParquetStream(str(tmp_path), seed=1, plan_for_later_rank_expansion_to=0)
+    it = iter(ds1)
+    head = [tuple(next(it).tolist()) for _ in range(7)]
+    state = ds1.state_dict()
+    ds2 = ParquetStream(str(tmp_path), seed=1, plan_for_later_rank_expansion_to=0)
+    ds2.load_state_dict(state)
+    tail = [tuple(r.tolist()) for r in ds2]
+    assert head + tail == rows
+    # rank sharding is disjoint
+    a = ParquetStream(str(tmp_path), seed=1, num_processes=3, process_rank=0, plan_for_later_rank_expansion_to=0)
+    b = ParquetStream(str(tmp_path), seed=1, num_processes=3, process_rank=1, plan_for_later_rank_expansion_to=0)
+    assert not set(a.parquet_files) & set(b.parquet_files)
+    # fingerprint mismatch restarts from the beginning instead of indexing out of bounds
+    bad = dict(state, fingerprint=["deadbeef"])
+    ds3 = ParquetStream(str(tmp_path), seed=1, plan_for_later_rank_expansion_to=0)
+    ds3.load_state_dict(bad)
+    assert ds3._file_idx == 0
+
+
+def test_collate_shift_and_padding_rules():
+    class Tok:
+        pad_id, eos_id = 9, 7
+
+    rows = [torch.arange(10), torch.tensor([1, 2, 9, 9, 9, 9, 9, 9, 9, 9])]
+    x, y, meta = generic_collate_fn(rows, tokenizer=Tok(), all_block_size_tensors=True)
+    assert x.shape == (2, 9) and y.shape == (2, 9) and x.dtype == torch.int64
+    assert torch.equal(y[0], torch.arange(1, 10))
+    assert x[1].tolist() == [1, 2, 7, 7, 7, 7, 7, 7, 7]  # pad -> eos in inputs only
+    assert y[1].tolist() == [2, 9, 9, 9, 9, 9, 9, 9, 9]
+    x2, y2, _ = generic_collate_fn([torch.arange(5), torch.arange(3)], tokenizer=Tok(), block_size=8)
+    assert x2.shape == (2, 4) and x2[1].tolist() == [0, 1, 2, 7]
+    with pytest.raises(StopIteration):
+        generic_collate_fn([torch.full((4,), 9)], tokenizer=Tok(), block_size=8)
+
+
+def test_stateful_loader_batches_and_random_tokens():
+    ds = RandomTokens(100, 17, seed=3)
+    loader = StatefulLoader(ds, 4, lambda rows: generic_collate_fn(rows, all_block_size_tensors=True), prefetch=2)
+    it = iter(loader)
+    x, y, _ = next(it)
+    assert x.shape == (4, 16) and int(x.max()) < 100 and torch.equal(x[:, 1:], y[:, :-1])
+    again = RandomTokens(100, 17, seed=3)
+    assert torch.equal(next(iter(again)), torch.cat([x[0, :1], y[0]]))
+
+
+def test_goldfish_masks():
+    labels = torch.randint(1, 1000, (2, 64))
+    out, idx = apply_tld(labels, GoldfishConfig(4, 1, 13, "static"))
+    assert (out[:, 1::4] == -100).all() and (out[:, 0] == labels[:, 0]).all()
+    for strat in ("hash-table", "hash-avalanche"):
+        a, da = apply_tld(labels, GoldfishConfig(4, 0, 5, strat))
+        b, _ = apply_tld(labels, GoldfishConfig(4, 0, 5, strat))
+        assert torch.equal(a, b)  # deterministic function of the context
+        assert (a[:, :4] == labels[:, :4]).all()  # the first context_width-1 labels are never dropped
+        assert 0 < int((a == -100).sum()) < labels.numel() // 2
+    # the hash is a bijection on 32 bits: distinct keys stay distinct
+    keys = torch.arange(0, 5000, dtype=torch.int64)
+    assert hashint(keys).unique().numel() == 5000
+
+
+def test_data_scheduler_weights():
+    entries = [DataEntry("rngds", "a", weight=30, scheduler=["linear", 10, 50, 10]), DataEntry("rngds", "b", scheduler=["base"]),
+               DataEntry("rngds", "c", weight=5, max_epoch=1)]
+    tracker = DataSchedulerTracker([e.weight for e in entries])
+    sched = DataScheduler(tracker, entries, max_steps=100)
+    sched.step(0)
+    assert tracker.weights == [10, 85.0, 5]
+    sched.step(5)
+    assert tracker.weights[0] == 30 and tracker.weights[1] == 65.0
+    tracker.epoch_count[2] = 1
+    sched.step(10)
+    assert tracker.weights == [50, 50.0, 0]
+
+
+def test_lr_and_batch_schedules():
+    kw = dict(warmup_steps=10, max_steps=100, cooldown_steps=20, min_lr=1e-5)
+    assert get_lr(1e-3, 5, schedule="cosine", **kw) == pytest.approx(5e-4)
+    assert get_lr(1e-3, 50, schedule="trapezoid", **kw) == 1e-3
+    assert get_lr(1e-3, 90, schedule="trapezoid", **kw) == pytest.approx(5e-4)
+    assert get_lr(1e-3, 100, schedule="trapezoid", **kw) == 1e-5
+    assert get_lr(1e-3, 55, schedule="cosine", warmup_steps=10, max_steps=100) == pytest.approx(5e-4, rel=1e-6)
+    with pytest.raises(ValueError):
+        get_lr(1e-3, 50, schedule="nope", **kw)
+    assert get_batch_size(0, 100, 8) == 1 and get_batch_size(50, 100, 8) == 4 and get_batch_size(200, 100, 8) == 8
+
+
+def test_settings_yaml_overrides_and_derivations(tmp_path, monkeypatch):
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    monkeypatch.delenv("SLURM_NTASKS", raising=False)
+    cfg = parse_cli([f"--config={ROOT}/launch_configs/nebel_zero_8xb200.yaml", f"--out_dir={tmp_path}",
+                     "--optim_config.lr=1e-3", "--fabric.optim_sharding=true", "--model_overwrite.mean_recurrence=16"])
+    assert cfg.gradient_accumulation_steps == 8 and cfg.devices == 8 and cfg.loader_block_size == 4097
+    assert cfg.optim_config["lr"] == 1e-3 and cfg.fabric.optim_sharding and cfg.model_config.mean_recurrence == 16
+    assert cfg.model_config.n_embd == 5280 and cfg.model_config.sampling_scheme == "fixed"
+    cfg.dump(str(tmp_path / "run_config.json"))
+    with pytest.raises(SystemExit):
+        parse_cli([f"--out_dir={tmp_path}", "--no_such_flag=1"])
+    with pytest.raises(ValueError):  # world batch must factor into micro-batch x accumulation x devices
+        parse_cli([f"--out_dir={tmp_path}", "--world_batch_size=12", "--micro_batch_size=5", "--max_steps=3", "--max_tokens=0"])
+
+
+def test_reference_yaml_loads(monkeypatch, tmp_path):
+    monkeypatch.setenv("WORLD_SIZE", "4096")
+    monkeypatch.setenv("SLURM_JOB_NUM_NODES", "512")
+    monkeypatch.setenv("SLURM_NTASKS_PER_NODE", "8")
+    monkeypatch.setenv("RUN_DIR", str(tmp_path))
+    cfg = parse_cli([f"--config={ROOT}/launch_configs/frontier_nebel_512_nodes.yaml"])
+    assert cfg.optimizer == "ELLISAdam" and cfg.optim_config["atan_adam"] and cfg.gradient_accumulation_steps == 1
+    assert cfg.partial_depth_eval == [1, 4, 8, 16, 64] and cfg.model_config.lockstep_n

@@ -1,0 +1,118 @@
+"""CPU parity of the training model against the unmodified reference modules (loaded from baseline/_ref)."""
+import math
+
+import pytest
+import torch
+
+import refload
+from recurrent_pretraining_b200.config import ModelConfig
+from recurrent_pretraining_b200.models.sampler import SCHEMES, sample_recurrence
+from recurrent_pretraining_b200.registry import name_to_config
+
+needs_ref = pytest.mark.skipif(not refload.available(), reason="reference not installed under baseline/_ref")
+
+TINY = dict(block_size=64, vocab_size=512, padding_multiple=64, n_embd=96, num_attention_heads=4,
+            num_key_value_heads=4, intermediate_size=160, n_layers_in_recurrent_block=2, n_layers_in_prelude=1,
+            n_layers_in_coda=1, mean_recurrence=4, mean_backprop_depth=2)
+
+
+@needs_ref
+def test_registry_matches_reference_shapes():
+    ref = refload.module("model_registry").name_to_config
+    for name, theirs in ref.items():
+        if theirs.get("architecture_class_name") not in ("GPT", "RecurrentGPT"):
+            continue
+        ours = name_to_config[name]
+        for key, val in theirs.items():
+            assert ours[key] == val, (name, key, ours.get(key), val)
+
+
+def test_flagship_parameter_count():
+    cfg = ModelConfig.from_name("nebel-raven-3.5b")
+    assert cfg.param_count() == 3_564_976_800
+    core = 4 * (cfg.param_count() - 65536 * 5280 - 5280 - 2 * 5280 * 5280) // 8
+    assert core == 1_581_592_320
+
+
+@needs_ref
+@pytest.mark.parametrize("name", ["nebel-raven-3.5b", "magpie-150m", "corone-raven-3.5b"])
+def test_state_dict_loss_and_grads_match_reference(name):
+    torch.manual_seed(0)
+    ref_model, _ = refload.build_train_model(name, **TINY)
+    cfg = ModelConfig.from_name(name, **TINY)
+    model = cfg.construct_model()
+    sd = ref_model.state_dict()
+    assert set(sd) == set(model.state_dict())
+    model.load_state_dict(sd)
+    ids = torch.randint(0, 512, (2, 64))
+    labels = torch.randint(0, 512, (2, 64))
+    labels[0, :5] = -100
+    ref_model.config.state_init = model.config.state_init = "zero"
+    for m in (ref_model, model):
+        m.train()
+    pair = torch.tensor([2, 2])
+    a = ref_model(ids, labels=labels, num_steps_pair=pair)
+    b = model(ids, labels=labels, num_steps_pair=pair)
+    assert torch.allclose(a["loss"], b["loss"], rtol=1e-5, atol=1e-6)
+    a["loss"].backward()
+    b["loss"].backward()
+    theirs = dict(ref_model.named_parameters())
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-4, atol=1e-7), n
+    # evaluation: mean_recurrence no-grad steps, logits returned
+    ref_model.eval(), model.eval()
+    with torch.no_grad():
+        la = ref_model(ids, return_logits=True)["logits"]
+        lb = model(ids, return_logits=True)["logits"]
+    assert torch.allclose(la, lb, rtol=1e-4, atol=1e-5)
+
+
+@needs_ref
+@pytest.mark.parametrize("scheme", [s for s in SCHEMES if s not in ("negative-binomial",)] + ["poisson-fill-curriculum-100"])
+def test_sampler_sequence_matches_reference(scheme):
+    ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **dict(TINY, mean_recurrence=32, mean_backprop_depth=8,
+                                                                       sampling_scheme=scheme))
+    ref_model.train()
+    for step in range(1, 40):
+        ref_model.step = step
+        n, k = ref_model.randomized_iteration_sampler()
+        ours = sample_recurrence(scheme, 32, 8, step)
+        assert ours == (int(n), int(k)), (scheme, step)
+
+
+def test_sampler_statistics_and_eval_mode():
+    draws = [sample_recurrence("poisson-lognormal-filling", 32, 8, s, lockstep_n=True, lockstep_k=True)
+             for s in range(1, 3000)]
+    total = sum(n + k for n, k in draws) / len(draws)
+    assert abs(total - 33) < 1.5  # E[p] ~ mean_recurrence + 1
+    assert all(k <= 8 and (k == 8 or n == 0) for n, k in draws)
+    assert sample_recurrence("poisson-lognormal-filling", 32, 8, 5, training=False) == (32, 0)
+    assert sample_recurrence("fixed", 32, 8, 5) == (24, 8)
+    a = sample_recurrence("poisson-fill", 32, 8, 7, rank=0)
+    b = sample_recurrence("poisson-fill", 32, 8, 7, rank=3)
+    c = sample_recurrence("poisson-fill", 32, 8, 7, rank=3, lockstep_n=True, lockstep_k=True)
+    assert a == c and isinstance(b, tuple)
+
+
+def test_state_init_sigma_and_knob():
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **TINY)
+    model = cfg.construct_model()
+    assert abs(model.state_sigma() - math.sqrt(0.4)) < 1e-6
+    x = model.initialize_state(torch.zeros(64, 64, 96))
+    assert abs(x.std().item() - math.sqrt(0.4) * 0.9866) < 0.02 and x.abs().max() <= 3 * math.sqrt(0.4) + 1e-5
+    cfg2 = ModelConfig.from_name("nebel-raven-3.5b", **dict(TINY, state_init_scale=0.4 / math.sqrt(0.4)))
+    assert abs(cfg2.construct_model().state_sigma() - 0.4) < 1e-6
+
+
+@needs_ref
+def test_init_statistics_match_reference_strategy():
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **dict(TINY, n_embd=192, intermediate_size=384))
+    ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **dict(TINY, n_embd=192, intermediate_size=384))
+    model = cfg.construct_model()
+    theirs = dict(ref_model.named_parameters())
+    for n, p in model.named_parameters():
+        if p.ndim < 2 or "qk_bias" in n:
+            continue
+        a, b = p.std().item(), theirs[n].std().item()
+        assert abs(a - b) < 0.15 * b + 1e-6, (n, a, b)
