@@ -1,0 +1,299 @@
+"""HF-compatible inference / finetuning model: ``RavenForCausalLM``.
+
+Public surface kept from recpre/raven_modeling_minimal.py:542-2323: ``forward(input_ids, input_embeds, input_states,
+attention_mask, position_ids, labels, num_steps, past_key_values, output_details, use_cache, cache_position,
+init_scale)`` returning ``CausalLMOutputRecurrentLatents``; the building blocks ``embed_inputs``, ``iterate_one_step``,
+``predict_from_latents``, ``initialize_state``; the ``generate`` dispatcher with the minimal, adaptive-compute,
+speculative and diffusion-style samplers (``models/generation.py``); the per-recurrence-step KV cache and its lookup
+strategies (``models/kv_cache.py``); the exit criteria (``models/exit_criteria.py``).  State-dict keys are identical to
+the training model, so checkpoints move between the two without renaming.
+
+The modules are the same block classes the training model uses; all arithmetic goes through ``ops.functional`` and
+runs the sm_100a kernels on a GPU.  The native decode engine (``engine/decode.py``) drives this model's weights with
+CUDA graphs for serving; ``generate`` here is the reference-faithful eager path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Union
+
+import torch
+import torch.nn as nn
+from transformers import GenerationMixin, PreTrainedModel
+from transformers.utils import ModelOutput
+
+from ..ops import functional as ops
+from ..ops import reference as ref
+from .blocks import Linear, make_block, make_norm
+from .generation import RavenGenerationMixin
+from .hf_config import RavenConfig
+from .kv_cache import RecurrentKVCache
+
+
+@dataclass
+class CausalLMOutputRecurrentLatents(ModelOutput):
+    loss: Optional[torch.Tensor] = None
+    log_ppl: Optional[torch.Tensor] = None
+    logits: Optional[torch.Tensor] = None
+    past_key_values: Optional[object] = None
+    latent_states: Optional[torch.Tensor] = None
+    hidden_states: Optional[torch.Tensor] = None
+    attention_maps: Optional[dict] = None
+    stats: Optional[dict] = None
+
+
+_DEFAULT_DETAILS = {"return_logits": True, "return_latents": True, "return_head": False, "return_stats": False}
+
+
+class RavenPreTrainedModel(PreTrainedModel):
+    config_class = RavenConfig
+    base_model_prefix = "model"
+    supports_gradient_checkpointing = True
+    _no_split_modules = ["SandwichBlock"]
+    _skip_keys_device_placement = ["past_key_values"]
+    _tied_weights_keys = {"lm_head.weight": "transformer.wte.weight"}
+    _supports_cache_class = True
+
+    def _init_weights(self, module):
+        """Weights are initialised by the block constructors (role-aware truncated normals); nothing to redo."""
+        return
+
+
+class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMixin):
+    def __init__(self, config: RavenConfig):
+        super().__init__(config)
+        self.config = config
+        mc = config.to_model_config()
+        self.model_config = mc
+        E = config.n_embd
+        P, R, C = config.n_layers_in_prelude, config.n_layers_in_recurrent_block, config.n_layers_in_coda
+        init = mc.init
+        off = P + R * config.mean_recurrence
+        self.transformer = nn.ModuleDict(dict(
+            wte=nn.Embedding(config.padded_vocab_size, E),
+            prelude=nn.ModuleList(make_block(mc, i) for i in range(P)),
+            adapter=Linear(2 * E, E, bias=config.bias, init=lambda w: init.init_weight_(w, "in_proj", P)),
+            core_block=nn.ModuleList(make_block(mc, i + P) for i in range(R)),
+            coda=nn.ModuleList(make_block(mc, i + off) for i in range(C)),
+            ln_f=make_norm(mc)))
+        init.init_weight_(self.transformer.wte.weight, "embedding")
+        self.emb_scale = config.init_values["embed_scale"]
+        self.lm_head = nn.Linear(E, config.padded_vocab_size, bias=False)
+        if config.tie_embeddings:
+            self.lm_head.weight = self.transformer.wte.weight
+        cos, sin = ref.rope_tables(E // config.n_heads, config.block_size, config.rope_base, 1)
+        self.register_buffer("freqs_cis", ref.freqs_cis_buffer(cos, sin), persistent=True)
+        self.gradient_checkpointing = False
+        self.post_init()
+
+    # -- HF plumbing ---------------------------------------------------------------------------------
+    def get_input_embeddings(self):
+        return self.transformer.wte
+
+    def get_output_embeddings(self):
+        return self.lm_head
+
+    def tie_weights(self, *a, **k):
+        if self.config.tie_embeddings:
+            self.lm_head.weight = self.transformer.wte.weight
+
+    # -- pieces --------------------------------------------------------------------------------------
+    def _rope(self, seq_len: int, position_ids=None, cache_position=None):
+        fc = self.freqs_cis[0, :, 0]
+        if position_ids is not None:
+            fc = fc.index_select(0, position_ids.reshape(-1))
+        elif cache_position is not None:
+            fc = fc[cache_position]
+        else:
+            fc = fc[:seq_len]
+        return fc[..., 0].contiguous(), fc[..., 1].contiguous()
+
+    def _attention(self, attn, x, rope, step_idx: int, cache):
+        B, S, E = x.shape
+        cos, sin = rope
+        qkv = attn.Wqkv(x)
+        q, k, v = ops.qk_bias_rope(qkv, attn.qk_bias, cos, sin, attn.n_head, attn.n_kv, attn.head_dim)
+        if cache is not None:
+            k, v = cache.update(k, v, step_idx)
+        y = ops.causal_attention(q, k, v, None, k.shape[1] - q.shape[1])
+        return attn.proj(y.reshape(B, S, E))
+
+    def _block(self, block, x, rope, step_idx: int, cache):
+        name = type(block).__name__
+        att = lambda h: self._attention(block.attn, h, rope, step_idx, cache)  # noqa: E731
+        if name == "SandwichBlock":
+            x = block.norm_2.forward_add(att(block.norm_1(x)), x)
+            return block.norm_4.forward_add(block.mlp(block.norm_3(x)), x)
+        if name == "TransformerPreNormBlock":
+            x = att(block.norm_1(x)) + x
+            return block.mlp(block.norm_2(x)) + x
+        if name == "TransformerPostNormBlock":
+            x = block.norm_1.forward_add(att(x), x)
+            return block.norm_2.forward_add(block.mlp(x), x)
+        raise NotImplementedError(f"block class {name} is not supported by the inference model")
+
+    def initialize_state(self, input_embeds, scale: float = 1.0):
+        """Truncated normal, sigma = init std * scale * embedding scale (recpre/raven_modeling_minimal.py:804-813)."""
+        std = self.config.init_values["std"] * scale
+        if std <= 0:
+            return torch.zeros_like(input_embeds)
+        seed = int(torch.randint(0, 2**31 - 1, (1,)))
+        return ops.trunc_normal_state(input_embeds, std * self.emb_scale, seed)
+
+    def _maybe_inject_noise(self, x, current_step: int, renorm: bool = True):
+        n0 = self.config.test_time_noise
+        if not n0 or n0 <= 0:
+            return x
+        n = n0 * self.config.init_values["std"] * self.emb_scale
+        kind = self.config.test_time_noise_type
+        if kind == "geom":
+            f = n / (current_step + 1)
+        elif kind == "sqrt":
+            f = n / math.sqrt(current_step + 1)
+        elif kind == "line":
+            f = max(n, (self.config.mean_recurrence - current_step) / self.config.mean_recurrence)
+        elif kind == "chi":
+            f = float(2 * torch.rand(1) * n)
+        elif kind == "fixed":
+            f = n
+        else:
+            raise ValueError(kind)
+        x = x * (1 - f) + torch.randn_like(x) * f
+        return self.transformer.core_block[-1].norm_4(x) if renorm else x
+
+    def core_block_forward(self, x, input_embeds, rope, cache, block_idx: int, current_step: int = 0):
+        x = self._maybe_inject_noise(x, current_step)
+        x = ops.adapter(x, input_embeds.to(x.dtype), self.transformer.adapter.weight)
+        for block in self.transformer.core_block:
+            block_idx += 1
+            x = self._block(block, x, rope, block_idx, cache)
+        return x, block_idx
+
+    def randomized_iteration_sampler(self):
+        """Log-normal Poisson depths on the global RNG in training mode, (mean_recurrence, 0) in eval mode."""
+        t = max(self.config.mean_recurrence - self.config.mean_backprop_depth, 0)
+        s = self.config.mean_backprop_depth
+        if not self.training:
+            return self.config.mean_recurrence, 0
+        sigma = 0.5
+        mu = math.log(t + s) - sigma**2 / 2
+        rate = torch.zeros((1,)).log_normal_(mean=mu, std=sigma)
+        p = int(torch.poisson(torch.tensor([float(rate)]))) + 1
+        return max(p - s, 0), min(s, p)
+
+    def iterate_forward(self, input_embeds, input_states, rope, block_idx, cache, num_steps=None, init_scale=1.0):
+        x = xk = self.initialize_state(input_embeds, init_scale) if input_states is None else input_states.clone()
+        if num_steps is None:
+            n, k = self.randomized_iteration_sampler()
+        elif hasattr(num_steps, "__len__") and len(num_steps) > 1:
+            n, k = int(num_steps[0]), int(num_steps[1])
+        else:
+            n, k = int(num_steps), 0
+        with torch.no_grad():
+            for step in range(n):
+                xk = x
+                x, block_idx = self.core_block_forward(x, input_embeds, rope, cache, block_idx, step)
+        for step in range(k):
+            xk = x
+            if self.gradient_checkpointing and self.training:
+                x, block_idx = torch.utils.checkpoint.checkpoint(self.core_block_forward, x, input_embeds, rope, cache,
+                                                                 block_idx, n + step, use_reentrant=False)
+            else:
+                x, block_idx = self.core_block_forward(x, input_embeds, rope, cache, block_idx, n + step)
+        return self.transformer.ln_f(x), n, k, xk.detach(), block_idx
+
+    # -- forward -------------------------------------------------------------------------------------
+    def forward(self, input_ids: Optional[torch.Tensor] = None, input_embeds=None, input_states=None,
+                attention_mask=None, position_ids=None, labels=None, num_steps=None, past_key_values=None,
+                output_details: dict = _DEFAULT_DETAILS, use_cache: bool = False, cache_position=None,
+                init_scale: float = 1.0, **kwargs) -> CausalLMOutputRecurrentLatents:
+        S = input_ids.shape[1] if input_ids is not None else input_embeds.shape[1]
+        rope = self._rope(S, position_ids, cache_position)
+        if input_embeds is None:
+            input_embeds = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+        elif self.emb_scale != 1:
+            input_embeds = input_embeds * self.emb_scale
+        if use_cache and past_key_values is None:
+            past_key_values = RecurrentKVCache(core_layers=self.config.n_layers_in_recurrent_block,
+                                               prelude_layers=self.config.n_layers_in_prelude)
+        block_idx = -1
+        for block in self.transformer.prelude:
+            block_idx += 1
+            input_embeds = self._block(block, input_embeds, rope, block_idx, past_key_values)
+        x, n, k, xk, block_idx = self.iterate_forward(input_embeds, input_states, rope, block_idx, past_key_values,
+                                                      num_steps, init_scale)
+        latent_states = x.detach().clone()
+        head_idx = 0
+        for block in self.transformer.coda:
+            head_idx -= 1
+            x = self._block(block, x, rope, head_idx, past_key_values)
+        x = self.transformer.ln_f(x)
+        logits = ops.linear(x, self.lm_head.weight).float()
+        if labels is not None:
+            loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1),
+                                                     ignore_index=-100)
+            log_ppl = loss.detach().clone()
+        else:
+            loss, log_ppl = torch.as_tensor(0.0), torch.as_tensor(0.0)
+        return CausalLMOutputRecurrentLatents(
+            loss=loss, log_ppl=log_ppl, logits=logits if output_details["return_logits"] else None,
+            past_key_values=past_key_values, hidden_states=x if output_details["return_head"] else None,
+            latent_states=latent_states if output_details["return_latents"] else None,
+            stats=self.get_stats(logits, x, latent_states, xk, input_embeds, n, k)
+            if output_details["return_stats"] else None)
+
+    # -- alternative entry points (used by the samplers and by external evaluation code) ---------------
+    @torch.no_grad()
+    def embed_inputs(self, input_ids, attention_mask=None, position_ids=None, past_key_values=None,
+                     use_cache: bool = False, cache_position=None, **kwargs):
+        rope = self._rope(input_ids.shape[1], position_ids, cache_position)
+        e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+        if use_cache and past_key_values is None:
+            past_key_values = RecurrentKVCache(core_layers=self.config.n_layers_in_recurrent_block,
+                                               prelude_layers=self.config.n_layers_in_prelude)
+        block_idx = -1
+        for block in self.transformer.prelude:
+            block_idx += 1
+            e = self._block(block, e, rope, block_idx, past_key_values)
+        return e, block_idx
+
+    @torch.no_grad()
+    def iterate_one_step(self, input_embeds, input_states, position_ids=None, cache_position=None, block_idx=0,
+                         attention_mask=None, past_key_values=None, current_step: int = 0):
+        rope = self._rope(input_embeds.shape[1], position_ids, cache_position)
+        x, block_idx = self.core_block_forward(input_states, input_embeds, rope, past_key_values, int(block_idx),
+                                               current_step)
+        return x, block_idx, current_step + 1
+
+    def predict_from_latents(self, latents, attention_mask=None, position_ids=None, cache_position=None,
+                             past_key_values=None):
+        rope = self._rope(latents.shape[1], position_ids, cache_position)
+        x = self.transformer.ln_f(latents)
+        head_idx = 0
+        for block in self.transformer.coda:
+            head_idx -= 1
+            x = self._block(block, x, rope, head_idx, past_key_values)
+        x = self.transformer.ln_f(x)
+        logits = ops.linear(x, self.lm_head.weight).float()
+        return CausalLMOutputRecurrentLatents(loss=torch.as_tensor(0.0), log_ppl=torch.as_tensor(0.0), logits=logits,
+                                              past_key_values=past_key_values, latent_states=x)
+
+    @torch.no_grad()
+    def get_stats(self, logits, x, latents, xk, input_embeds, n, k) -> dict:
+        probs = torch.softmax(logits.float(), dim=-1)
+        return {"entropy": float(-(probs * torch.log(probs + 1e-10)).sum(-1).mean()),
+                "residual": float((x.float() - latents.float()).norm(dim=-1).mean()),
+                "rel_residual": float(((latents.float() - xk.float()).norm(dim=-1) / latents.float().norm(dim=-1)).mean()),
+                "num_steps_no_grad": n, "num_steps_with_grad": k}
+
+    # -- conversion ------------------------------------------------------------------------------------
+    @classmethod
+    def from_training_model(cls, model, dtype: Optional[torch.dtype] = None) -> "RavenForCausalLM":
+        """Build the inference model from a training ``RecurrentGPT`` (same state-dict keys; weights are copied)."""
+        hf = cls(RavenConfig.from_model_config(model.config))
+        sd = {k: v for k, v in model.state_dict().items()}
+        hf.load_state_dict(sd, strict=True)
+        if dtype is not None:
+            hf = hf.to(dtype)
+        return hf

@@ -1,0 +1,146 @@
+"""HF-compatible inference model: parity with the unmodified reference HF file, cache semantics, samplers."""
+import pytest
+import torch
+
+import refload
+from recurrent_pretraining_b200.config import ModelConfig
+from recurrent_pretraining_b200.models.exit_criteria import get_adaptive_exit_evaluator
+from recurrent_pretraining_b200.models.hf import RavenForCausalLM
+from recurrent_pretraining_b200.models.hf_config import RavenConfig
+from recurrent_pretraining_b200.models.kv_cache import RecurrentKVCache
+
+needs_ref = pytest.mark.skipif(not refload.available(), reason="reference not installed under baseline/_ref")
+SMALL = dict(n_embd=96, n_heads=4, n_layers=8, block_size=128, vocab_size=66048, intermediate_size=160,
+             n_layers_in_recurrent_block=4, mean_recurrence=4, n_layers_in_prelude=2, n_layers_in_coda=2)
+
+
+def _ours(seed=0):
+    torch.manual_seed(seed)
+    return RavenForCausalLM(RavenConfig(**SMALL)).eval()
+
+
+def _reference_pair():
+    """Reference HF model with our weights.  Only a class attribute is adjusted at run time (transformers 5 wants a
+    dict for tied weights); the reference source is untouched."""
+    mod = refload.module("raven_modeling_minimal")
+    cfgmod = refload.module("raven_config_minimal")
+    mod.RavenForCausalLM._tied_weights_keys = {"lm_head.weight": "transformer.wte.weight"}
+    ours = _ours()
+    theirs = mod.RavenForCausalLM(cfgmod.RavenConfig(**SMALL)).eval()
+    theirs.load_state_dict(ours.state_dict())
+    return ours, theirs, mod
+
+
+@needs_ref
+def test_forward_logits_loss_and_cached_decoding_match_reference():
+    ours, theirs, mod = _reference_pair()
+    ids = torch.randint(0, 60000, (2, 16))
+    state = torch.randn(2, 16, 96) * 0.5
+    a = ours(ids, input_states=state, num_steps=3, labels=ids)
+    b = theirs(ids, input_states=state, num_steps=3, labels=ids)
+    assert torch.allclose(a.logits, b.logits, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(a.loss, b.loss, rtol=1e-5) and torch.allclose(a.latent_states, b.latent_states, atol=1e-4)
+    # prefill + token-by-token decoding through the per-step cache
+    oa = ours(ids[:, :10], num_steps=3, init_scale=0.0, use_cache=True)
+    ob = theirs(ids[:, :10], num_steps=3, init_scale=0.0, use_cache=True,
+                past_key_values=mod.HuginnDynamicCache(), cache_position=torch.arange(10))
+    assert torch.allclose(oa.logits, ob.logits, rtol=1e-4, atol=1e-4)
+    for t in range(10, 16):
+        pos = torch.tensor([t])
+        oa = ours(ids[:, t:t + 1], num_steps=3, init_scale=0.0, use_cache=True, past_key_values=oa.past_key_values,
+                  cache_position=pos)
+        ob = theirs(ids[:, t:t + 1], num_steps=3, init_scale=0.0, use_cache=True, past_key_values=ob.past_key_values,
+                    cache_position=pos)
+        assert torch.allclose(oa.logits, ob.logits, rtol=1e-4, atol=2e-4), t
+    assert oa.past_key_values.get_seq_length() == 16
+    assert abs(oa.past_key_values.get_memory_usage() - ob.past_key_values.get_memory_usage()) < 1e-6
+
+
+@needs_ref
+def test_kl_exit_hand_loop_matches_reference_primitives():
+    ours, theirs, mod = _reference_pair()
+    ids = torch.randint(0, 60000, (1, 9))
+    traces = []
+    for model, evaluator, cache in ((ours, get_adaptive_exit_evaluator(ours, "kl", 5e-4), RecurrentKVCache()),
+                                    (theirs, mod.get_adaptive_exit_evaluator(theirs, "kl", 5e-4),
+                                     mod.HuginnDynamicCache())):
+        aux = dict(past_key_values=cache, cache_position=torch.arange(9))
+        e, block_idx = model.embed_inputs(ids, **aux)
+        x = torch.zeros_like(e)
+        evaluator.init(x)
+        vals = []
+        for step in range(6):
+            x, block_idx, _ = model.iterate_one_step(e, x, block_idx=block_idx, **aux, current_step=step)
+            exits, out, v = evaluator.check(model, x, aux)
+            vals.append(float(v[0]))
+        traces.append((vals, out.logits))
+    assert traces[0][0] == pytest.approx(traces[1][0], rel=1e-3, abs=1e-6)
+    assert torch.allclose(traces[0][1], traces[1][1], rtol=1e-4, atol=2e-4)
+
+
+@needs_ref
+@pytest.mark.parametrize("strategy", ["latest-m4", "available-m4", "always-last-m4", "skip", "latest-m4-compress-s4",
+                                      "latest-m4-compress-anchor"])
+def test_cache_lookup_strategies_match_reference(strategy):
+    mod = refload.module("raven_modeling_minimal")
+    torch.manual_seed(1)
+    a, b = RecurrentKVCache(strategy), mod.HuginnDynamicCache(strategy)
+    depth_per_token = [3, 1, 2, 3, 1]  # recurrences computed for each position (ragged depth)
+    for pos, depth in enumerate(depth_per_token):
+        steps = [0, 1] + [2 + 4 * j + blk for j in range(depth) for blk in range(4)] + [-1, -2]
+        for s in steps:
+            k, v = torch.randn(1, 1, 2, 8), torch.randn(1, 1, 2, 8)
+            ka, va = a.update(k, v, s)
+            kb, vb = b.update(k.transpose(1, 2), v.transpose(1, 2), torch.tensor(s))
+            assert torch.equal(ka.transpose(1, 2), kb) and torch.equal(va.transpose(1, 2), vb), (pos, s)
+    a.clear_last_k_entries(2)
+    b.clear_last_k_entries(2)
+    assert a.get_seq_length() == b.get_seq_length() == 3
+    assert abs(a.get_memory_usage() - b.get_memory_usage()) < 1e-9
+
+
+def test_training_model_converts_to_inference_model():
+    torch.manual_seed(2)
+    cfg = ModelConfig.from_name("tiny-raven-cpu")
+    train_model = cfg.construct_model().eval()
+    hf = RavenForCausalLM.from_training_model(train_model).eval()
+    ids = torch.randint(0, 8192, (2, 32))
+    state = torch.zeros(2, 32, 256)
+    with torch.no_grad():
+        a = train_model(ids, return_logits=True, num_steps_pair=torch.tensor([3, 0]), input_states=state)["logits"]
+        b = hf(ids, input_states=state, num_steps=3).logits
+    assert torch.allclose(a, b, rtol=1e-4, atol=1e-4)
+    assert set(hf.state_dict()) == set(train_model.state_dict())
+
+
+def test_generate_paths_and_dispatch(tmp_path):
+    m = _ours(3)
+    ids = torch.randint(0, 60000, (2, 10))
+    plain = m.generate(ids, max_new_tokens=6, num_steps=4, init_scale=0.0)
+    assert plain.shape == (2, 16) and torch.equal(plain[:, :10], ids)
+    # adaptive compute with a threshold nobody reaches equals fixed-depth decoding and reports the step counts
+    out = m.generate(ids, max_new_tokens=6, num_steps=4, init_scale=0.0, criterion="kl", exit_threshold=0.0,
+                     generation_config=_cfg(return_dict_in_generate=True))
+    assert torch.equal(out.sequences, plain) and out.scores["compute_steps"][0] == [4, 4]
+    early = m.generate(ids, max_new_tokens=3, num_steps=8, init_scale=0.0, criterion="latent-diff", exit_threshold=10.0,
+                       generation_config=_cfg(return_dict_in_generate=True), cache_lookup_strategy="latest-m4")
+    assert early.scores["compute_steps"][0] == [1, 1]  # everything exits after the first recurrence
+    spec = m.generate(ids, max_new_tokens=6, draft_steps=2, lookahead_for_draft=3, num_steps=4, init_scale=0.0)
+    assert torch.equal(spec[:, :16], plain)  # greedy speculative decoding reproduces greedy decoding
+    cont = m.generate(ids, max_new_tokens=4, num_steps=4, init_scale=0.0, continuous_compute=True)
+    assert cont.shape == (2, 14)
+    diff = m.generate(ids[:1], max_new_tokens=4, headway=2, inner_recurrence=2, num_steps=4, init_scale=0.0)
+    assert diff.shape[0] == 1 and 10 < diff.shape[1] <= 14
+    sampled = m.generate(ids, max_new_tokens=3, num_steps=2, generation_config=_cfg(do_sample=True, temperature=0.7,
+                                                                                   top_k=50, top_p=0.9, min_p=0.01,
+                                                                                   repetition_penalty=1.2))
+    assert sampled.shape == (2, 13)
+    m.save_pretrained(str(tmp_path))
+    again = RavenForCausalLM.from_pretrained(str(tmp_path)).eval()
+    assert torch.equal(again.generate(ids, max_new_tokens=6, num_steps=4, init_scale=0.0), plain)
+
+
+def _cfg(**kw):
+    from types import SimpleNamespace
+
+    return SimpleNamespace(**kw)
