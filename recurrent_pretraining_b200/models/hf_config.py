@@ -62,6 +62,9 @@ class RavenConfig(PretrainedConfig):
                             "embedding": math.sqrt(2 / (5 * n_embd)), "embed_scale": math.sqrt(n_embd)}
         self.test_time_noise = kwargs.pop("test_time_noise", 0)
         self.test_time_noise_type = kwargs.pop("test_time_noise_type", "fixed")
+        for derived in ("tie_word_embeddings", "padded_vocab_size", "num_key_value_heads", "head_dim",
+                        "effective_expected_depth", "init_values"):
+            kwargs.pop(derived, None)
         super().__init__(tie_word_embeddings=tie_embeddings, **kwargs)
 
     # ---- bridge to the training-side config ---------------------------------------------------------
