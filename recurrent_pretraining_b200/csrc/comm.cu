@@ -42,8 +42,8 @@ __device__ __forceinline__ float4 ld_peer_f4(const float4* p) {
 // Cross-rank barrier: thread i publishes `epoch` in slot [rank] of rank i's flag array and waits until slot [i] of
 // its own array reaches `epoch`.  Optionally sums one float per rank (the squared-norm partials) after the wait.
 // status: 0 ok, ERR_WAIT_PEER_FLAG after `timeout_ns` without the peer's flag.
-__global__ void barrier_kernel(PeerPtrs flags, int rank, int N, uint32_t epoch, unsigned long long timeout_ns,
-                               PeerPtrs partials, float* total_out, int* err) {
+__global__ void barrier_kernel(const __grid_constant__ PeerPtrs flags, int rank, int N, uint32_t epoch, unsigned long long timeout_ns,
+                               const __grid_constant__ PeerPtrs partials, float* total_out, int* err) {
   __shared__ int ok_count;
   if (threadIdx.x == 0) ok_count = 0;
   __syncthreads();
@@ -79,7 +79,7 @@ __global__ void barrier_kernel(PeerPtrs flags, int rank, int N, uint32_t epoch, 
 // *sumsq += sum of squares of the reduced values.  count % 4 == 0, pointers 16-byte aligned.
 template <int N>
 __global__ void __launch_bounds__(512)
-reduce_scatter_kernel(PeerPtrs bufs, int rank, size_t start, size_t count, float* sumsq) {
+reduce_scatter_kernel(const __grid_constant__ PeerPtrs bufs, int rank, size_t start, size_t count, float* sumsq) {
   __shared__ float red[16];
   float4* own = reinterpret_cast<float4*>(reinterpret_cast<float*>(bufs.p[rank]) + start);
   const float4* peer[N];
@@ -113,7 +113,7 @@ reduce_scatter_kernel(PeerPtrs bufs, int rank, size_t start, size_t count, float
 
 // Pull all-gather of 16-byte units: own[slice q] = buf_q[slice q] for every q != rank, slices of `slice_vec` uint4.
 __global__ void __launch_bounds__(512)
-allgather_kernel(PeerPtrs bufs, int rank, int N, size_t slice_vec, size_t total_vec) {
+allgather_kernel(const __grid_constant__ PeerPtrs bufs, int rank, int N, size_t slice_vec, size_t total_vec) {
   uint4* own = reinterpret_cast<uint4*>(bufs.p[rank]);
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -133,7 +133,7 @@ allgather_kernel(PeerPtrs bufs, int rank, int N, size_t slice_vec, size_t total_
 // separate result buffer, so that no rank overwrites data a peer may still be reading).
 template <int N>
 __global__ void __launch_bounds__(512)
-allreduce_oneshot_kernel(PeerPtrs bufs, int rank, float* out, size_t count, float scale, float* sumsq) {
+allreduce_oneshot_kernel(const __grid_constant__ PeerPtrs bufs, int rank, float* out, size_t count, float scale, float* sumsq) {
   __shared__ float red[16];
   float ss = 0.f;
   const size_t nvec = count >> 2;
@@ -165,7 +165,7 @@ allreduce_oneshot_kernel(PeerPtrs bufs, int rank, float* out, size_t count, floa
 // bf16 -> fp32 variants for the communication sweep (bf16 buckets reduced in fp32)
 template <int N>
 __global__ void __launch_bounds__(512)
-reduce_scatter_bf16_kernel(PeerPtrs bufs, int rank, size_t start, size_t count, float* out_f32, float scale,
+reduce_scatter_bf16_kernel(const __grid_constant__ PeerPtrs bufs, int rank, size_t start, size_t count, float* out_f32, float scale,
                            float* sumsq) {
   __shared__ float red[16];
   float ss = 0.f;
@@ -220,7 +220,7 @@ struct AdamArgs2 {
 // (and optionally the fp32 master value) of every updated element to the same offset on all ranks.
 __global__ void __launch_bounds__(256)
 adamw_push_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
-                  PeerPtrs shadows, PeerPtrs masters, size_t n, const float* __restrict__ gnorm_sq, AdamArgs2 a) {
+                  const __grid_constant__ PeerPtrs shadows, const __grid_constant__ PeerPtrs masters, size_t n, const float* __restrict__ gnorm_sq, AdamArgs2 a) {
   float clip = 1.f;
   bool skip = false;
   if (gnorm_sq) {

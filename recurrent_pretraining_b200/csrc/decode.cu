@@ -1,0 +1,256 @@
+// Decode-side kernels of the native inference engine (all bandwidth-bound, bf16 data, fp32 math):
+//   * rope_append   : q/k bias + RoPE for the single new position of every sequence, q written to a packed buffer,
+//                     k and v appended in place to the per-recurrence-step cache slot [B, Lmax, Hkv, D]
+//   * decode_attn   : one query row per (sequence, head) against the cached keys/values of one slot, keys split
+//                     over `splits` CTAs with an online-softmax merge (flash-decoding); per-sequence lengths
+//   * kl_exit       : log-softmax of the current logits, KL(prev || cur) against the previous recurrence step,
+//                     threshold compare and first-exit bookkeeping, entirely on the device
+#include "common.cuh"
+
+namespace b200 {
+
+// qkv: [B, (H + 2 Hkv) * D] for the new token of each sequence; pos[b]: its absolute position.
+__global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qk_bias,
+                                   const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                   const int* __restrict__ pos, __nv_bfloat16* __restrict__ q_out,
+                                   __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int B,
+                                   int H, int Hkv, int D, int Lmax) {
+  const int wq = H * D, wk = Hkv * D, wtot = wq + 2 * wk;
+  const int vpr = wtot >> 3;
+  const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= B * vpr) return;
+  const int b = gid / vpr, c = (gid % vpr) << 3;
+  const int p = pos[b];
+  uint4 v = reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(b) * wtot)[c >> 3];
+  if (c < wq + wk) {
+    const bool is_q = c < wq;
+    const int cc = is_q ? c : c - wq;
+    const int h = cc / D, d = cc % D;
+    const float* cs = cosT + static_cast<size_t>(p) * (D >> 1) + (d >> 1);
+    const float* sn = sinT + static_cast<size_t>(p) * (D >> 1) + (d >> 1);
+    const float* bias = qk_bias ? qk_bias + (is_q ? 0 : H * D) + h * D + d : nullptr;
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(w[j]);
+      if (bias) f = unpack_bf16x2(pack_bf16x2(f.x + bias[2 * j], f.y + bias[2 * j + 1]));
+      w[j] = pack_bf16x2(f.x * cs[j] - f.y * sn[j], f.y * cs[j] + f.x * sn[j]);
+    }
+    v = make_uint4(w[0], w[1], w[2], w[3]);
+    if (is_q) {
+      reinterpret_cast<uint4*>(q_out + static_cast<size_t>(b) * wq)[c >> 3] = v;
+    } else {
+      reinterpret_cast<uint4*>(k_cache + (static_cast<size_t>(b) * Lmax + p) * wk)[cc >> 3] = v;
+    }
+  } else {
+    const int cc = c - wq - wk;
+    reinterpret_cast<uint4*>(v_cache + (static_cast<size_t>(b) * Lmax + p) * wk)[cc >> 3] = v;
+  }
+}
+
+// grid (splits, H, B), 128 threads = 4 warps; each warp walks keys l = split_begin + warp, +4, ...; a lane holds
+// D/32 (<= 4) dims of q.  Partial (m, l, o[D]) per split go to scratch and are merged by the last kernel.
+template <int DPL>  // dims per lane: D = 32 * DPL
+__global__ void __launch_bounds__(128)
+decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                   const __nv_bfloat16* __restrict__ vc, const int* __restrict__ lens, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int H, int Hkv, int Lmax, float scale_log2) {
+  constexpr int D = 32 * DPL;
+  const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (H / Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = lens[b];
+  const int per = (L + nsplit - 1) / nsplit;
+  const int l0 = split * per, l1 = min(L, l0 + per);
+  float qv[DPL], acc[DPL];
+  const __nv_bfloat16* qp = q + (static_cast<size_t>(b) * H + h) * D;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    qv[i] = bf2f(qp[lane + 32 * i]) * scale_log2;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, lsum = 0.f;
+  const size_t row = static_cast<size_t>(Hkv) * D;
+  const __nv_bfloat16* kb = kc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D;
+  const __nv_bfloat16* vb = vc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D;
+  for (int l = l0 + warp; l < l1; l += 4) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) s += qv[i] * bf2f(kb[l * row + lane + 32 * i]);
+    s = warp_sum(s);
+    const float mn = fmaxf(m, s);
+    const float alpha = exp2f(m - mn), p = exp2f(s - mn);
+    lsum = lsum * alpha + p;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = acc[i] * alpha + p * bf2f(vb[l * row + lane + 32 * i]);
+    m = mn;
+  }
+  // merge the 4 warps through shared memory
+  __shared__ float sm_m[4], sm_l[4], sm_o[4][D];
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = lsum; }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) sm_o[warp][lane + 32 * i] = acc[i];
+  __syncthreads();
+  if (warp == 0) {
+    float mm = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float ll = 0.f, o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float a = (sm_m[w] == -INFINITY) ? 0.f : exp2f(sm_m[w] - mm);
+      ll += sm_l[w] * a;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) o[i] += sm_o[w][lane + 32 * i] * a;
+    }
+    const size_t pidx = (static_cast<size_t>(b) * H + h) * nsplit + split;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) part_o[pidx * D + lane + 32 * i] = o[i];
+    if (lane == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = ll; }
+  }
+}
+
+template <int DPL>
+__global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int nsplit, int total /* B*H */) {
+  constexpr int D = 32 * DPL;
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (idx >= total) return;
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(static_cast<size_t>(idx) * nsplit + s) * 2]);
+  float ll = 0.f, o[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const size_t p = static_cast<size_t>(idx) * nsplit + s;
+    const float ms = part_ml[p * 2];
+    const float a = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    ll += part_ml[p * 2 + 1] * a;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] += part_o[p * D + lane + 32 * i] * a;
+  }
+  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) out[static_cast<size_t>(idx) * D + lane + 32 * i] = f2bf(o[i] * inv);
+}
+
+// One CTA per sequence.  logits: [B, V] fp32 of the current recurrence step.  prev_logp: [B, V] fp32 (in/out).
+// kl_out[b] = sum_v exp(prev) * (prev - cur).  exited[b] (in/out): set when kl < threshold and `armed` != 0;
+// at a sequence's FIRST exit its step count and argmax token are recorded.  live_count: number of sequences
+// that have not exited yet (host reads it every few steps instead of after every step).
+__global__ void __launch_bounds__(512)
+kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, float* __restrict__ kl_out,
+               int* __restrict__ exited, int* __restrict__ steps_taken, long long* __restrict__ token_out,
+               int* __restrict__ live_count, int V, float threshold, int step, int armed) {
+  __shared__ float red[16];
+  __shared__ int redi[16];
+  __shared__ float s_val;
+  const int b = blockIdx.x;
+  const float* x = logits + static_cast<size_t>(b) * V;
+  float* pl = prev_logp + static_cast<size_t>(b) * V;
+  float m = -INFINITY;
+  int am = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x)
+    if (x[i] > m) { m = x[i]; am = i; }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, am, o);
+    if (om > m || (om == m && oi < am)) { m = om; am = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = m; redi[threadIdx.x >> 5] = am; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w)
+      if (red[w] > red[0] || (red[w] == red[0] && redi[w] < redi[0])) { red[0] = red[w]; redi[0] = redi[w]; }
+    s_val = red[0];
+  }
+  __syncthreads();
+  m = s_val;
+  const int argmax = redi[0];
+  __syncthreads();
+  float s = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) s += __expf(x[i] - m);
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    s_val = m + __logf(t);
+  }
+  __syncthreads();
+  const float lse = s_val;
+  __syncthreads();
+  float kl = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float cur = x[i] - lse, prev = pl[i];
+    kl += __expf(prev) * (prev - cur);
+    pl[i] = cur;
+  }
+  kl = warp_sum(kl);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = kl;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    kl_out[b] = t;
+    if (!exited[b]) {
+      token_out[b] = argmax;       // latest prediction; frozen once the sequence has exited
+      steps_taken[b] = step + 1;
+      if (armed && t < threshold) {
+        exited[b] = 1;
+        atomicSub(live_count, 1);
+      }
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float* cosT, const float* sinT,
+                              const int* pos, void* q_out, void* k_cache, void* v_cache, int B, int H, int Hkv, int D,
+                              int Lmax, void* stream) {
+  if (D % 8) return -1;
+  const int n = B * ((H + 2 * Hkv) * D / 8);
+  rope_append_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(qkv), qk_bias, cosT, sinT, pos, reinterpret_cast<__nv_bfloat16*>(q_out),
+      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), B, H, Hkv, D, Lmax);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// scratch: part_o [B*H*splits*D] fp32, part_ml [B*H*splits*2] fp32 (caller-provided).
+B200_API int b200_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* lens, void* out,
+                                   float* part_o, float* part_ml, int B, int H, int Hkv, int D, int Lmax, int splits,
+                                   float scale, void* stream) {
+  if (D % 32 || D > 128 || splits < 1) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const float sl2 = scale * 1.4426950408889634f;
+  dim3 grid(splits, H, B);
+  const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(v_cache);
+  __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out);
+  const int total = B * H;
+#define RUN(DPL)                                                                                         \
+  decode_attn_kernel<DPL><<<grid, 128, 0, st>>>(qb, kb, vb, lens, part_o, part_ml, H, Hkv, Lmax, sl2);  \
+  decode_attn_merge_kernel<DPL><<<(total + 3) / 4, 128, 0, st>>>(part_o, part_ml, ob, splits, total);
+  switch (D / 32) {
+    case 1: RUN(1) break;
+    case 2: RUN(2) break;
+    case 3: RUN(3) break;
+    case 4: RUN(4) break;
+    default: return -1;
+  }
+#undef RUN
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+B200_API int b200_kl_exit(const float* logits, float* prev_logp, float* kl_out, int* exited, int* steps_taken,
+                          long long* token_out, int* live_count, int B, int V, float threshold, int step, int armed,
+                          void* stream) {
+  kl_exit_kernel<<<B, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, prev_logp, kl_out, exited, steps_taken,
+                                                                      token_out, live_count, V, threshold, step, armed);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

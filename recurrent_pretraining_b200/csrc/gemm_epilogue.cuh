@@ -5,13 +5,18 @@
 
 namespace b200 {
 
-enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_RESID = 3, OUT_SWIGLU = 4 };
+enum OutMode : int {
+  OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_RESID = 3, OUT_SWIGLU = 4,
+  OUT_BF16_T = 5,        // transposed store C[col, row] (skinny decode GEMMs computed as W x^T)
+  OUT_F32_T_ATOMIC = 6,  // transposed fp32 atomic accumulate (split-K partial sums)
+};
 
 struct GemmParams {
   int M, N, K1, K2;
   int ldc;        // elements
   int ld_resid;   // elements (OUT_BF16_RESID)
   int swiglu_n;   // row offset of the "up" half inside B (OUT_SWIGLU)
+  int ksplit;     // number of K ranges per output tile (>1 only with OUT_F32_T_ATOMIC)
   void* C;
   const __nv_bfloat16* resid;
   int* err;
@@ -22,6 +27,27 @@ struct GemmParams {
 template <int BN, int MODE>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, int row, int n0) {
   const bool row_ok = row < p.M;
+  if constexpr (MODE == OUT_BF16_T || MODE == OUT_F32_T_ATOMIC) {
+    // C is [N, M] row-major: lanes of a warp hold consecutive rows, so each column is one coalesced store
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      uint32_t v[16];
+      tmem_ld_32x16(taddr + c0, v);
+      tmem_ld_wait();
+      if (!row_ok) continue;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int col = n0 + c0 + i;
+        if (col < p.N) {
+          if constexpr (MODE == OUT_BF16_T)
+            reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(col) * p.ldc + row] = f2bf(__uint_as_float(v[i]));
+          else
+            atomicAdd(reinterpret_cast<float*>(p.C) + static_cast<size_t>(col) * p.ldc + row, __uint_as_float(v[i]));
+        }
+      }
+    }
+    return;
+  }
   constexpr int CH = (MODE == OUT_SWIGLU) ? 16 : 32;  // columns per step
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += CH) {

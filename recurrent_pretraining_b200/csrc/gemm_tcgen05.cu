@@ -60,7 +60,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int ksplit = p.ksplit > 1 ? p.ksplit : 1;
+  const int num_tiles = tiles_m * tiles_n * ksplit;   // work items: (output tile, K range)
   const int nk1 = (p.K1 + BK - 1) / BK;
   const int nk2 = (p.K2 + BK - 1) / BK;
   const int nk = nk1 + nk2;
@@ -96,9 +97,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM;
-        const int n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < nk; ++kb, ++it) {
+        const int ot = tile / ksplit, ks = tile % ksplit;
+        const int m0 = (ot % tiles_m) * BM;
+        const int n0 = (ot / tiles_m) * BN;
+        const int kb0 = static_cast<int>(static_cast<long long>(nk) * ks / ksplit);
+        const int kb1 = static_cast<int>(static_cast<long long>(nk) * (ks + 1) / ksplit);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
@@ -146,7 +150,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
-        for (int kb = 0; kb < nk; ++kb, ++it) {
+        const int ks = tile % ksplit;
+        const int kb0 = static_cast<int>(static_cast<long long>(nk) * ks / ksplit);
+        const int kb1 = static_cast<int>(static_cast<long long>(nk) * (ks + 1) / ksplit);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_WAIT_TMA_FULL)) { ok = false; break; }
@@ -160,10 +167,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                         : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                         : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb | k) ? 1u : 0u);
+            umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb > kb0 || k) ? 1u : 0u);
             if constexpr (MODE == OUT_SWIGLU) {
               const uint64_t b2 = make_smem_desc(sb + L::B_BYTES + k * 32, 16, 1024);
-              umma_bf16(d_tmem + BN, adesc, b2, IDESC, (kb | k) ? 1u : 0u);
+              umma_bf16(d_tmem + BN, adesc, b2, IDESC, (kb > kb0 || k) ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs have read it
@@ -178,8 +185,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+      const int ot = tile / ksplit;
+      const int m0 = (ot % tiles_m) * BM;
+      const int n0 = (ot / tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
@@ -256,7 +264,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.ksplit > 1 ? p.ksplit : 1);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
@@ -303,7 +311,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   if (b_mn && bn == 240) return -21;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   GemmParams p;
-  p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N;
+  p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
   if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240) && out_mode != OUT_SWIGLU) {
     const int rc2 = gemm_2cta_dispatch(A, A2, B, p, lda, lda2, ldb, a_mn, b_mn, out_mode, bn, max_ctas, st);
@@ -353,4 +361,49 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   }
 #undef DISPATCH_MODE
   return -24;
+}
+
+
+// Skinny (decode) GEMM:  out[Bt, N] = x[Bt, K] * W[N, K]^T  for Bt <= 64, computed as W * x^T so that the streamed
+// weight rows fill the 128-row MMA dimension and every SM pulls its own slice of W.  When N/128 tiles cannot occupy
+// the machine the K range is split and partial sums are accumulated with fp32 atomics into `work` ([Bt, N] fp32,
+// which this call zeroes); the caller then converts `work` to bf16.  Returns 1 if `work` holds the result, 0 if
+// `out` does, negative on error.
+B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* work, int Bt, int N, int K, int ldx,
+                              int ldw, int ldo, void* stream, int* err) {
+  if (Bt <= 0 || Bt > 64 || N <= 0 || K <= 0) return -30;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int bn = Bt <= 16 ? 16 : (Bt <= 32 ? 32 : 64);
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, W, N, K, ldw, BM, BK);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, x, Bt, K, ldx, bn, BK);
+  if (rc) return rc;
+  const int tiles = (N + BM - 1) / BM;
+  const int nk = (K + BK - 1) / BK;
+  int ksplit = 1;
+  if (work && tiles < num_sms()) {
+    ksplit = (num_sms() + tiles - 1) / tiles;
+    if (ksplit > nk / 4) ksplit = nk / 4 > 0 ? nk / 4 : 1;
+    if (ksplit > 16) ksplit = 16;
+  }
+  GemmParams p;
+  p.M = N; p.N = Bt; p.K1 = K; p.K2 = 0; p.ld_resid = 0; p.swiglu_n = 0; p.resid = nullptr; p.err = err;
+  p.ksplit = ksplit;
+  if (ksplit > 1) {
+    if (cudaMemsetAsync(work, 0, static_cast<size_t>(Bt) * N * sizeof(float), st) != cudaSuccess) return -31;
+    p.C = work; p.ldc = N;
+    switch (bn) {
+      case 16: rc = launch<16, false, false, OUT_F32_T_ATOMIC>(ta, ta, tb, p, st, 0); break;
+      case 32: rc = launch<32, false, false, OUT_F32_T_ATOMIC>(ta, ta, tb, p, st, 0); break;
+      default: rc = launch<64, false, false, OUT_F32_T_ATOMIC>(ta, ta, tb, p, st, 0); break;
+    }
+    return rc ? rc : 1;
+  }
+  p.C = out; p.ldc = ldo;
+  switch (bn) {
+    case 16: return launch<16, false, false, OUT_BF16_T>(ta, ta, tb, p, st, 0);
+    case 32: return launch<32, false, false, OUT_BF16_T>(ta, ta, tb, p, st, 0);
+    default: return launch<64, false, false, OUT_BF16_T>(ta, ta, tb, p, st, 0);
+  }
 }

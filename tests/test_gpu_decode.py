@@ -1,0 +1,125 @@
+"""Decode-side kernels and the native decode engine against the PyTorch statements / the eager HF model."""
+import math
+
+import pytest
+import torch
+
+from recurrent_pretraining_b200.config import ModelConfig
+from recurrent_pretraining_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+@pytest.fixture(scope="module")
+def small_model():
+    from recurrent_pretraining_b200.models.hf import RavenForCausalLM
+
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("smoke-raven-96", mean_recurrence=4)
+    return RavenForCausalLM.from_training_model(cfg.construct_model()).to(torch.bfloat16).cuda().eval()
+
+
+@pytest.mark.parametrize("B,N,K", [(1, 480, 480), (8, 1440, 480), (33, 2560, 1280), (64, 4096, 5280), (5, 200, 136)])
+def test_skinny_gemm_matches_matmul(small_model, B, N, K):
+    from recurrent_pretraining_b200.engine.decode import DecodeEngine
+
+    eng = DecodeEngine(small_model, max_batch=2, max_len=64, use_graphs=False)
+    x, w = _bf(B, K), _bf(N, K, scale=0.05)
+    y = eng._linear(x, w)
+    want = x.float() @ w.float().T
+    assert (y.float() - want).abs().max().item() < 0.02 * math.sqrt(K) * 0.05 * 4 + 0.02 * want.abs().max().item()
+
+
+def test_rope_append_and_decode_attention():
+    from recurrent_pretraining_b200.engine import decode as D
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    B, H, Dh, Lmax = 3, 5, 96, 80
+    lens = torch.tensor([17, 80, 41], dtype=torch.int32, device="cuda")
+    pos = (lens - 1).to(torch.int32)
+    kc, vc = _bf(B, Lmax, H, Dh), _bf(B, Lmax, H, Dh)
+    qkv = _bf(B, 3 * H * Dh)
+    bias = torch.randn(2, 1, H, Dh, device="cuda") * 0.1
+    cos, sin = (t.cuda() for t in ref.rope_tables(Dh, Lmax))
+    q = torch.empty(B, H * Dh, dtype=torch.bfloat16, device="cuda")
+    K._check(D._rope_append(qkv.data_ptr(), bias.contiguous().data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                            pos.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H, Dh, Lmax, K._stream()),
+             "rope_append")
+    for b in range(B):
+        p = int(pos[b])
+        qr, kr, vr = ref.qk_bias_rope(qkv[b:b + 1, None], bias, cos[p:p + 1], sin[p:p + 1], H, H, Dh)
+        assert torch.allclose(q[b].float(), qr.reshape(-1).float(), atol=2e-2)
+        assert torch.allclose(kc[b, p].float(), kr[0, 0].float(), atol=2e-2)
+        assert torch.equal(vc[b, p], vr[0, 0])
+    splits = 4
+    part_o = torch.empty(B * H * splits * Dh, device="cuda")
+    part_ml = torch.empty(B * H * splits * 2, device="cuda")
+    out = torch.empty_like(q)
+    K._check(D._decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), out.data_ptr(),
+                            part_o.data_ptr(), part_ml.data_ptr(), B, H, H, Dh, Lmax, splits, Dh ** -0.5, K._stream()),
+             "decode_attention")
+    for b in range(B):
+        L = int(lens[b])
+        want = ref.causal_attention(q[b].view(1, 1, H, Dh).float(), kc[b:b + 1, :L].float(), vc[b:b + 1, :L].float(),
+                                    None, L - 1)
+        assert torch.allclose(out[b].float(), want.reshape(-1), atol=2e-2, rtol=2e-2), b
+
+
+def test_kl_exit_kernel_matches_torch():
+    from recurrent_pretraining_b200.engine import decode as D
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    B, V = 4, 4096
+    prev = torch.log_softmax(torch.randn(B, V, device="cuda"), -1)
+    logits = torch.randn(B, V, device="cuda") * 2
+    logits[1] = prev[1] + 3.0  # same distribution as before -> KL 0 -> exits
+    want = torch.nn.functional.kl_div(torch.log_softmax(logits, -1), prev, reduction="none", log_target=True).sum(-1)
+    prev_buf = prev.clone()
+    kl = torch.zeros(B, device="cuda")
+    exited = torch.zeros(B, dtype=torch.int32, device="cuda")
+    steps = torch.zeros(B, dtype=torch.int32, device="cuda")
+    tok = torch.zeros(B, dtype=torch.int64, device="cuda")
+    live = torch.full((1,), B, dtype=torch.int32, device="cuda")
+    K._check(D._kl_exit(logits.data_ptr(), prev_buf.data_ptr(), kl.data_ptr(), exited.data_ptr(), steps.data_ptr(),
+                        tok.data_ptr(), live.data_ptr(), B, V, 5e-4, 6, 1, K._stream()), "kl_exit")
+    assert torch.allclose(kl, want, rtol=1e-3, atol=1e-5)
+    assert exited.tolist() == [0, 1, 0, 0] and int(live) == B - 1
+    assert torch.equal(tok, logits.argmax(-1)) and steps.tolist() == [7, 7, 7, 7]
+    assert torch.allclose(prev_buf, torch.log_softmax(logits, -1), atol=1e-4)
+
+
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_engine_matches_eager_model(small_model, use_graphs):
+    from recurrent_pretraining_b200.engine.decode import DecodeEngine
+
+    torch.manual_seed(1)
+    B, P, new = 2, 24, 6
+    ids = torch.randint(0, 4000, (B, P), device="cuda")
+    eng = DecodeEngine(small_model, max_batch=B, max_len=64, num_steps=4, use_graphs=use_graphs)
+    toks, stats = eng.generate(ids, new, init_scale=0.0)
+    assert stats["device_status"] == 0 and toks.shape == (B, P + new)
+    # the eager model, teacher-forced with the engine's tokens, must predict (nearly) the same next tokens
+    out = small_model(toks[:, :-1], num_steps=4, init_scale=0.0)
+    pred = out.logits[:, P - 1:, :]
+    top2 = pred.topk(2, dim=-1)
+    chosen = torch.gather(pred, -1, toks[:, P:].unsqueeze(-1)).squeeze(-1)
+    assert bool((chosen >= top2.values[..., 0] - 0.15).all()), (chosen, top2.values[..., 0])
+
+
+def test_engine_kl_exit_and_latent_reuse(small_model):
+    from recurrent_pretraining_b200.engine.decode import DecodeEngine
+
+    torch.manual_seed(2)
+    B, P = 2, 16
+    ids = torch.randint(0, 4000, (B, P), device="cuda")
+    eng = DecodeEngine(small_model, max_batch=B, max_len=48, num_steps=4, max_steps=8)
+    _, never = eng.generate(ids, 4, criterion="kl", exit_threshold=0.0, max_steps=8, init_scale=0.0, check_every=2)
+    assert all(s == [8, 8] for s in never["steps"])
+    _, always = eng.generate(ids, 4, criterion="kl", exit_threshold=1e9, max_steps=8, init_scale=0.0, check_every=1)
+    assert all(s == [1, 1] for s in always["steps"])
+    toks, reuse = eng.generate(ids, 4, criterion="kl", exit_threshold=5e-4, max_steps=8, continuous_compute=True)
+    assert toks.shape == (B, P + 4) and reuse["device_status"] == 0
