@@ -48,64 +48,84 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, const 
   }
 }
 
-// grid (splits, H, B), 128 threads = 4 warps; each warp walks keys l = split_begin + warp, +4, ...; a lane holds
-// D/32 (<= 4) dims of q.  Partial (m, l, o[D]) per split go to scratch and are merged by the last kernel.
-template <int DPL>  // dims per lane: D = 32 * DPL
+// grid (splits, H, B), 128 threads = 8 groups of 16 lanes; group g walks keys l = begin + g, +8, ...; lane j of a
+// group owns dims [8j, 8j+8) (one 16-byte load per key for K and for V).  Partial (m, l, o[D]) per split go to scratch
+// and are merged by decode_attn_merge_kernel.  DPL = D / 32 (the merge kernel's layout).
+template <int DPL>
 __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ lens, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int Hkv, int Lmax, float scale_log2) {
   constexpr int D = 32 * DPL;
+  constexpr int NG = 8;  // key groups per CTA
   const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (H / Hkv);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = threadIdx.x >> 4, j = threadIdx.x & 15;
+  const bool active = j * 8 < D;
   const int L = lens[b];
   const int per = (L + nsplit - 1) / nsplit;
   const int l0 = split * per, l1 = min(L, l0 + per);
-  float qv[DPL], acc[DPL];
+  float qv[8], acc[8];
   const __nv_bfloat16* qp = q + (static_cast<size_t>(b) * H + h) * D;
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) {
-    qv[i] = bf2f(qp[lane + 32 * i]) * scale_log2;
+  for (int i = 0; i < 8; ++i) {
+    qv[i] = active ? bf2f(qp[j * 8 + i]) * scale_log2 : 0.f;
     acc[i] = 0.f;
   }
   float m = -INFINITY, lsum = 0.f;
   const size_t row = static_cast<size_t>(Hkv) * D;
-  const __nv_bfloat16* kb = kc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D;
-  const __nv_bfloat16* vb = vc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D;
-  for (int l = l0 + warp; l < l1; l += 4) {
+  const __nv_bfloat16* kb = kc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D + j * 8;
+  const __nv_bfloat16* vb = vc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D + j * 8;
+  const unsigned gmask = 0xFFFFu << (threadIdx.x & 16);  // the 16 lanes of this group inside the warp
+  for (int l = l0 + grp; l < l1; l += NG) {
     float s = 0.f;
+    uint4 vv = make_uint4(0, 0, 0, 0);
+    if (active) {
+      const uint4 kk = *reinterpret_cast<const uint4*>(kb + l * row);
+      vv = *reinterpret_cast<const uint4*>(vb + l * row);
+      const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) s += qv[i] * bf2f(kb[l * row + lane + 32 * i]);
-    s = warp_sum(s);
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack_bf16x2(kw[i]);
+        s += qv[2 * i] * f.x + qv[2 * i + 1] * f.y;
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(gmask, s, o, 16);
     const float mn = fmaxf(m, s);
     const float alpha = exp2f(m - mn), p = exp2f(s - mn);
     lsum = lsum * alpha + p;
+    const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] = acc[i] * alpha + p * bf2f(vb[l * row + lane + 32 * i]);
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack_bf16x2(vw[i]);
+      acc[2 * i] = acc[2 * i] * alpha + p * f.x;
+      acc[2 * i + 1] = acc[2 * i + 1] * alpha + p * f.y;
+    }
     m = mn;
   }
-  // merge the 4 warps through shared memory
-  __shared__ float sm_m[4], sm_l[4], sm_o[4][D];
-  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = lsum; }
+  __shared__ float sm_m[NG], sm_l[NG], sm_o[NG][128];
+  if (j == 0) { sm_m[grp] = m; sm_l[grp] = lsum; }
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) sm_o[warp][lane + 32 * i] = acc[i];
+    for (int i = 0; i < 8; ++i) sm_o[grp][j * 8 + i] = acc[i];
+  }
   __syncthreads();
-  if (warp == 0) {
-    float mm = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
-    float ll = 0.f, o[DPL];
+  if (threadIdx.x < D) {
+    const int d = threadIdx.x;
+    float mm = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      const float a = (sm_m[w] == -INFINITY) ? 0.f : exp2f(sm_m[w] - mm);
-      ll += sm_l[w] * a;
+    for (int g = 0; g < NG; ++g) mm = fmaxf(mm, sm_m[g]);
+    float ll = 0.f, o = 0.f;
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) o[i] += sm_o[w][lane + 32 * i] * a;
+    for (int g = 0; g < NG; ++g) {
+      const float a = (sm_m[g] == -INFINITY) ? 0.f : exp2f(sm_m[g] - mm);
+      ll += sm_l[g] * a;
+      o += sm_o[g][d] * a;
     }
     const size_t pidx = (static_cast<size_t>(b) * H + h) * nsplit + split;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) part_o[pidx * D + lane + 32 * i] = o[i];
-    if (lane == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = ll; }
+    part_o[pidx * D + d] = o;
+    if (d == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = ll; }
   }
 }
 
@@ -205,9 +225,99 @@ kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, 
   }
 }
 
+// out = bf16(work); work = 0   (consumer of a split-K skinny GEMM that also re-arms its accumulator)
+__global__ void cast_zero_kernel(float* __restrict__ work, __nv_bfloat16* __restrict__ out, size_t n) {
+  const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i + 4 <= n) {
+    const float4 v = *reinterpret_cast<float4*>(work + i);
+    *reinterpret_cast<uint2*>(out + i) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    *reinterpret_cast<float4*>(work + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+    for (size_t k = i; k < n; ++k) { out[k] = f2bf(work[k]); work[k] = 0.f; }
+  }
+}
+
+// One CTA per row (decode batches have at most 64 rows):  s = bf16(a + x) with a in fp32 (then cleared) or bf16,
+// y1 = norm(s) * w1 and, if w2 is given, y2 = norm(y1) * w2 -- the sandwich pair n2 -> n3 (or n4 -> next n1) in one
+// launch.  Each norm rounds the normalised value to bf16 before the weight multiply, as the unfused kernels do.
+template <bool A_F32>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_pair_kernel(void* __restrict__ a, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w1,
+                        const float* __restrict__ w2, __nv_bfloat16* __restrict__ y1, __nv_bfloat16* __restrict__ y2,
+                        int E, float eps) {
+  __shared__ float red[8];
+  __shared__ float s_tot;
+  const size_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < E; i += 256) {
+    float av = 0.f;
+    if (a) {
+      if constexpr (A_F32) {
+        float* ap = reinterpret_cast<float*>(a) + row * E + i;
+        av = *ap;
+        *ap = 0.f;
+      } else {
+        av = bf2f(reinterpret_cast<const __nv_bfloat16*>(a)[row * E + i]);
+      }
+    }
+    const float sv = bf2f(f2bf(av + (x ? bf2f(x[row * E + i]) : 0.f)));
+    y1[row * E + i] = f2bf(sv);  // staged: overwritten with the normalised value below
+    ss += sv * sv;
+  }
+  auto block_total = [&](float v) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int k = 0; k < 8; ++k) t += red[k];
+      s_tot = t;
+    }
+    __syncthreads();
+    const float r = s_tot;
+    __syncthreads();
+    return r;
+  };
+  const float rstd1 = rsqrtf(block_total(ss) / static_cast<float>(E) + eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < E; i += 256) {
+    const float sv = bf2f(y1[row * E + i]);
+    const float o = bf2f(f2bf(bf2f(f2bf(sv * rstd1)) * (w1 ? w1[i] : 1.f)));
+    y1[row * E + i] = f2bf(o);
+    ss2 += o * o;
+  }
+  if (!y2) return;
+  const float rstd2 = rsqrtf(block_total(ss2) / static_cast<float>(E) + eps);
+  for (int i = threadIdx.x; i < E; i += 256) {
+    const float o = bf2f(y1[row * E + i]);
+    y2[row * E + i] = f2bf(bf2f(f2bf(o * rstd2)) * (w2 ? w2[i] : 1.f));
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+B200_API int b200_cast_zero(float* work, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  const size_t threads = (static_cast<size_t>(n) + 3) / 4;
+  cast_zero_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      work, reinterpret_cast<__nv_bfloat16*>(out), static_cast<size_t>(n));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// a: [rows, E] fp32 (a_is_f32, cleared after reading) or bf16 or null; y1 = n1(a + x); y2 = n2(y1) if y2 != null.
+B200_API int b200_add_rmsnorm_pair(void* a, int a_is_f32, const void* x, const float* w1, const float* w2, void* y1,
+                                   void* y2, int rows, int E, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(y1);
+  __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(y2);
+  if (a_is_f32) add_rmsnorm_pair_kernel<true><<<rows, 256, 0, st>>>(a, xb, w1, w2, o1, o2, E, eps);
+  else add_rmsnorm_pair_kernel<false><<<rows, 256, 0, st>>>(a, xb, w1, w2, o1, o2, E, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float* cosT, const float* sinT,
                               const int* pos, void* q_out, void* k_cache, void* v_cache, int B, int H, int Hkv, int D,
@@ -224,7 +334,7 @@ B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float
 B200_API int b200_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* lens, void* out,
                                    float* part_o, float* part_ml, int B, int H, int Hkv, int D, int Lmax, int splits,
                                    float scale, void* stream) {
-  if (D % 32 || D > 128 || splits < 1) return -1;
+  if (D % 32 || D > 128 || splits < 1 || ((Hkv * D) % 8)) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const float sl2 = scale * 1.4426950408889634f;
   dim3 grid(splits, H, B);

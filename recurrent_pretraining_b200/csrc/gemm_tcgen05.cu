@@ -367,10 +367,10 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
 // Skinny (decode) GEMM:  out[Bt, N] = x[Bt, K] * W[N, K]^T  for Bt <= 64, computed as W * x^T so that the streamed
 // weight rows fill the 128-row MMA dimension and every SM pulls its own slice of W.  When N/128 tiles cannot occupy
 // the machine the K range is split and partial sums are accumulated with fp32 atomics into `work` ([Bt, N] fp32,
-// which this call zeroes); the caller then converts `work` to bf16.  Returns 1 if `work` holds the result, 0 if
+// zeroed here when zero_work != 0); the caller then consumes `work` (b200_cast_zero / b200_add_rmsnorm_f32).  Returns 1 if `work` holds the result, 0 if
 // `out` does, negative on error.
 B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* work, int Bt, int N, int K, int ldx,
-                              int ldw, int ldo, void* stream, int* err) {
+                              int ldw, int ldo, int zero_work, void* stream, int* err) {
   if (Bt <= 0 || Bt > 64 || N <= 0 || K <= 0) return -30;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int bn = Bt <= 16 ? 16 : (Bt <= 32 ? 32 : 64);
@@ -391,7 +391,9 @@ B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* wo
   p.M = N; p.N = Bt; p.K1 = K; p.K2 = 0; p.ld_resid = 0; p.swiglu_n = 0; p.resid = nullptr; p.err = err;
   p.ksplit = ksplit;
   if (ksplit > 1) {
-    if (cudaMemsetAsync(work, 0, static_cast<size_t>(Bt) * N * sizeof(float), st) != cudaSuccess) return -31;
+    // zero_work = 0: the caller guarantees `work` is already zero (its consumer kernels clear it after reading)
+    if (zero_work && cudaMemsetAsync(work, 0, static_cast<size_t>(Bt) * N * sizeof(float), st) != cudaSuccess)
+      return -31;
     p.C = work; p.ldc = N;
     switch (bn) {
       case 16: rc = launch<16, false, false, OUT_F32_T_ATOMIC>(ta, ta, tb, p, st, 0); break;

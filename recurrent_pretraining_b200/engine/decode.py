@@ -27,7 +27,9 @@ from ..ops import cuda as K
 
 BF16 = torch.bfloat16
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
-_skinny = K._sig("b200_gemm_skinny", [_vp] * 4 + [_i] * 6 + [_vp, _vp])
+_skinny = K._sig("b200_gemm_skinny", [_vp] * 4 + [_i] * 7 + [_vp, _vp])
+_cast_zero = K._sig("b200_cast_zero", [_vp, _vp, C.c_longlong, _vp])
+_norm_pair = K._sig("b200_add_rmsnorm_pair", [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp])
 _rope_append = K._sig("b200_rope_append", [_vp] * 8 + [_i] * 5 + [_vp])
 _decode_attn = K._sig("b200_decode_attention", [_vp] * 7 + [_i] * 6 + [_f, _vp])
 _kl_exit = K._sig("b200_kl_exit", [_vp] * 7 + [_i, _i, _f, _i, _i, _vp])
@@ -62,6 +64,8 @@ class StaticRecurrentKVCache:
         end = self._seen_tokens
         self.k[s, :, end - n:end] = k
         self.v[s, :, end - n:end] = v
+        if end == n:  # first chunk: attend to the fresh (densely packed) tensors, not to strided cache views
+            return k, v
         return self.k[s, :, :end], self.v[s, :, :end]
 
     def get_seq_length(self, step_idx: int = 0) -> int:
@@ -117,22 +121,48 @@ class DecodeEngine:
         self.live = torch.zeros(1, dtype=torch.int32, device=d)
         self._graphs: dict = {}
         self._qk_bias = {}
+        self._norm_w: dict = {}
+        # persistent split-K accumulator (only the narrow E-wide outputs are ever split); kept zero between uses
+        self.work = torch.zeros(max_batch * 2 * self.E, dtype=torch.float32, device=d)
         self.weight_bytes_per_recurrence = sum(p.numel() * 2 for n, p in model.named_parameters()
                                                if ".core_block." in n or ".adapter." in n)
 
     # -- kernels --------------------------------------------------------------------------------------
-    def _linear(self, x, w):
-        """x [B, K] bf16 -> [B, N] bf16 through the skinny weight-streaming GEMM."""
+    def _linear(self, x, w, keep_f32: bool = False):
+        """x [B, K] bf16 -> [B, N] through the skinny weight-streaming GEMM.  Narrow outputs are accumulated over K
+        splits in the persistent fp32 ``work`` buffer (kept zero between uses by its consumers); ``keep_f32`` hands
+        that buffer to a fused consumer, otherwise it is converted (and cleared) here."""
         Bt, Kd = x.shape
         N = w.shape[0]
         out = torch.empty(Bt, N, dtype=BF16, device=x.device)
-        work = torch.empty(Bt, N, dtype=torch.float32, device=x.device)
-        rc = _skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), work.data_ptr(), Bt, N, Kd, x.stride(0), w.stride(0),
-                     N, K._stream(), K.err_word(x.device).data_ptr())
+        work = self.work[: Bt * N].view(Bt, N) if Bt * N <= self.work.numel() else None
+        rc = _skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), K._ptr(work), Bt, N, Kd, x.stride(0), w.stride(0),
+                     N, 0, K._stream(), K.err_word(x.device).data_ptr())
         K._launches += 1
         if rc < 0:
             raise RuntimeError(f"b200_gemm_skinny failed with code {rc}")
-        return work.to(BF16) if rc == 1 else out
+        if rc == 1:
+            if keep_f32:
+                return work
+            K._check(_cast_zero(work.data_ptr(), out.data_ptr(), Bt * N, K._stream()), "cast_zero")
+        return out
+
+    def _w(self, norm):
+        """fp32 copy of a norm weight, made once."""
+        key = id(norm)
+        if key not in self._norm_w:
+            self._norm_w[key] = None if norm.weight is None else norm.weight.detach().float().contiguous()
+        return self._norm_w[key]
+
+    def _pair(self, a, x, n1, n2=None):
+        """y1 = n1(a + x), y2 = n2(y1) in one launch; ``a`` may be the fp32 split-K buffer, bf16, or None."""
+        rows, E = (x if x is not None else a).shape
+        y1 = torch.empty(rows, E, dtype=BF16, device=self.dev)
+        y2 = torch.empty_like(y1) if n2 is not None else None
+        K._check(_norm_pair(K._ptr(a), int(a is not None and a.dtype == torch.float32), K._ptr(x), K._ptr(self._w(n1)),
+                            K._ptr(self._w(n2)) if n2 is not None else 0, y1.data_ptr(), K._ptr(y2), rows, E, n1.eps,
+                            K._stream()), "add_rmsnorm_pair")
+        return y1, y2
 
     def _bias(self, attn):
         key = id(attn)
@@ -153,45 +183,44 @@ class DecodeEngine:
         K._check(_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.lens.data_ptr(), o.data_ptr(),
                               self.part_o.data_ptr(), self.part_ml.data_ptr(), B, self.H, self.Hkv, self.D, self.Lmax,
                               self.splits, float(self.D) ** -0.5, K._stream()), "decode_attention")
-        return self._linear(o, attn.proj.weight)
+        return self._linear(o, attn.proj.weight, keep_f32=True)
 
-    def _block(self, block, x, slot: int):
-        n1, n2, n3, n4 = block.norm_1, block.norm_2, block.norm_3, block.norm_4
-        h, _ = K.rmsnorm_fwd(x, n1.weight, n1.eps)
+    def _block(self, block, x, h, slot: int, next_norm=None):
+        """Sandwich block on (residual x, h = norm_1(x)); returns (x', norm_1 of the next block applied to x')."""
         a = self._attention(block.attn, h, slot)
-        x, _, _ = K.add_rmsnorm_fwd(a, x, n2.weight, n2.eps)
-        h, _ = K.rmsnorm_fwd(x, n3.weight, n3.eps)
-        g = K.swiglu_fwd(self._linear(h, block.mlp.fc.weight))
-        m = self._linear(g, block.mlp.proj.weight)
-        x, _, _ = K.add_rmsnorm_fwd(m, x, n4.weight, n4.eps)
-        return x
+        x, h3 = self._pair(a, x, block.norm_2, block.norm_3)
+        g = K.swiglu_fwd(self._linear(h3, block.mlp.fc.weight))
+        m = self._linear(g, block.mlp.proj.weight, keep_f32=True)
+        return self._pair(m, x, block.norm_4, next_norm)
+
+    def _chain(self, blocks, x, slots, final_norm=None):
+        """Run consecutive sandwich blocks, fusing each block's last norm with the next block's first."""
+        h, _ = self._pair(None, x, blocks[0].norm_1)
+        for i, block in enumerate(blocks):
+            nxt = blocks[i + 1].norm_1 if i + 1 < len(blocks) else final_norm
+            x, h = self._block(block, x, h, slots[i], nxt)
+        return x, h
 
     def _embed(self):
         t = self.model.transformer
         e = K.embedding_fwd(self.tok, t.wte.weight, self.model.emb_scale)
-        for i, block in enumerate(t.prelude):
-            e = self._block(block, e, self.cache.slot(i))
+        e, _ = self._chain(list(t.prelude), e, [self.cache.slot(i) for i in range(self.P)])
         return e
 
     def _recurrence(self, s, e, step: int):
         t = self.model.transformer
         s = self._linear(torch.cat([s, e], dim=-1), t.adapter.weight)
-        for b, block in enumerate(t.core_block):
-            s = self._block(block, s, self.cache.slot(self.P + self.R * step + b))
+        slots = [self.cache.slot(self.P + self.R * step + b) for b in range(self.R)]
+        s, _ = self._chain(list(t.core_block), s, slots)
         return s
 
     def _head(self, s):
         t = self.model.transformer
-        ln = t.ln_f
-        x, _ = K.rmsnorm_fwd(s, ln.weight, ln.eps)
-        for i, block in enumerate(t.coda):
-            x = self._block(block, x, self.cache.slot(-(i + 1)))
-        x, _ = K.rmsnorm_fwd(x, ln.weight, ln.eps)
-        B = x.shape[0]
-        if B <= 64:
-            # the vocabulary projection is the widest weight stream of a token: same skinny path, fp32 result
-            lg = self._linear(x, self.model.lm_head.weight)
-            self.logits[:B].copy_(lg)
+        x, _ = self._pair(None, s, t.ln_f)
+        x, h = self._chain(list(t.coda), x, [self.cache.slot(-(i + 1)) for i in range(self.Cn)], final_norm=t.ln_f)
+        lg = self._linear(h, self.model.lm_head.weight)
+        B = lg.shape[0]
+        self.logits[:B].copy_(lg)
         return self.logits[:B]
 
     # -- graph helpers ----------------------------------------------------------------------------------

@@ -1,22 +1,48 @@
-"""Binding of the hand-written causal flash-attention kernels (tcgen05, head dims up to 128).
+"""Binding of the hand-written causal flash-attention kernels (tcgen05 MMAs, S/P/O tiles in tensor memory).
 
-``native_supported`` gates the kernel: shapes it does not cover fall back to the library attention in
-``ops.cuda`` (the fallback is explicit and visible in the launch list, never silent on the flagship shape).
+Forward and backward operate on the packed, already rotated qkv tensor [B, S, (H + 2 Hkv) * D]; head dims 64, 96 and
+128 are built.  Other head dims use the library attention in ``ops.cuda`` (visible in the launch list).
 """
 from __future__ import annotations
 
+import ctypes as C
+import os
+
 import torch
 
-ENABLED = False  # flipped to True once the kernels in csrc/attention.cu are built into the library
+from . import cuda as K
+
+_vp, _i, _f = C.c_void_p, C.c_int, C.c_float
+_fwd = K._sig("b200_attn_fwd", [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp])
+_bwd = K._sig("b200_attn_bwd", [_vp] * 7 + [_i] * 5 + [_f, _vp, _vp]) if hasattr(K.lib, "b200_attn_bwd") else None
+
+ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "1") == "1"
+NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
 
 
 def native_supported(head_dim: int, seq_len: int) -> bool:
-    return ENABLED and head_dim % 16 == 0 and head_dim <= 128
+    return ENABLED and head_dim in (64, 96, 128)
 
 
 def fwd(qkv_r, n_head, n_kv, D, scale):
-    raise NotImplementedError
+    B, S, W = qkv_r.shape
+    assert qkv_r.is_contiguous() and qkv_r.dtype == torch.bfloat16
+    o = torch.empty(B, S, n_head * D, dtype=torch.bfloat16, device=qkv_r.device)
+    lse = torch.empty(B, n_head, S, dtype=torch.float32, device=qkv_r.device)
+    K._check(_fwd(qkv_r.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, n_head, n_kv, D, float(scale), K._stream(),
+                  K.err_word(qkv_r.device).data_ptr()), "attn_fwd")
+    return o, lse
 
 
 def bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
-    raise NotImplementedError
+    """Gradient with respect to the packed rotated qkv tensor."""
+    B, S, W = qkv_r.shape
+    if not NATIVE_BWD:
+        return K._attention_bwd_library(do, qkv_r, n_head, n_kv, D, scale)
+    dqkv = torch.empty_like(qkv_r)
+    dq_acc = torch.zeros(B, S, n_head * D, dtype=torch.float32, device=qkv_r.device)
+    delta = torch.empty(B, n_head, S, dtype=torch.float32, device=qkv_r.device)
+    K._check(_bwd(qkv_r.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
+                  dqkv.data_ptr(), B, S, n_head, n_kv, D, float(scale), K._stream(),
+                  K.err_word(qkv_r.device).data_ptr()), "attn_bwd")
+    return dqkv

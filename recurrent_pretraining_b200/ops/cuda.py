@@ -375,13 +375,10 @@ def attention_fwd(qkv_r, n_head, n_kv, D, scale):
     return o.reshape(B, S, n_head * D), torch.empty(0, device=qkv_r.device)
 
 
-def attention_bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
-    """Gradient w.r.t. the packed rotated qkv tensor, returned packed as [B,S,(H+2Hkv)*D]."""
+def _attention_bwd_library(do, qkv_r, n_head, n_kv, D, scale):
+    """Backward through the library attention (recomputes its forward); used for head dims the native kernels do
+    not cover."""
     B, S, W = qkv_r.shape
-    from . import attention as A
-
-    if lse.numel():
-        return A.bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale)
     with torch.enable_grad():
         leaf = qkv_r.detach().requires_grad_(True)
         q, k, v = _views(leaf, n_head, n_kv, D)
@@ -390,9 +387,22 @@ def attention_bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
     return dqkv.contiguous()
 
 
+def attention_bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
+    """Gradient w.r.t. the packed rotated qkv tensor, returned packed as [B,S,(H+2Hkv)*D]."""
+    from . import attention as A
+
+    if lse.numel():
+        return A.bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale)
+    return _attention_bwd_library(do, qkv_r, n_head, n_kv, D, scale)
+
+
 def attention_infer(q, k, v, scale, q_offset=0):
     """Inference attention: q [B,Sq,H,D] against cached k,v [B,Sk,Hk,D]; query i sits at position q_offset+i."""
     Sq, Sk = q.shape[1], k.shape[1]
+    # the library attention is only ever given densely packed operands (a strided batch view of a static cache
+    # made its kernel fault)
+    if k.shape[0] > 1 and k.stride(0) != k.shape[1] * k.stride(1):
+        k, v = k.contiguous(), v.contiguous()
     if Sq == Sk and q_offset == 0:
         return _sdpa(q, k, v, scale, causal=True)
     if Sq == 1:

@@ -204,3 +204,35 @@ def test_linear_ce(C):
     assert abs(loss.item() - want.item()) < 2e-3 * max(1.0, abs(want.item()))
     _close(dx, xl.grad, 5e-2, 2e-4)
     _close(dw, wl.grad, 5e-2, 2e-4)
+
+
+def _packed_qkv(B, S, H, Hkv, D):
+    return _rand(B, S, (H + 2 * Hkv) * D, scale=0.7)
+
+
+def _attention_reference(qkv, H, Hkv, D, scale):
+    B, S, _ = qkv.shape
+    wq, wk = H * D, Hkv * D
+    q = qkv[..., :wq].reshape(B, S, H, D)
+    k = qkv[..., wq:wq + wk].reshape(B, S, Hkv, D)
+    v = qkv[..., wq + wk:].reshape(B, S, Hkv, D)
+    return ref.causal_attention(q.float(), k.float(), v.float(), scale), (q, k, v)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
+                                         (1, 1024, 2, 2, 96)])
+def test_flash_attention_forward(C, B, S, H, Hkv, D):
+    from recurrent_pretraining_b200.ops import attention as A
+
+    qkv = _packed_qkv(B, S, H, Hkv, D)
+    scale = D ** -0.5
+    o, lse = A.fwd(qkv, H, Hkv, D, scale)
+    torch.cuda.synchronize()
+    assert C.check_device_status() == 0
+    want, (q, k, v) = _attention_reference(qkv, H, Hkv, D, scale)
+    _close(o.view(B, S, H, D), want, 2e-2, 2e-2)
+    kk = k.float().repeat_interleave(H // Hkv, dim=2)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), kk) * scale
+    mask = torch.ones(S, S, dtype=torch.bool, device="cuda").triu(1)
+    want_lse = torch.logsumexp(scores.masked_fill(mask, float("-inf")), dim=-1)
+    _close(lse, want_lse, 1e-2, 2e-2)
