@@ -327,6 +327,289 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------ backward
+struct BwdBars {
+  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_ready, dq_full, dq_empty;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+struct AttnBwdParams {
+  int B, S, H, Hkv, D, wq, wk;
+  float scale, scale_log2;
+  const float* lse;     // [B, H, S]
+  const float* delta;   // [B, H, S]  rowsum(dO * O)
+  float* dq_acc;        // [B, S, H*D] fp32, zero on entry; receives sum over key blocks of dS K (unscaled)
+  __nv_bfloat16* dqkv;  // packed [B, S, (H + 2 Hkv) * D]; this kernel writes the k and v sections
+  int* err;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// write 32 consecutive bf16 of row r (columns c .. c+31 of a [128 x 128] tile) into a K-major 128B-swizzled tile
+__device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int r, int c, const uint32_t (&packed)[16]) {
+  uint8_t* prow = tile + (c >> 6) * PANEL_BYTES + r * 128;
+  const int chunk0 = (c & 63) >> 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int phys = (chunk0 + q) ^ (r & 7);
+    *reinterpret_cast<uint4*>(prow + phys * 16) =
+        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                const AttnBwdParams p) {
+  constexpr int KSTEPS_D = D / 16;
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T, dP = dO V^T
+  constexpr uint32_t IDESC_TT = make_idesc_bf16(128, D, 1, 1);     // dV += P^T dO, dK += dS^T Q
+  constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, D, 0, 1);     // dQ = dS K
+  constexpr int TILE_BYTES = 2 * PANEL_BYTES;
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;
+  uint8_t* sdO = sQ + TILE_BYTES;
+  uint8_t* sP = sdO + TILE_BYTES;
+  uint8_t* sdS = sP + TILE_BYTES;
+  BwdBars* bars = reinterpret_cast<BwdBars*>(sdS + TILE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int rep = p.H / p.Hkv;
+  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
+  const int per_head = nqb - kvb;            // query blocks at or below the diagonal
+  const int n_it = rep * per_head;
+  const int k0 = kvb * ATT_BN;
+  const int xk = p.wq + hk * D, xv = p.wq + p.wk + hk * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    mbar_init(&bars->qdo_full, 1);
+    mbar_init(&bars->qdo_empty, 1);
+    mbar_init(&bars->sdp_full, 1);
+    mbar_init(&bars->pds_ready, 4);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_empty, 4);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQKV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
+      tma_load_3d(sK, &tmQKV, &bars->kv_full, xk, k0, b);
+      tma_load_3d(sK + PANEL_BYTES, &tmQKV, &bars->kv_full, xk + 64, k0, b);
+      tma_load_3d(sV, &tmQKV, &bars->kv_full, xv, k0, b);
+      tma_load_3d(sV + PANEL_BYTES, &tmQKV, &bars->kv_full, xv + 64, k0, b);
+      int issued = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int h = hk * rep + it / per_head;
+        const int q0 = (kvb + it % per_head) * ATT_BM;
+        if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        mbar_expect_tx(&bars->qdo_full, 2 * TILE_BYTES);
+        tma_load_3d(sQ, &tmQKV, &bars->qdo_full, h * D, q0, b);
+        tma_load_3d(sQ + PANEL_BYTES, &tmQKV, &bars->qdo_full, h * D + 64, q0, b);
+        tma_load_3d(sdO, &tmDO, &bars->qdo_full, h * D, q0, b);
+        tma_load_3d(sdO + PANEL_BYTES, &tmDO, &bars->qdo_full, h * D + 64, q0, b);
+        issued = it + 1;
+      }
+      unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->kv_full, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      if (issued > 0) {
+        t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->qdo_full, (issued - 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sdO), aP = smem_u32(sP),
+                     aDS = smem_u32(sdS);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, p.err, ERR_WAIT_ATTN);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(&bars->qdo_full, ph, abort_flag, p.err, ERR_WAIT_ATTN) ||
+            !mbar_wait(&bars->dq_empty, ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < KSTEPS_D; ++t) {
+          const uint32_t off = (t >> 2) * PANEL_BYTES + (t & 3) * 32;
+          umma_bf16(tmem_base + COL_S, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
+                    IDESC_QK, t ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < KSTEPS_D; ++t) {
+          const uint32_t off = (t >> 2) * PANEL_BYTES + (t & 3) * 32;
+          umma_bf16(tmem_base + COL_DP, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024),
+                    IDESC_QK, t ? 1u : 0u);
+        }
+        umma_commit(&bars->sdp_full);
+        if (!mbar_wait(&bars->pds_ready, ph, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {  // contraction over the 128 query rows, 16 per step
+          const uint64_t aPt = make_smem_desc(aP + t * 2048, PANEL_BYTES, 1024);     // P^T  (MN-major A)
+          const uint64_t aSt = make_smem_desc(aDS + t * 2048, PANEL_BYTES, 1024);    // dS^T (MN-major A)
+          const uint64_t bDO = make_smem_desc(aDO + t * 2048, PANEL_BYTES, 1024);    // dO   (MN-major B)
+          const uint64_t bQ = make_smem_desc(aQ + t * 2048, PANEL_BYTES, 1024);      // Q    (MN-major B)
+          umma_bf16(tmem_base + COL_DV, aPt, bDO, IDESC_TT, (it | t) ? 1u : 0u);
+          umma_bf16(tmem_base + COL_DK, aSt, bQ, IDESC_TT, (it | t) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {  // contraction over the 128 keys
+          const uint64_t aS = make_smem_desc(aDS + (t >> 2) * PANEL_BYTES + (t & 3) * 32, 16, 1024);
+          const uint64_t bK = make_smem_desc(aK + t * 2048, PANEL_BYTES, 1024);      // K (MN-major B)
+          umma_bf16(tmem_base + COL_S, aS, bK, IDESC_DQ, t ? 1u : 0u);
+        }
+        umma_commit(&bars->dq_full);
+        umma_commit(&bars->qdo_empty);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const uint32_t ph = it & 1;
+      const int h = hk * rep + it / per_head;
+      const int qb = kvb + it % per_head;
+      const int qrow = qb * ATT_BM + r;
+      const bool row_ok = qrow < p.S;
+      const size_t stat = (static_cast<size_t>(b) * p.H + h) * p.S + qrow;
+      const float lse2 = row_ok ? p.lse[stat] * 1.4426950408889634f : 0.f;
+      const float delta = row_ok ? p.delta[stat] : 0.f;
+      if (!mbar_wait(&bars->sdp_full, ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (qb == kvb);
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN; c += 32) {
+        uint32_t sv[32], dpv[32];
+        tmem_ld_32x32(tmem_base + COL_S + lane_addr + c, sv);
+        tmem_ld_32x32(tmem_base + COL_DP + lane_addr + c, dpv);
+        tmem_ld_wait();
+        uint32_t pp[16], ds[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = 0.f, p1 = 0.f;
+          if (row_ok) {
+            if (!(diag && (k0 + c + i > qrow))) p0 = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+            if (!(diag && (k0 + c + i + 1 > qrow))) p1 = exp2f(__uint_as_float(sv[i + 1]) * p.scale_log2 - lse2);
+          }
+          pp[i >> 1] = pack_bf16x2(p0, p1);
+          ds[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(dpv[i]) - delta), p1 * (__uint_as_float(dpv[i + 1]) - delta));
+        }
+        store_row_chunk_sw128(sP, r, c, pp);
+        store_row_chunk_sw128(sdS, r, c, ds);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->pds_ready);
+      if (!mbar_wait(&bars->dq_full, ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + (static_cast<size_t>(b) * p.S + qrow) * (p.H * D) + h * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(tmem_base + COL_S + lane_addr + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            red_add_v4(dq_row + c + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                       __uint_as_float(v[i + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->dq_empty);
+    }
+    if (ok && n_it > 0) {
+      // all MMAs are complete (the last dq_full was waited on): write dV and scale * dK for this key block
+      const int key = k0 + r;
+      const size_t wtot = static_cast<size_t>(p.wq) + 2 * p.wk;
+      __nv_bfloat16* dk_row = p.dqkv + (static_cast<size_t>(b) * p.S + key) * wtot + p.wq + hk * D;
+      __nv_bfloat16* dv_row = dk_row + p.wk;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t v[16], k[16];
+        tmem_ld_32x16(tmem_base + COL_DV + lane_addr + c, v);
+        tmem_ld_32x16(tmem_base + COL_DK + lane_addr + c, k);
+        tmem_ld_wait();
+        if (key < p.S) {
+          uint32_t ov[8], ok2[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            ov[i >> 1] = pack_bf16x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            ok2[i >> 1] = pack_bf16x2(__uint_as_float(k[i]) * p.scale, __uint_as_float(k[i + 1]) * p.scale);
+          }
+          *reinterpret_cast<uint4*>(dv_row + c) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+          *reinterpret_cast<uint4*>(dv_row + c + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
+          *reinterpret_cast<uint4*>(dk_row + c) = make_uint4(ok2[0], ok2[1], ok2[2], ok2[3]);
+          *reinterpret_cast<uint4*>(dk_row + c + 8) = make_uint4(ok2[4], ok2[5], ok2[6], ok2[7]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int S, int H, int D) {
+  const size_t w = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<size_t>(B) * S * H) return;
+  const int h = static_cast<int>(w % H);
+  const size_t bs = w / H;
+  const __nv_bfloat16* op = o + (bs * H + h) * D;
+  const __nv_bfloat16* dp = d_o + (bs * H + h) * D;
+  float acc = 0.f;
+  for (int i = lane; i < D; i += 32) acc += bf2f(op[i]) * bf2f(dp[i]);
+  acc = warp_sum(acc);
+  if (lane == 0) delta[(static_cast<size_t>(bs / S) * H + h) * S + bs % S] = acc;
+}
+
+// dqkv[:, :, 0:wq] = bf16(scale * dq_acc)
+__global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, size_t rows,
+                                       int wq, int wtot, float scale) {
+  const int vpr = wq >> 2;
+  const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= rows * vpr) return;
+  const size_t row = gid / vpr;
+  const int c = static_cast<int>(gid % vpr) << 2;
+  const float4 v = *reinterpret_cast<const float4*>(dq_acc + row * wq + c);
+  *reinterpret_cast<uint2*>(dqkv + row * wtot + c) =
+      make_uint2(pack_bf16x2(v.x * scale, v.y * scale), pack_bf16x2(v.z * scale, v.w * scale));
+}
+
 }  // namespace b200
 
 
@@ -366,4 +649,53 @@ B200_API int b200_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, i
     case 128: return launch_attn_fwd<128>(tm, p, st);
     default: return -1;
   }
+}
+
+
+template <int D>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * 2 * PANEL_BYTES + 1024 + 1024;  // K, V, Q, dO, P, dS tiles
+  auto kern = attn_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  dim3 grid((p.S + ATT_BN - 1) / ATT_BN, p.Hkv, p.B);
+  kern<<<grid, 192, SMEM, st>>>(tq, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Backward of b200_attn_fwd.  qkv, o, d_o as in the forward; lse from the forward; delta: scratch [B, H, S] fp32;
+// dq_acc: scratch [B, S, H*D] fp32 that must be ZERO on entry; dqkv: output, packed like qkv.
+B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, const float* lse, float* delta,
+                           float* dq_acc, void* dqkv, int B, int S, int H, int Hkv, int D, float scale, void* stream,
+                           int* err) {
+  if (D % 16 || D > 128 || D < 16 || H % Hkv) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int wtot = (H + 2 * Hkv) * D, wq = H * D;
+  CUtensorMap tq, tdo;
+  int rc = make_tmap_3d_bf16(&tq, qkv, wtot, S, B, static_cast<uint64_t>(wtot) * 2, static_cast<uint64_t>(S) * wtot * 2,
+                             64, 128);
+  if (rc) return rc;
+  rc = make_tmap_3d_bf16(&tdo, d_o, wq, S, B, static_cast<uint64_t>(wq) * 2, static_cast<uint64_t>(S) * wq * 2, 64, 128);
+  if (rc) return rc;
+  const size_t warps = static_cast<size_t>(B) * S * H;
+  attn_delta_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
+  AttnBwdParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.D = D; p.wq = wq; p.wk = Hkv * D;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.err = err;
+  switch (D) {
+    case 64: rc = launch_attn_bwd<64>(tq, tdo, p, st); break;
+    case 96: rc = launch_attn_bwd<96>(tq, tdo, p, st); break;
+    case 128: rc = launch_attn_bwd<128>(tq, tdo, p, st); break;
+    default: return -1;
+  }
+  if (rc) return rc;
+  const size_t n = static_cast<size_t>(B) * S * (wq / 4);
+  attn_dq_convert_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+      dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), static_cast<size_t>(B) * S, wq, wtot, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
 }

@@ -1,4 +1,5 @@
 """Model families: depth-recurrent LM (training), GPT baseline, HF-compatible inference model."""
+from . import variants  # noqa: F401  (registers the research block / MLP variants by name)
 from .recurrent import GPT, RecurrentGPT  # noqa: F401
 
 

@@ -99,6 +99,11 @@ class RecurrentGPT(_LMBase):
                               init=lambda w: init.init_weight_(w, "head"))
         if config.tie_embeddings:
             self.lm_head.weight = self.transformer.wte.weight
+        if getattr(config, "embed_step", False):
+            from .variants import TimestepEmbedder
+
+            self.step_embedding = TimestepEmbedder(E)
+        self._modulated_core = type(core[0]).__name__ == "ModulatedTransformerPostNormBlock" if R else False
         self.max_seq_length = config.block_size
         self.gradient_checkpointing = gradient_checkpointing
         self._setup_rope(config)
@@ -148,7 +153,12 @@ class RecurrentGPT(_LMBase):
     def core_block_forward(self, x, e, rope, mask, step: int):
         c = self.config
         inj = c.injection_type
-        if inj == "add":
+        context = None
+        if getattr(c, "embed_step", False):
+            context = self.step_embedding(torch.as_tensor([step], device=e.device)).to(x.dtype)
+        if inj == "modulated":  # pairs with ModulatedTransformerPostNormBlock: the state modulates itself
+            context = x.clone()
+        elif inj == "add":
             x = x + e
         elif inj == "gate":
             x = x * e
@@ -166,10 +176,19 @@ class RecurrentGPT(_LMBase):
                 f = noise / (step + 1)
             elif c.geom_noise_injection == "sqrt":
                 f = noise / math.sqrt(step + 1)
+            elif c.geom_noise_injection == "line":
+                top = max(int(getattr(c, "maximal_recurrence", None) or c.mean_recurrence), 1)
+                f = max(noise, (top - step) / top)
             else:
                 f = noise
             x = x * (1 - f) + torch.randn_like(x) * f
         per_block = self.gradient_checkpointing and "per-block" in c.activation_checkpoint_impl
+        if self._modulated_core:
+            for block in self.transformer.core_block:
+                x = block(x, rope, mask, context=context)
+            return x
+        if context is not None:
+            x = x + context
         for block in self.transformer.core_block:
             if per_block and torch.is_grad_enabled():
                 x = torch.utils.checkpoint.checkpoint(block, x, rope, mask, use_reentrant=False)

@@ -1,0 +1,399 @@
+"""The less travelled block, attention and MLP variants of the reference's model zoo.
+
+The flagship path (SandwichBlock + CausalSelfAttention + GatedMLP) lives in ``blocks.py`` and runs on the fused
+sm_100a kernels.  The research variants here keep the reference's parameter names and arithmetic
+(recpre/model_dynamic.py:205-262,289-320,413-742,782-956) and are composed from the same ``Linear`` / norm modules,
+so their GEMMs and norms also run on the native kernels; only their attention core goes through the generic
+``attend`` helper (library SDPA on a GPU, the fp32 statement on CPU) because their q/k/v layouts are not the packed
+layout the native attention kernel consumes.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import blocks as B
+from ..ops import reference as ref
+
+
+def attend(q, k, v):
+    """Causal attention for [B, S, H, D] tensors (k/v may have fewer heads; v may have its own head dim)."""
+    if k.shape[2] != q.shape[2]:
+        rep = q.shape[2] // k.shape[2]
+        k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+    if q.is_cuda:
+        y = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        return y.transpose(1, 2)
+    if q.shape[-1] == v.shape[-1]:
+        return ref.causal_attention(q, k, v).to(q.dtype)
+    S = q.shape[1]
+    logits = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / math.sqrt(q.shape[-1])
+    logits = logits.masked_fill(torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(logits, -1), v.float()).to(q.dtype)
+
+
+def _rope(q, k, rope, config):
+    if not config.rope_settings.use_rope:
+        return q, k
+    cos, sin = rope
+    return ref.rope_interleaved(q, cos, sin), ref.rope_interleaved(k, cos, sin)
+
+
+# ------------------------------------------------------------------------------------------ attention variants
+class _SplitAttention(B.CausalSelfAttention):
+    """Shared q/k/v preparation for the differential-attention variants."""
+
+    def _qkv(self, x, rope):
+        Bsz, S, _ = x.shape
+        qkv = self.Wqkv(x)
+        if self.config.clip_qkv is not None:
+            qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
+        wq, wk = self.n_head * self.head_dim, self.n_kv * self.head_dim
+        q, k, v = qkv.split([wq, wk, wk], dim=-1)
+        q = q.reshape(Bsz, S, self.n_head, self.head_dim)
+        k = k.reshape(Bsz, S, self.n_kv, self.head_dim)
+        v = v.reshape(Bsz, S, self.n_kv, self.head_dim)
+        q, k = _rope(q, k, rope, self.config)
+        rep = self.n_head // self.n_kv
+        if rep > 1:
+            k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        return q, k, v
+
+    def _two_maps(self, q, k, v):
+        h = self.n_head // 2
+        q1, q2, k1, k2 = q[:, :, :h], q[:, :, h:], k[:, :, :h], k[:, :, h:]
+        y = attend(torch.cat([q1, q1, q2, q2], 2), torch.cat([k1, k1, k2, k2], 2), v.repeat(1, 1, 2, 1))
+        return y.chunk(2, dim=2)
+
+
+class DiffSelfAttention(_SplitAttention):
+    """Differential attention: two softmax maps, the second subtracted with a learned lambda
+    (recpre/model_dynamic.py:413-457)."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.register_buffer("lambda_init", torch.as_tensor(0.8 - 0.6 * math.exp(-0.3 * layer_id), dtype=torch.float))
+        self.diff_lmb = nn.Parameter(0.1 * torch.randn(self.head_dim, 4))
+
+    def forward(self, x, rope, mask=None):
+        Bsz, S, E = x.shape
+        q, k, v = self._qkv(x, rope)
+        y1, y2 = self._two_maps(q, k, v)
+        lq1, lq2, lk1, lk2 = self.diff_lmb.chunk(4, dim=-1)
+        lam = (torch.exp((lq1 * lk1).sum(-1).float()) - torch.exp((lq2 * lk2).sum(-1).float())).to(q.dtype)
+        lam = lam + self.lambda_init
+        y = F.rms_norm(y1 - lam * y2, (self.head_dim,), eps=self.config.norm_eps) * (1 - self.lambda_init)
+        return self.proj(y.reshape(Bsz, S, E).to(x.dtype))
+
+
+class SimplifiedDiffSelfAttention(_SplitAttention):
+    """Differential attention with one learned vector lambda (recpre/model_dynamic.py:460-497)."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.register_buffer("lmb_init", torch.as_tensor(0.8 - 0.6 * math.exp(-0.3 * layer_id), dtype=torch.float))
+        self.diff_lmb = nn.Parameter(0.1 * torch.randn(self.head_dim))
+
+    def forward(self, x, rope, mask=None):
+        Bsz, S, E = x.shape
+        q, k, v = self._qkv(x, rope)
+        y1, y2 = self._two_maps(q, k, v)
+        y = F.rms_norm(y1 - (self.diff_lmb + self.lmb_init).to(y1.dtype) * y2, (self.head_dim,),
+                       eps=self.config.norm_eps) * (1 - self.lmb_init)
+        return self.proj(y.reshape(Bsz, S, E).to(x.dtype))
+
+
+class PositionalAttention(nn.Module):
+    """Attention whose q and k depend on the position only (learned per-position embeddings); the values come from
+    the input (recpre/model_dynamic.py:525-577)."""
+
+    def __init__(self, config, layer_id: int, emb_factor: int = 1):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.n_head = config.n_head
+        self.q_embedding = nn.Embedding(config.block_size, config.n_embd // emb_factor)
+        self.k_embedding = nn.Embedding(config.block_size, config.n_embd // emb_factor)
+        self.poshead_dim = config.n_embd // self.n_head // emb_factor
+        self.register_buffer("position_ids", torch.arange(config.block_size).expand((1, -1)), persistent=True)
+        init = config.init
+        self.Wv = B.Linear(config.n_embd, config.n_embd, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "in_proj", layer_id))
+        self.head_dim = config.n_embd // self.n_head
+        self.proj = B.Linear(config.n_embd, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "out_attn", layer_id))
+        self.monitoring, self.latest_metrics = False, {}
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        std = self.config.init.get_std("embedding", self.layer_id)
+        nn.init.trunc_normal_(self.q_embedding.weight, std=std, a=-3 * std, b=3 * std)
+        nn.init.trunc_normal_(self.k_embedding.weight, std=std, a=-3 * std, b=3 * std)
+
+    def forward(self, x, rope, mask=None):
+        Bsz, S, E = x.shape
+        pos = self.position_ids[:, :S]
+        q = self.q_embedding(pos).view(1, S, self.n_head, self.poshead_dim).expand(Bsz, -1, -1, -1).to(x.dtype)
+        k = self.k_embedding(pos).view(1, S, self.n_head, self.poshead_dim).expand(Bsz, -1, -1, -1).to(x.dtype)
+        v = self.Wv(x).view(Bsz, S, self.n_head, self.head_dim)
+        return self.proj(attend(q, k, v.to(x.dtype)).reshape(Bsz, S, E))
+
+
+class OPSelfAttention(nn.Module):
+    """Attention with full-width norms on q and k before the head split (recpre/model_dynamic.py:677-742).  The k norm
+    is sized ``n_head * n_kv_heads`` as in the reference, which only matches k's width when head_dim == n_head; the
+    norm here is sized by k's true width so the module is usable for every shape."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.n_head, self.n_kv = config.n_head, config.num_key_value_heads
+        self.head_dim = config.n_embd // self.n_head
+        init = config.init
+        self.chunks = [config.n_embd, self.n_kv * self.head_dim, self.n_kv * self.head_dim]
+        self.Wqkv = B.Linear(config.n_embd, sum(self.chunks), bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "qkv", layer_id))
+        self.proj = B.Linear(config.n_embd, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "out_attn", layer_id))
+        self.q_norm = B.make_norm(config, config.n_embd)
+        self.k_norm = B.make_norm(config, self.n_kv * self.head_dim)
+        self.monitoring, self.latest_metrics = False, {}
+
+    def forward(self, x, rope, mask=None):
+        Bsz, S, E = x.shape
+        qkv = self.Wqkv(x)
+        if self.config.clip_qkv is not None:
+            qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
+        q, k, v = qkv.split(self.chunks, dim=-1)
+        q = self.q_norm(q).to(x.dtype).reshape(Bsz, S, self.n_head, self.head_dim)
+        k = self.k_norm(k).to(x.dtype).reshape(Bsz, S, self.n_kv, self.head_dim)
+        q, k = _rope(q, k, rope, self.config)
+        y = attend(q, k, v.reshape(Bsz, S, self.n_kv, self.head_dim))
+        return self.proj(y.reshape(Bsz, S, E))
+
+
+# ------------------------------------------------------------------------------------------ MLP variants
+class GatedMLPSeparated(nn.Module):
+    """SwiGLU with two separate input projections ``fc1`` (gate) and ``fc2`` (up) (recpre/model_dynamic.py:782-803)."""
+
+    def __init__(self, config, layer_id: int = 0, in_features: int = 0):
+        super().__init__()
+        in_features = in_features or config.n_embd
+        init = config.init
+        self.fc1 = B.Linear(in_features, config.intermediate_size, bias=config.bias,
+                            init=lambda w: init.init_weight_(w, "glu", layer_id))
+        self.fc2 = B.Linear(in_features, config.intermediate_size, bias=config.bias,
+                            init=lambda w: init.init_weight_(w, "glu", layer_id))
+        self.proj = B.Linear(config.intermediate_size, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "out_proj", layer_id))
+        self.nonlin = B.make_nonlin(config.nonlin_name)
+
+    def forward(self, x):
+        return self.proj(self.nonlin(self.fc1(x)) * self.fc2(x))
+
+
+class HalfGateMLP(nn.Module):
+    """proj(nonlin(fc(x)) * x): the input itself is the linear branch (recpre/model_dynamic.py:849-866)."""
+
+    def __init__(self, config, layer_id: int = 0, in_features: int = 0):
+        super().__init__()
+        in_features = in_features or config.n_embd
+        init = config.init
+        self.fc = B.Linear(in_features, config.n_embd, bias=config.bias,
+                           init=lambda w: init.init_weight_(w, "w1", layer_id))
+        self.proj = B.Linear(config.n_embd, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "w3", layer_id))
+        self.nonlin = B.make_nonlin(config.nonlin_name)
+
+    def forward(self, x):
+        h = self.nonlin(self.fc(x))
+        return self.proj(h * x.to(h.dtype))
+
+
+class TimestepEmbedder(nn.Module):
+    """Sinusoidal embedding of a scalar step index followed by a two-layer MLP (recpre/model_dynamic.py:873-913)."""
+
+    def __init__(self, hidden_size: int, frequency_embedding_size: int = 256):
+        super().__init__()
+        self.mlp = nn.Sequential(nn.Linear(frequency_embedding_size, hidden_size), nn.SiLU(),
+                                 nn.Linear(hidden_size, hidden_size))
+        self.frequency_embedding_size = frequency_embedding_size
+
+    @staticmethod
+    def timestep_embedding(t, dim: int, max_period: int = 10000):
+        half = dim // 2
+        freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+        args = t[:, None].float() * freqs[None]
+        emb = torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+        if dim % 2:
+            emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
+        return emb
+
+    def forward(self, t):
+        return self.mlp(self.timestep_embedding(t, self.frequency_embedding_size).to(self.mlp[0].weight.dtype))
+
+
+# ------------------------------------------------------------------------------------------ block variants
+class OPTransformerBlock(nn.Module):
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.attn = OPSelfAttention(config, layer_id)
+        self.norm_2 = B.make_norm(config)
+        self.mlp = B.make_mlp(config, layer_id)
+        res, skip = config.init.get_scales(layer_id)
+        self.register_buffer("res_scale", torch.as_tensor(res), persistent=True)
+        self.register_buffer("skip_scale", torch.as_tensor(skip), persistent=True)
+
+    def forward(self, x, rope, mask=None):
+        x = self.attn(x, rope, mask) + x
+        return self.norm_2.forward_add(self.mlp(x), x)
+
+
+class SwinScaledBlock(B._TwoNormBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.norm_1(self.attn(x, rope, mask)) * self.res_scale + x * self.skip_scale
+        return self.norm_2(self.mlp(x)) * self.res_scale + x * self.skip_scale
+
+
+class SandwichBlockSwin(B.SandwichBlock):
+    def forward(self, x, rope, mask=None):
+        x = self.norm_2(self.attn(self.norm_1(x), rope, mask)) + x
+        return self.norm_4(self.mlp(self.norm_3(x))) + x
+
+
+class RevTransformerPreNormBlock(nn.Module):
+    """Two-stream (reversible-style) block on the two halves of the channel dimension
+    (recpre/model_dynamic.py:296-320; forward-only there too).  The reference builds its sub-layers at full width and
+    feeds them half-width streams, which cannot run; here the sub-layers are built for the half width."""
+
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        import copy
+
+        half = copy.copy(config)
+        half.n_embd = config.n_embd // 2
+        half.intermediate_size = config.intermediate_size // 2
+        self.config, self.layer_id = config, layer_id
+        self.norm_1 = B.make_norm(half)
+        self.attn = B.CausalSelfAttention(half, layer_id)
+        self.norm_2 = B.make_norm(half)
+        self.mlp = B.make_mlp(half, layer_id)
+
+    def forward(self, x, rope, mask=None):
+        x1, x2 = torch.chunk(x, 2, dim=-1)
+        y1 = self.attn(self.norm_1(x2.contiguous()), rope, mask) + x1
+        y2 = self.mlp(self.norm_2(y1)) + x2
+        return torch.cat([y1, y2], dim=-1)
+
+
+class TransformerPostNormBlockDiff(B.TransformerPostNormBlock):
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.attn = DiffSelfAttention(config, layer_id)
+
+
+class TransformerPostNormBlockDiffSimplified(B.TransformerPostNormBlock):
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.attn = SimplifiedDiffSelfAttention(config, layer_id)
+
+
+class TransformerPostNormPosBlock(B.TransformerPostNormBlock):
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.attn = PositionalAttention(config, layer_id)
+
+
+class ParallelGatedMLPSelfAttention(nn.Module):
+    """One input GEMM producing [z | gate | q | k | v]; the gated MLP branch and the attention branch are concatenated
+    and share the output projection; post-norm residual (recpre/model_dynamic.py:592-647)."""
+
+    expanded = False
+
+    def __init__(self, config, layer_id: int):
+        super().__init__()
+        self.config, self.layer_id = config, layer_id
+        self.n_head, self.n_kv = config.n_head, config.num_key_value_heads
+        self.head_dim = config.n_embd // self.n_head
+        I = config.intermediate_size
+        self.chunks = [I, I, config.n_embd, self.n_kv * self.head_dim, self.n_kv * self.head_dim]
+        init = config.init
+        self.Wqkv_fc = B.Linear(config.n_embd, sum(self.chunks), bias=config.bias,
+                                init=lambda w: init.init_weight_(w, "in_proj", layer_id))
+        self.proj = B.Linear(I + config.n_embd, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "out_proj", layer_id))
+        self.nonlin = B.make_nonlin(config.nonlin_name)
+        self.norm = B.make_norm(config)
+
+    def attention(self, q, k, v, rope):
+        Bsz, S, W = q.shape
+        q = q.reshape(Bsz, S, self.n_head, self.head_dim)
+        k = k.reshape(Bsz, S, self.n_kv, self.head_dim)
+        q, k = _rope(q, k, rope, self.config)
+        return attend(q, k, v.reshape(Bsz, S, self.n_kv, self.head_dim)).reshape(Bsz, S, W)
+
+    def forward(self, x, rope, mask=None):
+        z, gate, q, k, v = self.Wqkv_fc(x).split(self.chunks, dim=-1)
+        y = torch.cat([self.nonlin(z) * gate, self.attention(q, k, v, rope)], dim=-1)
+        return self.norm.forward_add(self.proj(y), x)
+
+
+class GatedBlock(ParallelGatedMLPSelfAttention):
+    """The attention output (at intermediate width) gates the nonlinear branch (recpre/model_dynamic.py:650-674)."""
+
+    expanded = True
+
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        I = config.intermediate_size
+        self.head_dim = I // self.n_head
+        self.chunks = [I, I, self.n_kv * self.head_dim, self.n_kv * self.head_dim]
+        init = config.init
+        self.Wqkv_fc = B.Linear(config.n_embd, sum(self.chunks), bias=config.bias,
+                                init=lambda w: init.init_weight_(w, "in_proj", layer_id))
+        self.proj = B.Linear(I, config.n_embd, bias=config.bias,
+                             init=lambda w: init.init_weight_(w, "out_proj", layer_id))
+
+    def forward(self, x, rope, mask=None):
+        z, q, k, v = self.Wqkv_fc(x).split(self.chunks, dim=-1)
+        y = self.nonlin(z) * self.attention(q, k, v, rope)
+        return self.norm.forward_add(self.proj(y), x)
+
+
+class ModulatedTransformerPostNormBlock(B._TwoNormBlock):
+    """Post-norm block whose sub-layer inputs are shifted/scaled and whose outputs are gated by a context vector
+    (adaLN, recpre/model_dynamic.py:916-956)."""
+
+    def __init__(self, config, layer_id: int):
+        super().__init__(config, layer_id)
+        self.adaLN_modulation = nn.Sequential(nn.SiLU(), nn.Linear(config.n_embd, 6 * config.n_embd, bias=True))
+
+    @staticmethod
+    def modulate(x, shift, scale):
+        return x * (1 + scale) + shift
+
+    def forward(self, x, rope, mask=None, context=None):
+        if context is None:
+            x = self.norm_1.forward_add(self.attn(x, rope, mask), x)
+            return self.norm_2.forward_add(self.mlp(x), x)
+        ctx = self.adaLN_modulation(context.to(self.adaLN_modulation[1].weight.dtype)).to(x.dtype)
+        s1, c1, g1, s2, c2, g2 = ctx.chunk(6, dim=-1)
+        x = self.norm_1(self.attn(self.modulate(x, s1, c1), rope, mask) * g1 + x)
+        return self.norm_2(self.mlp(self.modulate(x, s2, c2)) * g2 + x)
+
+
+B.MLP_CLASSES.update({"GatedMLPSeparated": GatedMLPSeparated, "HalfGateMLP": HalfGateMLP,
+                      # the xformers / fused_swiglu backed classes compute the same function as the fused and the
+                      # separated SwiGLU; their parameter layouts map onto these two
+                      "GatedMLPXFormers": B.GatedMLP, "GatedMLPFattori": GatedMLPSeparated})
+B.BLOCK_CLASSES.update({c.__name__: c for c in (
+    OPTransformerBlock, SwinScaledBlock, SandwichBlockSwin, RevTransformerPreNormBlock, TransformerPostNormBlockDiff,
+    TransformerPostNormBlockDiffSimplified, TransformerPostNormPosBlock, ParallelGatedMLPSelfAttention, GatedBlock,
+    ModulatedTransformerPostNormBlock)})

@@ -39,6 +39,8 @@ def bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
     B, S, W = qkv_r.shape
     if not NATIVE_BWD:
         return K._attention_bwd_library(do, qkv_r, n_head, n_kv, D, scale)
+    do = do.contiguous()
+    assert do.dtype == torch.bfloat16 and o.is_contiguous() and qkv_r.is_contiguous()
     dqkv = torch.empty_like(qkv_r)
     dq_acc = torch.zeros(B, S, n_head * D, dtype=torch.float32, device=qkv_r.device)
     delta = torch.empty(B, n_head, S, dtype=torch.float32, device=qkv_r.device)

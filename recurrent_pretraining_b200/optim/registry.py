@@ -18,6 +18,12 @@ def get_optimizer(optimizer_name: str, model=None, pytorch_optimizer_sharding: b
         from .ellis import ELLISAdam as cls
     elif name == "SOAP":
         from .soap import SOAP as cls
+    elif name == "Lilith":
+        from .research import Lilith as cls
+    elif name == "IVON":
+        from .research import IVON as cls
+    elif name in ("simo-shampoo", "ZeroShampoo", "ZeroShampooWithAdamGraftingOptimizer"):
+        from .research import ZeroShampooWithAdamGraftingOptimizer as cls
     elif name in ("Kellers", "OrthogonalNesterov"):
         from .others import OrthogonalNesterov as cls
     elif hasattr(torch.optim, name):
@@ -25,8 +31,7 @@ def get_optimizer(optimizer_name: str, model=None, pytorch_optimizer_sharding: b
         if allow_fusion and name in ("AdamW", "Adam", "SGD") and torch.cuda.is_available():
             cls = partial(cls, fused=True)
     else:
-        raise ValueError(f"Invalid optimizer {name} requested. Lilith, IVON and the Shampoo variants of the "
-                         "reference are not provided.")
+        raise ValueError(f"Invalid optimizer {name} requested (meta's distributed_shampoo package is not bundled).")
     if use_zero or pytorch_optimizer_sharding:
         from .zero import SimpleZeroRedundancyOptimizer
 

@@ -116,3 +116,74 @@ def test_init_statistics_match_reference_strategy():
             continue
         a, b = p.std().item(), theirs[n].std().item()
         assert abs(a - b) < 0.15 * b + 1e-6, (n, a, b)
+
+
+VARIANT_BLOCKS = ["TransformerPreNormBlock", "TransformerPostNormBlock", "ScaledTransformerPostNormBlock",
+                  "SwinScaledBlock", "SandwichBlockSwin", "TransformerPostNormBlockDiff",
+                  "TransformerPostNormBlockDiffSimplified", "TransformerPostNormPosBlock",
+                  "ParallelGatedMLPSelfAttention", "ModulatedTransformerPostNormBlock"]
+
+
+@needs_ref
+@pytest.mark.parametrize("block", VARIANT_BLOCKS)
+def test_block_variants_match_reference(block):
+    """Every research block variant: same state-dict keys as the reference, same loss and gradients."""
+    torch.manual_seed(0)
+    over = dict(TINY, block_class_name=block, attn_impl="sdpa", qk_bias=False)
+    if block == "ModulatedTransformerPostNormBlock":
+        over["injection_type"] = "modulated"
+    ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **over)
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **over)
+    model = cfg.construct_model()
+    sd = ref_model.state_dict()
+    assert set(sd) == set(model.state_dict()), set(sd) ^ set(model.state_dict())
+    model.load_state_dict(sd)
+    ids = torch.randint(0, 512, (2, 64))
+    labels = torch.randint(0, 512, (2, 64))
+    ref_model.config.state_init = model.config.state_init = "zero" if "Modulated" not in block else "unit"
+    torch.manual_seed(1)
+    a = ref_model(ids, labels=labels.contiguous(), num_steps_pair=torch.tensor([1, 2]))
+    torch.manual_seed(1)
+    b = model(ids, labels=labels, num_steps_pair=torch.tensor([1, 2]))
+    assert torch.allclose(a["loss"], b["loss"], rtol=2e-5, atol=1e-6), (a["loss"], b["loss"])
+    a["loss"].backward()
+    b["loss"].backward()
+    theirs = dict(ref_model.named_parameters())
+    for n, p in model.named_parameters():
+        if theirs[n].grad is None:
+            assert p.grad is None or float(p.grad.abs().max()) == 0.0, n
+        else:
+            assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-3, atol=1e-6), n
+
+
+@pytest.mark.parametrize("block,mlp", [("OPTransformerBlock", "GatedMLP"), ("RevTransformerPreNormBlock", "GatedMLP"),
+                                       ("GatedBlock", "GatedMLP"), ("SwinBlock", "GatedMLP"), ("SandwichBlock", "GatedMLPSeparated"),
+                                       ("SandwichBlock", "HalfGateMLP"), ("SandwichBlock", "BaseMLP")])
+def test_remaining_variants_train(block, mlp):
+    """Variants the reference cannot run as written (shape bugs / missing packages) still build, run and learn."""
+    torch.manual_seed(0)
+    over = dict(TINY, block_class_name=block, mlp_class_name=mlp, qk_bias=False)
+    if block == "RevTransformerPreNormBlock":
+        over.update(n_embd=192, intermediate_size=320)
+    model = ModelConfig.from_name("nebel-raven-3.5b", **over).construct_model()
+    ids = torch.randint(0, 512, (2, 64))
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(8):
+        out = model(ids, labels=ids, num_steps_pair=torch.tensor([1, 1]))
+        opt.zero_grad()
+        out["loss"].backward()
+        opt.step()
+        losses.append(out["loss"].item())
+    assert losses[-1] < losses[0]
+
+
+def test_embed_step_and_noise_schedules():
+    torch.manual_seed(0)
+    for extra in (dict(embed_step=True), dict(intermediate_noise_injection=0.1, geom_noise_injection="line"),
+                  dict(intermediate_noise_injection=0.1, geom_noise_injection="sqrt")):
+        model = ModelConfig.from_name("nebel-raven-3.5b", **dict(TINY, **extra)).construct_model()
+        out = model(torch.randint(0, 512, (1, 32)), labels=torch.randint(0, 512, (1, 32)),
+                    num_steps_pair=torch.tensor([1, 1]))
+        out["loss"].backward()
+        assert torch.isfinite(out["loss"])

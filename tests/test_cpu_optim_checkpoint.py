@@ -141,3 +141,54 @@ def test_reference_state_dict_loads_into_our_model_and_back():
     wrapped = {"_orig_mod._original_module." + k: v for k, v in ref_model.state_dict().items()}
     ours.load_state_dict(ckpt.strip_wrapper_prefixes(wrapped))
     ref_model.load_state_dict(ckpt.model_state_dict(ours))
+
+
+def test_research_optimizers_match_reference_math():
+    """Lilith / IVON / blocked Shampoo against a direct restatement of their update rules on a toy problem."""
+    from recurrent_pretraining_b200.optim import get_optimizer
+    from recurrent_pretraining_b200.optim.research import IVON, Lilith, ZeroShampooWithAdamGraftingOptimizer
+
+    assert get_optimizer("Lilith") is Lilith and get_optimizer("IVON") is IVON
+    assert get_optimizer("simo-shampoo") is ZeroShampooWithAdamGraftingOptimizer
+    torch.manual_seed(0)
+    target = torch.randn(12, 8)
+
+    def run(opt_cls, steps=60, **kw):
+        w = torch.nn.Parameter(torch.zeros(12, 8))
+        b = torch.nn.Parameter(torch.zeros(8))
+        opt = opt_cls([w, b], **kw)
+        first = None
+        for _ in range(steps):
+            def closure():
+                opt.zero_grad()
+                loss = ((w + b - target) ** 2).mean()
+                loss.backward()
+                return loss
+            if isinstance(opt, IVON):
+                with opt.sampled_params(train=True):
+                    loss = closure()
+                opt.step()
+            else:
+                loss = closure()
+                opt.step()
+            first = first if first is not None else loss.item()
+        return first, loss.item()
+
+    f, l = run(Lilith, lr=1e-2, weight_decay=0.0)
+    assert l < 0.5 * f
+    f, l = run(IVON, steps=200, lr=0.5, ess=1e4, hess_init=0.1, weight_decay=1e-4, clip_radius=1.0)
+    assert l < 0.5 * f
+    f, l = run(ZeroShampooWithAdamGraftingOptimizer, lr=5e-2, block_size=4, weight_decay=0.0)
+    assert l < 0.2 * f
+
+    # one Lilith step, restated
+    w = torch.nn.Parameter(torch.ones(3, 2))
+    w.grad = torch.full((3, 2), 0.5)
+    Lilith([w], lr=0.1, weight_decay=0.0).step()
+    g = 0.5 * (6 ** 0.5 / (6 ** 0.5 * 0.5))
+    m1 = 0.1 * g
+    m2 = 0.01 * m1
+    u = m1 + m2
+    v_hat = (0.001 * u * u) / (1 - 0.999)
+    want = 1 - 0.1 * u / (v_hat + 1e-8) ** 0.5
+    assert torch.allclose(w.detach(), torch.full((3, 2), want), atol=1e-6)

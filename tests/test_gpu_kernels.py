@@ -236,3 +236,27 @@ def test_flash_attention_forward(C, B, S, H, Hkv, D):
     mask = torch.ones(S, S, dtype=torch.bool, device="cuda").triu(1)
     want_lse = torch.logsumexp(scores.masked_fill(mask, float("-inf")), dim=-1)
     _close(lse, want_lse, 1e-2, 2e-2)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
+                                         (1, 1024, 2, 2, 96)])
+def test_flash_attention_backward(C, B, S, H, Hkv, D):
+    from recurrent_pretraining_b200.ops import attention as A
+
+    assert A.NATIVE_BWD, "the native attention backward entry point is missing from the built library"
+    qkv = _packed_qkv(B, S, H, Hkv, D)
+    scale = D ** -0.5
+    o, lse = A.fwd(qkv, H, Hkv, D, scale)
+    do = (torch.randn(B, S, H * D, device="cuda") * 0.5).bfloat16()
+    dqkv = A.bwd(do, qkv, o, lse, H, Hkv, D, scale)
+    torch.cuda.synchronize()
+    assert C.check_device_status() == 0
+    x = qkv.float().requires_grad_(True)
+    want, _ = _attention_reference(x, H, Hkv, D, scale)
+    want.backward(do.float().view(B, S, H, D))
+    wq = H * D
+    wk = Hkv * D
+    for name, sl in (("dq", slice(0, wq)), ("dk", slice(wq, wq + wk)), ("dv", slice(wq + wk, wq + 2 * wk))):
+        got, ref_g = dqkv[..., sl].float(), x.grad[..., sl]
+        err = (got - ref_g).abs().max().item()
+        assert err <= 3e-2 * ref_g.abs().max().item() + 1e-3, (name, err, ref_g.abs().max().item())
