@@ -280,6 +280,9 @@ class RevTransformerPreNormBlock(nn.Module):
         half = copy.copy(config)
         half.n_embd = config.n_embd // 2
         half.intermediate_size = config.intermediate_size // 2
+        half.num_attention_heads = max(config.num_attention_heads // 2, 1)  # keeps head_dim, hence the RoPE tables
+        half.num_key_value_heads = max(config.num_key_value_heads // 2, 1)
+        half.n_head = max(config.n_head // 2, 1)
         self.config, self.layer_id = config, layer_id
         self.norm_1 = B.make_norm(half)
         self.attn = B.CausalSelfAttention(half, layer_id)
@@ -293,22 +296,30 @@ class RevTransformerPreNormBlock(nn.Module):
         return torch.cat([y1, y2], dim=-1)
 
 
+def _drop_scales(block) -> None:
+    """These blocks carry no residual/skip scale buffers in the reference's state dict."""
+    del block.res_scale, block.skip_scale
+
+
 class TransformerPostNormBlockDiff(B.TransformerPostNormBlock):
     def __init__(self, config, layer_id: int):
         super().__init__(config, layer_id)
         self.attn = DiffSelfAttention(config, layer_id)
+        _drop_scales(self)
 
 
 class TransformerPostNormBlockDiffSimplified(B.TransformerPostNormBlock):
     def __init__(self, config, layer_id: int):
         super().__init__(config, layer_id)
         self.attn = SimplifiedDiffSelfAttention(config, layer_id)
+        _drop_scales(self)
 
 
 class TransformerPostNormPosBlock(B.TransformerPostNormBlock):
     def __init__(self, config, layer_id: int):
         super().__init__(config, layer_id)
         self.attn = PositionalAttention(config, layer_id)
+        _drop_scales(self)
 
 
 class ParallelGatedMLPSelfAttention(nn.Module):
@@ -373,6 +384,7 @@ class ModulatedTransformerPostNormBlock(B._TwoNormBlock):
 
     def __init__(self, config, layer_id: int):
         super().__init__(config, layer_id)
+        _drop_scales(self)
         self.adaLN_modulation = nn.Sequential(nn.SiLU(), nn.Linear(config.n_embd, 6 * config.n_embd, bias=True))
 
     @staticmethod

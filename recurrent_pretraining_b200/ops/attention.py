@@ -16,7 +16,10 @@ _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _fwd = K._sig("b200_attn_fwd", [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp])
 _bwd = K._sig("b200_attn_bwd", [_vp] * 7 + [_i] * 5 + [_f, _vp, _vp]) if hasattr(K.lib, "b200_attn_bwd") else None
 
-ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "1") == "1"
+# Measured on the flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.57 ms, native backward 1.73 ms;
+# library (cuDNN) forward 0.18 ms, forward-recompute + backward 1.14 ms.  Until the native kernels win they are opt-in
+# for training (B200_NATIVE_ATTENTION=1); numerics tests always run them.
+ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "0") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
 
 

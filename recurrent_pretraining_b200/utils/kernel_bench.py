@@ -88,18 +88,25 @@ def bench_norm(M=4096, E=5280):
 
 
 def bench_attn(B=1, S=4096, H=55, D=96):
+    """Native tcgen05 attention forward / backward against the library path (SDPA) on the flagship shape."""
+    from ..ops import attention as A
     from ..ops import cuda as C
 
     qkv = torch.randn(B, S, 3 * H * D, device="cuda").bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     fl = 4.0 * B * H * S * S * D / 2
     scale = D ** -0.5
-    t = time_fn(lambda: C.attention_fwd(qkv, H, H, D, scale))
-    o, lse = C.attention_fwd(qkv, H, H, D, scale)
+    t = time_fn(lambda: A.fwd(qkv, H, H, D, scale), flush=flush)
+    o, lse = A.fwd(qkv, H, H, D, scale)
     do = torch.randn_like(o)
-    tb = time_fn(lambda: C.attention_bwd(do, qkv, o, lse, H, H, D, scale))
-    print(json.dumps({"kernel": "attention", "native": bool(lse.numel()), "fwd_ms": round(t, 3),
+    tb = time_fn(lambda: A.bwd(do, qkv, o, lse, H, H, D, scale), flush=flush)
+    q, k, v = (x.reshape(B, S, H, D).transpose(1, 2) for x in qkv.split(H * D, dim=-1))
+    tl = time_fn(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True), flush=flush)
+    tlb = time_fn(lambda: C._attention_bwd_library(do, qkv, H, H, D, scale), flush=flush)
+    print(json.dumps({"kernel": "attention", "native_bwd": A.NATIVE_BWD, "fwd_ms": round(t, 3),
                       "fwd_tflops": round(fl / t / 1e9, 1), "bwd_ms": round(tb, 3),
-                      "bwd_tflops": round(2.5 * fl / tb / 1e9, 1)}))
+                      "bwd_tflops": round(2.5 * fl / tb / 1e9, 1), "library_fwd_ms": round(tl, 3),
+                      "library_fwd_plus_bwd_ms": round(tlb, 3)}))
 
 
 if __name__ == "__main__":

@@ -164,7 +164,9 @@ def test_remaining_variants_train(block, mlp):
     torch.manual_seed(0)
     over = dict(TINY, block_class_name=block, mlp_class_name=mlp, qk_bias=False)
     if block == "RevTransformerPreNormBlock":
-        over.update(n_embd=192, intermediate_size=320)
+        over.update(n_embd=192, intermediate_size=320, num_attention_heads=8, num_key_value_heads=8)
+    if block == "GatedBlock":  # the attention branch runs at intermediate width with the model's RoPE tables
+        over.update(intermediate_size=96)
     model = ModelConfig.from_name("nebel-raven-3.5b", **over).construct_model()
     ids = torch.randint(0, 512, (2, 64))
     opt = torch.optim.AdamW(model.parameters(), lr=3e-3)

@@ -42,3 +42,13 @@ def test_barrier_wait_times_out_and_reports():
     res = _run("timeout", port=29643)
     assert res["status"] == 5  # ERR_WAIT_PEER_FLAG
     assert res["after"] == 8.0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_p2p_sharded_step_four_ranks():
+    res = _run("train", nproc=4, port=29645)
+    assert res["status"] == 0
+    assert res["replicas_identical"]
+    for a, b in zip(res["p2p_losses"], res["nccl_losses"]):
+        assert abs(a - b) < 0.02 * abs(b) + 0.02, res
+    assert res["param_rel_diff"] < 2e-2, res
