@@ -77,24 +77,41 @@ __global__ void barrier_kernel(const __grid_constant__ PeerPtrs flags, int rank,
 
 // In-place reduce-scatter of fp32: own[start .. start+count) = sum over ranks of buf_q[start .. start+count);
 // *sumsq += sum of squares of the reduced values.  count % 4 == 0, pointers 16-byte aligned.
-template <int N>
+template <int N, int U>
 __global__ void __launch_bounds__(512)
 reduce_scatter_kernel(const __grid_constant__ PeerPtrs bufs, int rank, size_t start, size_t count, float* sumsq) {
   __shared__ float red[16];
   float4* own = reinterpret_cast<float4*>(reinterpret_cast<float*>(bufs.p[rank]) + start);
   const float4* peer[N];
 #pragma unroll
-  for (int q = 0; q < N; ++q) peer[q] = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bufs.p[q]) + start);
+  for (int q = 0; q < N; ++q) peer[q] = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bufs.p[(q + rank) % N]) + start);
   float ss = 0.f;
   const size_t nvec = count >> 2;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float4 v[N];
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // U independent vectors per thread per trip: U * (N - 1) remote 16-byte loads in flight per thread
+  for (; i + (U - 1) * stride < nvec; i += U * stride) {
+    float4 v[U][N];
 #pragma unroll
-    for (int q = 0; q < N; ++q) v[q] = ld_peer_f4(peer[(q + rank) % N] + i);  // start with the local copy
-    float4 a = v[0];
+    for (int u = 0; u < U; ++u)
 #pragma unroll
-    for (int q = 1; q < N; ++q) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
+      for (int q = 0; q < N; ++q) v[u][q] = ld_peer_f4(peer[q] + i + u * stride);  // q = 0 is the local copy
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float4 a = v[u][0];
+#pragma unroll
+      for (int q = 1; q < N; ++q) { a.x += v[u][q].x; a.y += v[u][q].y; a.z += v[u][q].z; a.w += v[u][q].w; }
+      own[i + u * stride] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  for (; i < nvec; i += stride) {
+    float4 a = ld_peer_f4(peer[0] + i);
+#pragma unroll
+    for (int q = 1; q < N; ++q) {
+      const float4 w = ld_peer_f4(peer[q] + i);
+      a.x += w.x; a.y += w.y; a.z += w.z; a.w += w.w;
+    }
     own[i] = a;
     ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
   }
@@ -126,6 +143,21 @@ allgather_kernel(const __grid_constant__ PeerPtrs bufs, int rank, int N, size_t 
                  : "l"(src)
                  : "memory");
     own[i] = v;
+  }
+}
+
+// Push all-gather: this rank's slice is written into every peer's buffer at the same offset (stores need no
+// request/response round trip over NVLink, unlike the pull form above).
+__global__ void __launch_bounds__(512)
+allgather_push_kernel(const __grid_constant__ PeerPtrs bufs, int rank, int N, size_t slice_vec) {
+  const uint4* src = reinterpret_cast<const uint4*>(bufs.p[rank]) + static_cast<size_t>(rank) * slice_vec;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < slice_vec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = src[i];
+    for (int q = 1; q < N; ++q) {
+      const int dst = (rank + q) % N;
+      reinterpret_cast<uint4*>(bufs.p[dst])[static_cast<size_t>(rank) * slice_vec + i] = v;
+    }
   }
 }
 
@@ -332,8 +364,15 @@ B200_API int b200_reduce_scatter_f32(void* const* buf_ptrs, int rank, int N, lon
   if ((start & 3) || (count & 3)) return -3;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const PeerPtrs pp = make_ptrs(buf_ptrs, N);
+  // ctas > 0: that many CTAs; bit 16 of `ctas` selects the variant without unrolling (for the communication sweep)
+  const bool plain = ctas & 0x10000;
+  ctas &= 0xffff;
   const int grid = comm_grid(count >> 2, ctas > 0 ? ctas : 296);
-  DISPATCH_N(N, (reduce_scatter_kernel<NN><<<grid, 512, 0, st>>>(pp, rank, start, count, sumsq)))
+  if (plain) {
+    DISPATCH_N(N, (reduce_scatter_kernel<NN, 1><<<grid, 512, 0, st>>>(pp, rank, start, count, sumsq)))
+  } else {
+    DISPATCH_N(N, (reduce_scatter_kernel<NN, (NN <= 4 ? 4 : 2)><<<grid, 512, 0, st>>>(pp, rank, start, count, sumsq)))
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -346,6 +385,18 @@ B200_API int b200_allgather_bytes(void* const* buf_ptrs, int rank, int N, long l
   const int grid = comm_grid(slice_vec * N, ctas > 0 ? ctas : 296);
   allgather_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(buf_ptrs, N), rank, N,
                                                                             slice_vec, slice_vec * N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Push form of the all-gather: this rank's slice is stored into every peer.
+B200_API int b200_allgather_push_bytes(void* const* buf_ptrs, int rank, int N, long long slice_bytes, int ctas,
+                                       void* stream) {
+  if (slice_bytes <= 0) return 0;
+  if (slice_bytes & 15) return -3;
+  const size_t slice_vec = static_cast<size_t>(slice_bytes) >> 4;
+  const int grid = comm_grid(slice_vec, ctas > 0 ? ctas : 296);
+  allgather_push_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(buf_ptrs, N), rank, N,
+                                                                                 slice_vec);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -9,6 +9,7 @@ from __future__ import annotations
 import ctypes as C
 import json
 import statistics
+import sys
 
 import torch
 import torch.distributed as dist
@@ -96,6 +97,35 @@ def main():
                "one_shot_in_GBps": round((N - 1) * nbytes / t_one / 1e6, 1) if t_one == t_one else None}
         if rank == 0:
             print(json.dumps(rec), flush=True)
+    if "--phases" in sys.argv:
+        # each phase alone on a 256 MB bucket, by CTA count: inbound (pull) or outbound (push) bytes per GPU per second
+        nbytes = 256 * 2**20
+        n32 = nbytes // 4
+        per = (n32 + N - 1) // N
+        lo = rank * per
+        moved = (N - 1) * per * 4
+        K.lib.b200_allgather_push_bytes.restype = C.c_int
+        for ctas in (37, 74, 148, 296, 592):
+            def phase(call):
+                def run():
+                    barrier()
+                    K._check(call(C.c_void_p(K._stream())), "phase")
+                    barrier()
+                return run
+            rs_plain = phase(lambda st: K.lib.b200_reduce_scatter_f32(
+                buf.ptr_array(), rank, N, C.c_longlong(lo), C.c_longlong(per), None, ctas | 0x10000, st))
+            rs_unrolled = phase(lambda st: K.lib.b200_reduce_scatter_f32(
+                buf.ptr_array(), rank, N, C.c_longlong(lo), C.c_longlong(per), None, ctas, st))
+            ag_pull = phase(lambda st: K.lib.b200_allgather_bytes(buf.ptr_array(), rank, N, C.c_longlong(per * 4), ctas, st))
+            ag_push = phase(lambda st: K.lib.b200_allgather_push_bytes(buf.ptr_array(), rank, N, C.c_longlong(per * 4),
+                                                                       ctas, st))
+            rec = {"phase_sweep_MB": 256, "n_gpus": N, "ctas": ctas}
+            for name, fn in (("rs_plain", rs_plain), ("rs_unrolled", rs_unrolled), ("ag_pull", ag_pull),
+                             ("ag_push", ag_push)):
+                t = _time(fn, dev, reps=6, warmup=2)
+                rec[name + "_GBps"] = round(moved / t / 1e6, 1)
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
     status = K.check_device_status()
     if rank == 0:
         print(json.dumps({"device_status": status}))
