@@ -64,6 +64,15 @@ class RavenGenerationMixin:
     # ------------------------------------------------------------------------------------------------
     def _prep_generate_args(self, input_ids, generation_config, cache_lookup_strategy, model_kwargs):
         gc = _gen_config(self, generation_config)
+        overrides = {k: model_kwargs.pop(k) for k in ("return_dict_in_generate", "do_sample", "temperature", "top_k",
+                                                       "top_p", "min_p", "repetition_penalty")
+                     if k in model_kwargs}
+        if overrides:  # sampling / output options given as plain keyword arguments win over the stored config
+            import copy
+
+            gc = copy.copy(gc)
+            for k, v in overrides.items():
+                setattr(gc, k, v)
         if "max_new_tokens" in model_kwargs:
             max_new = model_kwargs.pop("max_new_tokens")
             if "max_length" in model_kwargs:

@@ -144,3 +144,23 @@ def _cfg(**kw):
     from types import SimpleNamespace
 
     return SimpleNamespace(**kw)
+
+
+def test_legacy_model_returns_attention_maps():
+    from recurrent_pretraining_b200.models import legacy
+    from recurrent_pretraining_b200.models.hf_config import RavenConfig
+
+    torch.manual_seed(0)
+    cfg = RavenConfig(n_embd=64, n_heads=4, n_layers=4, block_size=32, vocab_size=128, intermediate_size=96,
+                      n_layers_in_recurrent_block=2, n_layers_in_prelude=1, n_layers_in_coda=1, mean_recurrence=2)
+    model = legacy.RavenForCausalLM(cfg).eval()
+    ids = torch.randint(0, 128, (2, 12))
+    states = torch.zeros(2, 12, 64)
+    with torch.no_grad():
+        plain = model(ids, input_states=states, num_steps=2)
+        out = model(ids, input_states=states, num_steps=2, output_details={"return_attention": True})
+    assert plain.attention_maps is None
+    assert torch.allclose(plain.logits, out.logits, atol=1e-4)
+    assert set(out.attention_maps) == {0, 1, 2, 3, 4, -1}  # prelude 0, two recurrences of two blocks, coda
+    m = out.attention_maps[0]
+    assert m.shape == (2, 12, 12) and float(m.triu(1).abs().max()) == 0.0 and float(m[:, 0, 0].min()) == 1.0
