@@ -45,7 +45,7 @@ def main():
     dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
     sizes_mb = [1, 4, 16, 64, 256, 1024]
     max_bytes = sizes_mb[-1] * 2**20
-    buf = SymmetricBuffer(fabric, max_bytes)
+    buf = SymmetricBuffer(fabric, max_bytes + 4096 * N)  # slack: slices are rounded up to 512 B
     ctrl = SymmetricBuffer(fabric, 512)
     out = torch.empty(max_bytes // 4, dtype=torch.float32, device=dev)
     sumsq = torch.zeros(1, device=dev)
@@ -73,8 +73,9 @@ def main():
             barrier()
             K._check(K.lib.b200_reduce_scatter_f32(buf.ptr_array(), rank, N, C.c_longlong(lo), C.c_longlong(hi - lo),
                                                    C.c_void_p(sumsq.data_ptr()), 0, st), "rs")
-            barrier()
-            K._check(K.lib.b200_allgather_bytes(buf.ptr_array(), rank, N, C.c_longlong(per * 4), 0, st), "ag")
+            # No barrier here: the push writes slice `rank` of every peer's buffer, and the only reader of that
+            # slice (this rank's own reduce-scatter) has already finished on this stream.
+            K._check(K.lib.b200_allgather_push_bytes(buf.ptr_array(), rank, N, C.c_longlong(per * 4), 0, st), "ag")
             barrier()
 
         def ours_one_shot():

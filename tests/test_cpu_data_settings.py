@@ -146,3 +146,42 @@ def test_reference_yaml_loads(monkeypatch, tmp_path):
     cfg = parse_cli([f"--config={ROOT}/launch_configs/frontier_nebel_512_nodes.yaml"])
     assert cfg.optimizer == "ELLISAdam" and cfg.optim_config["atan_adam"] and cfg.gradient_accumulation_steps == 1
     assert cfg.partial_depth_eval == [1, 4, 8, 16, 64] and cfg.model_config.lockstep_n
+
+
+def test_offline_pipeline_tokenizer_pack_shuffle_count(tmp_path):
+    """Raw text -> tokenizer -> packed shards -> reshuffle -> counts -> readable by the training loader."""
+    import json as _json
+
+    import pyarrow.parquet as pq
+
+    from recurrent_pretraining_b200.data.datasets import ParquetStream
+    from recurrent_pretraining_b200.data.prepare import count_tokens, shuffle_shards, tokenize_pack, tokenizer_train
+    from recurrent_pretraining_b200.data.prepare.special_tokens import special_token_ids
+
+    assert special_token_ids(65536)["<|begin_text|>"] == 65504 and special_token_ids(65536)["<|end_text|>"] == 65505
+    assert special_token_ids(65536)["<|end_turn|>"] == 65508 and special_token_ids(65536)["<|pad|>"] == 65509
+    raw = tmp_path / "raw.jsonl"
+    with open(raw, "w") as f:
+        for i in range(200):
+            f.write(_json.dumps({"text": f"Document {i}: the quick brown fox jumps over {i * 7} lazy dogs.\n\\alpha == 3"}) + "\n")
+    V = 512
+    tok = tokenizer_train.train_tokenizer([str(raw)], vocab_size=V, out_dir=str(tmp_path / "tok"))
+    assert tok.get_vocab_size() == V
+    ids = special_token_ids(V)
+    assert tok.token_to_id("<|begin_text|>") == ids["<|begin_text|>"] == V - 32
+    text = "the quick brown fox 123"
+    assert tok.decode(tok.encode(text).ids) == text
+    info = tokenize_pack.prepare([str(raw)], lambda s: tok.encode(s).ids, ids["<|begin_text|>"], ids["<|end_text|>"],
+                                 str(tmp_path / "data"), block_size=32, num_shards=4, val_fraction=0.1, row_group_size=8)
+    assert info["documents"] == 200 and info["rows"] == info["tokens"] // 33 and len(info["train"]) == 4
+    before = count_tokens.count_folder(str(tmp_path / "data" / "train"), track_ids=[ids["<|begin_text|>"]])
+    first_rows = pq.read_table(info["train"][0]).column("input_ids").to_pylist()
+    assert all(len(r) == 33 for r in first_rows)
+    assert shuffle_shards.shuffle_shards(str(tmp_path / "data" / "train"), rounds=2, group_size=2) == 4
+    after = count_tokens.count_folder(str(tmp_path / "data" / "train"), track_ids=[ids["<|begin_text|>"]])
+    assert after["rows"] == before["rows"] and after["tokens"] == before["tokens"] and after["tracked"] == before["tracked"]
+    assert pq.read_table(info["train"][0]).column("input_ids").to_pylist() != first_rows
+    ds = ParquetStream(str(tmp_path / "data" / "train"), num_processes=1, process_rank=0, broadcast_glob=False,
+                       plan_for_later_rank_expansion_to=0)
+    rows = list(ds)
+    assert len(rows) == after["rows"] and rows[0].shape == (33,)
