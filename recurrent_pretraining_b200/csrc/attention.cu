@@ -328,6 +328,273 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 }
 
 
+// ------------------------------------------------------------------------------------------------ forward, v2
+// Two 128-query tiles (A = even query block 2i, B = odd block 2i+1) per CTA with one softmax warpgroup each, so the
+// tensor pipe works on one tile while the other tile's softmax runs:
+//   warp 8      TMA: Q_A, Q_B once; K_j / V_j through a 2-stage ring (shared by both tiles)
+//   warp 9      MMA: S_X = Q_X K_j^T into TMEM; O_X += P_X V_j with P_X read from TMEM (bf16, written over the first
+//               half of S_X's columns by the softmax warps) and accumulated in TMEM across all key blocks
+//   warps 0-3   softmax of tile A, warps 4-7 softmax of tile B: one row per thread, whole 128-column score row in
+//               registers, single pass; the running max is only raised (and O rescaled in TMEM) when it grew by more
+//               than 2^8, otherwise the stale max is kept -- P then stays below 256 and the final 1/l fixes the scale
+// TMEM columns: S_A [0,128)  S_B [128,256)  O_A [256,256+D)  O_B [384,384+D).
+struct Fwd2Bars {
+  uint64_t q_full;
+  uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
+  uint64_t s_full[2], p_ready[2], o_final[2];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+  constexpr int KSTEPS = D / 16;
+  constexpr uint32_t IDESC_S = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+  constexpr uint32_t IDESC_O = make_idesc_bf16(ATT_BM, D, 0, 1);
+  constexpr int TILE_BYTES = 2 * PANEL_BYTES;
+  constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                     // tile A, tile B
+  uint8_t* sK = sQ + 2 * TILE_BYTES;      // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;      // 2 stages
+  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + 2 * TILE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
+  const int npair = (nqb + 1) / 2;
+  const int pair = npair - 1 - blockIdx.x;  // heavy (late) pairs first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int qbA = 2 * pair, qbB = 2 * pair + 1;
+  const int nA = qbA + 1;                       // key blocks of tile A (block qbA is its diagonal)
+  const int nB = (qbB < nqb) ? qbB + 1 : 0;     // tile B may not exist (odd number of query blocks)
+  const int nmax = max(nA, nB);
+  const int xq = h * D, xk = p.wq + hk * D, xv = p.wq + p.wk + hk * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_ready[i], 4);
+      mbar_init(&bars->o_final[i], 1);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  // warps 0-3: softmax of tile A, 4-7: softmax of tile B, 8: TMA, 9: MMA, 10-11: idle (they complete the third
+  // warpgroup so that it can hand its registers to the softmax warpgroups)
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp == 8) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm);
+      mbar_expect_tx(&bars->q_full, 2 * TILE_BYTES);
+      tma_load_3d(sQ, &tm, &bars->q_full, xq, qbA * ATT_BM, b);
+      tma_load_3d(sQ + PANEL_BYTES, &tm, &bars->q_full, xq + 64, qbA * ATT_BM, b);
+      tma_load_3d(sQ + TILE_BYTES, &tm, &bars->q_full, xq, qbB * ATT_BM, b);   // rows past S read as zero
+      tma_load_3d(sQ + TILE_BYTES + PANEL_BYTES, &tm, &bars->q_full, xq + 64, qbB * ATT_BM, b);
+      int issued = 0;
+      for (int j = 0; j < nmax; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tm, &bars->k_full[s], xk, j * ATT_BN, b);
+        tma_load_3d(sK + s * TILE_BYTES + PANEL_BYTES, &tm, &bars->k_full[s], xk + 64, j * ATT_BN, b);
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) { issued = -(j + 1); break; }
+        mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
+        tma_load_3d(sV + s * TILE_BYTES, &tm, &bars->v_full[s], xv, j * ATT_BN, b);
+        tma_load_3d(sV + s * TILE_BYTES + PANEL_BYTES, &tm, &bars->v_full[s], xv + 64, j * ATT_BN, b);
+        issued = j + 1;
+      }
+      // every issued load must land before the CTA exits (issued < 0: K of block -issued-1 went out without its V)
+      const int k_issued = issued < 0 ? -issued : issued, v_issued = issued < 0 ? -issued - 1 : issued;
+      unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->q_full, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      for (int j = max(0, k_issued - 2); j < k_issued; ++j) {
+        t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->k_full[j & 1], (j >> 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      }
+      for (int j = max(0, v_issued - 2); j < v_issued; ++j) {
+        t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->v_full[j & 1], (j >> 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_s = [&](int x, int j) {  // S_x = Q_x K_j^T
+        const uint32_t kb = aK + (j & 1) * TILE_BYTES, qb = aQ + x * TILE_BYTES;
+#pragma unroll
+        for (int t = 0; t < KSTEPS; ++t) {
+          const uint32_t off = (t >> 2) * PANEL_BYTES + (t & 3) * 32;
+          umma_bf16(tmem_base + x * 128, make_smem_desc(qb + off, 16, 1024), make_smem_desc(kb + off, 16, 1024), IDESC_S,
+                    t ? 1u : 0u);
+        }
+        umma_commit(&bars->s_full[x]);
+      };
+      auto issue_pv = [&](int x, int j) {  // O_x += P_x V_j, P_x in TMEM over the first 64 columns of S_x
+        const uint32_t vb = aV + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int t = 0; t < ATT_BN / 16; ++t)
+          umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + t * 8,
+                       make_smem_desc(vb + t * 2048, PANEL_BYTES, 1024), IDESC_O, (j | t) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, p.err, ERR_WAIT_ATTN) &&
+                mbar_wait(&bars->k_full[0], 0, abort_flag, p.err, ERR_WAIT_ATTN);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        if (nB > 0) issue_s(1, 0);
+        umma_commit(&bars->k_empty[0]);
+      }
+      for (int j = 0; j < nmax && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1, ph1 = ((j + 1) >> 1) & 1;
+        if (!mbar_wait(&bars->v_full[s], ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+        if (j + 1 < nmax && !mbar_wait(&bars->k_full[s ^ 1], ph1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int nx = x ? nB : nA;
+          if (j >= nx) continue;
+          if (!mbar_wait(&bars->p_ready[x], j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(x, j);
+          if (j + 1 < nx) issue_s(x, j + 1);
+          else umma_commit(&bars->o_final[x]);
+        }
+        if (!ok) break;
+        umma_commit(&bars->v_empty[s]);
+        if (j + 1 < nmax) umma_commit(&bars->k_empty[s ^ 1]);
+      }
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int x = warp >> 2;                  // 0: tile A, 1: tile B
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int qb = x ? qbB : qbA;
+    const int nx = x ? nB : nA;
+    const int qrow = qb * ATT_BM + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t ts = tmem_base + x * 128 + lane_addr;          // S_x (and P_x over its first 64 columns)
+    const uint32_t to = tmem_base + 256 + x * 128 + lane_addr;    // O_x
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nx && ok; ++j) {
+      if (!mbar_wait(&bars->s_full[x], j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+      float sv[ATT_BN];
+#pragma unroll
+      for (int c = 0; c < ATT_BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]);
+      }
+      tmem_ld_wait();
+      if (j == qb) {  // diagonal block: keys beyond the query (this also covers keys past the end of the sequence)
+        const int limit = qrow - j * ATT_BN;
+#pragma unroll
+        for (int i = 0; i < ATT_BN; ++i)
+          if (i > limit) sv[i] = -INFINITY;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int i = 1; i < ATT_BN; ++i) mx = fmaxf(mx, sv[i]);
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      // raise the reference max only when it moved by more than the threshold (decided per warp: the TMEM accesses of
+      // the rescale are warp-collective)
+      const bool grow = (m_new - m > RESCALE_THRESHOLD) || (m == -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(to + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(to + c, v);
+          }
+        }
+        l *= alpha;
+        m = m_new;
+      }
+      const float neg_m = -m;
+      float rowsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < ATT_BN; c += 32) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2f(fmaf(sv[c + i], p.scale_log2, neg_m));
+          const float p1 = exp2f(fmaf(sv[c + i + 1], p.scale_log2, neg_m));
+          rowsum += p0 + p1;
+          packed[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(ts + (c >> 1), packed);
+      }
+      l += rowsum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[x]);
+    }
+    if (ok && nx > 0) {
+      if (mbar_wait(&bars->o_final[x], 0, abort_flag, p.err, ERR_WAIT_ATTN)) {
+        tc_fence_after();
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = p.o + (static_cast<size_t>(b) * p.S + qrow) * (p.H * D) + h * D;
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(to + c, v);
+          tmem_ld_wait();
+          if (qrow < p.S) {
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              o[i >> 1] = pack_bf16x2(__uint_as_float(v[i]) * inv_l, __uint_as_float(v[i + 1]) * inv_l);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(orow + c + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          }
+        }
+        if (qrow < p.S && p.lse)
+          p.lse[(static_cast<size_t>(b) * p.H + h) * p.S + qrow] = (m + log2f(l)) * 0.6931471805599453f;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ backward
 struct BwdBars {
   uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_ready, dq_full, dq_empty;
@@ -629,6 +896,29 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStrea
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+template <int D>
+static int launch_attn_fwd2(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * 2 * PANEL_BYTES + 1024 + 1024;  // Q_A, Q_B, 2 x K, 2 x V
+  auto kern = attn_fwd2_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
+  dim3 grid((nqb + 1) / 2, p.H, p.B);
+  kern<<<grid, 384, SMEM, st>>>(tm, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+static int g_attn_fwd_variant = 2;
+// 1: one query tile per CTA, P through shared memory; 2: two query tiles per CTA, P in tensor memory (default).
+B200_API int b200_attn_set_fwd_variant(int v) {
+  const int old = g_attn_fwd_variant;
+  if (v == 1 || v == 2) g_attn_fwd_variant = v;
+  return old;
+}
+
 // qkv: packed rotated [B, S, (H + 2 Hkv) * D] bf16; o: [B, S, H*D] bf16; lse: [B, H, S] fp32 (natural log).
 B200_API int b200_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, int H, int Hkv, int D, float scale,
                            void* stream, int* err) {
@@ -643,6 +933,14 @@ B200_API int b200_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, i
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = reinterpret_cast<__nv_bfloat16*>(o); p.lse = lse; p.err = err;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (g_attn_fwd_variant == 2) {
+    switch (D) {
+      case 64: return launch_attn_fwd2<64>(tm, p, st);
+      case 96: return launch_attn_fwd2<96>(tm, p, st);
+      case 128: return launch_attn_fwd2<128>(tm, p, st);
+      default: return -1;
+    }
+  }
   switch (D) {
     case 64: return launch_attn_fwd<64>(tm, p, st);
     case 96: return launch_attn_fwd<96>(tm, p, st);

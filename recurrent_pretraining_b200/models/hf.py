@@ -280,6 +280,49 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
                                               past_key_values=past_key_values, latent_states=x)
 
     @torch.no_grad()
+    def _prefill_with_varied_exit_steps(self, input_ids, exit_evaluator, past_key_values=None, init_scale: float = 1.0):
+        """Token-by-token "prefill" in which every position iterates until the exit criterion fires (at most
+        ``mean_recurrence`` steps).  Deliberately ignores the parallelism of causal attention: a tool for adaptive
+        compute experiments (recpre/raven_modeling_minimal.py:936-997).  Batch size 1."""
+        assert input_ids.shape[0] == 1, "per-position adaptive depth is defined for a single sequence"
+        if past_key_values is None:
+            past_key_values = RecurrentKVCache(core_layers=self.config.n_layers_in_recurrent_block,
+                                               prelude_layers=self.config.n_layers_in_prelude)
+        rows, compute_steps = [], []
+        for pos in range(input_ids.shape[1]):
+            where = torch.tensor([pos], device=input_ids.device)
+            aux = {"cache_position": where, "past_key_values": past_key_values, "attention_mask": None}
+            e, block_idx = self.embed_inputs(input_ids[:, pos:pos + 1], use_cache=True, **aux)
+            x = self.initialize_state(e, scale=init_scale)
+            exit_evaluator.init(x)
+            taken = 0
+            for step in range(self.config.mean_recurrence):
+                x, block_idx, _ = self.iterate_one_step(e, x, block_idx=block_idx, current_step=step, **aux)
+                taken = step + 1
+                new_exits, _, _ = exit_evaluator.check(self, x, aux)
+                if bool(new_exits.any()):
+                    break
+            compute_steps.append(taken)
+            rows.append(self.predict_from_latents(x, cache_position=where, past_key_values=past_key_values).logits)
+        return torch.cat(rows, dim=1), past_key_values, compute_steps
+
+    @torch.no_grad()
+    def forward_with_adaptive_compute(self, input_ids, exit_evaluator, labels=None, past_key_values=None,
+                                      output_details: dict = _DEFAULT_DETAILS, init_scale: float = 1.0, **kwargs):
+        """Forward pass with a per-position recurrence count chosen by ``exit_evaluator``; ``stats["compute_steps"]``
+        lists the count per position (recpre/raven_modeling_minimal.py:999-1035)."""
+        logits, past_key_values, steps = self._prefill_with_varied_exit_steps(input_ids, exit_evaluator, past_key_values,
+                                                                              init_scale)
+        if labels is not None:
+            loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1))
+            log_ppl = loss.detach().clone()
+        else:
+            loss, log_ppl = torch.as_tensor(0.0), torch.as_tensor(0.0)
+        return CausalLMOutputRecurrentLatents(loss=loss, log_ppl=log_ppl,
+                                              logits=logits if output_details["return_logits"] else None,
+                                              past_key_values=past_key_values, stats={"compute_steps": steps})
+
+    @torch.no_grad()
     def get_stats(self, logits, x, latents, xk, input_embeds, n, k) -> dict:
         probs = torch.softmax(logits.float(), dim=-1)
         return {"entropy": float(-(probs * torch.log(probs + 1e-10)).sum(-1).mean()),

@@ -19,6 +19,15 @@ _bwd = K._sig("b200_attn_bwd", [_vp] * 7 + [_i] * 5 + [_f, _vp, _vp]) if hasattr
 # Measured on the flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.57 ms, native backward 1.73 ms;
 # library (cuDNN) forward 0.18 ms, forward-recompute + backward 1.14 ms.  Until the native kernels win they are opt-in
 # for training (B200_NATIVE_ATTENTION=1); numerics tests always run them.
+_set_variant = K._sig("b200_attn_set_fwd_variant", [_i])
+
+
+def set_fwd_variant(v: int) -> int:
+    """1: one query tile per CTA (P through shared memory); 2: two query tiles per CTA, P in tensor memory (default).
+    Returns the previous setting."""
+    return int(_set_variant(int(v)))
+
+
 ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "0") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
 

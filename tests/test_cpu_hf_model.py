@@ -164,3 +164,22 @@ def test_legacy_model_returns_attention_maps():
     assert set(out.attention_maps) == {0, 1, 2, 3, 4, -1}  # prelude 0, two recurrences of two blocks, coda
     m = out.attention_maps[0]
     assert m.shape == (2, 12, 12) and float(m.triu(1).abs().max()) == 0.0 and float(m[:, 0, 0].min()) == 1.0
+
+
+def test_forward_with_adaptive_compute_per_position():
+    from recurrent_pretraining_b200.models.exit_criteria import KLExitEvaluator, NoOpExitEvaluator
+    from recurrent_pretraining_b200.models.hf import RavenForCausalLM
+    from recurrent_pretraining_b200.models.hf_config import RavenConfig
+
+    torch.manual_seed(0)
+    cfg = RavenConfig(n_embd=64, n_heads=4, n_layers=4, block_size=32, vocab_size=128, intermediate_size=96,
+                      n_layers_in_recurrent_block=2, n_layers_in_prelude=1, n_layers_in_coda=1, mean_recurrence=5)
+    model = RavenForCausalLM(cfg).eval()
+    ids = torch.randint(0, 128, (1, 7))
+    # without an exit every position runs the full depth and the result equals the ordinary (parallel) forward
+    full = model.forward_with_adaptive_compute(ids, NoOpExitEvaluator(), init_scale=0.0)
+    assert full.stats["compute_steps"] == [5] * 7
+    want = model(ids, num_steps=5, init_scale=0.0).logits
+    assert torch.allclose(full.logits, want, atol=2e-4), (full.logits - want).abs().max()
+    out = model.forward_with_adaptive_compute(ids, KLExitEvaluator(model, exit_threshold=1e9), labels=ids)
+    assert out.stats["compute_steps"] == [1] * 7 and torch.isfinite(out.loss)  # the first check already fires

@@ -221,12 +221,17 @@ def _attention_reference(qkv, H, Hkv, D, scale):
 
 @pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
                                          (1, 1024, 2, 2, 96)])
-def test_flash_attention_forward(C, B, S, H, Hkv, D):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_flash_attention_forward(C, B, S, H, Hkv, D, variant):
     from recurrent_pretraining_b200.ops import attention as A
 
     qkv = _packed_qkv(B, S, H, Hkv, D)
     scale = D ** -0.5
-    o, lse = A.fwd(qkv, H, Hkv, D, scale)
+    old = A.set_fwd_variant(variant)
+    try:
+        o, lse = A.fwd(qkv, H, Hkv, D, scale)
+    finally:
+        A.set_fwd_variant(old)
     torch.cuda.synchronize()
     assert C.check_device_status() == 0
     want, (q, k, v) = _attention_reference(qkv, H, Hkv, D, scale)
