@@ -338,6 +338,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 //               registers, single pass; the running max is only raised (and O rescaled in TMEM) when it grew by more
 //               than 2^8, otherwise the stale max is kept -- P then stays below 256 and the final 1/l fixes the scale
 // TMEM columns: S_A [0,128)  S_B [128,256)  O_A [256,256+D)  O_B [384,384+D).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x on the FMA pipe (no MUFU): floor by the 1.5 * 2^23 trick with round-down, cubic for the fractional part, the
+// integer part added into the exponent field.  Relative error about 1e-4, below bf16 resolution.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));
+  const float f = x - (t - 12582912.f);
+  float pl = fmaf(f, 0.077119089663028717f, 0.227564394474029541f);
+  pl = fmaf(pl, f, 0.695146143436431885f);
+  pl = fmaf(pl, f, 1.f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(t) << 23));
+}
+
 struct Fwd2Bars {
   uint64_t q_full;
   uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
@@ -354,6 +372,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   constexpr uint32_t IDESC_O = make_idesc_bf16(ATT_BM, D, 0, 1);
   constexpr int TILE_BYTES = 2 * PANEL_BYTES;
   constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+  constexpr int POLY_PAIRS_OF_4 = 0;        // measured: the softmax warps are issue-bound, the polynomial does not pay
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -498,6 +517,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t ts = tmem_base + x * 128 + lane_addr;          // S_x (and P_x over its first 64 columns)
     const uint32_t to = tmem_base + 256 + x * 128 + lane_addr;    // O_x
+    const float scale_log2 = p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nx && ok; ++j) {
@@ -518,15 +538,21 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         for (int i = 0; i < ATT_BN; ++i)
           if (i > limit) sv[i] = -INFINITY;
       }
-      float mx = sv[0];
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};  // four independent chains
 #pragma unroll
-      for (int i = 1; i < ATT_BN; ++i) mx = fmaxf(mx, sv[i]);
-      const float m_new = fmaxf(m, mx * p.scale_log2);
+      for (int i = 4; i < ATT_BN; i += 4) {
+        mx4[0] = fmaxf(mx4[0], sv[i]);
+        mx4[1] = fmaxf(mx4[1], sv[i + 1]);
+        mx4[2] = fmaxf(mx4[2], sv[i + 2]);
+        mx4[3] = fmaxf(mx4[3], sv[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_new = fmaxf(m, mx * scale_log2);
       // raise the reference max only when it moved by more than the threshold (decided per warp: the TMEM accesses of
       // the rescale are warp-collective)
       const bool grow = (m_new - m > RESCALE_THRESHOLD) || (m == -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
-        const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        const float alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - m_new);
         if (j > 0) {
 #pragma unroll
           for (int c = 0; c < D; c += 32) {
@@ -542,20 +568,23 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         m = m_new;
       }
       const float neg_m = -m;
-      float rowsum = 0.f;
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < ATT_BN; c += 32) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(fmaf(sv[c + i], p.scale_log2, neg_m));
-          const float p1 = exp2f(fmaf(sv[c + i + 1], p.scale_log2, neg_m));
-          rowsum += p0 + p1;
+          const float a0 = fmaf(sv[c + i], scale_log2, neg_m), a1 = fmaf(sv[c + i + 1], scale_log2, neg_m);
+          // POLY_PAIRS_OF_4 pairs in four go through the polynomial (FMA pipe) instead of the MUFU
+          const bool poly = POLY_PAIRS_OF_4 > 0 && ((i >> 1) & 3) < POLY_PAIRS_OF_4;
+          const float p0 = poly ? ex2_poly(a0) : ex2_approx(a0);
+          const float p1 = poly ? ex2_poly(a1) : ex2_approx(a1);
+          rs[(i >> 1) & 3] += p0 + p1;
           packed[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st_32x16(ts + (c >> 1), packed);
       }
-      l += rowsum;
+      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
