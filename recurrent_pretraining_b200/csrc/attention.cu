@@ -26,8 +26,18 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // 3-D bf16 tensor map {d0 (contiguous), d1, d2} with byte strides for d1 and d2; box {box0, box1, 1}, 128B swizzle.
+static int make_tmap_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
+                        CUtensorMapDataType dtype);
 static int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                              uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+  return make_tmap_3d(out, base, d0, d1, d2, stride1_bytes, stride2_bytes, box0, box1,
+                      CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+}
+// 3-D tensor map {d0 (contiguous), d1, d2}; box {box0, box1, 1}; 128-byte swizzle (box0 * element size must be 128).
+static int make_tmap_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
+                        CUtensorMapDataType dtype) {
   static EncodeTiledFn3 enc = nullptr;
   if (!enc) {
     void* ptr = nullptr;
@@ -42,7 +52,7 @@ static int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, ui
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(out, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
@@ -660,7 +670,7 @@ __device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int r, int 
 template <int D>
 __global__ void __launch_bounds__(192, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
   constexpr int KSTEPS_D = D / 16;
   constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T, dP = dO V^T
   constexpr uint32_t IDESC_TT = make_idesc_bf16(128, D, 1, 1);     // dV += P^T dO, dK += dS^T Q
@@ -785,8 +795,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const bool elected = (warp == 2 && lane == 0);   // issues the bulk reductions of dQ
+    uint8_t* stage = sP;                             // dQ staging (fp32, D/32 boxes of 16 KB) over the P and dS tiles
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
+    // The four warps meet at named barrier 1 twice per iteration; nobody leaves the loop between two meetings on a
+    // private decision: a failed wait raises the CTA abort flag, which everyone reads right after the barrier.
+    for (int it = 0; it < n_it; ++it) {
       const uint32_t ph = it & 1;
       const int h = hk * rep + it / per_head;
       const int qb = kvb + it % per_head;
@@ -795,7 +809,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       const size_t stat = (static_cast<size_t>(b) * p.H + h) * p.S + qrow;
       const float lse2 = row_ok ? p.lse[stat] * 1.4426950408889634f : 0.f;
       const float delta = row_ok ? p.delta[stat] : 0.f;
-      if (!mbar_wait(&bars->sdp_full, ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      ok = mbar_wait(&bars->sdp_full, ph, abort_flag, p.err, ERR_WAIT_ATTN);
+      if (elected) bulk_wait_read_all();             // the previous dQ tile has left the staging area
+      named_barrier_sync(1, 128);
+      if (*abort_flag) { ok = false; break; }
       tc_fence_after();
       const bool diag = (qb == kvb);
 #pragma unroll 1
@@ -822,25 +839,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->pds_ready);
-      if (!mbar_wait(&bars->dq_full, ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
-      tc_fence_after();
-      float* dq_row = p.dq_acc + (static_cast<size_t>(b) * p.S + qrow) * (p.H * D) + h * D;
+      ok = mbar_wait(&bars->dq_full, ph, abort_flag, p.err, ERR_WAIT_ATTN);
+      if (ok) {
+        // dQ tile: TMEM -> fp32 staging in shared memory (128-byte swizzle, boxes of 32 columns), then ONE bulk
+        // tensor reduction per box adds it to the global accumulator (rows past the sequence end are clipped)
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D; c += 16) {
-        uint32_t v[16];
-        tmem_ld_32x16(tmem_base + COL_S + lane_addr + c, v);
-        tmem_ld_wait();
-        if (row_ok) {
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + COL_S + lane_addr + c, v);
+          tmem_ld_wait();
+          uint8_t* row = stage + (c >> 5) * PANEL_BYTES + r * 128;
 #pragma unroll
-          for (int i = 0; i < 16; i += 4)
-            red_add_v4(dq_row + c + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                       __uint_as_float(v[i + 3]));
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(row + ((q ^ (r & 7)) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
+        tc_fence_before();
+        fence_proxy_async_smem();
       }
-      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->dq_empty);
+      named_barrier_sync(1, 128);
+      if (*abort_flag) { ok = false; break; }
+      if (elected) {
+#pragma unroll
+        for (int c = 0; c < D; c += 32)
+          tma_reduce_add_3d(&tmDQ, stage + (c >> 5) * PANEL_BYTES, h * D + c, qb * ATT_BM, b);
+        bulk_commit_group();
+      }
     }
+    if (elected) bulk_wait_all();
     if (ok && n_it > 0) {
       // all MMAs are complete (the last dq_full was waited on): write dV and scale * dK for this key block
       const int key = k0 + r;
@@ -980,7 +1008,8 @@ B200_API int b200_attn_fwd(const void* qkv, void* o, float* lse, int B, int S, i
 
 
 template <int D>
-static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t st) {
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdParams& p,
+                           cudaStream_t st) {
   constexpr int SMEM = 6 * 2 * PANEL_BYTES + 1024 + 1024;  // K, V, Q, dO, P, dS tiles
   auto kern = attn_bwd_kernel<D>;
   static bool configured = false;
@@ -989,7 +1018,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
     configured = true;
   }
   dim3 grid((p.S + ATT_BN - 1) / ATT_BN, p.Hkv, p.B);
-  kern<<<grid, 192, SMEM, st>>>(tq, tdo, p);
+  kern<<<grid, 192, SMEM, st>>>(tq, tdo, tdq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -1007,6 +1036,10 @@ B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, cons
   if (rc) return rc;
   rc = make_tmap_3d_bf16(&tdo, d_o, wq, S, B, static_cast<uint64_t>(wq) * 2, static_cast<uint64_t>(S) * wq * 2, 64, 128);
   if (rc) return rc;
+  CUtensorMap tdq;  // fp32 accumulator [B, S, H*D], boxes of 32 columns x 128 rows
+  rc = make_tmap_3d(&tdq, dq_acc, wq, S, B, static_cast<uint64_t>(wq) * 4, static_cast<uint64_t>(S) * wq * 4, 32, 128,
+                    CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+  if (rc) return rc;
   const size_t warps = static_cast<size_t>(B) * S * H;
   attn_delta_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
@@ -1015,9 +1048,9 @@ B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, cons
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.err = err;
   switch (D) {
-    case 64: rc = launch_attn_bwd<64>(tq, tdo, p, st); break;
-    case 96: rc = launch_attn_bwd<96>(tq, tdo, p, st); break;
-    case 128: rc = launch_attn_bwd<128>(tq, tdo, p, st); break;
+    case 64: rc = launch_attn_bwd<64>(tq, tdo, tdq, p, st); break;
+    case 96: rc = launch_attn_bwd<96>(tq, tdo, tdq, p, st); break;
+    case 128: rc = launch_attn_bwd<128>(tq, tdo, tdq, p, st); break;
     default: return -1;
   }
   if (rc) return rc;

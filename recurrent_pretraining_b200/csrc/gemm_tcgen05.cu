@@ -313,8 +313,10 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   GemmParams p;
   p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
-  if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240) && out_mode != OUT_SWIGLU) {
-    const int rc2 = gemm_2cta_dispatch(A, A2, B, p, lda, lda2, ldb, a_mn, b_mn, out_mode, bn, max_ctas, st);
+  if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240 || (out_mode == OUT_SWIGLU && !a_mn && !b_mn))) {
+    // SwiGLU on the pair kernel: a 256-wide MMA tile = 128 gate columns (CTA 0's half of B) + 128 up columns (CTA 1's)
+    const int bn2 = (out_mode == OUT_SWIGLU) ? 256 : bn;
+    const int rc2 = gemm_2cta_dispatch(A, A2, B, p, lda, lda2, ldb, a_mn, b_mn, out_mode, bn2, max_ctas, st);
     if (rc2 != -100) return rc2;
   }
   CUtensorMap ta, ta2, tb;

@@ -99,7 +99,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   constexpr int ACC_STRIDE = 256;
   constexpr int BNH = BN / 2;
   constexpr uint32_t IDESC = make_idesc_bf16(2 * BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-  static_assert(MODE != OUT_SWIGLU, "SwiGLU epilogue is provided by the 1-CTA kernel");
+  // SwiGLU: the pair's 256 accumulator columns are [128 gate | 128 up] of the same 128 output columns; CTA 0 stages
+  // the gate rows of B, CTA 1 the up rows (p.swiglu_n rows further down), and p.N is the OUTPUT width.
+  constexpr int BN_OUT = (MODE == OUT_SWIGLU) ? BN / 2 : BN;
+  static_assert(MODE != OUT_SWIGLU || (BN == 256 && !A_MN && !B_MN), "SwiGLU epilogue: NT GEMM with 256-wide MMA tiles");
   static_assert(!B_MN || (BNH % 64 == 0), "MN-major B needs 64-column chunks per CTA");
 
   extern __shared__ uint8_t smem_raw[];
@@ -120,7 +123,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int num_clusters = gridDim.x >> 1;
 
   const int tiles_m = (p.M + 2 * BM2 - 1) / (2 * BM2);
-  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_n = (p.N + BN_OUT - 1) / BN_OUT;
   const int num_tiles = tiles_m * tiles_n;
   const int nk1 = (p.K1 + BK2 - 1) / BK2;
   const int nk2 = (p.K2 + BK2 - 1) / BK2;
@@ -159,7 +162,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-        const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * BNH;
+        const int n0 = (MODE == OUT_SWIGLU) ? (tile / tiles_m) * BN_OUT + static_cast<int>(rank) * p.swiglu_n
+                                            : (tile / tiles_m) * BN + static_cast<int>(rank) * BNH;
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -232,11 +236,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-      const int n0 = (tile / tiles_m) * BN;
+      const int n0 = (tile / tiles_m) * BN_OUT;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_tile<BN, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
@@ -270,7 +274,8 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
     max_clusters = n;
   }
-  const int tiles = ((p.M + 2 * BM2 - 1) / (2 * BM2)) * ((p.N + BN - 1) / BN);
+  constexpr int BN_OUT = (MODE == OUT_SWIGLU) ? BN / 2 : BN;
+  const int tiles = ((p.M + 2 * BM2 - 1) / (2 * BM2)) * ((p.N + BN_OUT - 1) / BN_OUT);
   int clusters = tiles < max_clusters ? tiles : max_clusters;
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2;
   if (clusters <= 0) return 0;
@@ -281,7 +286,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
 // Entry used by b200_gemm: returns -100 when the 2-CTA kernel does not cover the request.
 int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,
                        int a_mn, int b_mn, int out_mode, int bn, int max_ctas, cudaStream_t st) {
-  if (out_mode == OUT_SWIGLU) return -100;
+  if (out_mode == OUT_SWIGLU && (a_mn || b_mn || bn != 256 || p.K2 > 0)) return -100;
   if (bn == 240 && b_mn) return -100;
   if (bn != 256 && bn != 240) return -100;
   const int K = p.K1 + p.K2;
@@ -295,7 +300,8 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     rc = make_tmap_2d_bf16(&ta2, A2, p.M, p.K2, lda2, BM2, BK2);
     if (rc) return rc;
   }
-  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, p.N, K, ldb, bn / 2, BK2);
+  const int brows = (out_mode == OUT_SWIGLU) ? 2 * p.N : p.N;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, brows, K, ldb, bn / 2, BK2);
   else rc = make_tmap_2d_bf16(&tb, B, K, p.N, ldb, BK2, 64);
   if (rc) return rc;
 
@@ -307,6 +313,7 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     case OUT_BF16_RESID: return launch2<BN_, AMN_, BMN_, OUT_BF16_RESID>(ta, ta2, tb, p, st, max_ctas); \
     default: return -100;                                                                           \
   }
+  if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
   if (!a_mn && !b_mn) {
     if (bn == 256) { DISPATCH2(256, false, false) }
     if (bn == 240) { DISPATCH2(240, false, false) }

@@ -14,7 +14,11 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+import os
+
 from ..ops import functional as ops
+
+FUSE_SWIGLU = os.environ.get("B200_FUSE_SWIGLU", "1") == "1"
 
 
 # ------------------------------------------------------------------------------------------
@@ -235,6 +239,8 @@ class GatedMLP(nn.Module):
         self.nonlin = make_nonlin(config.nonlin_name)
 
     def forward(self, x):
+        if self.is_silu and self.fc.bias is None and x.is_cuda and not torch.is_grad_enabled() and FUSE_SWIGLU:
+            return self.proj(ops.linear_swiglu(x, self.fc.weight))  # gate applied in the GEMM epilogue
         h = self.fc(x)
         if self.is_silu:
             return self.proj(ops.swiglu(h))

@@ -113,11 +113,37 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
         B, S, E = x.shape
         cos, sin = rope
         qkv = attn.Wqkv(x)
+        if x.is_cuda and x.dtype == torch.bfloat16 and S > 1 and not torch.is_grad_enabled():
+            y = self._native_prefill_attention(attn, qkv, cos, sin, step_idx, cache)
+            if y is not None:
+                return attn.proj(y)
         q, k, v = ops.qk_bias_rope(qkv, attn.qk_bias, cos, sin, attn.n_head, attn.n_kv, attn.head_dim)
         if cache is not None:
             k, v = cache.update(k, v, step_idx)
         y = ops.causal_attention(q, k, v, None, k.shape[1] - q.shape[1])
         return attn.proj(y.reshape(B, S, E))
+
+    def _native_prefill_attention(self, attn, qkv, cos, sin, step_idx: int, cache):
+        """First chunk of a sequence on a GPU: fused bias+RoPE kernel on the packed qkv, KV-cache append from views of
+        the rotated tensor, native causal attention on the packed tensor.  Returns None when the chunk has history."""
+        from ..ops import attention as A
+        from ..ops import cuda as K
+
+        H, Hkv, D = attn.n_head, attn.n_kv, attn.head_dim
+        if not A.native_prefill_supported(D):
+            return None
+        if cache is not None:
+            # the token counter advances when step 0 is written, so later steps of the same chunk already include it
+            seen = cache.get_seq_length(step_idx)
+            if seen != (0 if step_idx == 0 else qkv.shape[1]):
+                return None
+        B, S, _ = qkv.shape
+        qkv_r = K.rope_fwd(qkv.contiguous(), attn.qk_bias, cos.float().contiguous(), sin.float().contiguous(), H, Hkv, D)
+        if cache is not None:
+            wq, wk = H * D, Hkv * D
+            cache.update(qkv_r[..., wq:wq + wk].view(B, S, Hkv, D), qkv_r[..., wq + wk:].view(B, S, Hkv, D), step_idx)
+        y, _ = A.fwd(qkv_r, H, Hkv, D, D ** -0.5)
+        return y
 
     def _block(self, block, x, rope, step_idx: int, cache):
         name = type(block).__name__

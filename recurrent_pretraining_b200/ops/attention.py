@@ -32,6 +32,15 @@ ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "0") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
 
 
+PREFILL = os.environ.get("B200_NATIVE_PREFILL", "1") == "1"
+
+
+def native_prefill_supported(head_dim: int) -> bool:
+    """Inference prefill (fresh sequence, forward only) runs on the native kernel: no library call sits between the
+    decode engine and its KV cache."""
+    return PREFILL and head_dim in (64, 96, 128)
+
+
 def native_supported(head_dim: int, seq_len: int) -> bool:
     return ENABLED and head_dim in (64, 96, 128)
 

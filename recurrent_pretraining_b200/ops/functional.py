@@ -87,6 +87,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return ref.linear(x, weight)
 
 
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] in ONE GEMM whose epilogue applies the gate (forward only: the
+    pre-activation is never written, so this is for no-grad passes such as the untracked recurrences and inference)."""
+    assert not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad))
+    if x.is_cuda:
+        C = cuda_backend()
+        x2 = x.reshape(-1, x.shape[-1])
+        y = C.gemm(x2, _lp(weight), out_mode=C.OUT_SWIGLU)
+        return y.view(*x.shape[:-1], weight.shape[0] // 2)
+    return ref.swiglu(ref.linear(x, weight))
+
+
 class _Adapter(torch.autograd.Function):
     """y = x Ws^T + e We^T with W = [Ws | We] (no concatenation is materialised)."""
 

@@ -34,7 +34,8 @@ def time_fn(fn, reps=10, warmup=3, flush=None):
     return statistics.median(ts)
 
 
-def bench_gemm(M=4096):
+def bench_gemm(M=4096, only=None):
+    """``only``: run a single named shape (for profiler captures of one kernel)."""
     from ..ops import cuda as C
 
     E, I, V = 5280, 17920, 65536
@@ -43,6 +44,8 @@ def bench_gemm(M=4096):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     rows = []
     for name, N, K in shapes:
+        if only and name != only:
+            continue
         x = torch.randn(M, K, device="cuda").bfloat16()
         w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
         dy = torch.randn(M, N, device="cuda").bfloat16()
@@ -87,6 +90,21 @@ def bench_norm(M=4096, E=5280):
     print(json.dumps({"kernel": "rmsnorm_bwd", "ms": round(t, 3), "GBps": round(3 * x.numel() * 2 / t / 1e6, 1)}))
 
 
+def bench_swiglu(M=4096, E=5280, I=17920):
+    """Gate-up GEMM + SwiGLU: one GEMM with the gate in its epilogue against GEMM followed by the elementwise kernel."""
+    from ..ops import cuda as C
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    x = torch.randn(M, E, device="cuda").bfloat16()
+    w = (torch.randn(2 * I, E, device="cuda") * 0.02).bfloat16()
+    t_fused = time_fn(lambda: C.gemm(x, w, out_mode=C.OUT_SWIGLU), flush=flush)
+    t_pair = time_fn(lambda: C.swiglu_fwd(C.gemm_nt(x, w)), flush=flush)
+    fl = 2.0 * M * 2 * I * E
+    print(json.dumps({"kernel": "gate-up GEMM + SwiGLU", "fused_ms": round(t_fused, 3),
+                      "fused_tflops": round(fl / t_fused / 1e9, 1), "gemm_then_swiglu_ms": round(t_pair, 3)}))
+    assert C.check_device_status() == 0
+
+
 def bench_attn(B=1, S=4096, H=55, D=96):
     """Native tcgen05 attention forward / backward against the library path (SDPA) on the flagship shape."""
     from ..ops import attention as A
@@ -112,7 +130,9 @@ def bench_attn(B=1, S=4096, H=55, D=96):
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     if what in ("gemm", "all"):
-        bench_gemm()
+        bench_gemm(only=sys.argv[2] if len(sys.argv) > 2 else None)
+    if what in ("swiglu", "all"):
+        bench_swiglu()
     if what in ("norm", "all"):
         bench_norm()
     if what in ("attn", "all"):

@@ -57,7 +57,7 @@ def test_param_groups_and_registry():
         opt = get_optimizer(name)(get_param_groups(model.named_parameters()), lr=1e-3)
         assert hasattr(opt, "step")
     with pytest.raises(ValueError):
-        get_optimizer("Lilith")
+        get_optimizer("meta-shampoo")
 
 
 def test_fused_engine_equals_torch_engine_on_cpu_and_skips_first_step():
