@@ -366,9 +366,44 @@ __device__ __forceinline__ float ex2_poly(float x) {
   return __int_as_float(__float_as_int(pl) + (__float_as_int(t) << 23));
 }
 
+// three-input max and packed two-wide fp32 arithmetic (sm_100): half the issue slots of the scalar forms
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n"
+      "  .reg .b64 ra, rb, rc, rd;\n"
+      "  mov.b64 ra, {%2, %3};\n"
+      "  mov.b64 rb, {%4, %5};\n"
+      "  mov.b64 rc, {%6, %7};\n"
+      "  fma.rn.f32x2 rd, ra, rb, rc;\n"
+      "  mov.b64 {%0, %1}, rd;\n"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n"
+      "  .reg .b64 ra, rb, rd;\n"
+      "  mov.b64 ra, {%2, %3};\n"
+      "  mov.b64 rb, {%4, %5};\n"
+      "  add.rn.f32x2 rd, ra, rb;\n"
+      "  mov.b64 {%0, %1}, rd;\n"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+constexpr int FWD2_VSTAGES = 3;  // V is needed one step later than K is released: a third stage hides the load latency
 struct Fwd2Bars {
   uint64_t q_full;
-  uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
+  uint64_t k_full[2], k_empty[2], v_full[FWD2_VSTAGES], v_empty[FWD2_VSTAGES];
   uint64_t s_full[2], p_ready[2], o_final[2];
   uint32_t tmem_slot;
   int abort_flag;
@@ -388,8 +423,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                     // tile A, tile B
   uint8_t* sK = sQ + 2 * TILE_BYTES;      // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;      // 2 stages
-  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + 2 * TILE_BYTES);
+  uint8_t* sV = sK + 2 * TILE_BYTES;      // FWD2_VSTAGES stages
+  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + FWD2_VSTAGES * TILE_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -406,11 +441,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < FWD2_VSTAGES; ++i) {
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1);
-      mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->k_empty[i], 1);
-      mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->p_ready[i], 4);
       mbar_init(&bars->o_final[i], 1);
@@ -433,6 +470,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 8) {
+    // lane 0 feeds Q and the K ring, lane 1 the V ring: a stall of one ring does not delay requests of the other
     if (lane == 0) {
       tma_prefetch_desc(&tm);
       mbar_expect_tx(&bars->q_full, 2 * TILE_BYTES);
@@ -448,23 +486,30 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
         tma_load_3d(sK + s * TILE_BYTES, &tm, &bars->k_full[s], xk, j * ATT_BN, b);
         tma_load_3d(sK + s * TILE_BYTES + PANEL_BYTES, &tm, &bars->k_full[s], xk + 64, j * ATT_BN, b);
-        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) { issued = -(j + 1); break; }
+        issued = j + 1;
+      }
+      // every issued load must land before the CTA exits
+      unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->q_full, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      for (int j = max(0, issued - 2); j < issued; ++j) {
+        t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->k_full[j & 1], (j >> 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      }
+    } else if (lane == 1) {
+      int issued = 0;
+      for (int j = 0; j < nmax; ++j) {
+        const int s = j % FWD2_VSTAGES;
+        const uint32_t ph = (j / FWD2_VSTAGES) & 1;
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
         mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
         tma_load_3d(sV + s * TILE_BYTES, &tm, &bars->v_full[s], xv, j * ATT_BN, b);
         tma_load_3d(sV + s * TILE_BYTES + PANEL_BYTES, &tm, &bars->v_full[s], xv + 64, j * ATT_BN, b);
         issued = j + 1;
       }
-      // every issued load must land before the CTA exits (issued < 0: K of block -issued-1 went out without its V)
-      const int k_issued = issued < 0 ? -issued : issued, v_issued = issued < 0 ? -issued - 1 : issued;
-      unsigned long long t0 = globaltimer_ns();
-      while (!mbar_try_wait(&bars->q_full, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
-      for (int j = max(0, k_issued - 2); j < k_issued; ++j) {
-        t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bars->k_full[j & 1], (j >> 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
-      }
-      for (int j = max(0, v_issued - 2); j < v_issued; ++j) {
-        t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bars->v_full[j & 1], (j >> 1) & 1) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      for (int j = max(0, issued - FWD2_VSTAGES); j < issued; ++j) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->v_full[j % FWD2_VSTAGES], (j / FWD2_VSTAGES) & 1) &&
+               globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
       }
     }
   } else if (warp == 9) {
@@ -481,7 +526,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         umma_commit(&bars->s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {  // O_x += P_x V_j, P_x in TMEM over the first 64 columns of S_x
-        const uint32_t vb = aV + (j & 1) * TILE_BYTES;
+        const uint32_t vb = aV + (j % FWD2_VSTAGES) * TILE_BYTES;
 #pragma unroll
         for (int t = 0; t < ATT_BN / 16; ++t)
           umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + t * 8,
@@ -496,9 +541,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         umma_commit(&bars->k_empty[0]);
       }
       for (int j = 0; j < nmax && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1, ph1 = ((j + 1) >> 1) & 1;
-        if (!mbar_wait(&bars->v_full[s], ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+        const int s = j & 1, sv3 = j % FWD2_VSTAGES;
+        const uint32_t ph1 = ((j + 1) >> 1) & 1;
+        if (!mbar_wait(&bars->v_full[sv3], (j / FWD2_VSTAGES) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
         if (j + 1 < nmax && !mbar_wait(&bars->k_full[s ^ 1], ph1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -511,7 +556,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
           else umma_commit(&bars->o_final[x]);
         }
         if (!ok) break;
-        umma_commit(&bars->v_empty[s]);
+        umma_commit(&bars->v_empty[sv3]);
         if (j + 1 < nmax) umma_commit(&bars->k_empty[s ^ 1]);
       }
     }
@@ -548,14 +593,16 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         for (int i = 0; i < ATT_BN; ++i)
           if (i > limit) sv[i] = -INFINITY;
       }
-      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};  // four independent chains
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};  // four independent chains of three-input max
 #pragma unroll
-      for (int i = 4; i < ATT_BN; i += 4) {
-        mx4[0] = fmaxf(mx4[0], sv[i]);
-        mx4[1] = fmaxf(mx4[1], sv[i + 1]);
-        mx4[2] = fmaxf(mx4[2], sv[i + 2]);
-        mx4[3] = fmaxf(mx4[3], sv[i + 3]);
+      for (int i = 4; i + 7 < ATT_BN; i += 8) {
+        mx4[0] = fmax3(mx4[0], sv[i], sv[i + 1]);
+        mx4[1] = fmax3(mx4[1], sv[i + 2], sv[i + 3]);
+        mx4[2] = fmax3(mx4[2], sv[i + 4], sv[i + 5]);
+        mx4[3] = fmax3(mx4[3], sv[i + 6], sv[i + 7]);
       }
+      mx4[0] = fmax3(mx4[0], sv[ATT_BN - 4], sv[ATT_BN - 3]);
+      mx4[1] = fmax3(mx4[1], sv[ATT_BN - 2], sv[ATT_BN - 1]);
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m, mx * scale_log2);
       // raise the reference max only when it moved by more than the threshold (decided per warp: the TMEM accesses of
@@ -577,24 +624,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         l *= alpha;
         m = m_new;
       }
-      const float neg_m = -m;
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      const float2 neg_m2 = make_float2(-m, -m), scale2 = make_float2(scale_log2, scale_log2);
+      float2 rs[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int c = 0; c < ATT_BN; c += 32) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float a0 = fmaf(sv[c + i], scale_log2, neg_m), a1 = fmaf(sv[c + i + 1], scale_log2, neg_m);
+          const float2 a = ffma2(make_float2(sv[c + i], sv[c + i + 1]), scale2, neg_m2);
           // POLY_PAIRS_OF_4 pairs in four go through the polynomial (FMA pipe) instead of the MUFU
           const bool poly = POLY_PAIRS_OF_4 > 0 && ((i >> 1) & 3) < POLY_PAIRS_OF_4;
-          const float p0 = poly ? ex2_poly(a0) : ex2_approx(a0);
-          const float p1 = poly ? ex2_poly(a1) : ex2_approx(a1);
-          rs[(i >> 1) & 3] += p0 + p1;
-          packed[i >> 1] = pack_bf16x2(p0, p1);
+          const float2 pr = make_float2(poly ? ex2_poly(a.x) : ex2_approx(a.x), poly ? ex2_poly(a.y) : ex2_approx(a.y));
+          rs[(i >> 1) & 3] = fadd2(rs[(i >> 1) & 3], pr);
+          packed[i >> 1] = pack_bf16x2(pr.x, pr.y);
         }
         tmem_st_32x16(ts + (c >> 1), packed);
       }
-      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      {
+        const float2 t = fadd2(fadd2(rs[0], rs[1]), fadd2(rs[2], rs[3]));
+        l += t.x + t.y;
+      }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -955,7 +1004,7 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStrea
 
 template <int D>
 static int launch_attn_fwd2(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
-  constexpr int SMEM = 6 * 2 * PANEL_BYTES + 1024 + 1024;  // Q_A, Q_B, 2 x K, 2 x V
+  constexpr int SMEM = (4 + FWD2_VSTAGES) * 2 * PANEL_BYTES + 1024 + 512;  // Q_A, Q_B, 2 x K, 3 x V, barriers
   auto kern = attn_fwd2_kernel<D>;
   static bool configured = false;
   if (!configured) {
