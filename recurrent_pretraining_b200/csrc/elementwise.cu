@@ -159,6 +159,102 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Two-kernel form of the backward (used for large M): dx with one CTA per row (many rows in flight per SM), and the
+// weight gradient as a column reduction of dy * bf16(x * rstd) over row chunks; the second pass reads x and dy again,
+// normally from L2.
+template <int MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ w, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                      int E) {
+  __shared__ float red[32];
+  const int nvec = E >> 3;
+  const size_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * E);
+  const uint4* dr = reinterpret_cast<const uint4*>(dy + row * E);
+  const float rstd = rstd_in[row];
+  uint4 xq[MAXV], dq[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      xq[i] = xr[v];
+      dq[i] = dr[v];
+    }
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      const uint32_t qs[4] = {xq[i].x, xq[i].y, xq[i].z, xq[i].w}, ds[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w};
+      float wv[8];
+      if (w) {
+        const float4 wa = reinterpret_cast<const float4*>(w)[2 * v], wb = reinterpret_cast<const float4*>(w)[2 * v + 1];
+        wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[j] = 1.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = unpack_bf16x2(qs[j]), df = unpack_bf16x2(ds[j]);
+        dot += df.x * wv[2 * j] * (xf.x * rstd) + df.y * wv[2 * j + 1] * (xf.y * rstd);
+      }
+    }
+  }
+  const float mean = block_sum(dot, red) / static_cast<float>(E);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      const uint32_t qs[4] = {xq[i].x, xq[i].y, xq[i].z, xq[i].w}, ds[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w};
+      float wv[8];
+      if (w) {
+        const float4 wa = reinterpret_cast<const float4*>(w)[2 * v], wb = reinterpret_cast<const float4*>(w)[2 * v + 1];
+        wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[j] = 1.f;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = unpack_bf16x2(qs[j]), df = unpack_bf16x2(ds[j]);
+        o[j] = pack_bf16x2(rstd * (df.x * wv[2 * j] - xf.x * rstd * mean),
+                           rstd * (df.y * wv[2 * j + 1] - xf.y * rstd * mean));
+      }
+      reinterpret_cast<uint4*>(dx + row * E)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// partial[chunk, c] = sum over the rows of the chunk of dy[r, c] * bf16(x[r, c] * rstd[r]); 8 columns per thread.
+__global__ void __launch_bounds__(128)
+rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ rstd_in, float* __restrict__ partial, int M, int E, int rows_per) {
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= (E >> 3)) return;
+  const int r0 = blockIdx.y * rows_per, r1 = min(r0 + rows_per, M);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int r = r0; r < r1; ++r) {
+    const uint4 xq = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * E)[v];
+    const uint4 dq = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(r) * E)[v];
+    const float rstd = rstd_in[r];
+    const uint32_t qs[4] = {xq.x, xq.y, xq.z, xq.w}, ds[4] = {dq.x, dq.y, dq.z, dq.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 xf = unpack_bf16x2(qs[j]), df = unpack_bf16x2(ds[j]);
+      acc[2 * j] += df.x * bf2f(f2bf(xf.x * rstd));   // the forward rounded xhat to bf16 before the weight multiply
+      acc[2 * j + 1] += df.y * bf2f(f2bf(xf.y * rstd));
+    }
+  }
+  float* dst = partial + static_cast<size_t>(blockIdx.y) * E + v * 8;
+  reinterpret_cast<float4*>(dst)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  reinterpret_cast<float4*>(dst)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
 // out[c] = sum_r in[r, c]
 __global__ void colsum_kernel(const float* __restrict__ in, float* __restrict__ out, int R, int C) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -382,6 +478,18 @@ B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const float* w, con
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
   float* part = dw ? dw_partial : nullptr;
+  if (M >= 1024) {
+    // large M: the split form (dx with a CTA per row, dw as a chunked column reduction)
+    NORM_DISPATCH(E, (rmsnorm_bwd_dx_kernel<MAXV><<<M, NORM_THREADS, 0, st>>>(dyb, xb, w, rstd, dxb, E));)
+    if (dw) {
+      const int chunks = grid < 128 ? grid : 128;   // dw_partial holds `grid` rows
+      const int rows_per = (M + chunks - 1) / chunks;
+      dim3 g(blocks_for(E >> 3, 128), chunks);
+      rmsnorm_bwd_dw_kernel<<<g, 128, 0, st>>>(dyb, xb, rstd, dw_partial, M, E, rows_per);
+      colsum_kernel<<<blocks_for(E, 128), 128, 0, st>>>(dw_partial, dw, chunks, E);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   NORM_DISPATCH(E, (rmsnorm_bwd_kernel<MAXV><<<grid, NORM_THREADS, 0, st>>>(dyb, xb, w, rstd, dxb, part, M, E));)
   if (dw) colsum_kernel<<<blocks_for(E, 128), 128, 0, st>>>(dw_partial, dw, grid, E);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

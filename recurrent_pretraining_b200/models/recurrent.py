@@ -15,6 +15,7 @@ cross-entropy op, which never materialises the [tokens, vocab] logits unless ``r
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -25,6 +26,9 @@ from ..ops import functional as ops
 from ..ops import reference as ref
 from .blocks import Linear, make_block, make_mlp, make_norm
 from .sampler import sample_recurrence
+
+# e We^T (the input half of the linear adapter) is the same in every recurrence: compute it once per forward pass
+HOIST_ADAPTER = os.environ.get("B200_HOIST_ADAPTER", "1") == "1"
 
 
 def _rank() -> int:
@@ -150,9 +154,9 @@ class RecurrentGPT(_LMBase):
         n, k = self.sample_depths()
         return torch.as_tensor(n, dtype=torch.long), torch.as_tensor(k, dtype=torch.long)
 
-    def core_block_forward(self, x, e, rope, mask, step: int):
+    def core_block_forward(self, x, e, rope, mask, step: int, inj=None):
         c = self.config
-        inj = c.injection_type
+        inj_e, inj = inj, c.injection_type
         context = None
         if getattr(c, "embed_step", False):
             context = self.step_embedding(torch.as_tensor([step], device=e.device)).to(x.dtype)
@@ -162,6 +166,8 @@ class RecurrentGPT(_LMBase):
             x = x + e
         elif inj == "gate":
             x = x * e
+        elif inj == "linear" and inj_e is not None:
+            x = ops.adapter_state(x, inj_e, self.transformer.adapter.weight)   # e We^T was hoisted out of the loop
         elif inj == "linear":
             x = ops.adapter(x, e, self.transformer.adapter.weight)
             if self.transformer.adapter.bias is not None:
@@ -205,26 +211,36 @@ class RecurrentGPT(_LMBase):
             n, k = (pair[0], pair[1]) if len(pair) > 1 else (pair[0], 0)
         self.last_depths = (n, k)
         xk = x
+        inj = None
+        if (HOIST_ADAPTER and self.config.injection_type == "linear" and e.is_cuda and n + k > 1
+                and self.transformer.adapter.bias is None and x.dtype == e.dtype):
+            inj = ops.adapter_inject(e, self.transformer.adapter.weight)
         with torch.no_grad():
             for step in range(n):
                 xk = x
-                x = self.core_block_forward(x, e, rope, mask, step)
+                x = self.core_block_forward(x, e, rope, mask, step, inj)
         per_iter = self.gradient_checkpointing and "per-iteration" in self.config.activation_checkpoint_impl
         for step in range(k):
             xk = x
             if per_iter and torch.is_grad_enabled():
-                x = torch.utils.checkpoint.checkpoint(self.core_block_forward, x, e, rope, mask, n + step,
+                x = torch.utils.checkpoint.checkpoint(self.core_block_forward, x, e, rope, mask, n + step, inj,
                                                       use_reentrant=False)
             else:
-                x = self.core_block_forward(x, e, rope, mask, n + step)
+                x = self.core_block_forward(x, e, rope, mask, n + step, inj)
         return self.transformer.ln_f(x), n, k, xk.detach()
+
+    def _hoists_adapter(self) -> bool:
+        return (HOIST_ADAPTER and self.config.injection_type == "linear" and self.transformer.adapter.bias is None
+                and self.transformer.adapter.weight.is_cuda)
 
     def contributions_per_step(self, k: int) -> dict:
         """How many gradient contributions each parameter receives in one backward pass with k grad
         iterations: k for the core and the adapter, 2 for a tied embedding/head, 2 for ln_f, else 1."""
         out = {}
         for name, p in self.named_parameters():
-            if ".core_block." in name or ".adapter." in name:
+            if ".adapter." in name and self._hoists_adapter():
+                out[name] = max(k, 0) + (1 if k > 0 else 0)   # k state halves + one hoisted input half
+            elif ".core_block." in name or ".adapter." in name:
                 out[name] = max(k, 0)
             elif name.endswith("wte.weight") and self.config.tie_embeddings:
                 out[name] = 2

@@ -138,6 +138,83 @@ class _Adapter(torch.autograd.Function):
         return dx, de, dw
 
 
+def _half_wgrad(dy2, a2, weight, cols: slice):
+    """Gradient of one column half of the adapter weight; fused accumulation when the flat gradient buffer exists."""
+    C = cuda_backend()
+    if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+        C.gemm_tn(dy2, a2, out=weight.grad[:, cols], accumulate=True)
+        _notify(weight)
+        return None
+    dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy2.device)
+    C.gemm_tn(dy2, a2, out=dw[:, cols])
+    return dw.to(weight.dtype)
+
+
+class _AdapterInject(torch.autograd.Function):
+    """inj = e We^T, the loop-invariant half of the adapter (W = [Ws | We]): computed once per forward pass instead of
+    once per recurrence, and its two backward GEMMs run once on the summed gradient."""
+
+    @staticmethod
+    def forward(ctx, e, weight):
+        C = cuda_backend()
+        E = e.shape[-1]
+        e2 = e.reshape(-1, E)
+        ctx.save_for_backward(e2, weight)
+        ctx.eshape = e.shape
+        return C.gemm_nt(e2, _lp(weight)[:, E:]).view(e.shape)
+
+    @staticmethod
+    def backward(ctx, dinj):
+        C = cuda_backend()
+        e2, weight = ctx.saved_tensors
+        E = e2.shape[-1]
+        d2 = dinj.reshape(-1, E)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        de = C.gemm_nn(d2, _lp(weight)[:, E:]).view(ctx.eshape) if ctx.needs_input_grad[0] else None
+        dw = _half_wgrad(d2, e2, weight, slice(E, 2 * E)) if ctx.needs_input_grad[1] else None
+        return de, dw
+
+
+class _AdapterState(torch.autograd.Function):
+    """y = x Ws^T + inj with the addition in the GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, inj, weight):
+        C = cuda_backend()
+        E = x.shape[-1]
+        x2 = x.reshape(-1, E)
+        y = C.gemm(x2, _lp(weight)[:, :E], resid=inj.reshape(-1, E), out_mode=C.OUT_BF16_RESID)
+        ctx.save_for_backward(x2, weight)
+        ctx.xshape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = cuda_backend()
+        x2, weight = ctx.saved_tensors
+        E = x2.shape[-1]
+        dy2 = dy.reshape(-1, E)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = C.gemm_nn(dy2, _lp(weight)[:, :E]).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dinj = dy if ctx.needs_input_grad[1] else None
+        dw = _half_wgrad(dy2, x2, weight, slice(0, E)) if ctx.needs_input_grad[2] else None
+        return dx, dinj, dw
+
+
+def adapter_inject(e: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if e.is_cuda:
+        return _AdapterInject.apply(e, weight)
+    return ref.linear(e, weight[:, e.shape[-1]:])
+
+
+def adapter_state(x: torch.Tensor, inj: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if x.is_cuda:
+        return _AdapterState.apply(x, inj, weight)
+    return ref.linear(x, weight[:, :x.shape[-1]]) + inj
+
+
 def adapter(x: torch.Tensor, e: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if x.is_cuda:
         return _Adapter.apply(x, e, weight)

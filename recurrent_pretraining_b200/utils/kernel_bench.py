@@ -77,17 +77,19 @@ def bench_norm(M=4096, E=5280):
     from ..ops import cuda as C
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    M = M * 8  # 346 MB per tensor: larger than L2
+    if M == 4096:
+        bench_norm(M=512, E=E)  # the training shape (4096 rows) first, then 8x that: 346 MB per tensor, larger than L2
+    M = M * 8
     x = torch.randn(M, E, device="cuda").bfloat16()
     a = torch.randn(M, E, device="cuda").bfloat16()
     w = torch.ones(E, device="cuda")
     t = time_fn(lambda: C.rmsnorm_fwd(x, w, 1e-6), flush=flush)
-    print(json.dumps({"kernel": "rmsnorm_fwd", "ms": round(t, 3), "GBps": round(2 * x.numel() * 2 / t / 1e6, 1)}))
+    print(json.dumps({"kernel": "rmsnorm_fwd", "rows": M, "ms": round(t, 3), "GBps": round(2 * x.numel() * 2 / t / 1e6, 1)}))
     t = time_fn(lambda: C.add_rmsnorm_fwd(a, x, w, 1e-6), flush=flush)
     print(json.dumps({"kernel": "add_rmsnorm_fwd", "ms": round(t, 3), "GBps": round(4 * x.numel() * 2 / t / 1e6, 1)}))
     y, rstd = C.rmsnorm_fwd(x, w, 1e-6)
     t = time_fn(lambda: C.rmsnorm_bwd(a, x, w, rstd), flush=flush)
-    print(json.dumps({"kernel": "rmsnorm_bwd", "ms": round(t, 3), "GBps": round(3 * x.numel() * 2 / t / 1e6, 1)}))
+    print(json.dumps({"kernel": "rmsnorm_bwd", "rows": M, "ms": round(t, 3), "GBps": round(3 * x.numel() * 2 / t / 1e6, 1)}))
 
 
 def bench_swiglu(M=4096, E=5280, I=17920):

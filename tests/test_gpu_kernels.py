@@ -102,7 +102,7 @@ def test_gemm_residual_and_swiglu_epilogues(C):
     assert C.check_device_status() == 0
 
 
-@pytest.mark.parametrize("M,E", [(7, 256), (33, 480), (64, 5280), (5, 8200)])
+@pytest.mark.parametrize("M,E", [(7, 256), (33, 480), (64, 5280), (5, 8200), (1100, 480), (1536, 5280)])
 def test_rmsnorm_fwd_bwd(C, M, E):
     x, a = _rand(M, E), _rand(M, E)
     w = torch.rand(E, device="cuda") + 0.5
