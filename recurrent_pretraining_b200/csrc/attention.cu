@@ -954,6 +954,297 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------------------------------------ backward, v2
+// Transposed formulation: one CTA per (128-key block, kv head, batch) computes, for every query block i at or below
+// the diagonal (and every query head of the group),
+//     S^T  = K Q_i^T      dP^T = V dO_i^T          [key lanes x query columns] in TMEM
+//     P^T  = exp2(S^T scale - lse_q)               bf16, written over the consumed S^T columns (TMEM)
+//     dS^T = P^T (dP^T - delta_q)                  bf16, written over the consumed dP^T columns (TMEM) and to smem
+//     dV  += P^T dO_i     dK += dS^T Q_i           A operand straight from TMEM, accumulators in TMEM for the whole loop
+//     dQ_i = dS K                                  A = dS^T tile in smem read MN-major; added to the fp32 accumulator
+// so P never touches shared memory, the softmax needs no row reductions (lse and delta are per column), and the 32 KB
+// saved hold a second stage of Q_i / dO_i tiles: the next block's loads overlap this block's work.
+// Warps: 0 TMA, 1 MMA, 2-9 softmax (two threads per key row, 64 query columns each).
+// TMEM: ST [0,128): P^T packs into [0,32) and [96,128), dQ columns 0..63 go to the hole [32,96);
+//       DPT [128,256): dS^T packs into [128,160) and [224,256), dQ columns 64..D-1 go to [160,224);
+//       dV [256,256+D), dK [384,384+D).
+constexpr int BWD2_SLOTS = 4;   // Q_i, dO_i, Q_i+1, dO_i+1
+struct Bwd2Bars {
+  uint64_t kv_full, slot_full[BWD2_SLOTS], slot_empty[BWD2_SLOTS], sdp_full, pds_ready, dq_full, dq_empty;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                 const AttnBwdParams p) {
+  constexpr int KSTEPS_D = D / 16;
+  constexpr uint32_t IDESC_ST = make_idesc_bf16(128, 128, 0, 0);     // S^T = K Q^T, dP^T = V dO^T
+  constexpr uint32_t IDESC_ACC = make_idesc_bf16(128, D, 0, 1);      // dV += P^T dO, dK += dS^T Q  (A in TMEM)
+  constexpr uint32_t IDESC_DQA = make_idesc_bf16(128, 64, 1, 1);     // dQ[:, 0:64) = dS K
+  constexpr int DQB = D - 64;                                        // second piece of dQ (0, 32 or 64 columns)
+  constexpr uint32_t IDESC_DQB = make_idesc_bf16(128, DQB > 0 ? DQB : 16, 1, 1);
+  constexpr int TILE_BYTES = 2 * PANEL_BYTES;
+  constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
+  constexpr uint32_t COL_DQA = 32, COL_DQB = 160;
+
+  // 7 tiles of 32 KB leave no room for alignment slack: the dynamic shared window itself must be 1024-byte aligned
+  // (it is when the kernel has no static shared memory); a CTA that finds it otherwise reports and leaves.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0 && p.err) atomicCAS(p.err, 0, ERR_WAIT_ATTN);
+    return;
+  }
+  uint8_t* smem = smem_raw;
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sdS = sV + TILE_BYTES;
+  uint8_t* sSlot = sdS + TILE_BYTES;                       // BWD2_SLOTS tiles
+  float* s_stat = reinterpret_cast<float*>(sSlot + BWD2_SLOTS * TILE_BYTES);   // [2 parities][lse2 | delta][128]
+  Bwd2Bars* bars = reinterpret_cast<Bwd2Bars*>(s_stat + 2 * 2 * 128);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int rep = p.H / p.Hkv;
+  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
+  const int per_head = nqb - kvb;
+  const int n_it = rep * per_head;
+  const int k0 = kvb * ATT_BN;
+  const int xk = p.wq + hk * D, xv = p.wq + p.wk + hk * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int i = 0; i < BWD2_SLOTS; ++i) {
+      mbar_init(&bars->slot_full[i], 1);
+      mbar_init(&bars->slot_empty[i], 1);
+    }
+    mbar_init(&bars->sdp_full, 1);
+    mbar_init(&bars->pds_ready, 8);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_empty, 8);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQKV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
+      tma_load_3d(sK, &tmQKV, &bars->kv_full, xk, k0, b);
+      tma_load_3d(sK + PANEL_BYTES, &tmQKV, &bars->kv_full, xk + 64, k0, b);
+      tma_load_3d(sV, &tmQKV, &bars->kv_full, xv, k0, b);
+      tma_load_3d(sV + PANEL_BYTES, &tmQKV, &bars->kv_full, xv + 64, k0, b);
+      int issued = 0;   // tiles (two per iteration: Q then dO)
+      for (int t = 0; t < 2 * n_it; ++t) {
+        const int it = t >> 1;
+        const int h = hk * rep + it / per_head;
+        const int q0 = (kvb + it % per_head) * ATT_BM;
+        const int slot = t % BWD2_SLOTS;
+        if (!mbar_wait(&bars->slot_empty[slot], ((t / BWD2_SLOTS) & 1) ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        uint8_t* dst = sSlot + slot * TILE_BYTES;
+        mbar_expect_tx(&bars->slot_full[slot], TILE_BYTES);
+        if (t & 1) {
+          tma_load_3d(dst, &tmDO, &bars->slot_full[slot], h * D, q0, b);
+          tma_load_3d(dst + PANEL_BYTES, &tmDO, &bars->slot_full[slot], h * D + 64, q0, b);
+        } else {
+          tma_load_3d(dst, &tmQKV, &bars->slot_full[slot], h * D, q0, b);
+          tma_load_3d(dst + PANEL_BYTES, &tmQKV, &bars->slot_full[slot], h * D + 64, q0, b);
+        }
+        issued = t + 1;
+      }
+      unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bars->kv_full, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      for (int t = max(0, issued - BWD2_SLOTS); t < issued; ++t) {
+        t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->slot_full[t % BWD2_SLOTS], (t / BWD2_SLOTS) & 1) &&
+               globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sdS), aSlot = smem_u32(sSlot);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, p.err, ERR_WAIT_ATTN);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t ph = it & 1;
+        const int tq = 2 * it, tdo = 2 * it + 1;
+        const uint32_t aQ = aSlot + (tq % BWD2_SLOTS) * TILE_BYTES, aDO = aSlot + (tdo % BWD2_SLOTS) * TILE_BYTES;
+        if (!mbar_wait(&bars->slot_full[tq % BWD2_SLOTS], (tq / BWD2_SLOTS) & 1, abort_flag, p.err, ERR_WAIT_ATTN) ||
+            !mbar_wait(&bars->dq_empty, ph ^ 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < KSTEPS_D; ++t) {
+          const uint32_t off = (t >> 2) * PANEL_BYTES + (t & 3) * 32;
+          umma_bf16(tmem_base + COL_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
+                    IDESC_ST, t ? 1u : 0u);
+        }
+        if (!mbar_wait(&bars->slot_full[tdo % BWD2_SLOTS], (tdo / BWD2_SLOTS) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < KSTEPS_D; ++t) {
+          const uint32_t off = (t >> 2) * PANEL_BYTES + (t & 3) * 32;
+          umma_bf16(tmem_base + COL_DPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024),
+                    IDESC_ST, t ? 1u : 0u);
+        }
+        umma_commit(&bars->sdp_full);
+        if (!mbar_wait(&bars->pds_ready, ph, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {  // contraction over the 128 queries, 16 per step = 8 packed TMEM columns
+          const uint32_t pcol = (t < 4) ? t * 8 : 96 + (t - 4) * 8;
+          umma_bf16_ts(tmem_base + COL_DV, tmem_base + COL_ST + pcol, make_smem_desc(aDO + t * 2048, PANEL_BYTES, 1024),
+                       IDESC_ACC, (it | t) ? 1u : 0u);
+          umma_bf16_ts(tmem_base + COL_DK, tmem_base + COL_DPT + pcol, make_smem_desc(aQ + t * 2048, PANEL_BYTES, 1024),
+                       IDESC_ACC, (it | t) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {  // contraction over the 128 keys; A = dS^T tile read MN-major (M = queries)
+          const uint64_t aS = make_smem_desc(aDS + t * 2048, PANEL_BYTES, 1024);
+          umma_bf16(tmem_base + COL_DQA, aS, make_smem_desc(aK + t * 2048, PANEL_BYTES, 1024), IDESC_DQA,
+                    t ? 1u : 0u);
+          if constexpr (DQB > 0)
+            umma_bf16(tmem_base + COL_DQB, aS, make_smem_desc(aK + PANEL_BYTES + t * 2048, PANEL_BYTES, 1024),
+                      IDESC_DQB, t ? 1u : 0u);
+        }
+        umma_commit(&bars->dq_full);
+        umma_commit(&bars->slot_empty[tq % BWD2_SLOTS]);
+        umma_commit(&bars->slot_empty[tdo % BWD2_SLOTS]);
+      }
+    }
+  } else {
+    // warps 2..9: TMEM lane quadrant = warp % 4; the two warps with the same quadrant split the query columns
+    const int quad = warp & 3;
+    const int hsel = (warp - 2) >> 2;         // 0: warps 2-5 (query columns 0..63), 1: warps 6-9 (64..127)
+    const int r = quad * 32 + lane;           // key row (phase A) / query row (phase B)
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int wt = threadIdx.x - 64;          // 0..255 inside the softmax group
+    const int key = k0 + r;
+    // statistics of the first query block
+    auto load_stat = [&](int it) -> float {
+      const int h = hk * rep + it / per_head;
+      const int q = (kvb + it % per_head) * ATT_BM + (wt & 127);
+      if (it >= n_it || q >= p.S) return 0.f;
+      const size_t idx = (static_cast<size_t>(b) * p.H + h) * p.S + q;
+      return (wt < 128) ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
+    };
+    float stat_next = load_stat(0);
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t ph = it & 1;
+      const int h = hk * rep + it / per_head;
+      const int qb = kvb + it % per_head;
+      const int q0 = qb * ATT_BM;
+      float* st = s_stat + ph * 256;
+      st[wt] = stat_next;                      // [0,128): lse * log2(e), [128,256): delta of this query block
+      stat_next = load_stat(it + 1);           // prefetch for the next block
+      mbar_wait(&bars->sdp_full, ph, abort_flag, p.err, ERR_WAIT_ATTN);
+      named_barrier_sync(1, 256);              // statistics visible; uniform abort decision
+      if (*abort_flag) break;
+      tc_fence_after();
+      const bool diag = (qb == kvb);
+      const int nvalid = p.S - q0;             // query columns at or past nvalid do not exist
+      // this thread's 64 query columns, in two chunks of 32; the upper half walks downwards so that its packed
+      // stores (into the top of its own column range) never land on columns it has not read yet
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = hsel ? (96 - 32 * cc) : 32 * cc;
+        uint32_t sv[32], dpv[32];
+        tmem_ld_32x32(tmem_base + COL_ST + lane_addr + c, sv);
+        tmem_ld_32x32(tmem_base + COL_DPT + lane_addr + c, dpv);
+        tmem_ld_wait();
+        uint32_t pp[16], ds[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 l2 = *reinterpret_cast<const float2*>(st + c + i);
+          const float2 dl = *reinterpret_cast<const float2*>(st + 128 + c + i);
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -l2.x));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -l2.y));
+          if ((diag && key > q0 + c + i) || c + i >= nvalid) p0 = 0.f;
+          if ((diag && key > q0 + c + i + 1) || c + i + 1 >= nvalid) p1 = 0.f;
+          pp[i >> 1] = pack_bf16x2(p0, p1);
+          ds[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(dpv[i]) - dl.x), p1 * (__uint_as_float(dpv[i + 1]) - dl.y));
+        }
+        const uint32_t pcol = (hsel ? 96 + ((c - 64) >> 1) : (c >> 1));
+        tmem_st_32x16(tmem_base + COL_ST + lane_addr + pcol, pp);
+        tmem_st_32x16(tmem_base + COL_DPT + lane_addr + pcol, ds);
+        store_row_chunk_sw128(sdS, r, c, ds);  // dS^T tile [key rows][query columns] for the dQ MMA
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->pds_ready);
+      mbar_wait(&bars->dq_full, ph, abort_flag, p.err, ERR_WAIT_ATTN);
+      if (!*abort_flag) {
+        // dQ tile [query lanes x D]: warps 2-5 take columns 0..63, warps 6-9 columns 64..D-1
+        tc_fence_after();
+        const int qrow = q0 + r;
+        float* dq_row = p.dq_acc + (static_cast<size_t>(b) * p.S + qrow) * (p.H * D) + h * D;
+        const int ncols = hsel ? DQB : 64;
+        const uint32_t src = tmem_base + (hsel ? COL_DQB : COL_DQA) + lane_addr;
+        const int dcol0 = hsel ? 64 : 0;
+#pragma unroll
+        for (int c = 0; c < 64; c += 16) {
+          if (c < ncols) {
+            uint32_t v[16];
+            tmem_ld_32x16(src + c, v);
+            tmem_ld_wait();
+            if (qrow < p.S) {
+#pragma unroll
+              for (int i = 0; i < 16; i += 4)
+                red_add_v4(dq_row + dcol0 + c + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                           __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            }
+          }
+        }
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->dq_empty);
+    }
+    if (!*abort_flag && n_it > 0) {
+      // the last dq_full wait covered every MMA: write dV and scale * dK of this key block
+      const size_t wtot = static_cast<size_t>(p.wq) + 2 * p.wk;
+      __nv_bfloat16* base_row = p.dqkv + (static_cast<size_t>(b) * p.S + key) * wtot + p.wq + hk * D;
+      // warps 2-5 write dV, warps 6-9 write scale * dK
+      const uint32_t src = tmem_base + (hsel ? COL_DK : COL_DV) + lane_addr;
+      __nv_bfloat16* dst = base_row + (hsel ? 0 : p.wk);
+      const float mul = hsel ? p.scale : 1.f;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(src + c, v);
+        tmem_ld_wait();
+        if (key < p.S) {
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2)
+            o[i >> 1] = pack_bf16x2(__uint_as_float(v[i]) * mul, __uint_as_float(v[i + 1]) * mul);
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h)
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   float* __restrict__ delta, int B, int S, int H, int D) {
@@ -1071,6 +1362,29 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+template <int D>
+static int launch_attn_bwd2(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t st) {
+  constexpr int SMEM = (3 + BWD2_SLOTS) * 2 * PANEL_BYTES + 2048 + 256;  // K, V, dS^T, 4 Q/dO slots, statistics, barriers
+  auto kern = attn_bwd2_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  dim3 grid((p.S + ATT_BN - 1) / ATT_BN, p.Hkv, p.B);
+  kern<<<grid, 320, SMEM, st>>>(tq, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+static int g_attn_bwd_variant = 2;
+// 1: query-major tiles, P and dS through shared memory, dQ by bulk tensor reductions;
+// 2: transposed tiles, P^T / dS^T in tensor memory, double-buffered Q / dO (default).
+B200_API int b200_attn_set_bwd_variant(int v) {
+  const int old = g_attn_bwd_variant;
+  if (v == 1 || v == 2) g_attn_bwd_variant = v;
+  return old;
+}
+
 // Backward of b200_attn_fwd.  qkv, o, d_o as in the forward; lse from the forward; delta: scratch [B, H, S] fp32;
 // dq_acc: scratch [B, S, H*D] fp32 that must be ZERO on entry; dqkv: output, packed like qkv.
 B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, const float* lse, float* delta,
@@ -1096,11 +1410,20 @@ B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, cons
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.D = D; p.wq = wq; p.wk = Hkv * D;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv); p.err = err;
-  switch (D) {
-    case 64: rc = launch_attn_bwd<64>(tq, tdo, tdq, p, st); break;
-    case 96: rc = launch_attn_bwd<96>(tq, tdo, tdq, p, st); break;
-    case 128: rc = launch_attn_bwd<128>(tq, tdo, tdq, p, st); break;
-    default: return -1;
+  if (g_attn_bwd_variant == 2) {
+    switch (D) {
+      case 64: rc = launch_attn_bwd2<64>(tq, tdo, p, st); break;
+      case 96: rc = launch_attn_bwd2<96>(tq, tdo, p, st); break;
+      case 128: rc = launch_attn_bwd2<128>(tq, tdo, p, st); break;
+      default: return -1;
+    }
+  } else {
+    switch (D) {
+      case 64: rc = launch_attn_bwd<64>(tq, tdo, tdq, p, st); break;
+      case 96: rc = launch_attn_bwd<96>(tq, tdo, tdq, p, st); break;
+      case 128: rc = launch_attn_bwd<128>(tq, tdo, tdq, p, st); break;
+      default: return -1;
+    }
   }
   if (rc) return rc;
   const size_t n = static_cast<size_t>(B) * S * (wq / 4);

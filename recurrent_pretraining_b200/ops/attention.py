@@ -28,6 +28,15 @@ def set_fwd_variant(v: int) -> int:
     return int(_set_variant(int(v)))
 
 
+_set_bwd_variant = K._sig("b200_attn_set_bwd_variant", [_i])
+
+
+def set_bwd_variant(v: int) -> int:
+    """1: query-major tiles (P and dS through shared memory); 2: transposed tiles with P^T / dS^T in tensor memory
+    (default).  Returns the previous setting."""
+    return int(_set_bwd_variant(int(v)))
+
+
 ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "0") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
 

@@ -245,7 +245,8 @@ def test_flash_attention_forward(C, B, S, H, Hkv, D, variant):
 
 @pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
                                          (1, 1024, 2, 2, 96)])
-def test_flash_attention_backward(C, B, S, H, Hkv, D):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_flash_attention_backward(C, B, S, H, Hkv, D, variant):
     from recurrent_pretraining_b200.ops import attention as A
 
     assert A.NATIVE_BWD, "the native attention backward entry point is missing from the built library"
@@ -253,7 +254,11 @@ def test_flash_attention_backward(C, B, S, H, Hkv, D):
     scale = D ** -0.5
     o, lse = A.fwd(qkv, H, Hkv, D, scale)
     do = (torch.randn(B, S, H * D, device="cuda") * 0.5).bfloat16()
-    dqkv = A.bwd(do, qkv, o, lse, H, Hkv, D, scale)
+    old = A.set_bwd_variant(variant)
+    try:
+        dqkv = A.bwd(do, qkv, o, lse, H, Hkv, D, scale)
+    finally:
+        A.set_bwd_variant(old)
     torch.cuda.synchronize()
     assert C.check_device_status() == 0
     x = qkv.float().requires_grad_(True)
