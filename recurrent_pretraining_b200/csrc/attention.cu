@@ -1188,8 +1188,10 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       if (!*abort_flag) {
         // dQ tile [query lanes x D]: warps 2-5 take columns 0..63, warps 6-9 columns 64..D-1
         tc_fence_after();
+        // accumulator layout [b, h, query block, D/4, 128 rows, 4]: for one group of 4 columns the 128 rows are
+        // contiguous, so the 32 lanes of a reduction instruction cover 512 contiguous bytes
         const int qrow = q0 + r;
-        float* dq_row = p.dq_acc + (static_cast<size_t>(b) * p.S + qrow) * (p.H * D) + h * D;
+        float* dq_blk = p.dq_acc + ((static_cast<size_t>(b) * p.H + h) * nqb + qb) * (static_cast<size_t>(D) * ATT_BM) + r * 4;
         const int ncols = hsel ? DQB : 64;
         const uint32_t src = tmem_base + (hsel ? COL_DQB : COL_DQA) + lane_addr;
         const int dcol0 = hsel ? 64 : 0;
@@ -1202,7 +1204,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             if (qrow < p.S) {
 #pragma unroll
               for (int i = 0; i < 16; i += 4)
-                red_add_v4(dq_row + dcol0 + c + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                red_add_v4(dq_blk + ((dcol0 + c + i) >> 2) * (ATT_BM * 4), __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
                            __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
             }
           }
@@ -1259,6 +1261,33 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   for (int i = lane; i < D; i += 32) acc += bf2f(op[i]) * bf2f(dp[i]);
   acc = warp_sum(acc);
   if (lane == 0) delta[(static_cast<size_t>(bs / S) * H + h) * S + bs % S] = acc;
+}
+
+// Same for the block-interleaved accumulator of the v2 backward ([b, h, query block, D/4, 128 rows, 4]): one CTA per
+// (query block, head, batch) reads its D x 128 floats coalesced, transposes through shared memory, writes bf16 rows.
+template <int D>
+__global__ void __launch_bounds__(256)
+attn_dq_convert_blocked_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int S, int H, int wtot,
+                               float scale) {
+  constexpr int ROWS = 64;   // half a query block per CTA (static shared memory limit)
+  __shared__ float tile[ROWS][D + 1];
+  const int qb = blockIdx.x >> 1, r0 = (blockIdx.x & 1) * ROWS, h = blockIdx.y, b = blockIdx.z;
+  const int nqb = gridDim.x >> 1;
+  const float4* src = reinterpret_cast<const float4*>(
+      dq_acc + ((static_cast<size_t>(b) * H + h) * nqb + qb) * (static_cast<size_t>(D) * ATT_BM));
+  for (int i = threadIdx.x; i < (D / 4) * ROWS; i += blockDim.x) {
+    const int g = i / ROWS, r = i % ROWS;
+    const float4 v = src[g * ATT_BM + r0 + r];
+    tile[r][4 * g] = v.x; tile[r][4 * g + 1] = v.y; tile[r][4 * g + 2] = v.z; tile[r][4 * g + 3] = v.w;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ROWS * (D / 2); i += blockDim.x) {
+    const int r = i / (D / 2), c = (i % (D / 2)) * 2;
+    const int q = qb * ATT_BM + r0 + r;
+    if (q < S)
+      *reinterpret_cast<uint32_t*>(dqkv + (static_cast<size_t>(b) * S + q) * wtot + h * D + c) =
+          pack_bf16x2(tile[r][c] * scale, tile[r][c + 1] * scale);
+  }
 }
 
 // dqkv[:, :, 0:wq] = bf16(scale * dq_acc)
@@ -1386,7 +1415,7 @@ B200_API int b200_attn_set_bwd_variant(int v) {
 }
 
 // Backward of b200_attn_fwd.  qkv, o, d_o as in the forward; lse from the forward; delta: scratch [B, H, S] fp32;
-// dq_acc: scratch [B, S, H*D] fp32 that must be ZERO on entry; dqkv: output, packed like qkv.
+// dq_acc: scratch of B * H * ceil(S/128) * 128 * D floats that must be ZERO on entry; dqkv: output, packed like qkv.
 B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, const float* lse, float* delta,
                            float* dq_acc, void* dqkv, int B, int S, int H, int Hkv, int D, float scale, void* stream,
                            int* err) {
@@ -1426,6 +1455,16 @@ B200_API int b200_attn_bwd(const void* qkv, const void* o, const void* d_o, cons
     }
   }
   if (rc) return rc;
+  if (g_attn_bwd_variant == 2) {
+    dim3 cg(2 * ((S + ATT_BM - 1) / ATT_BM), H, B);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dqkv);
+    switch (D) {
+      case 64: attn_dq_convert_blocked_kernel<64><<<cg, 256, 0, st>>>(dq_acc, out, S, H, wtot, scale); break;
+      case 96: attn_dq_convert_blocked_kernel<96><<<cg, 256, 0, st>>>(dq_acc, out, S, H, wtot, scale); break;
+      default: attn_dq_convert_blocked_kernel<128><<<cg, 256, 0, st>>>(dq_acc, out, S, H, wtot, scale); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -12;
+  }
   const size_t n = static_cast<size_t>(B) * S * (wq / 4);
   attn_dq_convert_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
       dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), static_cast<size_t>(B) * S, wq, wtot, scale);

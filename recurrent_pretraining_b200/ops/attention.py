@@ -72,7 +72,8 @@ def bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
     do = do.contiguous()
     assert do.dtype == torch.bfloat16 and o.is_contiguous() and qkv_r.is_contiguous()
     dqkv = torch.empty_like(qkv_r)
-    dq_acc = torch.zeros(B, S, n_head * D, dtype=torch.float32, device=qkv_r.device)
+    # fp32 dQ accumulator, padded to whole 128-query blocks (the v2 kernel keeps it block-interleaved)
+    dq_acc = torch.zeros(B * n_head * ((S + 127) // 128) * 128 * D, dtype=torch.float32, device=qkv_r.device)
     delta = torch.empty(B, n_head, S, dtype=torch.float32, device=qkv_r.device)
     K._check(_bwd(qkv_r.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
                   dqkv.data_ptr(), B, S, n_head, n_kv, D, float(scale), K._stream(),
