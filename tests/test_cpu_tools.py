@@ -75,3 +75,11 @@ def test_server_batches_and_matches_direct_generation():
             pass
     finally:
         sched.close()
+
+
+def test_example_scripts_run():
+    import examples.inference_demo as demo
+    import examples.speculative_decoding_demo as spec
+
+    demo.main(["--max_new_tokens", "3"])
+    spec.main()
