@@ -81,6 +81,33 @@ __device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
                : "memory");
 }
 
+// All-gather fused into the GEMM: the B operand (weights [N, K], rows sharded over ranks) is pulled from the owners'
+// memory by four extra "copier" warps per CTA into this GPU's full-size buffer, N-tile by N-tile, while the MMA warps
+// consume the tiles that have already landed.  Tile order starts at this rank's own shard.  Copiers publish a finished
+// N-tile by incrementing done[tile] (release); producers acquire it before their first TMA load of that tile.  All
+// TMA loads read LOCAL memory; peers are only touched by plain 16-byte loads.
+constexpr int AG_MAX_RANKS = 8;
+struct AgParams {
+  const __nv_bfloat16* shard[AG_MAX_RANKS];   // shard[q]: rank q's rows [q * rows_per_shard, ...) as [rows, K] contiguous
+  __nv_bfloat16* wfull;                       // local [N, ldw] destination, also the TMA source of the GEMM
+  int* done;                                  // [tiles_n] counters, zero on entry
+  int n_ranks, rank, rows_per_shard, ldw;
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
 template <int BN>
 struct Smem2 {
   static constexpr int A_BYTES = BM2 * BK2 * 2;        // 16 KB
@@ -90,10 +117,10 @@ struct Smem2 {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
 };
 
-template <int BN, bool A_MN, bool B_MN, int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? 320 : 192, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
-             const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+             const __grid_constant__ CUtensorMap tmB, const GemmParams p, const __grid_constant__ AgParams ag) {
   using L = Smem2<BN>;
   constexpr int STAGES = L::STAGES;
   constexpr int ACC_STRIDE = 256;
@@ -128,6 +155,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int nk1 = (p.K1 + BK2 - 1) / BK2;
   const int nk2 = (p.K2 + BK2 - 1) / BK2;
   const int nk = nk1 + nk2;
+  // N-tile of a linear tile index; with the fused all-gather the order is rotated to start at this rank's shard
+  const int ag_first = AG ? (ag.rank * ag.rows_per_shard) / BN : 0;
+  auto n_tile_of = [&](int tile) { return AG ? (ag_first + tile / tiles_m) % tiles_n : tile / tiles_m; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -162,8 +192,24 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-        const int n0 = (MODE == OUT_SWIGLU) ? (tile / tiles_m) * BN_OUT + static_cast<int>(rank) * p.swiglu_n
-                                            : (tile / tiles_m) * BN + static_cast<int>(rank) * BNH;
+        const int nt = n_tile_of(tile);
+        const int n0 = (MODE == OUT_SWIGLU) ? nt * BN_OUT + static_cast<int>(rank) * p.swiglu_n
+                                            : nt * BN + static_cast<int>(rank) * BNH;
+        if constexpr (AG) {
+          // the weight rows of this N-tile must have landed in the local buffer (every CTA's copiers add one)
+          const unsigned long long t0 = globaltimer_ns();
+          while (ld_acquire_gpu(ag.done + nt) < static_cast<int>(gridDim.x)) {
+            if (*abort_flag || globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+              *abort_flag = 1;
+              if (p.err) atomicCAS(p.err, 0, ERR_WAIT_PEER_FLAG);
+              ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes of the copiers -> TMA reads
+        }
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -228,6 +274,44 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
       }
     }
+  } else if (AG && warp >= 6) {
+    // ------------------------------------------------------------------ copiers (warps 6..9 of every CTA)
+    if constexpr (AG) {
+      const int ct = threadIdx.x - 192;                       // 0..127
+      const size_t g = static_cast<size_t>(blockIdx.x) * 128 + ct, gstride = static_cast<size_t>(gridDim.x) * 128;
+      const int vec_per_row = (p.K1 + p.K2) >> 3;             // 16-byte vectors per weight row
+      for (int i = 0; i < tiles_n; ++i) {
+        const int nt = (ag_first + i) % tiles_n;
+        const int r0 = nt * BN, r1 = min(p.N, r0 + BN);
+        const size_t nvec = static_cast<size_t>(r1 - r0) * vec_per_row;
+        for (size_t v = g; v < nvec; v += 4 * gstride) {
+          uint4 buf[4];
+          size_t idx[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            idx[u] = v + u * gstride;
+            if (idx[u] < nvec) {
+              const int row = r0 + static_cast<int>(idx[u] / vec_per_row), col = static_cast<int>(idx[u] % vec_per_row);
+              const int owner = min(row / ag.rows_per_shard, ag.n_ranks - 1);
+              const __nv_bfloat16* src = ag.shard[owner] + static_cast<size_t>(row - owner * ag.rows_per_shard) * (vec_per_row * 8);
+              buf[u] = ld_peer_16(reinterpret_cast<const uint4*>(src) + col);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (idx[u] < nvec) {
+              const int row = r0 + static_cast<int>(idx[u] / vec_per_row), col = static_cast<int>(idx[u] % vec_per_row);
+              reinterpret_cast<uint4*>(ag.wfull + static_cast<size_t>(row) * ag.ldw)[col] = buf[u];
+            }
+          }
+        }
+        named_barrier_sync(2, 128);
+        if (ct == 0) {
+          __threadfence();
+          atomicAdd(ag.done + nt, 1);
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs, warps 2..5)
     const int quad = warp & 3;
@@ -236,7 +320,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-      const int n0 = (tile / tiles_m) * BN_OUT;
+      const int n0 = n_tile_of(tile) * BN_OUT;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
@@ -258,17 +342,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, int MODE>
+template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, const GemmParams& p,
-                   cudaStream_t stream, int max_ctas) {
+                   cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr) {
   using L = Smem2<BN>;
-  auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE>;
+  auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE, AG>;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return -10;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_sms() & ~1, 1, 1);
-    cfg.blockDim = dim3(192, 1, 1);
+    cfg.blockDim = dim3(AG ? 320 : 192, 1, 1);
     cfg.dynamicSmemBytes = L::TOTAL;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
@@ -279,7 +363,9 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
   int clusters = tiles < max_clusters ? tiles : max_clusters;
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2;
   if (clusters <= 0) return 0;
-  kern<<<2 * clusters, 192, L::TOTAL, stream>>>(ta, ta2, tb, p);
+  AgParams ag = {};
+  if (agp) ag = *agp;
+  kern<<<2 * clusters, AG ? 320 : 192, L::TOTAL, stream>>>(ta, ta2, tb, p, ag);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -329,3 +415,34 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
 }
 
 }  // namespace b200
+
+using namespace b200;
+
+// C[M, N] (bf16) = A[M, K] Wfull[N, K]^T where W's rows are sharded over `n_ranks` GPUs: shard_ptrs[q] is rank q's
+// [rows_per_shard, K] block (peer-mapped), wfull the local [N, K] buffer that the kernel fills while it multiplies
+// (afterwards it holds the gathered weight for the remaining uses in this step).  `done`: int[ceil(N / bn)], zeroed by
+// this call.  bn: 240 or 256 (0 picks).
+extern "C" __attribute__((visibility("default"))) int b200_ag_gemm(
+    const void* A, void* const* shard_ptrs, void* wfull, void* C, int* done, int M, int N, int K, int lda, int ldc,
+    int n_ranks, int rank, int rows_per_shard, int bn, void* stream, int* err) {
+  if (n_ranks < 1 || n_ranks > AG_MAX_RANKS || (K & 7) || M < 256) return -1;
+  if (bn == 0) bn = (N % 256 != 0 && N % 240 == 0) ? 240 : 256;
+  if (bn != 240 && bn != 256) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int tiles_n = (N + bn - 1) / bn;
+  if (cudaMemsetAsync(done, 0, sizeof(int) * tiles_n, st) != cudaSuccess) return -2;
+  GemmParams p;
+  p.M = M; p.N = N; p.K1 = K; p.K2 = 0; p.ldc = ldc; p.ld_resid = 0; p.swiglu_n = N; p.ksplit = 1;
+  p.C = C; p.resid = nullptr; p.err = err;
+  AgParams ag = {};
+  for (int q = 0; q < n_ranks; ++q) ag.shard[q] = reinterpret_cast<const __nv_bfloat16*>(shard_ptrs[q]);
+  ag.wfull = reinterpret_cast<__nv_bfloat16*>(wfull);
+  ag.done = done; ag.n_ranks = n_ranks; ag.rank = rank; ag.rows_per_shard = rows_per_shard; ag.ldw = K;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, M, K, lda, BM2, BK2);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, wfull, N, K, K, bn / 2, BK2);
+  if (rc) return rc;
+  if (bn == 240) return launch2<240, false, false, OUT_BF16, true>(ta, ta, tb, p, st, 0, &ag);
+  return launch2<256, false, false, OUT_BF16, true>(ta, ta, tb, p, st, 0, &ag);
+}

@@ -127,6 +127,38 @@ def main():
                 rec[name + "_GBps"] = round(moved / t / 1e6, 1)
             if rank == 0:
                 print(json.dumps(rec), flush=True)
+    if "--ag" in sys.argv:
+        # all-gather fused into the consuming GEMM (flagship QKV and gate-up projections, 4096 rows)
+        from ..parallel.ag_gemm import GatheredWeight
+
+        for name, Nw, Kw in (("qkv", 15840, 5280), ("mlp.fc", 35840, 5280)):
+            gw = GatheredWeight(fabric, Nw, Kw)
+            gw.shard.normal_(0, 0.02)
+            x = torch.randn(4096, Kw, device=dev).bfloat16()
+            torch.cuda.synchronize(dev)
+            dist.barrier(device_ids=[dev.index])
+
+            def fused():
+                gw.invalidate()
+                gw.gemm(x)
+
+            def library():
+                gw.gather_only()
+                K.gemm_nt(x, gw.full)
+
+            t_fused = _time(fused, dev, reps=6, warmup=2)
+            t_lib = _time(library, dev, reps=6, warmup=2)
+            gw.gather_only()
+            t_gemm = _time(lambda: K.gemm_nt(x, gw.full), dev, reps=6, warmup=2)
+            remote = (N - 1) / N * Nw * Kw * 2
+            rec = {"ag_gemm": name, "n_gpus": N, "M": 4096, "N": Nw, "K": Kw, "fused_ms": round(t_fused, 3),
+                   "gemm_only_ms": round(t_gemm, 3), "nccl_all_gather_then_gemm_ms": round(t_lib, 3),
+                   "remote_MB": round(remote / 1e6, 1), "link_floor_ms": round(remote / LINK_GBS / 1e6, 3),
+                   "fraction_of_roofline": round(max(t_gemm, remote / LINK_GBS / 1e6) / t_fused, 3)}
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+            dist.barrier(device_ids=[dev.index])
+            gw.close()
     status = K.check_device_status()
     if rank == 0:
         print(json.dumps({"device_status": status}))

@@ -94,6 +94,34 @@ def main():
         dist.barrier()
         ctrl.close()
         dist.destroy_process_group()
+    elif mode == "ag_gemm":
+        # all-gather fused into the GEMM: result and gathered weight against the plain library path
+        from recurrent_pretraining_b200.parallel.ag_gemm import GatheredWeight
+
+        fabric = Fabric.from_env(grad_sync="flat")
+        dev = fabric.device
+        out = {}
+        for (M, N, Kd) in ((512, 1440, 264), (1024, 2000, 528)):
+            torch.manual_seed(1)
+            w = (torch.randn(N, Kd, device=dev) * 0.2).bfloat16()      # identical on every rank (same seed)
+            x = torch.randn(M, Kd, device=dev).bfloat16()
+            gw = GatheredWeight(fabric, N, Kd)
+            gw.load_full(w)
+            torch.cuda.synchronize()
+            dist.barrier()                                              # every shard is in place
+            y = gw.gemm(x)
+            torch.cuda.synchronize()
+            dist.barrier()
+            want = x.float() @ w.float().T
+            err = ((y.float() - want).abs().max() / want.abs().max()).item()
+            out[f"{M}x{N}x{Kd}"] = {"rel_err": err, "weight_equal": bool(torch.equal(gw.full, w)),
+                                    "second_call_equal": bool(torch.equal(gw.gemm(x), y))}
+            gw.close()
+        status = K.check_device_status()
+        if fabric.global_rank == 0:
+            print("RESULT " + json.dumps({"cases": out, "status": status}))
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -52,3 +52,12 @@ def test_p2p_sharded_step_four_ranks():
     for a, b in zip(res["p2p_losses"], res["nccl_losses"]):
         assert abs(a - b) < 0.02 * abs(b) + 0.02, res
     assert res["param_rel_diff"] < 2e-2, res
+
+
+@needs2
+def test_all_gather_fused_gemm():
+    res = _run("ag_gemm", nproc=min(torch.cuda.device_count(), 4), port=29647)
+    assert res["status"] == 0
+    for name, case in res["cases"].items():
+        assert case["rel_err"] < 2e-2, (name, case)
+        assert case["weight_equal"] and case["second_call_equal"], (name, case)
