@@ -188,8 +188,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
       if (nk2 > 0) tma_prefetch_desc(&tmA2);
-      uint32_t it = 0;
+      // stage index and phase advance by increment (no division in the per-k-block path of this single thread)
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
+      const uint32_t fb0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // leader's full barriers: fb0 + 8 * stage
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
         const int nt = n_tile_of(tile);
@@ -210,14 +213,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes of the copiers -> TMA reads
         }
-        for (int kb = 0; kb < nk; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int kb = 0; kb < nk; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           if (leader) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
-          const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
+          const uint32_t fb = fb0 + 8u * s;
           const bool second = kb >= nk1;
           const int ka = (second ? (kb - nk1) : kb) * BK2;
           const int kbcol = second ? (p.K1 + ka) : ka;
@@ -234,43 +235,50 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
             for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (BK2 * 128), &tmB, fb, n0 + c * 64, kbcol);
           }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      uint32_t it = 0, tcount = 0;
+      uint32_t tcount = 0;
       bool ok = true;
+      // The tensor pipe needs a new MMA every ~120 cycles; this single thread must not spend longer than that per
+      // instruction, so stage, phase, shared-memory descriptors and barrier addresses all advance by increments.
+      int s = 0;
+      uint32_t ph = 0;
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t desc_hi_a = A_MN ? make_smem_desc(0, BK2 * 128, 1024) : make_smem_desc(0, 16, 1024);
+      const uint64_t desc_hi_b = B_MN ? make_smem_desc(0, BK2 * 128, 1024) : make_smem_desc(0, 16, 1024);
+      constexpr uint32_t KSTEP_A = (A_MN ? 2048 : 32) >> 4, KSTEP_B = (B_MN ? 2048 : 32) >> 4;
+      const uint32_t eb0 = mapa_shared(smem_u32(&empty_bar[0]), 0), eb1 = mapa_shared(smem_u32(&empty_bar[0]), 1);
+      const uint32_t tb0 = mapa_shared(smem_u32(&tfull_bar[0]), 0), tb1 = mapa_shared(smem_u32(&tfull_bar[0]), 1);
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
-        for (int kb = 0; kb < nk; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int kb = 0; kb < nk; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_WAIT_TMA_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint32_t sb = sa + L::A_BYTES;
+          const uint32_t sa = smem0 + s * L::STAGE_BYTES;
+          uint64_t adesc = desc_hi_a | ((sa & 0x3FFFF) >> 4);
+          uint64_t bdesc = desc_hi_b | (((sa + L::A_BYTES) & 0x3FFFF) >> 4);
 #pragma unroll
           for (int k = 0; k < BK2 / 16; ++k) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, BK2 * 128, 1024)
-                                        : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK2 * 128, 1024)
-                                        : make_smem_desc(sb + k * 32, 16, 1024);
             umma2_bf16(d_tmem, adesc, bdesc, IDESC, (kb | k) ? 1u : 0u);
+            adesc += KSTEP_A;   // the start-address field sits in the low bits: stepping it is a plain add
+            bdesc += KSTEP_B;
           }
-          const uint32_t eb = smem_u32(&empty_bar[s]);
-          umma2_commit(mapa_shared(eb, 0));
-          umma2_commit(mapa_shared(eb, 1));
+          umma2_commit(eb0 + 8u * s);
+          umma2_commit(eb1 + 8u * s);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) {
-          const uint32_t tb = smem_u32(&tfull_bar[acc]);
-          umma2_commit(mapa_shared(tb, 0));
-          umma2_commit(mapa_shared(tb, 1));
+          umma2_commit(tb0 + 8u * acc);
+          umma2_commit(tb1 + 8u * acc);
         }
       }
     }
