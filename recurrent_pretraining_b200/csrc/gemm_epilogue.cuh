@@ -9,6 +9,7 @@ enum OutMode : int {
   OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_RESID = 3, OUT_SWIGLU = 4,
   OUT_BF16_T = 5,        // transposed store C[col, row] (skinny decode GEMMs computed as W x^T)
   OUT_F32_T_ATOMIC = 6,  // transposed fp32 atomic accumulate (split-K partial sums)
+  OUT_BF16_ROPE = 7,     // bf16 store of a packed qkv row: q/k columns get their bias added and are rotated
 };
 
 struct GemmParams {
@@ -20,6 +21,12 @@ struct GemmParams {
   void* C;
   const __nv_bfloat16* resid;
   int* err;
+  // OUT_BF16_ROPE: columns [0, rope_width) are q and k heads of rope_D channels; row r sits at position r % rope_S;
+  // tables are [rope_S, rope_D / 2] fp32; bias (may be null) is indexed by the column.
+  const float* rope_cos;
+  const float* rope_sin;
+  const float* rope_bias;
+  int rope_S, rope_D, rope_width;
 };
 
 // taddr: TMEM address of (this warp's lane quadrant, first accumulator column); row: global row of this thread;
@@ -78,7 +85,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         for (int i = 0; i < 16; ++i)
           if (i < nvalid) crow[i] = f2bf(f[i]);
       }
-    } else if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID) {
+    } else if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_BF16_ROPE) {
       uint32_t v[32];
       __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
       const bool vec = active && nvalid == width && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
@@ -127,6 +134,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (i < nvalid) f[i] += bf2f(rrow[i]);
+        }
+      }
+      if constexpr (MODE == OUT_BF16_ROPE) {
+        // interleaved pairs (2j, 2j+1) of every q/k head: (x0, x1) -> (x0 cos - x1 sin, x1 cos + x0 sin) after the bias
+        if (col < p.rope_width) {
+          const int half = p.rope_D >> 1;
+          const float* ct = p.rope_cos + static_cast<size_t>(row % p.rope_S) * half;
+          const float* st = p.rope_sin + static_cast<size_t>(row % p.rope_S) * half;
+          int d = col % p.rope_D;     // channel of the first column of this chunk inside its head (even)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            if (i < width && col + i < p.rope_width) {
+              float x0 = f[i], x1 = f[i + 1];
+              if (p.rope_bias) {
+                x0 += __ldg(p.rope_bias + col + i);
+                x1 += __ldg(p.rope_bias + col + i + 1);
+              }
+              const float cs = __ldg(ct + (d >> 1)), sn = __ldg(st + (d >> 1));
+              f[i] = x0 * cs - x1 * sn;
+              f[i + 1] = x1 * cs + x0 * sn;
+            }
+            d += 2;
+            if (d >= p.rope_D) d -= p.rope_D;
+          }
         }
       }
       if (vec) {

@@ -296,6 +296,13 @@ B200_API int b200_gemm_set_2cta(int enable) {
 //   out_mode: see OutMode.  For OUT_SWIGLU, N is the output width I and B holds 2I rows ([gate; up]).
 //   bn: tile width (256, 240 or 128); 0 picks one.  max_ctas > 0 caps the grid (used to leave SMs to a
 //   concurrent communication kernel).
+// Arguments of the next OUT_BF16_ROPE call (host-side state of the calling thread; set right before b200_gemm).
+struct RopeArgs { const float* cos; const float* sin; const float* bias; int S, D, width; };
+static thread_local RopeArgs g_rope = {nullptr, nullptr, nullptr, 0, 0, 0};
+B200_API void b200_gemm_set_rope(const float* cos, const float* sin, const float* bias, int S, int D, int width) {
+  g_rope = {cos, sin, bias, S, D, width};
+}
+
 B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, const void* resid, int M, int N,
                        int K1, int K2, int lda, int lda2, int ldb, int ldc, int ld_resid, int a_mn, int b_mn,
                        int out_mode, int bn, int max_ctas, void* stream, int* err) {
@@ -310,9 +317,12 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   }
   if (b_mn && bn == 240) return -21;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  GemmParams p;
+  GemmParams p = {};
   p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
+  p.rope_cos = g_rope.cos; p.rope_sin = g_rope.sin; p.rope_bias = g_rope.bias;
+  p.rope_S = g_rope.S; p.rope_D = g_rope.D; p.rope_width = g_rope.width;
+  if (out_mode == OUT_BF16_ROPE && (!p.rope_cos || p.rope_D <= 0 || (p.rope_D & 1) || (p.rope_width & 1))) return -25;
   if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240 || (out_mode == OUT_SWIGLU && !a_mn && !b_mn))) {
     // SwiGLU on the pair kernel: a 256-wide MMA tile = 128 gate columns (CTA 0's half of B) + 128 up columns (CTA 1's)
     const int bn2 = (out_mode == OUT_SWIGLU) ? 256 : bn;
@@ -346,6 +356,12 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   if (out_mode == OUT_SWIGLU) {
     if (a_mn || b_mn || bn != 128) return -23;
     return launch<128, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  }
+  if (out_mode == OUT_BF16_ROPE) {
+    if (a_mn || b_mn) return -24;
+    if (bn == 240) return launch<240, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
+    if (bn == 128) return launch<128, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
+    return launch<256, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
   }
   if (!a_mn && !b_mn) {
     if (bn == 256) { DISPATCH_MODE(256, false, false) }
@@ -389,7 +405,7 @@ B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* wo
     if (ksplit > nk / 4) ksplit = nk / 4 > 0 ? nk / 4 : 1;
     if (ksplit > 16) ksplit = 16;
   }
-  GemmParams p;
+  GemmParams p = {};
   p.M = N; p.N = Bt; p.K1 = K; p.K2 = 0; p.ld_resid = 0; p.swiglu_n = 0; p.resid = nullptr; p.err = err;
   p.ksplit = ksplit;
   if (ksplit > 1) {

@@ -408,6 +408,11 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     default: return -100;                                                                           \
   }
   if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_BF16_ROPE) {
+    if (a_mn || b_mn) return -100;
+    if (bn == 240) return launch2<240, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
+    return launch2<256, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
+  }
   if (!a_mn && !b_mn) {
     if (bn == 256) { DISPATCH2(256, false, false) }
     if (bn == 240) { DISPATCH2(240, false, false) }
@@ -439,7 +444,7 @@ extern "C" __attribute__((visibility("default"))) int b200_ag_gemm(
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int tiles_n = (N + bn - 1) / bn;
   if (cudaMemsetAsync(done, 0, sizeof(int) * tiles_n, st) != cudaSuccess) return -2;
-  GemmParams p;
+  GemmParams p = {};
   p.M = M; p.N = N; p.K1 = K; p.K2 = 0; p.ldc = ldc; p.ld_resid = 0; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = nullptr; p.err = err;
   AgParams ag = {};

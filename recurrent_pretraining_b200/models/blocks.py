@@ -19,6 +19,7 @@ import os
 from ..ops import functional as ops
 
 FUSE_SWIGLU = os.environ.get("B200_FUSE_SWIGLU", "1") == "1"
+FUSE_ROPE = os.environ.get("B200_FUSE_ROPE", "1") == "1"
 
 
 # ------------------------------------------------------------------------------------------
@@ -170,6 +171,12 @@ class CausalSelfAttention(nn.Module):
     def forward(self, x, rope, mask=None):
         B, S, E = x.shape
         cos, sin = rope
+        plain = not (self.config.qk_norm or self.monitoring or self.config.attn_impl == "debug-skip")
+        if (plain and FUSE_ROPE and x.is_cuda and self.config.clip_qkv is None and self.Wqkv.bias is None
+                and self.config.rope_settings.use_rope):
+            # bias + rotation ride in the epilogue of the QKV GEMM
+            y = ops.qkv_rope_attention(x, self.Wqkv.weight, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+            return self.proj(y)
         qkv = self.Wqkv(x)
         if self.config.clip_qkv is not None:
             qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)

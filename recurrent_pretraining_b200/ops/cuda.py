@@ -51,6 +51,8 @@ _ce_rows = _sig("b200_ce_rows", [_vp] * 6 + [_i] * 4 + [_f, _i, _f, _vp])
 _set_2cta = _sig("b200_gemm_set_2cta", [_i])
 
 OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_BF16_RESID, OUT_SWIGLU = range(5)
+OUT_BF16_ROPE = 7
+_set_rope = _sig("b200_gemm_set_rope", [_vp, _vp, _vp, _i, _i, _i])
 
 
 def set_gemm_2cta(enable: bool) -> bool:
@@ -116,8 +118,9 @@ def _mat(t: torch.Tensor):
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, resid=None, n_out=None, bn=0,
-         max_ctas=0):
-    """C[M,N] (+)= A B^T.  ``a``: [M,K] (or [K,M] if a_mn), ``b``: [N,K] (or [K,N] if b_mn)."""
+         max_ctas=0, rope=None):
+    """C[M,N] (+)= A B^T.  ``a``: [M,K] (or [K,M] if a_mn), ``b``: [N,K] (or [K,N] if b_mn).
+    ``rope`` (OUT_BF16_ROPE): (cos [S, D/2] fp32, sin, bias flat fp32 or None, S, D, width of the q+k columns)."""
     a, ar, ac, lda = _mat(a)
     b, br, bc, ldb = _mat(b)
     M, K1 = (ac, ar) if a_mn else (ar, ac)
@@ -134,13 +137,17 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, 
     if n_out is not None:
         N = n_out
     if out is None:
-        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU) else torch.float32
+        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU, OUT_BF16_ROPE) else torch.float32
         out = torch.empty((M, N), dtype=dt, device=a.device)
     assert out.dim() == 2 and out.stride(1) == 1 and out.shape[0] == M and out.shape[1] == N
     ld_resid = 0
     if resid is not None:
         assert resid.dtype == BF16 and resid.stride(1) == 1
         ld_resid = resid.stride(0)
+    if out_mode == OUT_BF16_ROPE:
+        cos, sin, bias, S, D, width = rope
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[-1] * 2 == D
+        _set_rope(_ptr(cos), _ptr(sin), _ptr(bias), int(S), int(D), int(width))
     rc = _gemm(_ptr(a), _ptr(a2), _ptr(b), _ptr(out), _ptr(resid), M, N, K1, K2, lda, lda2, ldb, out.stride(0),
                ld_resid, int(a_mn), int(b_mn), out_mode, bn, max_ctas, _stream(), _ptr(err_word(a.device)))
     _check(rc, "b200_gemm")

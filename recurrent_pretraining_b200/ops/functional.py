@@ -301,6 +301,47 @@ class _RopeAttention(torch.autograd.Function):
         return dqkv, dbias, None, None, None, None, None, None
 
 
+class _QKVRopeAttention(torch.autograd.Function):
+    """x [B,S,E], Wqkv -> causal attention output: the QKV projection adds the q/k bias and rotates q and k in its GEMM
+    epilogue (no separate pass over the packed tensor), then the attention kernel runs on the packed rotated tensor.
+    Backward: attention backward into one packed buffer, inverse rotation in place, then the two Wqkv GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, qk_bias, cos, sin, n_head, n_kv, head_dim, scale):
+        C = cuda_backend()
+        B, S, E = x.shape
+        x2 = x.reshape(-1, E)
+        bias = None if qk_bias is None else qk_bias.detach().float().reshape(-1).contiguous()
+        width = (n_head + n_kv) * head_dim
+        qkv_r = C.gemm(x2, _lp(weight), out_mode=C.OUT_BF16_ROPE,
+                       rope=(cos, sin, bias, S, head_dim, width)).view(B, S, -1)
+        o, lse = C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale)
+        ctx.save_for_backward(x2, weight, qkv_r, o, lse, cos, sin)
+        ctx.meta = (n_head, n_kv, head_dim, scale, qk_bias is not None, x.shape)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        C = cuda_backend()
+        x2, weight, qkv_r, o, lse, cos, sin = ctx.saved_tensors
+        n_head, n_kv, head_dim, scale, has_bias, xshape = ctx.meta
+        dqkv = C.attention_bwd(do.contiguous(), qkv_r, o, lse, n_head, n_kv, head_dim, scale)
+        dqkv, dbias = C.rope_bwd_(dqkv, cos, sin, n_head, n_kv, head_dim, has_bias and ctx.needs_input_grad[2])
+        d2 = dqkv.view(-1, dqkv.shape[-1])
+        dx = C.gemm_nn(d2, _lp(weight)).view(xshape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(d2, x2, weight) if ctx.needs_input_grad[1] else None
+        return dx, dw, dbias, None, None, None, None, None, None
+
+
+def qkv_rope_attention(x, weight, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int, scale: float | None = None):
+    """Wqkv projection + qk-bias + RoPE + causal attention; the GPU path fuses bias and rotation into the GEMM."""
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if x.is_cuda and cos.dtype == torch.float32 and cos.shape[0] == x.shape[1]:
+        return _QKVRopeAttention.apply(x, weight, qk_bias, cos.contiguous(), sin.contiguous(), n_head, n_kv, head_dim,
+                                       scale)
+    return rope_attention(linear(x, weight), qk_bias, cos, sin, n_head, n_kv, head_dim, scale)
+
+
 def rope_attention(qkv, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int, scale: float | None = None):
     """Fused qk-bias + RoPE + causal attention on a packed qkv tensor; returns [B, S, n_head*head_dim]."""
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale

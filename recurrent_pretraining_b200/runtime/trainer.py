@@ -53,9 +53,16 @@ def set_torch_flags(cfg) -> None:
 def setup_fabric(cfg) -> Fabric:
     sync = cfg.grad_sync
     strategy = cfg.fabric_strategy
-    if strategy not in ("simple-ddp", "ddp", "single", "zero"):
-        raise ValueError(f"fabric_strategy {strategy!r}: FSDP / AxoNN variants are delegated to external libraries in "
-                         "the reference and are not provided; use simple-ddp (p2p) or zero")
+    if strategy.startswith("fsdp"):
+        # The reference hands these names to Lightning's FSDP wrapper (train.py:115-142).  The sharded mode here covers
+        # what SHARD_GRAD_OP provides on one node: gradients are reduce-scattered, optimizer state lives 1/N per rank and
+        # the updated bf16 weights are pushed to every rank by the same kernel.
+        if sync not in (None, "p2p"):
+            raise ValueError(f"fabric_strategy {strategy!r} runs on the fused sharded path (grad_sync: p2p)")
+        sync = "p2p" if torch.cuda.is_available() else "flat"
+    elif strategy not in ("simple-ddp", "ddp", "single", "zero"):
+        raise ValueError(f"fabric_strategy {strategy!r}: tensor parallelism through AxoNN is an external library in the "
+                         "reference and is not provided; use simple-ddp, zero or fsdp-*")
     fabric = Fabric.from_env(grad_sync=sync, precision=cfg.fabric_precision)
     if sync is None and fabric.is_distributed and fabric.device.type == "cuda":
         fabric.grad_sync = "p2p"

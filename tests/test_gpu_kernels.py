@@ -270,3 +270,18 @@ def test_flash_attention_backward(C, B, S, H, Hkv, D, variant):
         got, ref_g = dqkv[..., sl].float(), x.grad[..., sl]
         err = (got - ref_g).abs().max().item()
         assert err <= 3e-2 * ref_g.abs().max().item() + 1e-3, (name, err, ref_g.abs().max().item())
+
+
+@pytest.mark.parametrize("T,S,H,D,E", [(128, 64, 5, 96, 264), (520, 260, 3, 64, 136), (4096, 4096, 2, 96, 72)])
+def test_gemm_rope_epilogue(C, T, S, H, D, E):
+    """QKV projection whose epilogue adds the q/k bias and rotates q and k, against GEMM followed by the rope kernel."""
+    x, w = _rand(T, E), _rand(3 * H * D, E, scale=0.3)
+    bias = torch.randn(2 * H * D, device="cuda") * 0.1
+    cos, sin = (t.cuda().contiguous() for t in ref.rope_tables(D, S))
+    got = C.gemm(x, w, out_mode=C.OUT_BF16_ROPE, rope=(cos, sin, bias, S, D, 2 * H * D))
+    torch.cuda.synchronize()
+    assert C.check_device_status() == 0
+    qkv = (x.float() @ w.float().T).view(T // S, S, 3 * H * D)
+    q, k, v = ref.qk_bias_rope(qkv, bias.view(2, 1, H, D), cos, sin, H, H, D)
+    want = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
+    _close(got, want, 2e-2, 2e-2 * math.sqrt(E))
