@@ -185,3 +185,18 @@ def test_offline_pipeline_tokenizer_pack_shuffle_count(tmp_path):
                        plan_for_later_rank_expansion_to=0)
     rows = list(ds)
     assert len(rows) == after["rows"] and rows[0].shape == (33,)
+
+
+def test_every_launch_config_parses_and_names_a_known_model(tmp_path):
+    import glob
+
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.settings import parse_cli
+
+    files = sorted(glob.glob(f"{ROOT}/launch_configs/*.yaml"))
+    assert len(files) >= 7
+    for f in files:
+        cfg = parse_cli([f"--config={f}", f"--out_dir={tmp_path}"])
+        mc = ModelConfig.from_name(cfg.model_name, **(cfg.model_overwrite or {}))
+        assert mc.n_embd % mc.num_attention_heads == 0 and cfg.micro_batch_size >= 1, f
+        assert cfg.optimizer and cfg.fabric_strategy, f
