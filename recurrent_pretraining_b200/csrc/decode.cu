@@ -15,6 +15,8 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, const 
                                    const int* __restrict__ pos, __nv_bfloat16* __restrict__ q_out,
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int B,
                                    int H, int Hkv, int D, int Lmax) {
+  pdl_wait();
+  pdl_trigger();
   const int wq = H * D, wk = Hkv * D, wtot = wq + 2 * wk;
   const int vpr = wtot >> 3;
   const int gid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -56,6 +58,8 @@ __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ lens, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int Hkv, int Lmax, float scale_log2) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int D = 32 * DPL;
   constexpr int NG = 8;  // key groups per CTA
   const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
@@ -132,6 +136,8 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 template <int DPL>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int nsplit, int total /* B*H */) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int D = 32 * DPL;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -162,6 +168,8 @@ __global__ void __launch_bounds__(512)
 kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, float* __restrict__ kl_out,
                int* __restrict__ exited, int* __restrict__ steps_taken, long long* __restrict__ token_out,
                int* __restrict__ live_count, int V, float threshold, int step, int armed) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[16];
   __shared__ int redi[16];
   __shared__ float s_val;
@@ -227,6 +235,8 @@ kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, 
 
 // out = bf16(work); work = 0   (consumer of a split-K skinny GEMM that also re-arms its accumulator)
 __global__ void cast_zero_kernel(float* __restrict__ work, __nv_bfloat16* __restrict__ out, size_t n) {
+  pdl_wait();
+  pdl_trigger();
   const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i + 4 <= n) {
     const float4 v = *reinterpret_cast<float4*>(work + i);
@@ -245,6 +255,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_pair_kernel(void* __restrict__ a, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w1,
                         const float* __restrict__ w2, __nv_bfloat16* __restrict__ y1, __nv_bfloat16* __restrict__ y2,
                         int E, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[8];
   __shared__ float s_tot;
   const size_t row = blockIdx.x;
@@ -301,7 +313,7 @@ using namespace b200;
 B200_API int b200_cast_zero(float* work, void* out, long long n, void* stream) {
   if (n <= 0) return 0;
   const size_t threads = (static_cast<size_t>(n) + 3) / 4;
-  cast_zero_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(cast_zero_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       work, reinterpret_cast<__nv_bfloat16*>(out), static_cast<size_t>(n));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -314,8 +326,8 @@ B200_API int b200_add_rmsnorm_pair(void* a, int a_is_f32, const void* x, const f
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(y1);
   __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(y2);
-  if (a_is_f32) add_rmsnorm_pair_kernel<true><<<rows, 256, 0, st>>>(a, xb, w1, w2, o1, o2, E, eps);
-  else add_rmsnorm_pair_kernel<false><<<rows, 256, 0, st>>>(a, xb, w1, w2, o1, o2, E, eps);
+  if (a_is_f32) launch_k(add_rmsnorm_pair_kernel<true>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
+  else launch_k(add_rmsnorm_pair_kernel<false>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -324,7 +336,7 @@ B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float
                               int Lmax, void* stream) {
   if (D % 8) return -1;
   const int n = B * ((H + 2 * Hkv) * D / 8);
-  rope_append_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(rope_append_kernel, dim3((n + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(qkv), qk_bias, cosT, sinT, pos, reinterpret_cast<__nv_bfloat16*>(q_out),
       reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), B, H, Hkv, D, Lmax);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -344,8 +356,8 @@ B200_API int b200_decode_attention(const void* q, const void* k_cache, const voi
   __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out);
   const int total = B * H;
 #define RUN(DPL)                                                                                         \
-  decode_attn_kernel<DPL><<<grid, 128, 0, st>>>(qb, kb, vb, lens, part_o, part_ml, H, Hkv, Lmax, sl2);  \
-  decode_attn_merge_kernel<DPL><<<(total + 3) / 4, 128, 0, st>>>(part_o, part_ml, ob, splits, total);
+  launch_k(decode_attn_kernel<DPL>, grid, dim3(128), 0, st, qb, kb, vb, lens, part_o, part_ml, H, Hkv, Lmax, sl2);  \
+  launch_k(decode_attn_merge_kernel<DPL>, dim3((total + 3) / 4), dim3(128), 0, st, part_o, part_ml, ob, splits, total);
   switch (D / 32) {
     case 1: RUN(1) break;
     case 2: RUN(2) break;
@@ -360,7 +372,7 @@ B200_API int b200_decode_attention(const void* q, const void* k_cache, const voi
 B200_API int b200_kl_exit(const float* logits, float* prev_logp, float* kl_out, int* exited, int* steps_taken,
                           long long* token_out, int* live_count, int B, int V, float threshold, int step, int armed,
                           void* stream) {
-  kl_exit_kernel<<<B, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, prev_logp, kl_out, exited, steps_taken,
+  launch_k(kl_exit_kernel, dim3(B), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream),logits, prev_logp, kl_out, exited, steps_taken,
                                                                       token_out, live_count, V, threshold, step, armed);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

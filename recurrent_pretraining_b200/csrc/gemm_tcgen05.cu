@@ -87,6 +87,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // everything above overlapped the predecessor's tail; operands and outputs are touched from here on
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -268,11 +270,18 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
-  kern<<<grid, 192, SMEM, stream>>>(ta, ta2, tb, p);
+  if (launch_k(kern, dim3(grid), dim3(192), SMEM, stream, ta, ta2, tb, p) != cudaSuccess) return -11;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace b200
+
+int g_b200_pdl = 0;
+extern "C" __attribute__((visibility("default"))) int b200_set_pdl(int on) {
+  const int old = g_b200_pdl;
+  g_b200_pdl = on ? 1 : 0;
+  return old;
+}
 
 namespace b200 {
 int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,

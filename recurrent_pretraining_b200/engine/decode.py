@@ -20,6 +20,7 @@ exited; a sequence's token is frozen at its first exit (recpre/raven_modeling_mi
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -27,6 +28,8 @@ from ..ops import cuda as K
 
 BF16 = torch.bfloat16
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
+_set_pdl = K._sig("b200_set_pdl", [_i])
+PDL = os.environ.get("B200_DECODE_PDL", "0") == "1"  # off until measured on the target box
 _skinny = K._sig("b200_gemm_skinny", [_vp] * 4 + [_i] * 7 + [_vp, _vp])
 _cast_zero = K._sig("b200_cast_zero", [_vp, _vp, C.c_longlong, _vp])
 _norm_pair = K._sig("b200_add_rmsnorm_pair", [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp])
@@ -228,17 +231,29 @@ class DecodeEngine:
         """Replay ``fn`` as a CUDA graph.  ``fn`` must be idempotent (read inputs, write separate outputs): it is
         executed once eagerly as a warm-up and once more during capture before the first replay."""
         if not self.use_graphs:
-            return fn()
+            return self._with_pdl(fn)
         g = self._graphs.get(key)
         if g is None:
-            fn()
+            self._with_pdl(fn)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = fn()
+                out = self._with_pdl(fn)
             g = self._graphs[key] = (graph, out)
         g[0].replay()
         return g[1]
+
+    @staticmethod
+    def _with_pdl(fn):
+        """Run ``fn`` with programmatic dependent launch on for the decode kernels: each kernel's prologue overlaps the
+        tail of its predecessor (the attribute is recorded into a graph at capture time)."""
+        if not PDL:
+            return fn()
+        old = _set_pdl(1)
+        try:
+            return fn()
+        finally:
+            _set_pdl(old)
 
     def _fresh_state(self, init_scale: float):
         self._seed += 1

@@ -102,5 +102,46 @@ def exit_flag():
     fabric.shutdown()
 
 
+def tensor_parallel():
+    """Two-way tensor parallel model against the unsharded model: same loss, gradient shards equal slices."""
+    import copy
+
+    from recurrent_pretraining_b200.parallel.tensor_parallel import gather_full_weight, tensor_parallelize
+
+    fabric = Fabric.from_env(backend="gloo", grad_sync="chunked")
+    rank, tp = fabric.global_rank, fabric.world_size
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("tiny-raven-cpu", **OV)
+    full = cfg.construct_model()
+    sharded = tensor_parallelize(copy.deepcopy(full))
+    ids = torch.randint(0, cfg.padded_vocab_size, (2, 65), generator=torch.Generator().manual_seed(5))
+    pair = torch.tensor([1, 2])
+    a = full(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair)["loss"]
+    b = sharded(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair)["loss"]
+    a.backward()
+    b.backward()
+    fp, sp = dict(full.named_parameters()), dict(sharded.named_parameters())
+    name = "transformer.core_block.0.attn.Wqkv.weight"
+    H, D, E = cfg.n_head, cfg.n_embd // cfg.n_head, cfg.n_embd
+    h = H // tp
+    want = torch.cat([fp[name].grad[sec * H * D:(sec + 1) * H * D].view(H, D, E)[rank * h:(rank + 1) * h].reshape(h * D, E)
+                      for sec in range(3)], 0)
+    g_qkv = (sp[name].grad - want).abs().max().item()
+    name2 = "transformer.core_block.1.mlp.proj.weight"
+    I = cfg.intermediate_size // tp
+    g_proj = (sp[name2].grad - fp[name2].grad[:, rank * I:(rank + 1) * I]).abs().max().item()
+    g_norm = (sp["transformer.ln_f.weight"].grad - fp["transformer.ln_f.weight"].grad).abs().max().item()
+    g_emb = (sp["transformer.wte.weight"].grad - fp["transformer.wte.weight"].grad).abs().max().item()
+    gathered = gather_full_weight(sp[name2].data, dim=1)
+    out = {"loss_full": a.item(), "loss_tp": b.item(), "g_qkv": g_qkv, "g_proj": g_proj, "g_norm": g_norm, "g_emb": g_emb,
+           "gather_ok": bool(torch.equal(gathered, fp[name2].data)),
+           "params_local": sum(p.numel() for p in sharded.parameters()), "params_full": sum(p.numel() for p in full.parameters())}
+    if rank == 0:
+        print("RESULT " + json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
-    {"parity": parity, "rank_failure": rank_failure, "exit_flag": exit_flag}[sys.argv[1]]()
+    {"parity": parity, "rank_failure": rank_failure, "exit_flag": exit_flag,
+     "tensor_parallel": tensor_parallel}[sys.argv[1]]()

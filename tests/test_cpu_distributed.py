@@ -59,3 +59,11 @@ def test_train_entry_point_runs_saves_and_resumes(tmp_path):
     assert (tmp_path / "run_config.json").exists() and (tmp_path / "model_config.json").exists()
     r2 = _torchrun(base + ["--max_steps=8"], 29619)
     assert "Resumed from" in r2.stdout and "step       8" in r2.stdout and "step       3 " not in r2.stdout
+
+
+def test_tensor_parallel_blocks_match_the_unsharded_model():
+    r = _torchrun([os.path.join(HERE, "cpu_dp_worker.py"), "tensor_parallel"], 29631)
+    res = _result(r)
+    assert abs(res["loss_full"] - res["loss_tp"]) < 1e-5, res
+    assert max(res["g_qkv"], res["g_proj"], res["g_norm"], res["g_emb"]) < 1e-5, res
+    assert res["gather_ok"] and res["params_local"] < res["params_full"]
