@@ -83,3 +83,7 @@ def test_example_scripts_run():
 
     demo.main(["--max_new_tokens", "3"])
     spec.main()
+    import examples.trajectory_analysis as traj
+
+    rows = traj.main(["--steps", "6", "--tokens", "3"])
+    assert len(rows) == 3 and all(len(r["xy"]) == 7 for r in rows)
