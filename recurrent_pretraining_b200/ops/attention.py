@@ -16,8 +16,26 @@ _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _fwd = K._sig("b200_attn_fwd", [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp])
 _bwd = K._sig("b200_attn_bwd", [_vp] * 7 + [_i] * 5 + [_f, _vp, _vp]) if hasattr(K.lib, "b200_attn_bwd") else None
 
+_set_variant = K._sig("b200_attn_set_fwd_variant", [_i])
+
+
+def set_fwd_variant(v: int) -> int:
+    """1: one query tile per CTA (P through shared memory); 2: two query tiles per CTA, P in tensor memory (default).
+    Returns the previous setting."""
+    return int(_set_variant(int(v)))
+
+
+_set_bwd_variant = K._sig("b200_attn_set_bwd_variant", [_i])
+
+
+def set_bwd_variant(v: int) -> int:
+    """1: query-major tiles (P and dS through shared memory); 2: transposed tiles with P^T / dS^T in tensor memory
+    (default).  Returns the previous setting."""
+    return int(_set_bwd_variant(int(v)))
+
+
 # Training runs on the native kernels (B200_NATIVE_ATTENTION=0 selects the library SDPA instead).  Measured on the
-# flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.256 ms / backward 1.13 ms, library forward 0.18 ms /
+# flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.256 ms / backward 1.04 ms, library forward 0.18 ms /
 # forward-recompute + backward + copies 1.15-1.24 ms; the whole training step is the same either way (728.8 vs 728.9 ms).
 ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "1") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
