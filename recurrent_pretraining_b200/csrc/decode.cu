@@ -10,20 +10,31 @@
 namespace b200 {
 
 // qkv: [B, (H + 2 Hkv) * D] for the new token of each sequence; pos[b]: its absolute position.
-__global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qk_bias,
+template <bool F32_IN>
+__global__ void rope_append_kernel(const void* __restrict__ qkv_in, const float* __restrict__ qk_bias,
                                    const float* __restrict__ cosT, const float* __restrict__ sinT,
                                    const int* __restrict__ pos, __nv_bfloat16* __restrict__ q_out,
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int B,
                                    int H, int Hkv, int D, int Lmax) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   const int wq = H * D, wk = Hkv * D, wtot = wq + 2 * wk;
   const int vpr = wtot >> 3;
   const int gid = blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= B * vpr) return;
   const int b = gid / vpr, c = (gid % vpr) << 3;
   const int p = pos[b];
-  uint4 v = reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(b) * wtot)[c >> 3];
+  uint4 v;
+  if constexpr (F32_IN) {  // the stream-K accumulator: round to bf16 as the plain GEMM store does, and re-arm it
+    float4* src = reinterpret_cast<float4*>(const_cast<float*>(reinterpret_cast<const float*>(qkv_in)) +
+                                            static_cast<size_t>(b) * wtot + c);
+    const float4 f0 = src[0], f1 = src[1];
+    src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    v = make_uint4(pack_bf16x2(f0.x, f0.y), pack_bf16x2(f0.z, f0.w), pack_bf16x2(f1.x, f1.y), pack_bf16x2(f1.z, f1.w));
+  } else {
+    v = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(qkv_in) + static_cast<size_t>(b) * wtot)[c >> 3];
+  }
   if (c < wq + wk) {
     const bool is_q = c < wq;
     const int cc = is_q ? c : c - wq;
@@ -58,8 +69,8 @@ __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ lens, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int Hkv, int Lmax, float scale_log2) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   constexpr int D = 32 * DPL;
   constexpr int NG = 8;  // key groups per CTA
   const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
@@ -81,30 +92,61 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const __nv_bfloat16* kb = kc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D + j * 8;
   const __nv_bfloat16* vb = vc + static_cast<size_t>(b) * Lmax * row + static_cast<size_t>(hk) * D + j * 8;
   const unsigned gmask = 0xFFFFu << (threadIdx.x & 16);  // the 16 lanes of this group inside the warp
-  for (int l = l0 + grp; l < l1; l += NG) {
-    float s = 0.f;
-    uint4 vv = make_uint4(0, 0, 0, 0);
-    if (active) {
-      const uint4 kk = *reinterpret_cast<const uint4*>(kb + l * row);
-      vv = *reinterpret_cast<const uint4*>(vb + l * row);
-      const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
+  // U keys per group and trip: all 2 U loads are in flight together (the walk is latency-bound otherwise: one
+  // dependent memory round trip per key), the U score reductions interleave, one softmax update covers the U keys
+  constexpr int U = 4;
+  for (int l = l0 + grp; l < l1; l += NG * U) {
+    uint4 kk[U], vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int lu = l + u * NG;
+      kk[u] = vv[u] = make_uint4(0, 0, 0, 0);
+      if (active && lu < l1) {
+        kk[u] = __ldg(reinterpret_cast<const uint4*>(kb + lu * row));
+        vv[u] = __ldg(reinterpret_cast<const uint4*>(vb + lu * row));
+      }
+    }
+    float s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t kw[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+      s[u] = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = unpack_bf16x2(kw[i]);
-        s += qv[2 * i] * f.x + qv[2 * i + 1] * f.y;
+        s[u] += qv[2 * i] * f.x + qv[2 * i + 1] * f.y;
       }
     }
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(gmask, s, o, 16);
-    const float mn = fmaxf(m, s);
-    const float alpha = exp2f(m - mn), p = exp2f(s - mn);
-    lsum = lsum * alpha + p;
-    const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+    for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = unpack_bf16x2(vw[i]);
-      acc[2 * i] = acc[2 * i] * alpha + p * f.x;
-      acc[2 * i + 1] = acc[2 * i + 1] * alpha + p * f.y;
+      for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(gmask, s[u], o, 16);
+    }
+    float mn = m;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (l + u * NG >= l1) s[u] = -INFINITY;   // u = 0 is always a real key, so mn is finite below
+      mn = fmaxf(mn, s[u]);
+    }
+    const float alpha = exp2f(m - mn);
+    float pu[U], psum = 0.f;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      pu[u] = exp2f(s[u] - mn);
+      psum += pu[u];
+    }
+    lsum = lsum * alpha + psum;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack_bf16x2(vw[i]);
+        acc[2 * i] += pu[u] * f.x;
+        acc[2 * i + 1] += pu[u] * f.y;
+      }
     }
     m = mn;
   }
@@ -136,22 +178,27 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 template <int DPL>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int nsplit, int total /* B*H */) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   constexpr int D = 32 * DPL;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (idx >= total) return;
-  float mm = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(static_cast<size_t>(idx) * nsplit + s) * 2]);
-  float ll = 0.f, o[DPL];
+  // lane s holds split s's (max, sum) -- one parallel load instead of a serial walk (nsplit <= 32, checked by the host)
+  const float2 ml = lane < nsplit ? *reinterpret_cast<const float2*>(part_ml + (static_cast<size_t>(idx) * nsplit + lane) * 2)
+                                  : make_float2(-INFINITY, 0.f);
+  float mm = ml.x;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+  const float a_mine = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - mm);
+  const float ll = warp_sum(ml.y * a_mine);
+  float o[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+#pragma unroll 4
   for (int s = 0; s < nsplit; ++s) {
+    const float a = __shfl_sync(0xffffffffu, a_mine, s);
     const size_t p = static_cast<size_t>(idx) * nsplit + s;
-    const float ms = part_ml[p * 2];
-    const float a = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-    ll += part_ml[p * 2 + 1] * a;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o[i] += part_o[p * D + lane + 32 * i] * a;
   }
@@ -168,8 +215,8 @@ __global__ void __launch_bounds__(512)
 kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, float* __restrict__ kl_out,
                int* __restrict__ exited, int* __restrict__ steps_taken, long long* __restrict__ token_out,
                int* __restrict__ live_count, int V, float threshold, int step, int armed) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   __shared__ float red[16];
   __shared__ int redi[16];
   __shared__ float s_val;
@@ -235,8 +282,8 @@ kl_exit_kernel(const float* __restrict__ logits, float* __restrict__ prev_logp, 
 
 // out = bf16(work); work = 0   (consumer of a split-K skinny GEMM that also re-arms its accumulator)
 __global__ void cast_zero_kernel(float* __restrict__ work, __nv_bfloat16* __restrict__ out, size_t n) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i + 4 <= n) {
     const float4 v = *reinterpret_cast<float4*>(work + i);
@@ -255,8 +302,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_pair_kernel(void* __restrict__ a, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w1,
                         const float* __restrict__ w2, __nv_bfloat16* __restrict__ y1, __nv_bfloat16* __restrict__ y2,
                         int E, float eps) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
   pdl_wait();
-  pdl_trigger();
   __shared__ float red[8];
   __shared__ float s_tot;
   const size_t row = blockIdx.x;
@@ -306,6 +353,108 @@ add_rmsnorm_pair_kernel(void* __restrict__ a, const __nv_bfloat16* __restrict__ 
   }
 }
 
+// Register-resident form of the kernel above for E % 8 == 0 and E <= 256 * 8 * NV: every thread owns NV vectors of
+// eight channels, all global loads (a, x, both weights) are issued before the first reduction, and nothing is staged
+// through y1 -- one memory round trip plus two block reductions instead of three dependent passes over the row.
+template <bool A_F32, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_pair_vec_kernel(void* __restrict__ a, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w1,
+                            const float* __restrict__ w2, __nv_bfloat16* __restrict__ y1, __nv_bfloat16* __restrict__ y2,
+                            int E, float eps) {
+  pdl_trigger();   // the successor may become resident now; it waits for this grid's completion before it reads
+  pdl_wait();
+  __shared__ float red[2][8];
+  const size_t row = blockIdx.x;
+  const int nvec = E >> 3;
+  float v[NV][8], g1[NV][8], g2[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int idx = threadIdx.x + k * 256;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[k][j] = 0.f; g1[k][j] = 1.f; g2[k][j] = 1.f; }
+    if (idx < nvec) {
+      const size_t off = row * E + static_cast<size_t>(idx) * 8;
+      float av[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+      if (x) xv = *reinterpret_cast<const uint4*>(x + off);
+      if (a) {
+        if constexpr (A_F32) {
+          float4* ap = reinterpret_cast<float4*>(reinterpret_cast<float*>(a) + off);
+          const float4 a0 = ap[0], a1 = ap[1];
+          ap[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+          ap[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          av[0] = a0.x; av[1] = a0.y; av[2] = a0.z; av[3] = a0.w;
+          av[4] = a1.x; av[5] = a1.y; av[6] = a1.z; av[7] = a1.w;
+        } else {
+          const uint4 ab = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a) + off);
+          const uint32_t aw[4] = {ab.x, ab.y, ab.z, ab.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 t = unpack_bf16x2(aw[j]); av[2 * j] = t.x; av[2 * j + 1] = t.y; }
+        }
+      }
+      if (w1) {
+        const float4 t0 = reinterpret_cast<const float4*>(w1)[2 * idx], t1 = reinterpret_cast<const float4*>(w1)[2 * idx + 1];
+        g1[k][0] = t0.x; g1[k][1] = t0.y; g1[k][2] = t0.z; g1[k][3] = t0.w;
+        g1[k][4] = t1.x; g1[k][5] = t1.y; g1[k][6] = t1.z; g1[k][7] = t1.w;
+      }
+      if (y2 && w2) {
+        const float4 t0 = reinterpret_cast<const float4*>(w2)[2 * idx], t1 = reinterpret_cast<const float4*>(w2)[2 * idx + 1];
+        g2[k][0] = t0.x; g2[k][1] = t0.y; g2[k][2] = t0.z; g2[k][3] = t0.w;
+        g2[k][4] = t1.x; g2[k][5] = t1.y; g2[k][6] = t1.z; g2[k][7] = t1.w;
+      }
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack_bf16x2(xw[j]);
+        const float s0 = bf2f(f2bf(av[2 * j] + t.x)), s1 = bf2f(f2bf(av[2 * j + 1] + t.y));
+        v[k][2 * j] = s0;
+        v[k][2 * j + 1] = s1;
+        ss += s0 * s0 + s1 * s1;
+      }
+    }
+  }
+  auto block_total = [&](float t, int which) {
+    t = warp_sum(t);
+    if ((threadIdx.x & 31) == 0) red[which][threadIdx.x >> 5] = t;
+    __syncthreads();
+    float r = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r += red[which][k];
+    return r;
+  };
+  const float rstd1 = rsqrtf(block_total(ss, 0) / static_cast<float>(E) + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx < nvec) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf2f(f2bf(bf2f(f2bf(v[k][j] * rstd1)) * g1[k][j]));
+        ss2 += v[k][j] * v[k][j];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(v[k][2 * j], v[k][2 * j + 1]);
+      *reinterpret_cast<uint4*>(y1 + row * E + static_cast<size_t>(idx) * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (!y2) return;
+  const float rstd2 = rsqrtf(block_total(ss2, 1) / static_cast<float>(E) + eps);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx < nvec) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16x2(bf2f(f2bf(v[k][2 * j] * rstd2)) * g2[k][2 * j], bf2f(f2bf(v[k][2 * j + 1] * rstd2)) * g2[k][2 * j + 1]);
+      *reinterpret_cast<uint4*>(y2 + row * E + static_cast<size_t>(idx) * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -326,19 +475,38 @@ B200_API int b200_add_rmsnorm_pair(void* a, int a_is_f32, const void* x, const f
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(y1);
   __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(y2);
-  if (a_is_f32) launch_k(add_rmsnorm_pair_kernel<true>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
+  const int nv = (E % 8 == 0) ? (E / 8 + 255) / 256 : 0;
+  const bool aligned = !((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y1) |
+                          reinterpret_cast<uintptr_t>(y2) | reinterpret_cast<uintptr_t>(w1) | reinterpret_cast<uintptr_t>(w2)) & 15);
+#define PAIR_VEC(NV)                                                                                                   \
+  if (a_is_f32) launch_k(add_rmsnorm_pair_vec_kernel<true, NV>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps); \
+  else launch_k(add_rmsnorm_pair_vec_kernel<false, NV>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
+  if (aligned && nv == 1) { PAIR_VEC(1) }
+  else if (aligned && nv == 2) { PAIR_VEC(2) }
+  else if (aligned && nv == 3) { PAIR_VEC(3) }
+  else if (aligned && nv == 4) { PAIR_VEC(4) }
+  else if (a_is_f32) launch_k(add_rmsnorm_pair_kernel<true>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
   else launch_k(add_rmsnorm_pair_kernel<false>, dim3(rows), dim3(256), 0, st, a, xb, w1, w2, o1, o2, E, eps);
+#undef PAIR_VEC
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// qkv_is_f32 != 0: qkv is the fp32 accumulator of a stream-K skinny GEMM (cleared after reading), else bf16.
 B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float* cosT, const float* sinT,
                               const int* pos, void* q_out, void* k_cache, void* v_cache, int B, int H, int Hkv, int D,
-                              int Lmax, void* stream) {
+                              int Lmax, void* stream, int qkv_is_f32) {
   if (D % 8) return -1;
   const int n = B * ((H + 2 * Hkv) * D / 8);
-  launch_k(rope_append_kernel, dim3((n + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-      reinterpret_cast<const __nv_bfloat16*>(qkv), qk_bias, cosT, sinT, pos, reinterpret_cast<__nv_bfloat16*>(q_out),
-      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), B, H, Hkv, D, Lmax);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  __nv_bfloat16* qo = reinterpret_cast<__nv_bfloat16*>(q_out);
+  __nv_bfloat16* kc = reinterpret_cast<__nv_bfloat16*>(k_cache);
+  __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(v_cache);
+  if (qkv_is_f32)
+    launch_k(rope_append_kernel<true>, dim3((n + 255) / 256), dim3(256), 0, st, qkv, qk_bias, cosT, sinT, pos, qo, kc, vc,
+             B, H, Hkv, D, Lmax);
+  else
+    launch_k(rope_append_kernel<false>, dim3((n + 255) / 256), dim3(256), 0, st, qkv, qk_bias, cosT, sinT, pos, qo, kc, vc,
+             B, H, Hkv, D, Lmax);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -346,7 +514,7 @@ B200_API int b200_rope_append(const void* qkv, const float* qk_bias, const float
 B200_API int b200_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* lens, void* out,
                                    float* part_o, float* part_ml, int B, int H, int Hkv, int D, int Lmax, int splits,
                                    float scale, void* stream) {
-  if (D % 32 || D > 128 || splits < 1 || ((Hkv * D) % 8)) return -1;
+  if (D % 32 || D > 128 || splits < 1 || splits > 32 || ((Hkv * D) % 8)) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const float sl2 = scale * 1.4426950408889634f;
   dim3 grid(splits, H, B);

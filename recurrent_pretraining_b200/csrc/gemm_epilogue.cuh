@@ -27,6 +27,9 @@ struct GemmParams {
   const float* rope_sin;
   const float* rope_bias;
   int rope_S, rope_D, rope_width;
+  int streamk;    // OUT_F32_T_ATOMIC: every CTA takes an equal contiguous share of the (tile, k-block) space
+  int early_a;    // the A operand does not depend on the preceding kernel: its first tiles are requested before the
+                  // programmatic-dependent-launch wait (no effect without that launch attribute)
 };
 
 // taddr: TMEM address of (this warp's lane quadrant, first accumulator column); row: global row of this thread;

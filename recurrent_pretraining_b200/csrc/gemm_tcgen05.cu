@@ -43,9 +43,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   // accumulator width in TMEM columns: SwiGLU keeps gate and up side by side
   constexpr int ACC_COLS = (MODE == OUT_SWIGLU) ? 2 * BN : BN;
   static_assert(ACC_COLS <= 256, "accumulator too wide");
-  constexpr int ACC_STRIDE = 256;
+  // two accumulators; tensor memory is allocated in powers of two >= 32 columns, and only as much as they need, so
+  // that a dependent kernel launched early (programmatic dependent launch) can allocate beside a resident one
+  constexpr int ACC_STRIDE = ACC_COLS <= 16 ? 16 : (ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256)));
+  constexpr int TMEM_COLS = 2 * ACC_STRIDE;
   constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
 
+  pdl_trigger();   // a dependent kernel may become resident beside this one; it waits for this grid before it reads
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
@@ -65,6 +69,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int nk1 = (p.K1 + BK - 1) / BK;
   const int nk2 = (p.K2 + BK - 1) / BK;
   const int nk = nk1 + nk2;
+  // Work items of this CTA, by index: (output tile, k-block range).  Default: items blockIdx.x, +gridDim.x, ... of the
+  // (tile, K range) list.  Stream-K: the CTA owns units [u0, u1) of the flattened (tile, k-block) space -- an equal
+  // share for every CTA, whatever the tile count -- and its i-th item is the part of tile u0 / nk + i inside it.
+  const long long sk_total = static_cast<long long>(tiles_m) * tiles_n * nk;
+  const long long sk_u0 = sk_total * blockIdx.x / gridDim.x, sk_u1 = sk_total * (blockIdx.x + 1) / gridDim.x;
+  const int sk_t0 = static_cast<int>(sk_u0 / nk);
+  auto work_item = [&](int i, int& ot, int& kb0, int& kb1) -> bool {
+    if (p.streamk) {
+      ot = sk_t0 + i;
+      const long long base = static_cast<long long>(ot) * nk;
+      if (base >= sk_u1 || sk_u0 >= sk_u1) return false;
+      kb0 = i == 0 ? static_cast<int>(sk_u0 - base) : 0;
+      kb1 = sk_u1 - base < nk ? static_cast<int>(sk_u1 - base) : nk;
+      return true;
+    }
+    const int tile = blockIdx.x + i * gridDim.x;
+    if (tile >= num_tiles) return false;
+    ot = tile / ksplit;
+    const int ks = tile % ksplit;
+    kb0 = static_cast<int>(static_cast<long long>(nk) * ks / ksplit);
+    kb1 = static_cast<int>(static_cast<long long>(nk) * (ks + 1) / ksplit);
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -80,15 +107,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();      // everything above overlapped the predecessor's tail; operands and outputs are touched from here on
-  pdl_trigger();
+  // Everything above overlapped the predecessor's tail; operands and outputs are touched from here on.  With early_a
+  // the A operand is constant data (decode weights): the producer thread starts streaming it before it waits for the
+  // predecessor, which only produces the B operand.
+  const bool early_thread = p.early_a && threadIdx.x == 0;
+  if (!early_thread) pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -98,37 +128,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (nk2 > 0) tma_prefetch_desc(&tmA2);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int ot = tile / ksplit, ks = tile % ksplit;
-        const int m0 = (ot % tiles_m) * BM;
-        const int n0 = (ot / tiles_m) * BN;
-        const int kb0 = static_cast<int>(static_cast<long long>(nk) * ks / ksplit);
-        const int kb1 = static_cast<int>(static_cast<long long>(nk) * (ks + 1) / ksplit);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
-          uint8_t* sa = smem + s * L::STAGE_BYTES;
-          uint8_t* sb = sa + L::A_BYTES;
-          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-          const bool second = kb >= nk1;
-          const int ka = (second ? (kb - nk1) : kb) * BK;          // k offset inside the A operand
-          const int kbcol = second ? (p.K1 + ka) : ka;             // k offset inside B
-          if constexpr (!A_MN) {
-            if (second) tma_load_2d(sa, &tmA2, &full_bar[s], ka, m0);
-            else tma_load_2d(sa, &tmA, &full_bar[s], ka, m0);
-          } else {
+      // phase 0 (early_a only): A tiles of the first STAGES k-blocks, before the wait for the predecessor;
+      // phase 1: everything else (for those first k-blocks only the B tiles are left)
+      for (int phase = early_thread ? 0 : 1; phase < 2 && ok; ++phase) {
+        it = 0;
+        int ot, kb0, kb1;
+        bool more = true;
+        for (int wi = 0; ok && more && work_item(wi, ot, kb0, kb1); ++wi) {
+          const int m0 = (ot % tiles_m) * BM;
+          const int n0 = (ot / tiles_m) * BN;
+          for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            if (phase == 0 && it >= STAGES) { more = false; break; }
+            const bool a_done = early_thread && phase == 1 && it < STAGES;   // loaded in phase 0
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            uint8_t* sa = smem + s * L::STAGE_BYTES;
+            uint8_t* sb = sa + L::A_BYTES;
+            const bool second = kb >= nk1;
+            const int ka = (second ? (kb - nk1) : kb) * BK;          // k offset inside the A operand
+            const int kbcol = second ? (p.K1 + ka) : ka;             // k offset inside B
+            if (!a_done) {
+              if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_WAIT_STAGE_EMPTY)) { ok = false; break; }
+              mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+              if constexpr (!A_MN) {
+                if (second) tma_load_2d(sa, &tmA2, &full_bar[s], ka, m0);
+                else tma_load_2d(sa, &tmA, &full_bar[s], ka, m0);
+              } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, ka);
-          }
-          if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[s], kbcol, n0);
-            if constexpr (MODE == OUT_SWIGLU) tma_load_2d(sb + L::B_BYTES, &tmB, &full_bar[s], kbcol, n0 + p.swiglu_n);
-          } else {
+                for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[s], m0 + c * 64, ka);
+              }
+            }
+            if (phase == 0) continue;
+            if constexpr (!B_MN) {
+              tma_load_2d(sb, &tmB, &full_bar[s], kbcol, n0);
+              if constexpr (MODE == OUT_SWIGLU) tma_load_2d(sb + L::B_BYTES, &tmB, &full_bar[s], kbcol, n0 + p.swiglu_n);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, kbcol);
+              for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, kbcol);
+            }
           }
         }
+        if (phase == 0) pdl_wait();
       }
       // drain: every issued load must have landed before the CTA may exit
       const uint32_t issued = it;
@@ -146,15 +186,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      int ot, kb0, kb1;
+      for (int wi = 0; ok && work_item(wi, ot, kb0, kb1); ++wi, ++tcount) {
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
-        const int ks = tile % ksplit;
-        const int kb0 = static_cast<int>(static_cast<long long>(nk) * ks / ksplit);
-        const int kb1 = static_cast<int>(static_cast<long long>(nk) * (ks + 1) / ksplit);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -184,10 +222,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+    int ot, kb0, kb1;
+    for (int wi = 0; work_item(wi, ot, kb0, kb1); ++wi, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      const int ot = tile / ksplit;
       const int m0 = (ot % tiles_m) * BM;
       const int n0 = (ot / tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
@@ -205,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -268,6 +306,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.ksplit > 1 ? p.ksplit : 1);
   int grid = tiles < num_sms() ? tiles : num_sms();
+  if (p.streamk) {  // one CTA per SM as long as each gets at least four k-blocks
+    const long long units = static_cast<long long>(tiles) * ((p.K1 + BK - 1) / BK + (p.K2 + BK - 1) / BK);
+    grid = units / 4 < num_sms() ? static_cast<int>(units / 4 > 0 ? units / 4 : 1) : num_sms();
+  }
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
   if (launch_k(kern, dim3(grid), dim3(192), SMEM, stream, ta, ta2, tb, p) != cudaSuccess) return -11;
@@ -391,6 +433,9 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
 }
 
 
+static int g_skinny_streamk = 1;
+B200_API int b200_skinny_set_streamk(int on) { const int old = g_skinny_streamk; g_skinny_streamk = on; return old; }
+
 // Skinny (decode) GEMM:  out[Bt, N] = x[Bt, K] * W[N, K]^T  for Bt <= 64, computed as W * x^T so that the streamed
 // weight rows fill the 128-row MMA dimension and every SM pulls its own slice of W.  When N/128 tiles cannot occupy
 // the machine the K range is split and partial sums are accumulated with fp32 atomics into `work` ([Bt, N] fp32,
@@ -408,16 +453,16 @@ B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* wo
   if (rc) return rc;
   const int tiles = (N + BM - 1) / BM;
   const int nk = (K + BK - 1) / BK;
-  int ksplit = 1;
-  if (work && tiles < num_sms()) {
-    ksplit = (num_sms() + tiles - 1) / tiles;
-    if (ksplit > nk / 4) ksplit = nk / 4 > 0 ? nk / 4 : 1;
-    if (ksplit > 16) ksplit = 16;
-  }
+  // Fewer weight-row tiles than SMs: stream-K.  A fixed K split leaves tiles * ksplit work items, which rarely divide
+  // by the SM count (N = 5280: 42 tiles * 4 = 168 items on 148 SMs ran as two waves, 57 % of the machine); with
+  // stream-K every SM streams the same number of weight bytes.
+  const bool streamk = work && tiles < num_sms() && nk >= 8 && g_skinny_streamk;
   GemmParams p = {};
   p.M = N; p.N = Bt; p.K1 = K; p.K2 = 0; p.ld_resid = 0; p.swiglu_n = 0; p.resid = nullptr; p.err = err;
-  p.ksplit = ksplit;
-  if (ksplit > 1) {
+  p.ksplit = 1;
+  p.streamk = streamk ? 1 : 0;
+  p.early_a = 1;   // W is constant between launches: stream it while the predecessor (which produces x) still runs
+  if (streamk) {
     // zero_work = 0: the caller guarantees `work` is already zero (its consumer kernels clear it after reading)
     if (zero_work && cudaMemsetAsync(work, 0, static_cast<size_t>(Bt) * N * sizeof(float), st) != cudaSuccess)
       return -31;

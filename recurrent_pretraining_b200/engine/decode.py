@@ -29,11 +29,11 @@ from ..ops import cuda as K
 BF16 = torch.bfloat16
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _set_pdl = K._sig("b200_set_pdl", [_i])
-PDL = os.environ.get("B200_DECODE_PDL", "0") == "1"  # measured slower on B200 (33.9 vs 30.4 ms per token): off
+PDL = os.environ.get("B200_DECODE_PDL", "0") == "1"  # measured within noise of off (23.1-23.5 vs 23.5 ms per token): off
 _skinny = K._sig("b200_gemm_skinny", [_vp] * 4 + [_i] * 7 + [_vp, _vp])
 _cast_zero = K._sig("b200_cast_zero", [_vp, _vp, C.c_longlong, _vp])
 _norm_pair = K._sig("b200_add_rmsnorm_pair", [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp])
-_rope_append = K._sig("b200_rope_append", [_vp] * 8 + [_i] * 5 + [_vp])
+_rope_append = K._sig("b200_rope_append", [_vp] * 8 + [_i] * 5 + [_vp, _i])
 _decode_attn = K._sig("b200_decode_attention", [_vp] * 7 + [_i] * 6 + [_f, _vp])
 _kl_exit = K._sig("b200_kl_exit", [_vp] * 7 + [_i, _i, _f, _i, _i, _vp])
 
@@ -100,7 +100,9 @@ class DecodeEngine:
         self.cache = StaticRecurrentKVCache(self.P + rec_slots + self.Cn, max_batch, max_len, self.Hkv, self.D,
                                             self.dev, self.P, self.R, self.Cn, compress)
         self.use_graphs = use_graphs
-        self.splits = attn_splits or max(1, min(8, (2 * 148) // max(1, max_batch * self.H)))
+        # flash-decoding splits of the key range: enough CTAs (128 threads each) to fill every SM's thread slots at small
+        # batch -- the per-key walk is latency-bound, so more, shorter walks win (B=1: 16 splits, B=8: 5, B>=32: 1)
+        self.splits = attn_splits or max(1, min(16, (16 * 148) // max(1, max_batch * self.H)))
         cos, sin = model._rope(max_len)
         self.cos, self.sin = cos.float().contiguous(), sin.float().contiguous()
         d = self.dev
@@ -125,8 +127,9 @@ class DecodeEngine:
         self._graphs: dict = {}
         self._qk_bias = {}
         self._norm_w: dict = {}
-        # persistent split-K accumulator (only the narrow E-wide outputs are ever split); kept zero between uses
-        self.work = torch.zeros(max_batch * 2 * self.E, dtype=torch.float32, device=d)
+        # persistent fp32 accumulator of the stream-K skinny GEMMs (outputs up to the packed qkv width: qkv, attn.proj,
+        # mlp.proj, adapter); kept zero between uses -- every consumer clears what it reads
+        self.work = torch.zeros(max_batch * max(2 * self.E, (self.H + 2 * self.Hkv) * self.D), dtype=torch.float32, device=d)
         self.weight_bytes_per_recurrence = sum(p.numel() * 2 for n, p in model.named_parameters()
                                                if ".core_block." in n or ".adapter." in n)
 
@@ -175,13 +178,13 @@ class DecodeEngine:
 
     def _attention(self, attn, h, slot: int):
         B = h.shape[0]
-        qkv = self._linear(h, attn.Wqkv.weight)
+        qkv = self._linear(h, attn.Wqkv.weight, keep_f32=True)   # bf16, or the fp32 stream-K accumulator
         q = torch.empty(B, self.H * self.D, dtype=BF16, device=h.device)
         kc, vc = self.cache.k[slot], self.cache.v[slot]
         bias = self._bias(attn)
         K._check(_rope_append(qkv.data_ptr(), K._ptr(bias), self.cos.data_ptr(), self.sin.data_ptr(),
                               self.pos.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, self.H, self.Hkv,
-                              self.D, self.Lmax, K._stream()), "rope_append")
+                              self.D, self.Lmax, K._stream(), int(qkv.dtype == torch.float32)), "rope_append")
         o = torch.empty_like(q)
         K._check(_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.lens.data_ptr(), o.data_ptr(),
                               self.part_o.data_ptr(), self.part_ml.data_ptr(), B, self.H, self.Hkv, self.D, self.Lmax,

@@ -23,7 +23,8 @@ def small_model():
     return RavenForCausalLM.from_training_model(cfg.construct_model()).to(torch.bfloat16).cuda().eval()
 
 
-@pytest.mark.parametrize("B,N,K", [(1, 480, 480), (8, 1440, 480), (33, 2560, 1280), (64, 4096, 5280), (5, 200, 136)])
+@pytest.mark.parametrize("B,N,K", [(1, 480, 480), (8, 1440, 480), (33, 2560, 1280), (64, 4096, 5280), (5, 200, 136),
+                                   (1, 5280, 5280), (8, 5280, 17920), (16, 15840, 5280)])
 def test_skinny_gemm_matches_matmul(small_model, B, N, K):
     from recurrent_pretraining_b200.engine.decode import DecodeEngine
 
@@ -33,6 +34,40 @@ def test_skinny_gemm_matches_matmul(small_model, B, N, K):
     y = eng._linear(x, w)
     want = x.float() @ w.float().T
     assert (y.float() - want).abs().max().item() < 0.02 * math.sqrt(K) * 0.05 * 4 + 0.02 * want.abs().max().item()
+    assert not eng.work.any(), "the stream-K accumulator must be handed back cleared"
+
+
+@pytest.mark.parametrize("E", [5280, 2048, 96, 100])
+@pytest.mark.parametrize("a_kind", ["f32", "bf16", "none"])
+def test_add_rmsnorm_pair(E, a_kind):
+    from recurrent_pretraining_b200.engine import decode as D
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    torch.manual_seed(E)
+    rows, eps = 3, 1e-6
+    x = _bf(rows, E)
+    a = {"f32": torch.randn(rows, E, device="cuda"), "bf16": _bf(rows, E), "none": None}[a_kind]
+    w1, w2 = torch.rand(E, device="cuda") + 0.5, torch.rand(E, device="cuda") + 0.5
+    y1, y2 = torch.empty_like(x), torch.empty_like(x)
+    s = (x.float() + (a.float() if a is not None else 0)).bfloat16().float()
+
+    def norm(t, w):
+        return ((t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)).bfloat16().float() * w).bfloat16().float()
+
+    want1 = norm(s, w1)
+    want2 = norm(want1, w2)
+    a_in = a.clone() if a is not None else None
+    K._check(D._norm_pair(K._ptr(a_in), int(a_kind == "f32"), x.data_ptr(), w1.data_ptr(), w2.data_ptr(), y1.data_ptr(),
+                          y2.data_ptr(), rows, E, eps, K._stream()), "add_rmsnorm_pair")
+    assert torch.allclose(y1.float(), want1, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(y2.float(), want2, atol=3e-2, rtol=2e-2)
+    if a_kind == "f32":
+        assert not a_in.any(), "the fp32 accumulator is cleared after reading"
+    y1b = torch.empty_like(x)
+    a_in = a.clone() if a is not None else None
+    K._check(D._norm_pair(K._ptr(a_in), int(a_kind == "f32"), x.data_ptr(), w1.data_ptr(), 0, y1b.data_ptr(), 0, rows, E,
+                          eps, K._stream()), "add_rmsnorm_pair")
+    assert torch.equal(y1b, y1)
 
 
 def test_rope_append_and_decode_attention():
@@ -47,9 +82,16 @@ def test_rope_append_and_decode_attention():
     bias = torch.randn(2, 1, H, Dh, device="cuda") * 0.1
     cos, sin = (t.cuda() for t in ref.rope_tables(Dh, Lmax))
     q = torch.empty(B, H * Dh, dtype=torch.bfloat16, device="cuda")
+    # fp32 input (the stream-K accumulator, cleared by the kernel) must give the same result as the bf16 input
+    acc = qkv.float()
+    q32, kc32, vc32 = torch.empty_like(q), kc.clone(), vc.clone()
+    K._check(D._rope_append(acc.data_ptr(), bias.contiguous().data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                            pos.data_ptr(), q32.data_ptr(), kc32.data_ptr(), vc32.data_ptr(), B, H, H, Dh, Lmax,
+                            K._stream(), 1), "rope_append")
     K._check(D._rope_append(qkv.data_ptr(), bias.contiguous().data_ptr(), cos.data_ptr(), sin.data_ptr(),
-                            pos.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H, Dh, Lmax, K._stream()),
+                            pos.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H, Dh, Lmax, K._stream(), 0),
              "rope_append")
+    assert torch.equal(q32, q) and torch.equal(kc32, kc) and torch.equal(vc32, vc) and not acc.any()
     for b in range(B):
         p = int(pos[b])
         qr, kr, vr = ref.qk_bias_rope(qkv[b:b + 1, None], bias, cos[p:p + 1], sin[p:p + 1], H, H, Dh)
