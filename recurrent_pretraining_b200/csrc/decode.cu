@@ -294,6 +294,29 @@ __global__ void cast_zero_kernel(float* __restrict__ work, __nv_bfloat16* __rest
   }
 }
 
+// y[t, i] = silu(g) * u with g = acc[t, i], u = acc[t, I + i] rounded to bf16 first (as the bf16 GEMM store would),
+// acc = 0 afterwards: consumer of the stream-K gate-up projection.
+__global__ void swiglu_acc_kernel(float* __restrict__ acc, __nv_bfloat16* __restrict__ y, size_t T, int I) {
+  pdl_trigger();
+  pdl_wait();
+  const int vpr = I >> 2;
+  const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= T * vpr) return;
+  const size_t t = gid / vpr;
+  const int c = static_cast<int>(gid % vpr) * 4;
+  float4* gp = reinterpret_cast<float4*>(acc + t * 2 * I + c);
+  float4* up = reinterpret_cast<float4*>(acc + t * 2 * I + I + c);
+  const float4 g4 = *gp, u4 = *up;
+  *gp = make_float4(0.f, 0.f, 0.f, 0.f);
+  *up = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float g[4] = {bf2f(f2bf(g4.x)), bf2f(f2bf(g4.y)), bf2f(f2bf(g4.z)), bf2f(f2bf(g4.w))};
+  const float u[4] = {bf2f(f2bf(u4.x)), bf2f(f2bf(u4.y)), bf2f(f2bf(u4.z)), bf2f(f2bf(u4.w))};
+  float o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  *reinterpret_cast<uint2*>(y + t * I + c) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+}
+
 // One CTA per row (decode batches have at most 64 rows):  s = bf16(a + x) with a in fp32 (then cleared) or bf16,
 // y1 = norm(s) * w1 and, if w2 is given, y2 = norm(y1) * w2 -- the sandwich pair n2 -> n3 (or n4 -> next n1) in one
 // launch.  Each norm rounds the normalised value to bf16 before the weight multiply, as the unfused kernels do.
@@ -458,6 +481,14 @@ add_rmsnorm_pair_vec_kernel(void* __restrict__ a, const __nv_bfloat16* __restric
 }  // namespace b200
 
 using namespace b200;
+
+B200_API int b200_swiglu_acc(float* acc, void* y, long long T, int I, void* stream) {
+  if (I % 4 || T <= 0) return -1;
+  const size_t n = static_cast<size_t>(T) * (I / 4);
+  launch_k(swiglu_acc_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+           acc, reinterpret_cast<__nv_bfloat16*>(y), static_cast<size_t>(T), I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 B200_API int b200_cast_zero(float* work, void* out, long long n, void* stream) {
   if (n <= 0) return 0;

@@ -135,8 +135,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int ot, kb0, kb1;
         bool more = true;
         for (int wi = 0; ok && more && work_item(wi, ot, kb0, kb1); ++wi) {
-          const int m0 = (ot % tiles_m) * BM;
-          const int n0 = (ot / tiles_m) * BN;
+          int mt, nt;
+          tile_coords(ot, tiles_m, tiles_n, p.raster, mt, nt);
+          const int m0 = mt * BM, n0 = nt * BN;
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             if (phase == 0 && it >= STAGES) { more = false; break; }
             const bool a_done = early_thread && phase == 1 && it < STAGES;   // loaded in phase 0
@@ -226,8 +227,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int wi = 0; work_item(wi, ot, kb0, kb1); ++wi, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      const int m0 = (ot % tiles_m) * BM;
-      const int n0 = (ot / tiles_m) * BN;
+      int mt, nt;
+      tile_coords(ot, tiles_m, tiles_n, p.raster, mt, nt);
+      const int m0 = mt * BM, n0 = nt * BN;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
@@ -318,6 +320,9 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
 
 }  // namespace b200
 
+static int g_raster = 8;   // m tiles per raster group of the large GEMMs (0: m fastest)
+B200_API int b200_gemm_set_raster(int group) { const int old = g_raster; g_raster = group < 0 ? 0 : group; return old; }
+
 int g_b200_pdl = 0;
 extern "C" __attribute__((visibility("default"))) int b200_set_pdl(int on) {
   const int old = g_b200_pdl;
@@ -371,6 +376,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   GemmParams p = {};
   p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
+  p.raster = g_raster;
   p.rope_cos = g_rope.cos; p.rope_sin = g_rope.sin; p.rope_bias = g_rope.bias;
   p.rope_S = g_rope.S; p.rope_D = g_rope.D; p.rope_width = g_rope.width;
   if (out_mode == OUT_BF16_ROPE && (!p.rope_cos || p.rope_D <= 0 || (p.rope_D & 1) || (p.rope_width & 1))) return -25;
@@ -456,7 +462,10 @@ B200_API int b200_gemm_skinny(const void* x, const void* W, void* out, float* wo
   // Fewer weight-row tiles than SMs: stream-K.  A fixed K split leaves tiles * ksplit work items, which rarely divide
   // by the SM count (N = 5280: 42 tiles * 4 = 168 items on 148 SMs ran as two waves, 57 % of the machine); with
   // stream-K every SM streams the same number of weight bytes.
-  const bool streamk = work && tiles < num_sms() && nk >= 8 && g_skinny_streamk;
+  // More tiles than SMs but not a multiple of them (gate-up: 280 tiles = 1.89 waves) gains too, as long as the batch is
+  // narrow: the accumulation costs 128 x Bt atomics per (tile, CTA) piece.
+  const bool streamk = work && nk >= 8 && g_skinny_streamk &&
+                       (tiles < num_sms() || (Bt <= 16 && tiles % num_sms() != 0));
   GemmParams p = {};
   p.M = N; p.N = Bt; p.K1 = K; p.K2 = 0; p.ld_resid = 0; p.swiglu_n = 0; p.resid = nullptr; p.err = err;
   p.ksplit = 1;

@@ -157,7 +157,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int nk = nk1 + nk2;
   // N-tile of a linear tile index; with the fused all-gather the order is rotated to start at this rank's shard
   const int ag_first = AG ? (ag.rank * ag.rows_per_shard) / BN : 0;
-  auto n_tile_of = [&](int tile) { return AG ? (ag_first + tile / tiles_m) % tiles_n : tile / tiles_m; };
+  // (m tile, n tile) of a linear index: grouped raster, except that the fused all-gather walks whole n tiles in shard
+  // order (its counters are per n tile)
+  auto tile_mn = [&](int tile, int& mi, int& ni) {
+    if constexpr (AG) {
+      mi = tile % tiles_m;
+      ni = (ag_first + tile / tiles_m) % tiles_n;
+    } else {
+      tile_coords(tile, tiles_m, tiles_n, p.raster, mi, ni);
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -194,8 +203,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       bool ok = true;
       const uint32_t fb0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // leader's full barriers: fb0 + 8 * stage
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-        const int nt = n_tile_of(tile);
+        int mt, nt;
+        tile_mn(tile, mt, nt);
+        const int m0 = mt * (2 * BM2) + static_cast<int>(rank) * BM2;
         const int n0 = (MODE == OUT_SWIGLU) ? nt * BN_OUT + static_cast<int>(rank) * p.swiglu_n
                                             : nt * BN + static_cast<int>(rank) * BNH;
         if constexpr (AG) {
@@ -327,8 +337,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      const int m0 = (tile % tiles_m) * (2 * BM2) + static_cast<int>(rank) * BM2;
-      const int n0 = n_tile_of(tile) * BN_OUT;
+      int mt, nt;
+      tile_mn(tile, mt, nt);
+      const int m0 = mt * (2 * BM2) + static_cast<int>(rank) * BM2;
+      const int n0 = nt * BN_OUT;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);

@@ -32,6 +32,7 @@ _set_pdl = K._sig("b200_set_pdl", [_i])
 PDL = os.environ.get("B200_DECODE_PDL", "0") == "1"  # measured within noise of off (23.1-23.5 vs 23.5 ms per token): off
 _skinny = K._sig("b200_gemm_skinny", [_vp] * 4 + [_i] * 7 + [_vp, _vp])
 _cast_zero = K._sig("b200_cast_zero", [_vp, _vp, C.c_longlong, _vp])
+_swiglu_acc = K._sig("b200_swiglu_acc", [_vp, _vp, C.c_longlong, _i, _vp])
 _norm_pair = K._sig("b200_add_rmsnorm_pair", [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp])
 _rope_append = K._sig("b200_rope_append", [_vp] * 8 + [_i] * 5 + [_vp, _i])
 _decode_attn = K._sig("b200_decode_attention", [_vp] * 7 + [_i] * 6 + [_f, _vp])
@@ -129,7 +130,10 @@ class DecodeEngine:
         self._norm_w: dict = {}
         # persistent fp32 accumulator of the stream-K skinny GEMMs (outputs up to the packed qkv width: qkv, attn.proj,
         # mlp.proj, adapter); kept zero between uses -- every consumer clears what it reads
-        self.work = torch.zeros(max_batch * max(2 * self.E, (self.H + 2 * self.Hkv) * self.D), dtype=torch.float32, device=d)
+        widest = max(2 * self.E, (self.H + 2 * self.Hkv) * self.D)
+        if max_batch <= 16:  # narrow batches also accumulate the gate-up projection this way
+            widest = max(widest, max(b.mlp.fc.weight.shape[0] for b in self._all_blocks()))
+        self.work = torch.zeros(max_batch * widest, dtype=torch.float32, device=d)
         self.weight_bytes_per_recurrence = sum(p.numel() * 2 for n, p in model.named_parameters()
                                                if ".core_block." in n or ".adapter." in n)
 
@@ -152,6 +156,10 @@ class DecodeEngine:
                 return work
             K._check(_cast_zero(work.data_ptr(), out.data_ptr(), Bt * N, K._stream()), "cast_zero")
         return out
+
+    def _all_blocks(self):
+        t = self.model.transformer
+        return list(t.prelude) + list(t.core_block) + list(t.coda)
 
     def _w(self, norm):
         """fp32 copy of a norm weight, made once."""
@@ -195,7 +203,12 @@ class DecodeEngine:
         """Sandwich block on (residual x, h = norm_1(x)); returns (x', norm_1 of the next block applied to x')."""
         a = self._attention(block.attn, h, slot)
         x, h3 = self._pair(a, x, block.norm_2, block.norm_3)
-        g = K.swiglu_fwd(self._linear(h3, block.mlp.fc.weight))
+        gu = self._linear(h3, block.mlp.fc.weight, keep_f32=True)
+        if gu.dtype == torch.float32:
+            g = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=BF16, device=self.dev)
+            K._check(_swiglu_acc(gu.data_ptr(), g.data_ptr(), gu.shape[0], gu.shape[1] // 2, K._stream()), "swiglu_acc")
+        else:
+            g = K.swiglu_fwd(gu)
         m = self._linear(g, block.mlp.proj.weight, keep_f32=True)
         return self._pair(m, x, block.norm_4, next_norm)
 

@@ -59,6 +59,19 @@ def set_gemm_2cta(enable: bool) -> bool:
     """Select the 2-CTA (cta_group::2, 256-row tiles) GEMM where it applies; returns the previous setting."""
     return bool(_set_2cta(int(enable)))
 
+_set_raster = _sig("b200_gemm_set_raster", [_i])
+
+
+def set_gemm_raster(group: int) -> int:
+    """Tile order of the large GEMMs: ``group`` consecutive m tiles are walked across all n tiles before the next
+    group (a wave of the persistent grid then covers a near-square block of tiles and re-uses both operand panels from
+    L2); 0 = m fastest over the whole matrix.  Returns the previous setting."""
+    return int(_set_raster(int(group)))
+
+
+if os.environ.get("B200_GEMM_RASTER"):
+    set_gemm_raster(int(os.environ["B200_GEMM_RASTER"]))
+
 BF16 = torch.bfloat16
 
 

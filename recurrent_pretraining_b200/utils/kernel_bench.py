@@ -1,5 +1,5 @@
 """Micro-benchmarks of the hot kernels on the flagship shapes, reported against the library GEMM and the measured
-machine peaks.  ``python -m recurrent_pretraining_b200.utils.kernel_bench [gemm|norm|attn|all]``.
+machine peaks.  ``python -m recurrent_pretraining_b200.utils.kernel_bench [gemm|swiglu|norm|attn|skinny [shape [batch]]|all]``.
 
 Timing: CUDA events on the launching stream after warm-up, L2 flushed between timed launches by writing a 256 MB
 buffer, median of the repeats.
@@ -7,6 +7,7 @@ buffer, median of the repeats.
 from __future__ import annotations
 
 import json
+import os
 import statistics
 import sys
 
@@ -129,6 +130,48 @@ def bench_attn(B=1, S=4096, H=55, D=96):
                       "library_fwd_plus_bwd_ms": round(tlb, 3)}))
 
 
+def bench_skinny(only=None, B=1, iters=20):
+    """The decode engine's weight-streaming GEMM (out[B, N] = x W^T computed as W x^T) on the flagship projections,
+    inside a CUDA graph of ``iters`` launches over four rotating weight copies (so nothing is served from L2)."""
+    from ..engine import decode as D
+    from ..ops import cuda as K
+
+    shapes = {"qkv": (15840, 5280), "proj": (5280, 5280), "fc": (35840, 5280), "mlpproj": (5280, 17920)}
+    work = torch.zeros(B * 15840, device="cuda")
+    err = K.err_word(torch.device("cuda", 0))
+    for name, (N, Kd) in shapes.items():
+        if only and only != name:
+            continue
+        Ws = [(torch.randn(N, Kd, device="cuda") * 0.02).bfloat16() for _ in range(4)]
+        x = torch.randn(B, Kd, device="cuda").bfloat16()
+        out = torch.empty(B, N, dtype=torch.bfloat16, device="cuda")
+        wk = work if B * N <= work.numel() else None
+
+        def launch(i):
+            rc = D._skinny(x.data_ptr(), Ws[i % 4].data_ptr(), out.data_ptr(), K._ptr(wk), B, N, Kd, Kd, Kd, N, 0,
+                           K._stream(), err.data_ptr())
+            if rc < 0:
+                raise RuntimeError(f"b200_gemm_skinny failed with code {rc}")
+            return rc
+
+        for i in range(3):
+            mode = launch(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        pdl = os.environ.get("B200_DECODE_PDL", "0") == "1"   # programmatic dependent launch between the launches
+        old = D._set_pdl(1) if pdl else 0
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                launch(i)
+        if pdl:
+            D._set_pdl(old)
+        t = time_fn(g.replay, reps=5, warmup=1) / iters
+        work.zero_()
+        print(json.dumps({"kernel": "skinny_gemm", "shape": name, "batch": B, "N": N, "K": Kd,
+                          "path": "stream-K fp32 atomics" if mode == 1 else "bf16 store", "pdl": pdl, "us": round(t * 1e3, 1),
+                          "weight_TBps": round(N * Kd * 2 / t / 1e9, 2), "device_status": K.check_device_status()}))
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     if what in ("gemm", "all"):
@@ -139,3 +182,5 @@ if __name__ == "__main__":
         bench_norm()
     if what in ("attn", "all"):
         bench_attn()
+    if what in ("skinny", "all"):
+        bench_skinny(only=sys.argv[2] if len(sys.argv) > 2 else None, B=int(sys.argv[3]) if len(sys.argv) > 3 else 1)

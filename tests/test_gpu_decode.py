@@ -24,7 +24,7 @@ def small_model():
 
 
 @pytest.mark.parametrize("B,N,K", [(1, 480, 480), (8, 1440, 480), (33, 2560, 1280), (64, 4096, 5280), (5, 200, 136),
-                                   (1, 5280, 5280), (8, 5280, 17920), (16, 15840, 5280)])
+                                   (1, 5280, 5280), (8, 5280, 17920), (16, 15840, 5280), (8, 20000, 512)])
 def test_skinny_gemm_matches_matmul(small_model, B, N, K):
     from recurrent_pretraining_b200.engine.decode import DecodeEngine
 
@@ -35,6 +35,18 @@ def test_skinny_gemm_matches_matmul(small_model, B, N, K):
     want = x.float() @ w.float().T
     assert (y.float() - want).abs().max().item() < 0.02 * math.sqrt(K) * 0.05 * 4 + 0.02 * want.abs().max().item()
     assert not eng.work.any(), "the stream-K accumulator must be handed back cleared"
+
+
+def test_swiglu_from_accumulator():
+    from recurrent_pretraining_b200.engine import decode as D
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    T, I = 3, 1000
+    acc = torch.randn(T, 2 * I, device="cuda") * 2
+    h = acc.bfloat16()
+    y = torch.empty(T, I, dtype=torch.bfloat16, device="cuda")
+    K._check(D._swiglu_acc(acc.data_ptr(), y.data_ptr(), T, I, K._stream()), "swiglu_acc")
+    assert torch.equal(y, K.swiglu_fwd(h)) and not acc.any()
 
 
 @pytest.mark.parametrize("E", [5280, 2048, 96, 100])
