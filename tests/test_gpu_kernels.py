@@ -42,6 +42,23 @@ def test_gemm_nt(C, M, N, K):
     _close(out, a.float() @ b.float().T, 2e-2, 2e-2 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("group", [0, 3, 8, 64])
+def test_gemm_tile_raster_orders(C, group):
+    """Every raster group size visits every output tile exactly once (partial last group, group > tile rows)."""
+    old = C.set_gemm_raster(group)
+    try:
+        for M, N, K in [(2900, 1304, 136), (1300, 3000, 72)]:     # 12 x 6 and 6 x 12 tiles of 256 x 256
+            a, b = _rand(M, K), _rand(N, K)
+            _close(C.gemm_nt(a, b), a.float() @ b.float().T, 2e-2, 2e-2 * math.sqrt(K))
+            g = torch.ones(N, K, device="cuda")
+            dy, x = _rand(M, N), _rand(M, K)
+            C.gemm_tn(dy, x, out=g, accumulate=True)              # += : a tile visited twice would show
+            _close(g, 1 + dy.float().T @ x.float(), 2e-2, 2e-2 * math.sqrt(M))
+    finally:
+        C.set_gemm_raster(old)
+    assert C.check_device_status() == 0
+
+
 @pytest.mark.parametrize("bn", [128, 240, 256])
 def test_gemm_nt_tile_widths(C, bn):
     a, b = _rand(384, 320), _rand(720, 320)
