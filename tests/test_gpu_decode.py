@@ -165,6 +165,22 @@ def test_engine_matches_eager_model(small_model, use_graphs):
     assert bool((chosen >= top2.values[..., 0] - 0.15).all()), (chosen, top2.values[..., 0])
 
 
+def test_engine_with_programmatic_dependent_launch(small_model, monkeypatch):
+    """The captured token graph with programmatic launch edges (each kernel triggers its successor at entry and waits
+    for its predecessor before it reads; the skinny GEMM requests weight tiles before that wait) decodes correctly."""
+    from recurrent_pretraining_b200.engine import decode as D
+
+    torch.manual_seed(1)
+    B, P, new = 2, 24, 6
+    ids = torch.randint(0, 4000, (B, P), device="cuda")
+    monkeypatch.setattr(D, "PDL", True)
+    toks, stats = D.DecodeEngine(small_model, max_batch=B, max_len=64, num_steps=4).generate(ids, new, init_scale=0.0)
+    assert stats["device_status"] == 0 and toks.shape == (B, P + new)
+    pred = small_model(toks[:, :-1], num_steps=4, init_scale=0.0).logits[:, P - 1:, :]
+    chosen = torch.gather(pred, -1, toks[:, P:].unsqueeze(-1)).squeeze(-1)
+    assert bool((chosen >= pred.max(-1).values - 0.15).all())
+
+
 def test_engine_kl_exit_and_latent_reuse(small_model):
     from recurrent_pretraining_b200.engine.decode import DecodeEngine
 
