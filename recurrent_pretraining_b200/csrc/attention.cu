@@ -430,8 +430,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
   const int npair = (nqb + 1) / 2;
-  const int pair = npair - 1 - blockIdx.x;  // heavy (late) pairs first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid (heads, pairs, batch): CTAs are issued in linear order, so all heads of the heaviest (latest) pair go first and
+  // the lightest pairs fill the tail -- longest-first over the whole grid, not per head
+  const int pair = npair - 1 - blockIdx.y;
+  const int h = blockIdx.x, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
   const int qbA = 2 * pair, qbB = 2 * pair + 1;
   const int nA = qbA + 1;                       // key blocks of tile A (block qbA is its diagonal)
@@ -1006,7 +1008,9 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // grid (kv heads, key blocks, batch): key block 0 meets every query block, the last one a single block; in linear
+  // order all heads of the heaviest key block go first (longest-first over the whole grid)
+  const int kvb = blockIdx.y, hk = blockIdx.x, b = blockIdx.z;
   const int rep = p.H / p.Hkv;
   const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
   const int per_head = nqb - kvb;
@@ -1343,7 +1347,7 @@ static int launch_attn_fwd2(const CUtensorMap& tm, const AttnParams& p, cudaStre
     configured = true;
   }
   const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
-  dim3 grid((nqb + 1) / 2, p.H, p.B);
+  dim3 grid(p.H, (nqb + 1) / 2, p.B);
   kern<<<grid, 384, SMEM, st>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
@@ -1411,7 +1415,7 @@ static int launch_attn_bwd2(const CUtensorMap& tq, const CUtensorMap& tdo, const
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
     configured = true;
   }
-  dim3 grid((p.S + ATT_BN - 1) / ATT_BN, p.Hkv, p.B);
+  dim3 grid(p.Hkv, (p.S + ATT_BN - 1) / ATT_BN, p.B);
   kern<<<grid, 384, SMEM, st>>>(tq, tdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
