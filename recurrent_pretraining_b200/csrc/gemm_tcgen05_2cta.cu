@@ -302,23 +302,26 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int nt = (ag_first + i) % tiles_n;
         const int r0 = nt * BN, r1 = min(p.N, r0 + BN);
         const size_t nvec = static_cast<size_t>(r1 - r0) * vec_per_row;
-        for (size_t v = g; v < nvec; v += 4 * gstride) {
-          uint4 buf[4];
-          size_t idx[4];
+        // AG_DEPTH independent 16-byte peer loads per thread are in flight before the first store: a peer load takes
+        // microseconds, and the bytes in flight (threads x depth x 16) must cover latency x link bandwidth
+        constexpr int AG_DEPTH = 12;
+        for (size_t v = g; v < nvec; v += AG_DEPTH * gstride) {
+          uint4 buf[AG_DEPTH];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            idx[u] = v + u * gstride;
-            if (idx[u] < nvec) {
-              const int row = r0 + static_cast<int>(idx[u] / vec_per_row), col = static_cast<int>(idx[u] % vec_per_row);
+          for (int u = 0; u < AG_DEPTH; ++u) {
+            const size_t idx = v + u * gstride;
+            if (idx < nvec) {
+              const int row = r0 + static_cast<int>(idx / vec_per_row), col = static_cast<int>(idx % vec_per_row);
               const int owner = min(row / ag.rows_per_shard, ag.n_ranks - 1);
               const __nv_bfloat16* src = ag.shard[owner] + static_cast<size_t>(row - owner * ag.rows_per_shard) * (vec_per_row * 8);
               buf[u] = ld_peer_16(reinterpret_cast<const uint4*>(src) + col);
             }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (idx[u] < nvec) {
-              const int row = r0 + static_cast<int>(idx[u] / vec_per_row), col = static_cast<int>(idx[u] % vec_per_row);
+          for (int u = 0; u < AG_DEPTH; ++u) {
+            const size_t idx = v + u * gstride;
+            if (idx < nvec) {
+              const int row = r0 + static_cast<int>(idx / vec_per_row), col = static_cast<int>(idx % vec_per_row);
               reinterpret_cast<uint4*>(ag.wfull + static_cast<size_t>(row) * ag.ldw)[col] = buf[u];
             }
           }

@@ -45,6 +45,8 @@ def main():
     dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
     sizes_mb = [1, 4, 16, 64, 256, 1024]
     max_bytes = sizes_mb[-1] * 2**20
+    if "--ag-only" in sys.argv:   # only the fused all-gather GEMM rows
+        sizes_mb = []
     buf = SymmetricBuffer(fabric, max_bytes + 4096 * N)  # slack: slices are rounded up to 512 B
     ctrl = SymmetricBuffer(fabric, 512)
     out = torch.empty(max_bytes // 4, dtype=torch.float32, device=dev)
@@ -127,7 +129,7 @@ def main():
                 rec[name + "_GBps"] = round(moved / t / 1e6, 1)
             if rank == 0:
                 print(json.dumps(rec), flush=True)
-    if "--ag" in sys.argv:
+    if "--ag" in sys.argv or "--ag-only" in sys.argv:
         # all-gather fused into the consuming GEMM (flagship QKV and gate-up projections, 4096 rows)
         from ..parallel.ag_gemm import GatheredWeight
 
