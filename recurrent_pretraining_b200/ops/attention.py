@@ -35,7 +35,7 @@ def set_bwd_variant(v: int) -> int:
 
 
 # Training runs on the native kernels (B200_NATIVE_ATTENTION=0 selects the library SDPA instead).  Measured on the
-# flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.227 ms / backward 0.99 ms, library forward 0.18 ms /
+# flagship shape (B=1, S=4096, 55 heads of 96): native forward 0.222 ms / backward 0.99 ms, library forward 0.18 ms /
 # forward-recompute + backward + copies 1.15-1.24 ms; the whole training step is the same either way (728.8 vs 728.9 ms).
 ENABLED = os.environ.get("B200_NATIVE_ATTENTION", "1") == "1"
 NATIVE_BWD = _bwd is not None and os.environ.get("B200_NATIVE_ATTENTION_BWD", "1") == "1"
