@@ -376,7 +376,9 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   GemmParams p = {};
   p.M = M; p.N = N; p.K1 = K1; p.K2 = K2; p.ldc = ldc; p.ld_resid = ld_resid; p.swiglu_n = N; p.ksplit = 1;
   p.C = C; p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.err = err;
-  p.raster = g_raster;
+  // a very long contraction (the head's input gradient, K = vocabulary) keeps the m-fastest order: every wave then
+  // shares each B k-slice among all 16 m tiles at once (measured 1173 vs 998 TFLOP/s with groups of 8)
+  p.raster = (K1 + K2 >= 32768) ? 0 : g_raster;
   p.rope_cos = g_rope.cos; p.rope_sin = g_rope.sin; p.rope_bias = g_rope.bias;
   p.rope_S = g_rope.S; p.rope_D = g_rope.D; p.rope_width = g_rope.width;
   if (out_mode == OUT_BF16_ROPE && (!p.rope_cos || p.rope_D <= 0 || (p.rope_D & 1) || (p.rope_width & 1))) return -25;
