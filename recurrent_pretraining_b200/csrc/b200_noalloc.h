@@ -13,8 +13,11 @@
  *   - computes dx = d(rmsnorm)/dx and, if dw != NULL, dw[E] = sum over rows of dy * normalised(x), exactly like
  *     b200_rmsnorm_bwd; the caller passes every input and output buffer (bf16 dy, x, dx; fp32 w, rstd, dw).
  *   - allocates nothing: no cudaMalloc / cudaFree and no allocating library routine is called, ever.
- *   - limits: E must be a multiple of 8 and at most B200_NOALLOC_MAX_E (8192); M >= 1.  Anything else is
- *     refused with a negative return code and a message retrievable with b200_noalloc_last_error().
+ *   - limits: E must be a multiple of 8 and at most B200_NOALLOC_MAX_E (8192); M >= 1.  dy, x, rstd and dx must
+ *     not be NULL; dy, x and dx must be 16-byte aligned (rows are moved 8 bf16 values at a time; with E a
+ *     multiple of 8 every row of a 16-byte aligned matrix is), w, rstd and dw 4-byte aligned.  Anything else
+ *     is refused on the host, before any launch, with a negative return code and a message retrievable with
+ *     b200_noalloc_last_error(); the pointers must still be device pointers of the current device.
  *   - cost: every GPU whose context loads this library holds the scratch array
  *     (B200_NOALLOC_MAX_CTAS x B200_NOALLOC_MAX_E floats = 4.6 MiB) until the process exits.
  *   - the first call on each device looks up the device address of the array (cudaGetSymbolAddress) with that

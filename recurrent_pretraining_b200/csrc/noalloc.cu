@@ -109,6 +109,7 @@ __global__ void noalloc_colsum_kernel(const float* __restrict__ in, float* __res
 }
 
 constexpr int NA_MAX_DEVICES = 64;
+// Written without a lock: host threads that race on the first call of a device all store the same address.
 static float* g_scratch_ptr[NA_MAX_DEVICES] = {nullptr};
 static thread_local char g_last_error[256] = "";
 
@@ -151,6 +152,12 @@ B200_API int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
     return fail(-1, "row width E=%ld is not supported: it must be a multiple of 8 and at most %ld", E,
                 B200_NOALLOC_MAX_E);
   if (M <= 0) return fail(-1, "row count M=%ld must be positive", M);
+  // A bad pointer would fault on the device and take the caller's whole context with it: refuse it here instead.
+  if (!dy || !x || !rstd || !dx) return fail(-1, "dy, x, rstd and dx must not be NULL");
+  const uintptr_t vec = reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx);
+  if (vec & 15) return fail(-1, "dy, x and dx must be 16-byte aligned (the kernel moves 8 bf16 values at a time)");
+  const uintptr_t f32 = reinterpret_cast<uintptr_t>(rstd) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(dw);
+  if (f32 & 3) return fail(-1, "w, rstd and dw must be 4-byte aligned");
   int rc = 0;
   float* scratch = scratch_for_current_device(&rc);
   if (!scratch) return rc;

@@ -37,6 +37,8 @@ class RandomTokens(IterableDataset):
     def load_state_dict(self, sd, **_):
         self._pos = int(sd["pos"])
 
+    load_local_state = load_state_dict
+
 
 class ParquetStream(IterableDataset):
     def __init__(self, dataset_folder_path: str = "", seed: int = 12345, shuffle: bool = True, num_processes: int = 1,
@@ -100,8 +102,13 @@ class ParquetStream(IterableDataset):
                 "fingerprint": self.fingerprint, "rng_state": self._rng_state}
 
     def state_dict(self) -> dict:
-        """Per-rank states gathered into lists indexed by rank (a different world size can reload them)."""
-        local = self.local_state()
+        return self.state_from_local(self.local_state())
+
+    def load_local_state(self, local: dict) -> None:
+        self.load_state_dict({k: [v] for k, v in local.items()}, _rank=0)
+
+    def state_from_local(self, local: dict) -> dict:
+        """Per-rank states gathered into lists indexed by rank (a different world size can reload them).  Collective."""
         if dist.is_available() and dist.is_initialized():
             states = [None] * dist.get_world_size()
             dist.all_gather_object(states, local)
@@ -109,10 +116,10 @@ class ParquetStream(IterableDataset):
             states = [local]
         return {k: [s[k] for s in states] for k in local}
 
-    def load_state_dict(self, sd: dict, offset_ranks: bool = False) -> None:
+    def load_state_dict(self, sd: dict, offset_ranks: bool = False, _rank=None) -> None:
         import pyarrow.parquet as pq
 
-        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        rank = _rank if _rank is not None else (dist.get_rank() if dist.is_available() and dist.is_initialized() else 0)
         pick = lambda key: sd[key][rank % len(sd["fingerprint"])]  # noqa: E731
         if pick("fingerprint") != self.fingerprint:
             print(f"WARNING dataset fingerprint mismatch: expected {self.fingerprint}, got {pick('fingerprint')}")
@@ -125,6 +132,9 @@ class ParquetStream(IterableDataset):
         if state is not None:
             self._rng = random.Random()
             self._rng.setstate(tuple(state) if not isinstance(state, tuple) else state)
+        if pick("row_group_idx") < 0 and pick("fingerprint") == self.fingerprint:
+            self._buffer, self._row_group_idx = [], 0     # saved before the first row group was read
+            return
         self._read_buffer(pq.ParquetFile(self.parquet_files[self._file_idx]))
         self._buffer = self._buffer[:row_idx]
         self._row_group_idx += 1
@@ -161,6 +171,8 @@ class TextRows(IterableDataset):
     def load_state_dict(self, sd, **_):
         self._pos = int(sd["pos"])
 
+    load_local_state = load_state_dict
+
 
 class WeightedMixture(IterableDataset):
     """Draws the next row from one of several sources according to (scheduled) weights."""
@@ -183,9 +195,24 @@ class WeightedMixture(IterableDataset):
             except StopIteration:
                 alive[i] = False
 
+    def local_state(self):
+        from .loader import local_state
+
+        return {"sources": [local_state(s) for s in self.sources], "rng": self._rng.getstate()}
+
+    def state_from_local(self, local):
+        from .loader import saved_state
+
+        return {"sources": [saved_state(s, l) for s, l in zip(self.sources, local["sources"])], "rng": local["rng"]}
+
     def state_dict(self):
-        return {"sources": [s.state_dict() if hasattr(s, "state_dict") else None for s in self.sources],
-                "rng": self._rng.getstate()}
+        return self.state_from_local(self.local_state())
+
+    def load_local_state(self, local) -> None:
+        for s, st in zip(self.sources, local["sources"]):
+            if st is not None and hasattr(s, "load_local_state"):
+                s.load_local_state(st)
+        self._rng.setstate(local["rng"])
 
     def load_state_dict(self, sd, **_):
         for s, st in zip(self.sources, sd["sources"]):

@@ -1,11 +1,36 @@
 """Stateful batch loader: wraps an iterable token source, collates micro-batches, pins them and prefetches on a
-background thread (the role of torchdata's StatefulDataLoader in the reference, train.py:742-753)."""
+background thread (the role of torchdata's StatefulDataLoader in the reference, train.py:742-753).
+
+Resume is exact with prefetching: the producer thread takes a (non-collective) snapshot of the source right after the
+last row of every batch has been drawn and queues it with the batch; ``state_dict`` returns the snapshot that belongs
+to the last batch the consumer received, so batches that were prefetched but never trained on are produced again after a
+resume.  Collectives that a source needs to assemble its saved state (the per-rank gather of the parquet stream) run in
+``state_dict``, on the calling thread, never on the producer thread.
+"""
 from __future__ import annotations
 
 import queue
 import threading
 
 import torch
+
+
+def local_state(ds):
+    """Snapshot of a source without any collective."""
+    if hasattr(ds, "local_state"):
+        return ds.local_state()
+    if hasattr(ds, "state_dict"):
+        return ds.state_dict()
+    return None
+
+
+def saved_state(ds, local):
+    """The form of ``local`` that goes into a checkpoint (a source may gather it over ranks here)."""
+    if local is None:
+        return None
+    if hasattr(ds, "state_from_local"):
+        return ds.state_from_local(local)
+    return local
 
 
 class StatefulLoader:
@@ -15,7 +40,8 @@ class StatefulLoader:
         self.pin = pin_memory and torch.cuda.is_available()
         self.prefetch, self.drop_last = prefetch, drop_last
         self.batches_yielded = 0
-        self._restore_state = None
+        self._snapshot = None        # source state after the last batch handed to the consumer
+        self._running = False
 
     def _produce(self, out: queue.Queue, stop: threading.Event):
         try:
@@ -31,18 +57,28 @@ class StatefulLoader:
                         break
                     if self.pin:
                         batch = tuple(t.pin_memory() if torch.is_tensor(t) else t for t in batch)
-                    snapshot = self.dataset.state_dict() if self.prefetch == 0 and hasattr(self.dataset, "state_dict") \
-                        else None
-                    out.put((batch, snapshot))
+                    # the source generator is suspended at its yield: this snapshot is exactly "after this batch"
+                    snapshot = local_state(self.dataset)
+                    while not stop.is_set():
+                        try:
+                            out.put((batch, snapshot), timeout=0.2)
+                            break
+                        except queue.Full:
+                            continue
                     rows = []
-            if rows and not self.drop_last:
-                out.put((self.collate_fn(rows), None))
+            if rows and not self.drop_last and not stop.is_set():
+                out.put((self.collate_fn(rows), local_state(self.dataset)))
         except Exception as exc:  # surface loader errors in the training thread
             out.put(exc)
         finally:
-            out.put(None)
+            try:
+                out.put(None, timeout=1.0)
+            except queue.Full:
+                pass
 
     def __iter__(self):
+        if self._snapshot is None:
+            self._snapshot = local_state(self.dataset)
         if self.prefetch <= 0:
             rows = []
             for row in self.dataset:
@@ -54,11 +90,13 @@ class StatefulLoader:
                         return
                     rows = []
                     self.batches_yielded += 1
+                    self._snapshot = local_state(self.dataset)
                     yield batch
             return
         q: queue.Queue = queue.Queue(maxsize=self.prefetch)
         stop = threading.Event()
         t = threading.Thread(target=self._produce, args=(q, stop), daemon=True)
+        self._running = True
         t.start()
         try:
             while True:
@@ -68,19 +106,27 @@ class StatefulLoader:
                 if isinstance(item, Exception):
                     raise item
                 self.batches_yielded += 1
+                self._snapshot = item[1]
                 yield item[0]
         finally:
             stop.set()
+            self._running = False
+            t.join(timeout=5.0)
+            # the producer ran ahead of the consumer: put the source back to where the consumer stopped
+            if self._snapshot is not None and hasattr(self.dataset, "load_local_state"):
+                self.dataset.load_local_state(self._snapshot)
 
     def state_dict(self):
-        """Loader position.  With prefetching the source is ahead of the consumer by at most ``prefetch`` batches;
-        resuming skips nothing twice because the source state is rewound by replaying from ``batches_yielded``."""
+        """Loader position: the source state that belongs to the last batch the consumer received."""
+        snap = self._snapshot if (self._snapshot is not None or self._running) else local_state(self.dataset)
         sd = {"batches_yielded": self.batches_yielded}
-        if hasattr(self.dataset, "state_dict"):
-            sd["dataset"] = self.dataset.state_dict()
+        saved = saved_state(self.dataset, snap)
+        if saved is not None:
+            sd["dataset"] = saved
         return sd
 
     def load_state_dict(self, sd):
         self.batches_yielded = sd.get("batches_yielded", 0)
         if "dataset" in sd and hasattr(self.dataset, "load_state_dict"):
             self.dataset.load_state_dict(sd["dataset"])
+        self._snapshot = local_state(self.dataset)

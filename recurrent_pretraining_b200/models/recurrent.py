@@ -38,6 +38,20 @@ def _rank() -> int:
 
 
 class _LMBase(nn.Module):
+    # Set by the data-parallel stepper for the micro-batch that ends an accumulation window: ``cb(name)`` is called
+    # during backward as soon as the gradient of a phase-boundary tensor exists, i.e. when every layer after that
+    # boundary has finished its backward pass and its weight gradients are complete (parallel/p2p.py).
+    _phase_cb = None
+
+    def _phase(self, t: torch.Tensor, name: str) -> torch.Tensor:
+        cb = self._phase_cb
+        if cb is not None and torch.is_grad_enabled() and t.requires_grad:
+            def hook(grad, _cb=cb, _name=name):
+                _cb(_name)
+
+            t.register_hook(hook)
+        return t
+
     def _setup_rope(self, config) -> None:
         length = config.randomize_positions_from or config.block_size
         cos, sin = ref.rope_tables(config.head_size, length, config.rope_settings.rope_base,
@@ -260,9 +274,12 @@ class RecurrentGPT(_LMBase):
                                                     device=input_ids.device))[0]
         rope = self._rope(S, position_ids)
         e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+        self._phase(e, "prelude")        # gradient of the embedding output: the prelude has gone backward
         for block in self.transformer.prelude:
             e = block(e, rope, attention_mask)
+        self._phase(e, "core")           # gradient of the prelude output: all recurrences and the adapter are done
         x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
+        self._phase(x, "coda")           # gradient of the coda input: the coda blocks are done
         x_rec = x
         in_coda = self.gradient_checkpointing and "in-coda" in cfg.activation_checkpoint_impl
         for block in self.transformer.coda:
@@ -334,7 +351,10 @@ class GPT(_LMBase):
         S = input_ids.shape[1]
         rope = self._rope(S, position_ids)
         x = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
-        for block in self.transformer.h:
+        half = len(self.transformer.h) // 2
+        for i, block in enumerate(self.transformer.h):
+            if i == half and i > 0:
+                self._phase(x, "upper")  # gradient here: the upper half of the stack has gone backward
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 x = torch.utils.checkpoint.checkpoint(block, x, rope, attention_mask, use_reentrant=False)
             else:

@@ -5,12 +5,15 @@ tensors take ``torch.autograd.Function``s whose forward and backward launch the 
 kernels through ``ops.cuda``; there is no silent fallback on a GPU: if the native library
 is missing the import of ``ops.cuda`` raises.
 
-Weight gradients on the CUDA path can be accumulated straight into a persistent fp32
-gradient buffer by the wgrad GEMM epilogue: a parameter that carries ``_fused_grad = True``
-and a preallocated ``.grad`` gets ``grad += dy^T x`` in place and autograd sees ``None``.
-After each contribution the optional callback ``param._on_grad(param)`` is invoked; the data
-parallel fabric uses it to learn when a bucket is complete (the recurrent core receives k
-contributions per step, the tied embedding two).
+Weight gradients on the CUDA path go straight into a persistent fp32 gradient buffer from the
+wgrad GEMM epilogue: a parameter that carries ``_fused_grad = True`` and a preallocated ``.grad``
+gets ``grad (+)= dy^T x`` in place and autograd sees ``None``.  The buffers are never cleared between
+optimizer steps: ``param._written`` (bit 0: first half of the columns, bit 1: second half; reset at the
+start of every accumulation window by the training engine) tells whether a contribution stores or
+accumulates, which saves one read and one write of every gradient per step.
+
+In the parameter-sharded mode a weight may carry ``_ag`` (gathered by its first GEMM of a step) and
+``_gather_wait`` (a side-stream pull that the first use has to wait for).
 """
 from __future__ import annotations
 
@@ -32,26 +35,57 @@ def cuda_backend():
     return _cuda
 
 
+def _sync_gather(weight: torch.Tensor) -> None:
+    """Parameter-sharded mode: make sure the local bf16 copy of ``weight`` holds this step's values."""
+    h = getattr(weight, "_ag", None)
+    if h is not None and h.pending:
+        h.pull_now()
+    b = getattr(weight, "_gather_wait", None)
+    if b is not None:
+        torch.cuda.current_stream().wait_event(b.gather_event)
+        weight._gather_wait = None
+
+
 def _lp(weight: torch.Tensor) -> torch.Tensor:
     """bf16 compute copy of a parameter: the persistent shadow kept by the optimizer when present."""
     lp = getattr(weight, "_lp", None)
     if lp is not None:
+        if hasattr(weight, "_gather_wait"):
+            _sync_gather(weight)
         return lp
     return weight if weight.dtype == torch.bfloat16 else weight.detach().to(torch.bfloat16)
 
 
-def _notify(p: torch.Tensor) -> None:
-    cb = getattr(p, "_on_grad", None)
-    if cb is not None:
-        cb(p)
+def _ag_pending(weight: torch.Tensor) -> bool:
+    h = getattr(weight, "_ag", None)
+    return h is not None and h.pending
+
+
+def _gemm_nt_w(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x2 W^T through the weight's bf16 copy; the first use of a row-sharded weight in a step gathers it inside the
+    GEMM kernel."""
+    h = getattr(weight, "_ag", None)
+    if h is not None and h.pending:
+        y = h.gemm(x2)
+        if y is not None:
+            return y
+    return cuda_backend().gemm_nt(x2, _lp(weight))
+
+
+def _store_first(weight: torch.Tensor, mask: int = 3) -> bool:
+    """True when this is the first contribution of the accumulation window to the column halves in ``mask``
+    (the caller then stores instead of accumulating)."""
+    w = getattr(weight, "_written", 3)
+    weight._written = w | mask
+    weight._gemm_written = True
+    return (w & mask) == 0
 
 
 def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
-    """dW = dy2^T x2.  Returns the tensor for autograd, or None after fused accumulation."""
+    """dW = dy2^T x2.  Returns the tensor for autograd, or None after writing into the fused gradient buffer."""
     C = cuda_backend()
     if getattr(weight, "_fused_grad", False) and weight.grad is not None:
-        C.gemm_tn(dy2, x2, out=weight.grad, accumulate=True)
-        _notify(weight)
+        C.gemm_tn(dy2, x2, out=weight.grad, accumulate=not _store_first(weight))
         return None
     return C.gemm_tn(dy2, x2, out_dtype=torch.float32).to(weight.dtype)
 
@@ -64,7 +98,7 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, weight):
         C = cuda_backend()
         x2 = x.reshape(-1, x.shape[-1])
-        y = C.gemm_nt(x2, _lp(weight))
+        y = _gemm_nt_w(x2, weight)
         ctx.save_for_backward(x2, weight)
         ctx.xshape = x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -91,6 +125,8 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] in ONE GEMM whose epilogue applies the gate (forward only: the
     pre-activation is never written, so this is for no-grad passes such as the untracked recurrences and inference)."""
     assert not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad))
+    if x.is_cuda and _ag_pending(weight):
+        return swiglu(linear(x, weight))     # the gathering GEMM has the plain epilogue; once per step
     if x.is_cuda:
         C = cuda_backend()
         x2 = x.reshape(-1, x.shape[-1])
@@ -127,9 +163,8 @@ class _Adapter(torch.autograd.Function):
         dw = None
         if ctx.needs_input_grad[2]:
             if getattr(weight, "_fused_grad", False) and weight.grad is not None:
-                C.gemm_tn(dy2, x2, out=weight.grad[:, :E], accumulate=True)
-                C.gemm_tn(dy2, e2, out=weight.grad[:, E:], accumulate=True)
-                _notify(weight)
+                C.gemm_tn(dy2, x2, out=weight.grad[:, :E], accumulate=not _store_first(weight, 1))
+                C.gemm_tn(dy2, e2, out=weight.grad[:, E:], accumulate=not _store_first(weight, 2))
             else:
                 dw = torch.empty(weight.shape, dtype=torch.float32, device=dy.device)
                 C.gemm_tn(dy2, x2, out=dw[:, :E])
@@ -142,8 +177,8 @@ def _half_wgrad(dy2, a2, weight, cols: slice):
     """Gradient of one column half of the adapter weight; fused accumulation when the flat gradient buffer exists."""
     C = cuda_backend()
     if getattr(weight, "_fused_grad", False) and weight.grad is not None:
-        C.gemm_tn(dy2, a2, out=weight.grad[:, cols], accumulate=True)
-        _notify(weight)
+        mask = 1 if cols.start == 0 else 2
+        C.gemm_tn(dy2, a2, out=weight.grad[:, cols], accumulate=not _store_first(weight, mask))
         return None
     dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy2.device)
     C.gemm_tn(dy2, a2, out=dw[:, cols])
@@ -336,7 +371,7 @@ class _QKVRopeAttention(torch.autograd.Function):
 def qkv_rope_attention(x, weight, qk_bias, cos, sin, n_head: int, n_kv: int, head_dim: int, scale: float | None = None):
     """Wqkv projection + qk-bias + RoPE + causal attention; the GPU path fuses bias and rotation into the GEMM."""
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
-    if x.is_cuda and cos.dtype == torch.float32 and cos.shape[0] == x.shape[1]:
+    if x.is_cuda and cos.dtype == torch.float32 and cos.shape[0] == x.shape[1] and not _ag_pending(weight):
         return _QKVRopeAttention.apply(x, weight, qk_bias, cos.contiguous(), sin.contiguous(), n_head, n_kv, head_dim,
                                        scale)
     return rope_attention(linear(x, weight), qk_bias, cos, sin, n_head, n_kv, head_dim, scale)
@@ -407,8 +442,9 @@ class _Embedding(torch.autograd.Function):
         C = cuda_backend()
         ids, weight = ctx.saved_tensors
         if getattr(weight, "_fused_grad", False) and weight.grad is not None:
+            if _store_first(weight):
+                weight.grad.zero_()          # the scatter-add needs a cleared buffer when nothing was stored before it
             C.embedding_bwd(dy.contiguous(), ids, weight.grad, ctx.scale)
-            _notify(weight)
             return None, None, None
         dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy.device)
         C.embedding_bwd(dy.contiguous(), ids, dw, ctx.scale)
@@ -445,8 +481,10 @@ class _LinearCE(torch.autograd.Function):
         weight = ctx.weight
         dx = (dx * dloss.to(dx.dtype)).view(ctx.xshape)
         if getattr(weight, "_fused_grad", False) and weight.grad is not None:
-            weight.grad.addcmul_(dw, dloss.to(dw.dtype))
-            _notify(weight)
+            if _store_first(weight):
+                torch.mul(dw, dloss.to(dw.dtype), out=weight.grad)
+            else:
+                weight.grad.addcmul_(dw, dloss.to(dw.dtype))
             return dx, None, None, None, None, None
         return dx, (dw * dloss).to(weight.dtype), None, None, None, None
 

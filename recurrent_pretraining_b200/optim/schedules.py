@@ -25,5 +25,5 @@ def get_lr(base_lr: float, step: int, warmup_steps: int, max_steps: int, cooldow
 def get_batch_size(step: int, batch_size_ramp: int, final_accumulation: int) -> int:
     """Gradient-accumulation steps during a linear batch-size ramp (train.py:856-862)."""
     if batch_size_ramp and step < batch_size_ramp:
-        return max(int(step / batch_size_ramp * final_accumulation), 1)
+        return max(math.ceil(step / batch_size_ramp * final_accumulation), 1)
     return final_accumulation

@@ -9,8 +9,12 @@ broadcast, rank-0 printing, save/load helpers) with a different data path on GPU
   by a division by the world size (recpre/utils.py:1004-1043).  Used on CPU/gloo and as the NCCL baseline.
 * ``grad_sync="flat"``     -- one NCCL all-reduce per flat optimizer-group buffer (no pack/unpack copies); the
   1/world factor is folded into the fused optimizer kernel.
-* ``grad_sync="p2p"``      -- hand-written one-shot / two-shot all-reduce kernels over NVLink peer memory on
-  symmetric buffers, which also produce the squared gradient norm (``parallel.p2p``).
+* ``grad_sync="p2p"``      -- hand-written kernels over NVLink peer memory on symmetric buffers: bucketed reduce-scatter
+  overlapped with the backward pass, sharded optimizer state, update that stores the new bf16 weights into every rank
+  (``parallel.p2p``).  One node, at most 8 ranks; anything else falls back to ``flat`` with a notice.
+* ``grad_sync="p2p-host"`` -- the bookkeeping of ``p2p`` on ``torch.distributed`` collectives (any backend; tests).
+* ``grad_sync="zero3"``    -- as ``p2p`` with fp32 masters sharded as well and the updated bf16 weights pulled by the
+  next forward pass (all-gather fused into the first consuming GEMM for the row-sharded QKV / gate-up weights).
 """
 from __future__ import annotations
 
@@ -60,6 +64,13 @@ class Fabric:
             dist.init_process_group(backend, rank=rank, world_size=world,
                                     timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
         sync = grad_sync or ("flat" if use_cuda else "chunked")
+        if sync in ("p2p", "zero3") and world > 1:
+            local_world = int(env.get("LOCAL_WORLD_SIZE", env.get("SLURM_NTASKS_PER_NODE", world)))
+            if not use_cuda or local_world != world or world > 8:
+                if rank == 0:
+                    print(f"grad_sync={sync!r} needs all ranks on one node (<= 8 GPUs); world {world}, "
+                          f"{local_world} per node: using the NCCL 'flat' path", flush=True)
+                sync = "flat" if use_cuda else "chunked"
         return cls(device, rank, world, local, sync, precision)
 
     # -- basic collectives -----------------------------------------------------------------
@@ -121,7 +132,11 @@ class Fabric:
     # -- gradient synchronisation ----------------------------------------------------------
     @property
     def uses_p2p(self) -> bool:
-        return self.grad_sync == "p2p" and self.is_distributed and self.device.type == "cuda"
+        return self.grad_sync in ("p2p", "zero3") and self.is_distributed and self.device.type == "cuda"
+
+    @property
+    def shards_masters(self) -> bool:
+        return self.grad_sync == "zero3" and self.uses_p2p
 
     def buffer_allocator(self, group_index: int):
         """Allocator for the flat buffers of optimizer group ``group_index`` (symmetric memory in p2p mode)."""
@@ -135,12 +150,25 @@ class Fabric:
 
     def register_flat_groups(self, groups, model=None, optimizer=None) -> None:
         self.flat_groups = groups
-        if self.uses_p2p:
-            from .p2p import P2PReducer
+        if self.grad_sync == "p2p-host" and self.is_distributed:
+            # the sharded step with torch.distributed collectives instead of the NVLink kernels (CPU / gloo): the
+            # same ownership, buckets and optimizer-state layout, used to check the host-side logic
+            from .p2p import ShardedStepper
 
-            self._p2p = P2PReducer(self, groups, self._p2p_alloc)
-            if optimizer is not None:
-                optimizer.shard(self._p2p.ranges)
+            self._p2p = ShardedStepper(self, groups, optimizer, model, backend="torch")
+        if self.uses_p2p:
+            from .p2p import AgHandle, ShardedStepper
+
+            self._p2p = ShardedStepper(self, groups, optimizer, model, zero3=self.shards_masters,
+                                       allocator=self._p2p_alloc)
+            if self.shards_masters:
+                # the big row-sharded projections are gathered by their first GEMM of a step
+                for gi, g in enumerate(groups[:1]):
+                    for t, (name, p) in enumerate(zip(g.names, g.params)):
+                        if name.endswith(("attn.Wqkv.weight", "mlp.fc.weight")) and p.dim() == 2:
+                            h = AgHandle(self._p2p, gi, t)
+                            if h.usable:
+                                p._ag = h
 
     def fused_reduce_and_step(self, optimizer, max_norm: float, grad_scale: float, do_update: bool) -> bool:
         """Run the fused reduce-scatter + sharded update + parameter push when available."""
@@ -150,9 +178,10 @@ class Fabric:
         return True
 
     def begin_backward(self, model, accumulating: bool) -> None:
-        """Hook point for overlap schedulers (bucket readiness counting); nothing to prepare for the flat path."""
+        """Called before the forward pass of every micro-batch: arms the overlap scheduler (bucket reductions fired
+        from the model's phase hooks during backward) and starts the parameter gathers of the sharded mode."""
         if self._p2p is not None:
-            self._p2p.begin_backward(model, accumulating)
+            self._p2p.begin_step(model, accumulating)
 
     def reduce_gradients(self, optimizer) -> bool:
         """Sum the flat gradient buffers over ranks.  Returns True when the squared norm of the reduced
@@ -203,6 +232,20 @@ class Fabric:
             n = g.numel()
             g.copy_(flat[off:off + n].view_as(g))
             off += n
+
+    def sync_parameters(self) -> None:
+        """Parameter-sharded mode: complete the local bf16 weights outside a training step (validation, export)."""
+        if self._p2p is not None:
+            self._p2p.sync_parameters()
+
+    def device_status(self) -> int:
+        """Status word of the kernels' bounded waits on this rank (0: no wait ran out).  Synchronises the device, so the
+        training loop reads it only where it synchronises anyway."""
+        if self.device.type != "cuda":
+            return 0
+        from ..ops import cuda as K
+
+        return K.check_device_status()
 
     # -- teardown --------------------------------------------------------------------------
     def shutdown(self) -> None:

@@ -43,8 +43,11 @@ def checkpoint_stem(out_dir: str, run_name: str, microbatch_step: int) -> str:
     return os.path.join(checkpoint_dir(out_dir), f"step-{microbatch_step:08d}-{run_name}")
 
 
-def model_state_dict(model, reference_prefixes: bool = False) -> dict:
-    sd = {k: v.detach().to("cpu", copy=True) if torch.is_tensor(v) else v for k, v in model.state_dict().items()}
+def model_state_dict(model, reference_prefixes: bool = False, engine=None) -> dict:
+    if engine is not None and hasattr(engine, "model_state_dict") and getattr(engine, "mode", "") == "fused":
+        sd = engine.model_state_dict()     # reassembles fp32 masters that exist only as per-rank pieces
+    else:
+        sd = {k: v.detach().to("cpu", copy=True) if torch.is_tensor(v) else v for k, v in model.state_dict().items()}
     sd = {k: (v.float() if torch.is_tensor(v) and v.dtype == torch.bfloat16 and k != "freqs_cis" else v)
           for k, v in sd.items()}
     if reference_prefixes:
@@ -61,12 +64,11 @@ def save_checkpoint(fabric, state: dict, out_dir: str, run_name: str, reference_
     """``state`` holds live objects: model, engine (optimizer + counters), train_dataloader, data_scheduler, plus plain
     values.  Returns the written path (None on ranks that do not write)."""
     engine = state.get("engine")
-    if engine is not None and getattr(engine.fabric, "_p2p", None) is not None:
-        engine.fabric._p2p.gather_master()  # collective: make fp32 masters complete on every rank
     payload = {}
     for key, value in state.items():
         if key == "model":
-            payload[key] = model_state_dict(value, reference_prefixes)
+            # collective on the sharded paths: stale or sharded fp32 masters are completed from their owners
+            payload[key] = model_state_dict(value, reference_prefixes, engine)
         elif key == "engine":
             payload["optimizer"] = [value.state_dict()]
         elif key in ("train_dataloader", "data_scheduler") and value is not None:
@@ -88,19 +90,53 @@ def save_checkpoint(fabric, state: dict, out_dir: str, run_name: str, reference_
 
 
 def find_latest(out_dir: str, run_name: str, local_rank: int) -> str | None:
-    best, best_step = None, -1
-    for p in glob.glob(os.path.join(checkpoint_dir(out_dir), f"step-*-{run_name}_{local_rank}.pth")):
-        m = re.search(r"step-(\d+)-", os.path.basename(p))
-        if m and int(m.group(1)) > best_step:
-            best, best_step = p, int(m.group(1))
-    return best
+    """Newest checkpoint file of the run for this local rank; when the run was saved by fewer ranks (resume on a
+    larger world), the newest file of rank 0."""
+    for rank in (local_rank, 0):
+        best, best_step = None, -1
+        for p in glob.glob(os.path.join(checkpoint_dir(out_dir), f"step-*-{run_name}_{rank}.pth")):
+            m = re.search(r"step-(\d+)-", os.path.basename(p))
+            if m and int(m.group(1)) > best_step:
+                best, best_step = p, int(m.group(1))
+        if best is not None:
+            return best
+    return None
+
+
+def sibling_paths(path: str) -> list:
+    """All per-rank files of the checkpoint that ``path`` belongs to, ordered by the rank suffix."""
+    m = re.match(r"(.*)_(\d+)\.pth$", path)
+    if not m:
+        return [path]
+    found = []
+    for p in glob.glob(m.group(1) + "_*.pth"):
+        mm = re.match(r".*_(\d+)\.pth$", p)
+        if mm:
+            found.append((int(mm.group(1)), p))
+    return [p for _, p in sorted(found)]
 
 
 def load_checkpoint(fabric, state: dict, path: str, strict: bool = True) -> dict:
+    """``path`` is this rank's file; when the world size changed since the save and no file exists for this rank,
+    pass any rank's file: model, counters and loader state are identical in all of them, and the sharded optimizer
+    state is re-cut from the whole set of files."""
     ckpt = torch.load(path, map_location="cpu", weights_only=False)
+
+    def all_engine_states():
+        out = []
+        for p in sibling_paths(path):
+            other = ckpt if p == path else torch.load(p, map_location="cpu", weights_only=False)
+            opt = other["optimizer"]
+            out.append(opt[0] if isinstance(opt, list) else opt)
+        return out
+
     for key, value in ckpt.items():
         if key == "model":
             sd = strip_wrapper_prefixes(value)
+            engine = state.get("engine")
+            if engine is not None and getattr(engine, "mode", "") == "fused":
+                engine.load_model_state(sd, strict)
+                continue
             model = state["model"]
             own = model.state_dict()
             with torch.no_grad():
@@ -114,7 +150,8 @@ def load_checkpoint(fabric, state: dict, path: str, strict: bool = True) -> dict
                 raise KeyError(f"missing keys in checkpoint: {missing[:5]}")
         elif key == "optimizer":
             if state.get("engine") is not None:
-                state["engine"].load_state_dict(value[0] if isinstance(value, list) else value)
+                state["engine"].load_state_dict(value[0] if isinstance(value, list) else value,
+                                                other_shards=all_engine_states)
         elif key in ("train_dataloader", "data_scheduler"):
             if state.get(key) is not None:
                 state[key].load_state_dict(value)

@@ -51,22 +51,26 @@ def set_torch_flags(cfg) -> None:
 
 
 def setup_fabric(cfg) -> Fabric:
+    """``fabric_strategy`` names of the reference (train.py:111-158) mapped onto the gradient-sync modes of
+    ``parallel.fabric``: the DDP names run the overlapped reduce-scatter + sharded update (``p2p``); ``zero`` and
+    ``fsdp-grad`` the same (gradients and optimizer state are what they shard); ``fsdp-full`` / ``fsdp-hybrid*`` / ``zero3``
+    additionally shard the fp32 parameters and gather the bf16 weights in the forward pass (``zero3``)."""
     sync = cfg.grad_sync
     strategy = cfg.fabric_strategy
-    if strategy.startswith("fsdp"):
-        # The reference hands these names to Lightning's FSDP wrapper (train.py:115-142).  The sharded mode here covers
-        # what SHARD_GRAD_OP provides on one node: gradients are reduce-scattered, optimizer state lives 1/N per rank and
-        # the updated bf16 weights are pushed to every rank by the same kernel.
+    if strategy in ("fsdp-full", "fsdp-hybrid", "fsdp-hybrid2", "zero3"):
+        if sync not in (None, "zero3"):
+            raise ValueError(f"fabric_strategy {strategy!r} shards parameters: grad_sync must be zero3 (or unset)")
+        sync = "zero3" if torch.cuda.is_available() else "flat"
+    elif strategy.startswith("fsdp"):
         if sync not in (None, "p2p"):
             raise ValueError(f"fabric_strategy {strategy!r} runs on the fused sharded path (grad_sync: p2p)")
         sync = "p2p" if torch.cuda.is_available() else "flat"
     elif strategy not in ("simple-ddp", "ddp", "single", "zero"):
         raise ValueError(f"fabric_strategy {strategy!r}: tensor parallelism through AxoNN is an external library in the "
-                         "reference and is not provided; use simple-ddp, zero or fsdp-*")
-    fabric = Fabric.from_env(grad_sync=sync, precision=cfg.fabric_precision)
-    if sync is None and fabric.is_distributed and fabric.device.type == "cuda":
-        fabric.grad_sync = "p2p"
-    return fabric
+                         "reference and is not provided; use simple-ddp, zero, zero3 or fsdp-*")
+    if sync is None and torch.cuda.is_available() and int(os.environ.get("WORLD_SIZE", os.environ.get("SLURM_NTASKS", 1))) > 1:
+        sync = "p2p"
+    return Fabric.from_env(grad_sync=sync, precision=cfg.fabric_precision)
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -124,6 +128,29 @@ def slurm_seconds_left() -> Optional[float]:
         return None
 
 
+_ELLIS_FUSED = {"update_clipping", "atan_adam", "running_init", "decouple_wd"}
+_ELLIS_OFF = {"nesterov": False, "eps_adjustment": False, "kahan_sum_compensation": False, "buffer_dtype": None,
+              "tensor_wise_finite_check": False, "tensor_wise_gradient_normalization": False,
+              "adafactor_like_beta_corrections": False, "brute_force_clip": None, "poly_ema_p": None, "foreach": None}
+
+
+def fused_optimizer_flags(name: str, optim_config: dict) -> Optional[dict]:
+    """Keyword flags for ``TrainEngine`` when the optimizer can run on the fused flat path, else None.  Covered: AdamW,
+    and ELLISAdam with any of update_clipping / atan_adam / running_init / decouple_wd (the flags of the reference's
+    production run, launch_configs/frontier_nebel_512_nodes.yaml:28-41); every other ELLISAdam option must be off."""
+    if name in ("AdamW", "FusedAdamW"):
+        return {}
+    if name != "ELLISAdam":
+        return None
+    for k, off in _ELLIS_OFF.items():
+        if optim_config.get(k, off) not in (off, False, None):
+            return None
+    return {"atan2": bool(optim_config.get("atan_adam", False)),
+            "update_clipping": bool(optim_config.get("update_clipping", False)),
+            "running_init": bool(optim_config.get("running_init", False)),
+            "decouple_wd": bool(optim_config.get("decouple_wd", True))}
+
+
 # ------------------------------------------------------------------------------------------------------
 def startup(cfg, fabric: Fabric) -> dict:
     t0 = time.time()
@@ -153,18 +180,21 @@ def startup(cfg, fabric: Fabric) -> dict:
     lr_fn = functools.partial(get_lr, lr, warmup_steps=cfg.warmup_steps, max_steps=max_steps,
                               cooldown_steps=cfg.cooldown_steps, schedule=cfg.lr_schedule, min_lr=cfg.min_lr)
     optimizer = None
-    use_fused = cfg.optimizer in ("AdamW", "FusedAdamW") and fabric.device.type == "cuda"
+    fused_flags = fused_optimizer_flags(cfg.optimizer, oc) if fabric.device.type == "cuda" else None
+    use_fused = fused_flags is not None
     if not use_fused:
         from ..optim import get_optimizer, get_param_groups
 
         model.to(fabric.device)
         groups = get_param_groups(model.named_parameters(), cfg.no_weight_decay_for_bias_and_norm_params)
         optimizer = get_optimizer(cfg.optimizer, model=model, use_zero=cfg.fabric.optim_sharding)(groups, lr=lr, **oc)
-    engine = TrainEngine(model, fabric, lr=lr, weight_decay=oc.get("weight_decay", 0.1),
-                         betas=oc.get("betas", (0.9, 0.95)), eps=oc.get("eps", 1e-8), grad_clip=cfg.grad_clip,
+    ellis = cfg.optimizer == "ELLISAdam"      # its constructor defaults differ from AdamW's (recpre/optim.py:729-735)
+    engine = TrainEngine(model, fabric, lr=lr, weight_decay=oc.get("weight_decay", 1e-2 if ellis else 0.1),
+                         betas=oc.get("betas", (0.9, 0.99) if ellis else (0.9, 0.95)),
+                         eps=oc.get("eps", 1e-6 if ellis else 1e-8), grad_clip=cfg.grad_clip,
                          grad_accum=cfg.gradient_accumulation_steps, skip_first_step=cfg.skip_first_optimizer_step,
                          no_weight_decay_for_bias_and_norm_params=cfg.no_weight_decay_for_bias_and_norm_params,
-                         optimizer=optimizer, lr_fn=lambda step: lr_fn(step=step))
+                         optimizer=optimizer, lr_fn=lambda step: lr_fn(step=step), **(fused_flags or {}))
     tracker = DataSchedulerTracker([e.weight for e in cfg.data_config["train_data"]])
     scheduler = DataScheduler(tracker, cfg.data_config["train_data"], max_steps)
     train_loader = create_dataloader(cfg, fabric, tokenizer, cfg.data_config["train_data"], cfg.train_data_dir,
@@ -181,6 +211,7 @@ def startup(cfg, fabric: Fabric) -> dict:
         if path is not None:
             ckpt.load_checkpoint(fabric, state, path, strict=False)
             engine.micro_step = state["microbatch_step"]
+            engine.window_base = engine.micro_step
             engine.optimizer_step = state["optimizer_step"]
             fabric.print(f"Resumed from {path} at micro-batch step {state['microbatch_step']}")
     fabric.barrier()
@@ -194,6 +225,7 @@ def validate(cfg, fabric, state) -> dict:
     ranks (train.py:343-386)."""
     model, mc = state["model"], cfg.model_config
     depths = list(cfg.partial_depth_eval) + [mc.mean_recurrence] if mc.is_recurrent else [0]
+    fabric.sync_parameters()
     model.eval()
     sums = torch.zeros(len(depths), device=fabric.device)
     n = 0
@@ -210,10 +242,23 @@ def validate(cfg, fabric, state) -> dict:
     return {f"val_loss_depth_{d}": float(v) for d, v in zip(depths, means)}
 
 
+def check_device_waits(fabric, state) -> None:
+    """Raise when a kernel of this rank timed out on a wait (a peer's flag, a pipeline barrier).  A timed-out wait in the
+    gradient reduction already poisons that step's norm, so the update is skipped; the run still must not go on, because
+    the ranks no longer agree on what they skipped."""
+    code = fabric.device_status()
+    if code:
+        state["should_exit_training"] = True
+        raise RuntimeError(f"a GPU kernel gave up on a bounded wait (status {code}) at micro-batch step "
+                           f"{state['microbatch_step']}; resume from the last checkpoint")
+
+
 def maybe_save(cfg, fabric, state, force: bool = False) -> None:
     step = state["microbatch_step"]
-    due = force or (cfg.save_step_interval and step % cfg.save_step_interval == 0 and step > 0) or \
-        (cfg.save_first_step and step == 1)
+    # interval saves wait for the end of an accumulation window (train.py:912): the partial gradient sums are not part
+    # of a checkpoint
+    due = force or (cfg.save_step_interval and step % cfg.save_step_interval == 0 and step > 0
+                    and not state.get("is_accumulating", False)) or (cfg.save_first_step and step == 1)
     if not due and cfg.save_n_min_before_job_done is not None and step % 32 == 0:
         left = slurm_seconds_left()
         t = fabric.all_reduce(torch.tensor([left if left is not None else 1e9], device=fabric.device), "mean")
@@ -258,6 +303,7 @@ def train(cfg, fabric, state) -> None:
         total_tokens += tokens_per_mb * fabric.world_size
         if state["microbatch_step"] % max(cfg.log_step_interval, 1) == 0:
             loss = float(out["loss"])  # host sync only at log points
+            check_device_waits(fabric, state)
             if not math.isfinite(loss) and not cfg.allow_nonfinite_loss:
                 state["should_exit_training"] = True
                 fabric.print(f"non-finite loss {loss} at step {state['microbatch_step']}")
@@ -290,10 +336,17 @@ def train(cfg, fabric, state) -> None:
             fabric.print(" | ".join(f"{k} {v:.4f}" for k, v in vm.items()))
         state["data_scheduler"].step(state["microbatch_step"])
         if state["microbatch_step"] % 32 == 0:
-            flag = torch.tensor([1.0 if state["should_exit_training"] else 0.0], device=fabric.device)
+            # element 0: exit flag, MIN over ranks (all must ask); element 1: minus the device status word, MIN over
+            # ranks = the worst status anywhere, so that every rank stops when one rank's kernels gave up on a peer
+            code = fabric.device_status()
+            flag = torch.tensor([1.0 if state["should_exit_training"] else 0.0, -float(code)], device=fabric.device)
             if fabric.is_distributed:
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-            if bool(flag.item()):
+            flag = flag.tolist()
+            if flag[1] < 0:
+                raise RuntimeError(f"a GPU kernel gave up on a bounded wait on some rank (status {int(-flag[1])}, "
+                                   f"this rank {code}); parameters may have diverged -- resume from the last checkpoint")
+            if bool(flag[0]):
                 fabric.print("all ranks requested exit; stopping")
                 break
         maybe_save(cfg, fabric, state)

@@ -142,6 +142,90 @@ def tensor_parallel():
     dist.destroy_process_group()
 
 
+def _train(fabric, flags, steps=5, accum=1):
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("tiny-raven-cpu", **OV)
+    model = cfg.construct_model()
+    eng = TrainEngine(model, fabric, lr=2e-3, weight_decay=0.05, eps=1e-6, mode="fused", grad_accum=accum, **flags)
+    losses, norms = [], []
+    g = torch.Generator().manual_seed(7 + 1000 * fabric.global_rank)
+    for i in range(steps * accum):
+        ids = torch.randint(0, cfg.padded_vocab_size, (2, 65), generator=g)
+        out = eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]))
+        losses.append(out["loss"].item())
+        if out["grad_norm"] is not None:
+            norms.append(float(out["grad_norm"]))
+    params = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    return eng, losses, norms, params
+
+
+def sharded_step():
+    """The sharded optimizer step (per-tensor ownership, buckets fired from the model's phase hooks, sharded moments)
+    on gloo collectives against the replicated flat path, for AdamW and for the ELLISAdam flags; then the parameter-
+    sharded layout and the re-cut of a two-rank optimizer checkpoint for one rank."""
+    from recurrent_pretraining_b200.optim.fused import FusedAdamW
+    from recurrent_pretraining_b200.parallel.flat import flatten_group
+    from recurrent_pretraining_b200.parallel.p2p import ShardedStepper
+
+    fabric = Fabric.from_env(backend="gloo", grad_sync="p2p-host")
+    plain = Fabric(fabric.device, fabric.global_rank, fabric.world_size, fabric.local_rank, "chunked")
+    out = {}
+    ellis = dict(atan2=True, update_clipping=True, running_init=True, decouple_wd=True)
+    for tag, flags, accum in (("adamw", {}, 1), ("ellis", ellis, 1), ("accum", {}, 2)):
+        e1, l1, n1, p1 = _train(fabric, flags, accum=accum)
+        fired = {b.name for b in e1.fabric._p2p.buckets.values()}
+        e2, l2, n2, p2 = _train(plain, flags, accum=accum)
+        out[tag] = {"loss_diff": max(abs(a - b) for a, b in zip(l1, l2)),
+                    "norm_diff": max(abs(a - b) for a, b in zip(n1, n2)),
+                    "param_diff": (p1 - p2).abs().max().item(), "buckets": sorted(fired),
+                    "state_numel": sum(g.state["m"].numel() for g in e1.flat_groups),
+                    "full_numel": sum(g.state["m"].numel() for g in e2.flat_groups)}
+        if tag == "ellis":
+            sharded_sd, full_opt = e1.state_dict(), e2.optimizer
+    # re-cut: both ranks' optimizer state -> a replicated (unsharded) optimizer
+    both = [None, None]
+    dist.all_gather_object(both, sharded_sd)
+    want = [(g.state["m"].clone(), g.state["v"].clone()) for g in full_opt.groups]
+    fresh = FusedAdamW(full_opt.groups, **ellis)        # replaces the groups' moments by zeros of full size
+    fresh.load_state_dict(both[fabric.global_rank]["optimizer"], lambda: [b["optimizer"] for b in both])
+    out["recut_diff"] = max(max((g.state["m"] - m).abs().max().item(), (g.state["v"] - v).abs().max().item())
+                            for g, (m, v) in zip(fresh.groups, want))
+
+    # parameter-sharded layout: synthetic gradients, one update, against the replicated result
+    torch.manual_seed(3)
+    shapes = {"transformer.coda.0.attn.Wqkv.weight": (48, 16), "transformer.core_block.0.mlp.fc.weight": (64, 16),
+              "transformer.prelude.0.attn.proj.weight": (16, 16), "transformer.adapter.weight": (16, 32)}
+    vals = {k: torch.randn(*v) for k, v in shapes.items()}
+    grads = {k: torch.randn(*v) for k, v in shapes.items()}
+
+    def build(shard):
+        params = [torch.nn.Parameter(v.clone()) for v in vals.values()]
+        g = flatten_group(params, list(shapes), torch.device("cpu"), True, {"lr": 1e-2, "base_lr": 1.0,
+                                                                           "weight_decay": 0.1}, shard=shard)
+        for p, k in zip(params, shapes):
+            p.grad.copy_(grads[k])
+        return g
+
+    gs = build((fabric.world_size, fabric.global_rank))
+    opt_s = FusedAdamW([gs], lr=1e-2)
+    st = ShardedStepper(fabric, [gs], opt_s, None, zero3=True, backend="torch")
+    for b in st.buckets.values():
+        b.fired = True
+    st.master_sharded = [True]
+    st._step_torch(opt_s, 1.0, 1.0 / fabric.world_size, True)
+    gr = build(None)
+    gr.grad.mul_(fabric.world_size)
+    opt_r = FusedAdamW([gr], lr=1e-2)
+    opt_r.step(max_norm=1.0, grad_scale=1.0 / fabric.world_size)
+    out["zero3_shadow_diff"] = (gs.shadow.float() - gr.shadow.float()).abs().max().item()
+    full = st.full_master(0, 1)
+    out["zero3_master_diff"] = (full - gr.master[gr.offsets[1]:gr.offsets[1] + full.numel()].view_as(full)).abs().max().item()
+    out["zero3_master_numel"] = [gs.master.numel(), gr.master.numel()]
+    if fabric.global_rank == 0:
+        print("RESULT " + json.dumps(out))
+    fabric.shutdown()
+
+
 if __name__ == "__main__":
     {"parity": parity, "rank_failure": rank_failure, "exit_flag": exit_flag,
-     "tensor_parallel": tensor_parallel}[sys.argv[1]]()
+     "tensor_parallel": tensor_parallel, "sharded_step": sharded_step}[sys.argv[1]]()

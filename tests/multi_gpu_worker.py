@@ -15,61 +15,72 @@ from recurrent_pretraining_b200.parallel.fabric import Fabric  # noqa: E402
 from recurrent_pretraining_b200.runtime.engine import TrainEngine  # noqa: E402
 
 
-def run_training(sync: str, steps: int = 4):
-    fabric = Fabric.from_env(grad_sync=sync)
+ELLIS = dict(atan2=True, update_clipping=True, running_init=True, decouple_wd=True)
+DEPTHS = [(1, 2), (0, 3), (2, 1), (1, 2), (3, 1), (0, 2)]    # (n, k) varies from step to step, as with the sampler
+
+
+def run_training(fabric, steps: int = 6, flags=None, accum: int = 1):
     torch.manual_seed(0)
     cfg = ModelConfig.from_name("smoke-raven-96", lockstep_n=True, lockstep_k=True)
     with torch.device(fabric.device):
         model = cfg.construct_model()
-    eng = TrainEngine(model, fabric, lr=1e-3)
+    eng = TrainEngine(model, fabric, lr=1e-3, eps=1e-6, grad_accum=accum, **(flags or {}))
     g = torch.Generator().manual_seed(100 + fabric.global_rank)
     losses, norms = [], []
-    for i in range(steps):
+    for i in range(steps * accum):
         ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), generator=g).to(fabric.device)
         state = (torch.randn(2, 128, cfg.n_embd, generator=g) * 0.6).to(fabric.device).bfloat16()
-        out = eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]), input_states=state)
+        out = eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor(DEPTHS[(i // accum) % len(DEPTHS)]),
+                             input_states=state)
         losses.append(out["loss"].item())
-        norms.append(out["grad_norm"].item())
+        if out["grad_norm"] is not None:
+            norms.append(out["grad_norm"].item())
+    fabric.sync_parameters()
     torch.cuda.synchronize()
     shadow = torch.cat([g_.shadow.float().cpu() for g_ in eng.flat_groups])
-    return fabric, eng, losses, norms, shadow
+    return eng, losses, norms, shadow
+
+
+def compare_modes(sync: str, flags=None, accum: int = 1):
+    """The sharded step (``sync``) against the NCCL all-reduce + replicated update on the same data."""
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    fabric = Fabric.from_env(grad_sync=sync)
+    eng, l1, n1, s1 = run_training(fabric, flags=flags, accum=accum)
+    status = K.check_device_status()
+    mine = s1.to(fabric.device)
+    ref = mine.clone()
+    dist.broadcast(ref, 0)
+    same = torch.tensor([float(torch.equal(mine, ref))], device=fabric.device)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    st = fabric._p2p
+    info = {"overlap_fired": sorted(b.name for b in st.buckets.values()), "bytes": st.persistent_bytes(),
+            "ag_weights": sum(1 for g_ in eng.flat_groups for p in g_.params if hasattr(p, "_ag"))}
+    # checkpoint view of the fp32 parameters (collective): must equal the replicated run's masters
+    sd = eng.model_state_dict()
+    st.close()
+    fabric._p2p = None
+    fabric2 = Fabric(fabric.device, fabric.global_rank, fabric.world_size, fabric.local_rank, "flat")
+    eng2, l2, n2, s2 = run_training(fabric2, flags=flags, accum=accum)
+    sd2 = eng2.model_state_dict()
+    master_rel = max(((sd[k].float() - sd2[k].float()).norm() / (sd2[k].float().norm() + 1e-12)).item()
+                     for k in sd2 if k != "freqs_cis")
+    rel = ((s1 - s2).norm() / s2.norm()).item()
+    return fabric, {"losses": l1, "nccl_losses": l2, "norms": n1, "nccl_norms": n2,
+                    "replicas_identical": bool(same.item()), "param_rel_diff": rel, "master_rel_diff": master_rel,
+                    "status": status, **info}
 
 
 def main():
     mode = sys.argv[1]
     from recurrent_pretraining_b200.ops import cuda as K
 
-    if mode == "train":
-        fabric, eng, l1, n1, s1 = run_training("p2p")
-        status = K.check_device_status()
-        # all ranks must hold identical bf16 parameters after the pushes
-        mine = s1.to(fabric.device)
-        ref = mine.clone()
-        dist.broadcast(ref, 0)
-        same = bool(torch.equal(mine, ref))
-        if fabric._p2p is not None:
-            fabric._p2p.close()
-            fabric._p2p = None
-        # same run with the NCCL flat all-reduce + replicated update as the oracle
-        fabric2 = Fabric(fabric.device, fabric.global_rank, fabric.world_size, fabric.local_rank, "flat")
-        torch.manual_seed(0)
-        cfg = ModelConfig.from_name("smoke-raven-96", lockstep_n=True, lockstep_k=True)
-        with torch.device(fabric.device):
-            model = cfg.construct_model()
-        eng2 = TrainEngine(model, fabric2, lr=1e-3)
-        g = torch.Generator().manual_seed(100 + fabric.global_rank)
-        l2, n2 = [], []
-        for i in range(4):
-            ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), generator=g).to(fabric.device)
-            state = (torch.randn(2, 128, cfg.n_embd, generator=g) * 0.6).to(fabric.device).bfloat16()
-            out = eng2.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]), input_states=state)
-            l2.append(out["loss"].item())
-            n2.append(out["grad_norm"].item())
-        s2 = torch.cat([g_.shadow.float().cpu() for g_ in eng2.flat_groups])
-        rel = ((s1 - s2).norm() / s2.norm()).item()
+    if mode in ("train", "train_ellis", "train_accum", "zero3", "zero3_ellis"):
+        sync = "zero3" if mode.startswith("zero3") else "p2p"
+        flags = ELLIS if mode.endswith("ellis") else None
+        fabric, res = compare_modes(sync, flags, accum=2 if mode == "train_accum" else 1)
         if fabric.global_rank == 0:
-            print("RESULT " + json.dumps({"p2p_losses": l1, "nccl_losses": l2, "p2p_norms": n1, "nccl_norms": n2,
-                                          "replicas_identical": same, "param_rel_diff": rel, "status": status}))
+            print("RESULT " + json.dumps(res))
         dist.barrier()
         dist.destroy_process_group()
     elif mode == "timeout":

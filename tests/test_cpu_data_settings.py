@@ -82,6 +82,45 @@ def test_stateful_loader_batches_and_random_tokens():
     assert torch.equal(next(iter(again)), torch.cat([x[0, :1], y[0]]))
 
 
+@pytest.mark.parametrize("kind", ["random", "parquet"])
+def test_loader_resume_with_prefetch_is_exact(tmp_path, kind):
+    """Stop after k batches while the producer thread is several batches ahead, save, reload into a fresh loader: the
+    continuation equals the uninterrupted stream (nothing skipped, nothing repeated)."""
+    import time
+
+    if kind == "parquet":
+        _write_shards(tmp_path, n_files=3, groups=3, rows=7)
+
+    def make():
+        ds = RandomTokens(100, 9, seed=5, length=60) if kind == "random" else \
+            ParquetStream(str(tmp_path), seed=2, plan_for_later_rank_expansion_to=0)
+        return StatefulLoader(ds, 2, lambda rows: generic_collate_fn(rows, all_block_size_tensors=True), prefetch=4)
+
+    full = [x.clone() for x, _, _ in make()]
+    assert len(full) >= 12
+    for k in (1, 5, 8):
+        loader = make()
+        it = iter(loader)
+        head = [next(it)[0].clone() for _ in range(k)]
+        time.sleep(0.3)                      # let the producer fill its queue: it is now 4-5 batches ahead
+        state = loader.state_dict()
+        resumed = make()
+        resumed.load_state_dict(state)
+        tail = [x.clone() for x, _, _ in resumed]
+        got = head + tail
+        assert len(got) == len(full), (k, len(got), len(full))
+        assert all(torch.equal(a, b) for a, b in zip(got, full)), k
+        it.close()
+    # the same loader object can also go on after its iterator was closed early
+    loader = make()
+    it = iter(loader)
+    head = [next(it)[0].clone() for _ in range(3)]
+    time.sleep(0.2)
+    it.close()
+    rest = [x.clone() for x, _, _ in loader]
+    assert all(torch.equal(a, b) for a, b in zip(head + rest, full)) and len(head + rest) == len(full)
+
+
 def test_goldfish_masks():
     labels = torch.randint(1, 1000, (2, 64))
     out, idx = apply_tld(labels, GoldfishConfig(4, 1, 13, "static"))
@@ -121,6 +160,7 @@ def test_lr_and_batch_schedules():
     with pytest.raises(ValueError):
         get_lr(1e-3, 50, schedule="nope", **kw)
     assert get_batch_size(0, 100, 8) == 1 and get_batch_size(50, 100, 8) == 4 and get_batch_size(200, 100, 8) == 8
+    assert get_batch_size(30, 100, 8) == 3      # ceil, as train.py:856-862 of the reference
 
 
 def test_settings_yaml_overrides_and_derivations(tmp_path, monkeypatch):

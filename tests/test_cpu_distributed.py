@@ -67,3 +67,18 @@ def test_tensor_parallel_blocks_match_the_unsharded_model():
     assert abs(res["loss_full"] - res["loss_tp"]) < 1e-5, res
     assert max(res["g_qkv"], res["g_proj"], res["g_norm"], res["g_emb"]) < 1e-5, res
     assert res["gather_ok"] and res["params_local"] < res["params_full"]
+
+
+def test_sharded_step_matches_replicated_update():
+    """Per-tensor sharded optimizer step (buckets, sharded moments, ELLISAdam flags, accumulation windows, parameter-
+    sharded masters, re-cut of a two-rank optimizer checkpoint) against the replicated flat update."""
+    r = _torchrun([os.path.join(HERE, "cpu_dp_worker.py"), "sharded_step"], 29633)
+    res = _result(r)
+    for tag in ("adamw", "ellis", "accum"):
+        c = res[tag]
+        assert c["loss_diff"] < 2e-5 and c["norm_diff"] < 2e-5 and c["param_diff"] < 2e-5, (tag, c)
+        assert c["buckets"] == ["coda", "core", "last", "prelude"], c
+        assert c["state_numel"] < 0.6 * c["full_numel"], c
+    assert res["recut_diff"] < 1e-6, res
+    assert res["zero3_shadow_diff"] < 1e-2 and res["zero3_master_diff"] < 1e-6, res
+    assert res["zero3_master_numel"][0] < 0.6 * res["zero3_master_numel"][1], res

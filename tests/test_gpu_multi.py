@@ -25,16 +25,38 @@ def _run(mode: str, nproc: int = 2, port: int = 29641):
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 
 
-@needs2
-def test_p2p_sharded_step_matches_nccl_allreduce():
-    res = _run("train")
-    assert res["status"] == 0
-    assert res["replicas_identical"]
-    for a, b in zip(res["p2p_losses"], res["nccl_losses"]):
+def _check_parity(res, sharded_master: bool = False):
+    assert res["status"] == 0, res
+    assert res["replicas_identical"], res
+    for a, b in zip(res["losses"], res["nccl_losses"]):
         assert abs(a - b) < 0.02 * abs(b) + 0.02, res
-    for a, b in zip(res["p2p_norms"], res["nccl_norms"]):
+    for a, b in zip(res["norms"], res["nccl_norms"]):
         assert abs(a - b) < 0.05 * abs(b) + 1e-3, res
     assert res["param_rel_diff"] < 2e-2, res
+    assert res["master_rel_diff"] < 2e-2, res
+
+
+@needs2
+@pytest.mark.parametrize("mode", ["train", "train_ellis", "train_accum"])
+def test_p2p_sharded_step_matches_nccl_allreduce(mode):
+    """Bucketed reduce-scatter fired from the backward pass + sharded update + bf16 push against NCCL all-reduce +
+    replicated update, with the recurrence depths changing from step to step; AdamW, the ELLISAdam flags, and a
+    two-micro-batch accumulation window."""
+    res = _run(mode)
+    _check_parity(res)
+    assert res["overlap_fired"] == ["coda", "core", "last", "prelude"], res
+
+
+@needs2
+@pytest.mark.parametrize("mode", ["zero3", "zero3_ellis"])
+def test_parameter_sharded_step_matches_nccl_allreduce(mode):
+    """fp32 masters and optimizer state 1/N per rank, bf16 weights pulled in the forward pass (QKV and gate-up inside
+    their first GEMM): same losses, norms and parameters as the replicated path, and less memory."""
+    res = _run(mode, port=29649)
+    _check_parity(res)
+    assert res["ag_weights"] > 0, res
+    b = res["bytes"]
+    assert b["master"] < 0.6 * b["grad"] and b["moments"] < 0.6 * 2 * b["grad"], res
 
 
 @needs2
@@ -46,12 +68,8 @@ def test_barrier_wait_times_out_and_reports():
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_p2p_sharded_step_four_ranks():
-    res = _run("train", nproc=4, port=29645)
-    assert res["status"] == 0
-    assert res["replicas_identical"]
-    for a, b in zip(res["p2p_losses"], res["nccl_losses"]):
-        assert abs(a - b) < 0.02 * abs(b) + 0.02, res
-    assert res["param_rel_diff"] < 2e-2, res
+    _check_parity(_run("train", nproc=4, port=29645))
+    _check_parity(_run("zero3", nproc=4, port=29651))
 
 
 @needs2

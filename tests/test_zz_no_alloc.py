@@ -53,6 +53,13 @@ def test_noalloc_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert torch.equal(dx, dx_ref), f"call {call}: dx differs"
         _close(dw, dw_ref, 2e-2, 2e-2 * M ** 0.5)
+        # and against the plain fp32 statement of the op
+        x32 = x.float().requires_grad_(True)
+        w32 = w.clone().requires_grad_(True)
+        y = (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16).float() * w32
+        y.backward(dy.float())
+        _close(dx, x32.grad, 3e-2, 3e-2)
+        _close(dw, w32.grad, 2e-2, 2e-2 * M ** 0.5)
 
 
 def test_noalloc_rejects_oversize_rows():
@@ -63,3 +70,25 @@ def test_noalloc_rejects_oversize_rows():
     assert b"at most 8192" in lib.b200_noalloc_last_error()
     rc = fn(t.data_ptr(), t.data_ptr(), 0, t.data_ptr(), t.data_ptr(), 0, 1, 100, 0)
     assert rc == -1
+
+
+def test_noalloc_rejects_bad_pointers_before_any_launch():
+    """A NULL or misaligned buffer is refused on the host (rc -1, nothing launched), because on the device it would be
+    a fault that costs the embedding application its CUDA context."""
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    lib, fn = _lib()
+    M, E = 4, 64
+    x = torch.randn(M, E + 8, device="cuda").bfloat16()
+    dy = torch.randn(M, E, device="cuda").bfloat16()
+    rstd = torch.ones(M, device="cuda")
+    dx = torch.full((M, E), 7.0, device="cuda").bfloat16()
+    torch.cuda.synchronize()
+    before = K.launch_count()
+    rc = fn(dy.data_ptr(), x.data_ptr(), 0, rstd.data_ptr(), 0, 0, M, E, 0)           # dx == NULL
+    assert rc == -1 and b"NULL" in lib.b200_noalloc_last_error()
+    rc = fn(dy.data_ptr(), x.data_ptr() + 2, 0, rstd.data_ptr(), dx.data_ptr(), 0, M, E, 0)   # x off by one element
+    assert rc == -1 and b"16-byte" in lib.b200_noalloc_last_error()
+    torch.cuda.synchronize()
+    assert K.launch_count() == before
+    assert bool((dx.float() == 7.0).all())      # the output was never touched
