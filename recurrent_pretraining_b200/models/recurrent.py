@@ -24,6 +24,7 @@ import torch.utils.checkpoint
 
 from ..ops import functional as ops
 from ..ops import reference as ref
+from ..utils import nvtx
 from .blocks import Linear, make_block, make_mlp, make_norm
 from .sampler import sample_recurrence
 
@@ -51,6 +52,16 @@ class _LMBase(nn.Module):
 
             t.register_hook(hook)
         return t
+
+    def _ckpt(self):
+        """Checkpoint callable for the configured policy (plain recomputation, or selectively kept GEMM / attention
+        outputs: ``sac``, ``sac-attn``, ``sac%N`` in ``activation_checkpoint_impl``)."""
+        fn = getattr(self, "_ckpt_fn", None)
+        if fn is None:
+            from ..ops.sac import checkpoint_fn
+
+            fn = self._ckpt_fn = checkpoint_fn(self.config.activation_checkpoint_impl)
+        return fn
 
     def _setup_rope(self, config) -> None:
         length = config.randomize_positions_from or config.block_size
@@ -211,7 +222,7 @@ class RecurrentGPT(_LMBase):
             x = x + context
         for block in self.transformer.core_block:
             if per_block and torch.is_grad_enabled():
-                x = torch.utils.checkpoint.checkpoint(block, x, rope, mask, use_reentrant=False)
+                x = self._ckpt()(block, x, rope, mask)
             else:
                 x = block(x, rope, mask)
         return x
@@ -237,8 +248,7 @@ class RecurrentGPT(_LMBase):
         for step in range(k):
             xk = x
             if per_iter and torch.is_grad_enabled():
-                x = torch.utils.checkpoint.checkpoint(self.core_block_forward, x, e, rope, mask, n + step, inj,
-                                                      use_reentrant=False)
+                x = self._ckpt()(self.core_block_forward, x, e, rope, mask, n + step, inj)
             else:
                 x = self.core_block_forward(x, e, rope, mask, n + step, inj)
         return self.transformer.ln_f(x), n, k, xk.detach()
@@ -273,21 +283,24 @@ class RecurrentGPT(_LMBase):
             position_ids = torch.sort(torch.randint(0, cfg.randomize_positions_from, (S,),
                                                     device=input_ids.device))[0]
         rope = self._rope(S, position_ids)
-        e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
-        self._phase(e, "prelude")        # gradient of the embedding output: the prelude has gone backward
-        for block in self.transformer.prelude:
-            e = block(e, rope, attention_mask)
-        self._phase(e, "core")           # gradient of the prelude output: all recurrences and the adapter are done
-        x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
+        with nvtx.range("prelude"):
+            e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
+            self._phase(e, "prelude")    # gradient of the embedding output: the prelude has gone backward
+            for block in self.transformer.prelude:
+                e = block(e, rope, attention_mask)
+            self._phase(e, "core")       # gradient of the prelude output: all recurrences and the adapter are done
+        with nvtx.range("recurrence"):
+            x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
         self._phase(x, "coda")           # gradient of the coda input: the coda blocks are done
         x_rec = x
         in_coda = self.gradient_checkpointing and "in-coda" in cfg.activation_checkpoint_impl
-        for block in self.transformer.coda:
-            if in_coda and torch.is_grad_enabled():
-                x = torch.utils.checkpoint.checkpoint(block, x, rope, attention_mask, use_reentrant=False)
-            else:
-                x = block(x, rope, attention_mask)
-        x = self.transformer.ln_f(x)
+        with nvtx.range("coda"):
+            for block in self.transformer.coda:
+                if in_coda and torch.is_grad_enabled():
+                    x = self._ckpt()(block, x, rope, attention_mask)
+                else:
+                    x = block(x, rope, attention_mask)
+            x = self.transformer.ln_f(x)
         if self.monitoring:
             self.monitor_module(x, x_rec, xk, e, n, k)
         loss, logits, log_ppl = self._loss(x, labels, return_logits or labels is None)
@@ -356,7 +369,7 @@ class GPT(_LMBase):
             if i == half and i > 0:
                 self._phase(x, "upper")  # gradient here: the upper half of the stack has gone backward
             if self.gradient_checkpointing and torch.is_grad_enabled():
-                x = torch.utils.checkpoint.checkpoint(block, x, rope, attention_mask, use_reentrant=False)
+                x = self._ckpt()(block, x, rope, attention_mask)
             else:
                 x = block(x, rope, attention_mask)
         x = self.transformer.ln_f(x)

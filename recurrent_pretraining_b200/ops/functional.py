@@ -22,6 +22,7 @@ import math
 import torch
 
 from . import reference as ref
+from . import sac
 
 _cuda = None
 
@@ -98,7 +99,7 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, weight):
         C = cuda_backend()
         x2 = x.reshape(-1, x.shape[-1])
-        y = _gemm_nt_w(x2, weight)
+        (y,) = sac.run_op("mm", lambda: (_gemm_nt_w(x2, weight),))
         ctx.save_for_backward(x2, weight)
         ctx.xshape = x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -144,7 +145,7 @@ class _Adapter(torch.autograd.Function):
         E = x.shape[-1]
         x2, e2 = x.reshape(-1, E), e.reshape(-1, E)
         w = _lp(weight)
-        y = C.gemm_nt(x2, w, a2=e2)  # the K loop runs over x then e against the two column halves of W
+        (y,) = sac.run_op("mm", lambda: (C.gemm_nt(x2, w, a2=e2),))  # K loop: x then e against the two halves of W
         ctx.save_for_backward(x2, e2, weight)
         ctx.xshape = x.shape
         return y.view(x.shape)
@@ -196,7 +197,8 @@ class _AdapterInject(torch.autograd.Function):
         e2 = e.reshape(-1, E)
         ctx.save_for_backward(e2, weight)
         ctx.eshape = e.shape
-        return C.gemm_nt(e2, _lp(weight)[:, E:]).view(e.shape)
+        (y,) = sac.run_op("mm", lambda: (C.gemm_nt(e2, _lp(weight)[:, E:]),))
+        return y.view(e.shape)
 
     @staticmethod
     def backward(ctx, dinj):
@@ -219,7 +221,8 @@ class _AdapterState(torch.autograd.Function):
         C = cuda_backend()
         E = x.shape[-1]
         x2 = x.reshape(-1, E)
-        y = C.gemm(x2, _lp(weight)[:, :E], resid=inj.reshape(-1, E), out_mode=C.OUT_BF16_RESID)
+        (y,) = sac.run_op("mm", lambda: (C.gemm(x2, _lp(weight)[:, :E], resid=inj.reshape(-1, E),
+                                                  out_mode=C.OUT_BF16_RESID),))
         ctx.save_for_backward(x2, weight)
         ctx.xshape = x.shape
         return y.view(x.shape)
@@ -321,7 +324,7 @@ class _RopeAttention(torch.autograd.Function):
     def forward(ctx, qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, scale):
         C = cuda_backend()
         qkv_r = C.rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
-        o, lse = C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale)
+        o, lse = sac.run_op("attn", lambda: C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale))
         ctx.save_for_backward(qkv_r, o, lse, cos, sin)
         ctx.meta = (n_head, n_kv, head_dim, scale, qk_bias is not None)
         return o
@@ -348,9 +351,9 @@ class _QKVRopeAttention(torch.autograd.Function):
         x2 = x.reshape(-1, E)
         bias = None if qk_bias is None else qk_bias.detach().float().reshape(-1).contiguous()
         width = (n_head + n_kv) * head_dim
-        qkv_r = C.gemm(x2, _lp(weight), out_mode=C.OUT_BF16_ROPE,
-                       rope=(cos, sin, bias, S, head_dim, width)).view(B, S, -1)
-        o, lse = C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale)
+        (qkv_r,) = sac.run_op("mm", lambda: (C.gemm(x2, _lp(weight), out_mode=C.OUT_BF16_ROPE,
+                                                    rope=(cos, sin, bias, S, head_dim, width)).view(B, S, -1),))
+        o, lse = sac.run_op("attn", lambda: C.attention_fwd(qkv_r, n_head, n_kv, head_dim, scale))
         ctx.save_for_backward(x2, weight, qkv_r, o, lse, cos, sin)
         ctx.meta = (n_head, n_kv, head_dim, scale, qk_bias is not None, x.shape)
         return o

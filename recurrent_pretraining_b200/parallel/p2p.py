@@ -31,6 +31,7 @@ import os
 import torch
 import torch.distributed as dist
 
+from ..utils import nvtx
 from .segments import BUCKET_ORDER, GATHER_ORDER, GroupShards, bucket_of
 from .symm import SymmetricBuffer
 
@@ -249,6 +250,10 @@ class ShardedStepper:
         if b.fired:
             return
         b.fired = True
+        with nvtx.range(f"reduce-scatter:{name}"):
+            self._fire_now(b, ctas)
+
+    def _fire_now(self, b: _Bucket, ctas: int) -> None:
         self._fix_unwritten(b)
         if self.backend != "cuda" or self.world == 1:
             return

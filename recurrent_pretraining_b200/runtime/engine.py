@@ -24,6 +24,7 @@ from typing import Optional
 import torch
 
 from ..optim.fused import FusedAdamW
+from ..utils import nvtx
 from ..optim.groups import get_param_groups
 from ..parallel.flat import flatten_group
 
@@ -98,12 +99,14 @@ class TrainEngine:
             if (self.micro_step - 1 - self.window_base) % self.grad_accum == 0:
                 self._begin_window()
             self.fabric.begin_backward(model, accumulating)
-        out = model(input_ids, labels=labels, **fwd_kwargs)
+        with nvtx.range("forward"):
+            out = model(input_ids, labels=labels, **fwd_kwargs)
         loss = out["loss"]
-        if self.mode == "fused":
-            loss.backward()
-        else:
-            (loss / self.grad_accum).backward()
+        with nvtx.range("backward"):
+            if self.mode == "fused":
+                loss.backward()
+            else:
+                (loss / self.grad_accum).backward()
         result = {"loss": loss.detach(), "log_ppl": out["log_ppl"], "grad_norm": None,
                   "depths": getattr(model, "last_depths", (0, 0))}
         if accumulating:
@@ -114,7 +117,9 @@ class TrainEngine:
         if self.mode == "fused":
             world = self.fabric.world_size
             scale = 1.0 / (self.grad_accum * world)
-            if self.fabric.fused_reduce_and_step(self.optimizer, self.grad_clip, scale, do_update):
+            with nvtx.range("reduce+update"):
+                fused_done = self.fabric.fused_reduce_and_step(self.optimizer, self.grad_clip, scale, do_update)
+            if fused_done:
                 result["grad_norm"] = self.optimizer.grad_norm(scale)
                 self.last_grad_norm = result["grad_norm"]
                 self.optimizer_step += 1

@@ -85,3 +85,59 @@ def test_chat_compare_and_step_recorder():
     s = rec.summary()
     assert s["calls"] == 1 and s["tokens"] >= 5 and 1 <= s["mean_steps"] <= 6
     assert model.generate.__name__ != "patched"
+
+
+def test_adaptive_compute_wrapper_records_steps(tmp_path):
+    from recurrent_pretraining_b200.evaluate.adaptive_eval import AUTO_THRESHOLDS, AdaptiveComputeLM
+    from recurrent_pretraining_b200.models.hf import RavenForCausalLM
+    from recurrent_pretraining_b200.models.hf_config import RavenConfig
+
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **TINY)
+    model = RavenForCausalLM(RavenConfig.from_model_config(cfg)).eval()
+    lm = AdaptiveComputeLM(model, ByteTok(), criterion="latent-diff", exit_threshold="auto", max_steps=6, max_gen_toks=5,
+                           device="cpu")
+    assert lm.exit_threshold == AUTO_THRESHOLDS["latent-diff"]
+    out = lm.generate_until([("hello", {"until": ["\n"], "max_gen_toks": 5}), ("abc", {"max_gen_toks": 3})])
+    assert len(out) == 2 and len(lm.step_log) == 2
+    summ = lm.compute_summary()
+    assert summ["tokens"] == sum(len(r) for r in lm.step_log) and 1 <= summ["mean_steps"] <= 6
+    lm.dump(str(tmp_path / "steps.json"))
+    import json
+
+    assert json.load(open(tmp_path / "steps.json"))["criterion"] == "latent-diff"
+
+
+def test_saturation_eval_and_pass_at_k(tmp_path):
+    from recurrent_pretraining_b200.evaluate import pass_at_k as pk
+    from recurrent_pretraining_b200.evaluate.local_lm_eval import parse_kv
+    from recurrent_pretraining_b200.evaluate.saturation_eval import sample_scores, sweep
+
+    depth = {"d": 0}
+
+    def fake_eval(task):
+        d = depth["d"]
+        if "gsm8k" in task:
+            rows = [{"exact_match": float(i < d), "filter": "flexible-extract"} for i in range(4)] + \
+                   [{"exact_match": 1.0, "filter": "strict-match"}]
+            return {"samples": {task: rows}}
+        return {"samples": {task + "_a": [{"acc": 1.0}], task + "_b": [{"acc": float(d > 2)}]}}
+
+    curve = sweep("gsm8k_cot", [1, 3], lambda d: depth.update(d=d), fake_eval, out_dir=str(tmp_path))
+    assert curve == {1: 0.25, 3: 0.75}
+    assert torch.load(tmp_path / "saturation_gsm8k_cot_3_0.pth")[3] == [1.0, 1.0, 1.0, 0.0]
+    depth["d"] = 4
+    assert sample_scores("mmlu", fake_eval("mmlu")) == [1.0, 1.0]
+    # unbiased estimator against its definition
+    from math import comb
+
+    for n, c, k in ((10, 3, 1), (10, 3, 5), (5, 5, 2), (8, 0, 3), (4, 1, 4)):
+        want = 1.0 - (comb(n - c, k) / comb(n, k) if n - c >= k else 0.0)
+        assert abs(pk.pass_at_k_estimate(n, c, k) - want) < 1e-12
+    docs = [{"prompt": "def add(a, b):\n"}]
+    preds = pk.build_predictions([["    return a + b\n", "    return a * b\n"]], docs)
+    res = pk.pass_at_k(["assert add(2, 3) == 5"], preds, k=[1, 2], timeout_s=20)
+    assert res == {"pass@1": 0.5, "pass@2": 1.0}
+    assert pk.build_predictions_instruct([["    return 1\n```\nthanks"]], docs)[0][0].endswith("return 1\n")
+    assert parse_kv("pretrained=x/y,mean_recurrence=32,exit_threshold=1e-2,flag=true") == \
+        {"pretrained": "x/y", "mean_recurrence": 32, "exit_threshold": 0.01, "flag": True}

@@ -87,3 +87,82 @@ def test_example_scripts_run():
 
     rows = traj.main(["--steps", "6", "--tokens", "3"])
     assert len(rows) == 3 and all(len(r["xy"]) == 7 for r in rows)
+
+
+def test_nvtx_ranges_mark_the_phases_of_a_step():
+    import torch
+
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.runtime.engine import TrainEngine
+    from recurrent_pretraining_b200.utils import nvtx
+
+    nvtx.enable(True)
+    nvtx.reset()
+    try:
+        cfg = ModelConfig.from_name("tiny-raven-cpu")
+        eng = TrainEngine(cfg.construct_model(), lr=1e-3, mode="torch")
+        ids = torch.randint(0, cfg.padded_vocab_size, (1, 33))
+        eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 1]))
+        assert nvtx.opened() == ["forward", "prelude", "recurrence", "coda", "backward"]
+    finally:
+        nvtx.enable(False)
+        nvtx.reset()
+
+
+def test_rope_formulations_agree():
+    import torch
+
+    from recurrent_pretraining_b200.ops import reference as ref
+    from recurrent_pretraining_b200.ops import rope_variants as rv
+
+    torch.manual_seed(0)
+    B, S, H, D = 2, 17, 3, 8
+    x = torch.randn(B, S, H, D)
+    cos, sin = ref.rope_tables(D, S, 50000.0)
+    want = ref.rope_interleaved(x, cos, sin)
+    ang = rv.angles(D, S)
+    assert torch.allclose(rv.rope_complex(x, rv.complex_table(D, S)), want, atol=1e-5)
+    assert torch.allclose(rv.rope_matrix(x, ang), want, atol=1e-5)
+    half = rv.rope_rotate_half(rv.to_half_layout(x), ang)
+    assert torch.allclose(rv.from_half_layout(half), want, atol=1e-5)
+    assert not torch.allclose(rv.rope_rotate_half(x, ang), want, atol=1e-3)   # the layouts are NOT interchangeable
+
+
+def test_utils_extras(tmp_path):
+    import torch
+    import torch.nn.functional as F
+
+    from recurrent_pretraining_b200.utils import extras
+
+    # streaming save / load
+    sd = {"a": torch.randn(5, 3), "b": torch.arange(7, dtype=torch.int64), "c": torch.randn(4).bfloat16(),
+          "empty": torch.empty(0)}
+    with extras.incremental_save(str(tmp_path / "ck.zip")) as sv:
+        for k, v in sd.items():
+            sv.store(k, v)
+        sv.store_meta({"step": 3})
+    got, meta = extras.load_incremental(str(tmp_path / "ck.zip"))
+    assert meta == {"step": 3} and all(torch.equal(got[k], v) and got[k].dtype == v.dtype for k, v in sd.items())
+    assert set(extras.load_incremental(str(tmp_path / "ck.zip"), names=["b"])[0]) == {"b"}
+    # chunked CE == plain CE; several ignore ids; vocabulary slice
+    torch.manual_seed(0)
+    logits, tg = torch.randn(2, 37, 50), torch.randint(0, 50, (2, 37))
+    tg[0, :5] = 49
+    want = F.cross_entropy(logits.view(-1, 50), torch.where(tg == 49, -100, tg).view(-1), ignore_index=-100)
+    assert torch.allclose(extras.chunked_cross_entropy(logits, tg, 16, ignore_indices=[-100, 49]), want, atol=1e-6)
+    assert torch.allclose(extras.chunked_cross_entropy(logits, tg, 0, ignore_indices=[-100, 49]), want, atol=1e-6)
+    sl = extras.chunked_cross_entropy(logits, tg, 8, ignore_indices=[-100], target_range=(10, 30))
+    keep = (tg >= 10) & (tg < 30)
+    assert torch.allclose(sl, F.cross_entropy(logits[keep][:, 10:30], tg[keep] - 10), atol=1e-6)
+    # exact-match statistics
+    V, pad = 11, 10
+    labels = torch.tensor([[1, 2, 3, 4, 5, pad], [1, 2, 3, 4, 5, 6]])
+    lg = F.one_hot(labels.clamp(max=V - 1), V).float()
+    lg[1, 4] = F.one_hot(torch.tensor(0), V).float()        # row 1 misses position 4
+    st = extras.batch_exact_match(lg, labels, ["x", "y"], [1, 2], [2, 3], pad)
+    assert st[1][2] == [(True, "x"), (True, "y")] and st[2][3] == [(True, "x"), (False, "y")]
+    assert st["natural_suffix"][2] == [(True, "x"), (False, "y")]
+    red = extras.reduce_memorization_metrics([st], dataset_names=["y"])
+    assert red["em/2/3"] == 0.5 and red["em/y/2/3"] == 0.0 and red["em/natural_suffix/unmasked"] == 0.5
+    assert extras.flops_per_param(4, 2, 8, 100) == 2 * 100 * 4 + 2 * 4 * 8 * 16
+    assert extras.gptneox_tflops(1.0, 1, 1, 8, 2, 16, 32, True) > extras.gptneox_tflops(1.0, 1, 1, 8, 2, 16, 32, False)

@@ -96,3 +96,43 @@ def test_training_dynamics_track_fp32_torch_engine():
     for a, b in zip(lc, lg):
         assert abs(a - b) < 0.05 * abs(a) + 0.05, (lc, lg)
     assert lg[-1] < lg[0]  # the re-seen batch is (partly) memorised by both engines
+
+
+def _one_backward(model, ids, state, pair):
+    from recurrent_pretraining_b200.ops import cuda as K
+
+    for p in model.parameters():
+        p.grad = None
+    before = K.launch_count()
+    out = model(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair, input_states=state)
+    out["loss"].backward()
+    torch.cuda.synchronize()
+    return out["loss"].item(), {n: p.grad.float().clone() for n, p in model.named_parameters()}, K.launch_count() - before
+
+
+@pytest.mark.parametrize("impl", ["per-iteration", "per-iteration-sac", "per-iteration-sac-attn", "per-block-sac%2",
+                                  "in-coda-per-block-sac"])
+def test_activation_checkpoint_policies_give_the_same_gradients(impl):
+    """Plain recomputation and the selective policies (kept GEMM / attention outputs) against no checkpointing: same loss
+    and gradients; a selective policy launches fewer kernels than plain recomputation of the same regions."""
+    torch.manual_seed(4)
+    base = ModelConfig.from_name("smoke-raven-96")
+    cfg = ModelConfig.from_name("smoke-raven-96", activation_checkpoint_impl=impl)
+    plain = base.construct_model().cuda().bfloat16()
+    ckpt = cfg.construct_model(gradient_checkpointing=True).cuda().bfloat16()
+    ckpt.load_state_dict(plain.state_dict())
+    ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), device="cuda")
+    state = (torch.randn(2, 128, cfg.n_embd, device="cuda") * 0.6).bfloat16()
+    pair = torch.tensor([1, 2])
+    l0, g0, n0 = _one_backward(plain, ids, state, pair)
+    l1, g1, n1 = _one_backward(ckpt, ids, state, pair)
+    assert l1 == pytest.approx(l0, rel=1e-6)
+    for n in g0:
+        assert _rel(g1[n], g0[n]) < 1e-3, (impl, n, _rel(g1[n], g0[n]))
+    assert n1 > n0          # something was recomputed
+    if "sac" in impl:
+        full = ModelConfig.from_name("smoke-raven-96", activation_checkpoint_impl=impl.split("-sac")[0])
+        m2 = full.construct_model(gradient_checkpointing=True).cuda().bfloat16()
+        m2.load_state_dict(plain.state_dict())
+        _, _, n2 = _one_backward(m2, ids, state, pair)
+        assert n1 < n2, (n0, n1, n2)   # kept outputs: fewer kernels than recomputing everything
