@@ -304,6 +304,8 @@ def run_ours(args):
             row = r["host"][0].to(device)
             engine.model(row[:, :-1], labels=row[:, 1:])["loss"].backward()
             rec["grad_rel_err_vs_nccl"] = max_over_ranks(stepper.reduce_check(), device)
+            if stepper.last_check:
+                rec["grad_check_worst"] = sorted(stepper.last_check, key=lambda x: -x[1])[:4]
         except Exception as exc:  # noqa: BLE001
             rec["consistency_error"] = f"{type(exc).__name__}: {exc}"[:200]
     fabric_closed = False

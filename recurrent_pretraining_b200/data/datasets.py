@@ -140,6 +140,103 @@ class ParquetStream(IterableDataset):
         self._row_group_idx += 1
 
 
+class BufferShuffledParquet(IterableDataset):
+    """The ``pqds`` source: a plain stream over parquet shards (files ``rank::world``) with a shuffle buffer
+    (recpre/huggingface_dataset.py:34-121, which uses HF ``datasets`` streaming with ``shuffle(buffer_size=1024)``).
+    Here the buffer is filled with the next ``buffer_size`` rows, shuffled with a seeded RNG and drained, which keeps the
+    position resumable exactly: the state is (file, record batch, rows emitted from the current buffer, RNG state at the
+    fill), so a resume re-reads one buffer and skips what was already emitted."""
+
+    def __init__(self, dataset_folder_path: str = "", seed: int = 12345, shuffle: bool = True, num_processes: int = 1,
+                 process_rank: int = 0, prefix: str = "", shuffle_filenames: bool = True, column: str = "input_ids",
+                 buffer_size: int = 1024, read_batch: int = 256, return_data_id: bool = False, data_id=None,
+                 broadcast_glob: bool = True):
+        files = None
+        distributed = dist.is_available() and dist.is_initialized()
+        if not (broadcast_glob and distributed) or process_rank == 0:
+            files = sorted(str(p) for p in Path(dataset_folder_path).glob(f"{prefix}*.parquet"))
+            if shuffle_filenames:
+                random.Random(seed).shuffle(files)
+        if broadcast_glob and distributed:
+            box = [files]
+            dist.broadcast_object_list(box, 0)
+            files = box[0]
+        if not files:
+            raise FileNotFoundError(f"No files found at {dataset_folder_path} with prefix {prefix}.")
+        self.parquet_files = files[process_rank::num_processes] if num_processes > 1 else files
+        if not self.parquet_files:
+            raise ValueError(f"Empty dataset on rank {process_rank}")
+        self.fingerprint = hashlib.shake_128(str(self.parquet_files).encode()).hexdigest(4)
+        self.shuffle, self.column, self.buffer_size, self.read_batch = shuffle, column, buffer_size, read_batch
+        self.return_data_id, self.data_id = return_data_id, data_id
+        self._rng = random.Random(seed)
+        self._start = (0, 0)          # (file index, record batch index) where the current buffer starts
+        self._emitted = 0             # rows of the current buffer already handed out
+        self._fill_rng = self._rng.getstate()
+
+    def _rows_from(self, file_idx: int, batch_idx: int):
+        """Yield (row, (file index, next record batch index)) from a position on."""
+        import pyarrow.parquet as pq
+
+        for fi in range(file_idx, len(self.parquet_files)):
+            pf = pq.ParquetFile(self.parquet_files[fi])
+            for bi, rb in enumerate(pf.iter_batches(batch_size=self.read_batch, columns=[self.column],
+                                                     use_threads=False)):
+                if fi == file_idx and bi < batch_idx:
+                    continue
+                rows = rb.column(0).to_pylist()
+                for j, r in enumerate(rows):
+                    last = j == len(rows) - 1
+                    yield r, ((fi, bi + 1) if last else None)
+
+    def __iter__(self):
+        skip = self._emitted
+        while True:
+            self._rng.setstate(self._fill_rng)
+            buf, nxt = [], None
+            for r, boundary in self._rows_from(*self._start):
+                buf.append(r)
+                if boundary is not None and len(buf) >= self.buffer_size:
+                    nxt = boundary        # buffers end on record-batch boundaries, so a position is (file, batch)
+                    break
+            if not buf:
+                return
+            if self.shuffle:
+                self._rng.shuffle(buf)
+            after_rng = self._rng.getstate()
+            for i in range(skip, len(buf)):
+                self._emitted = i + 1
+                row = torch.as_tensor(buf[i], dtype=torch.long)
+                yield {"input_ids": row, "data_id": self.data_id} if self.return_data_id else row
+            skip = 0
+            if nxt is None:
+                self._start, self._emitted, self._fill_rng = (len(self.parquet_files), 0), 0, after_rng
+                return
+            self._start, self._emitted, self._fill_rng = nxt, 0, after_rng
+
+    def iter_batches(self, batch_size: int = 128):
+        """Unshuffled token batches straight from the files (a sanity path that bypasses the buffer)."""
+        import pyarrow.parquet as pq
+
+        for f in self.parquet_files:
+            for rb in pq.ParquetFile(f).iter_batches(batch_size=batch_size, columns=[self.column], use_threads=False):
+                yield torch.as_tensor(rb.column(0).to_pylist(), dtype=torch.long)
+
+    def state_dict(self):
+        return {"start": tuple(self._start), "emitted": self._emitted, "fill_rng": self._fill_rng,
+                "fingerprint": self.fingerprint}
+
+    def load_state_dict(self, sd, **_):
+        if sd.get("fingerprint") != self.fingerprint:
+            print(f"WARNING dataset fingerprint mismatch: expected {self.fingerprint}, got {sd.get('fingerprint')}")
+            return
+        self._start, self._emitted = tuple(sd["start"]), int(sd["emitted"])
+        st = sd["fill_rng"]
+        self._fill_rng = (st[0], tuple(st[1]), st[2]) if not isinstance(st[1], tuple) else st
+
+    load_local_state = load_state_dict
+
+
 class TextRows(IterableDataset):
     """Raw-text rows (dicts) sharded by rank; tokenisation happens in the collate function."""
 

@@ -63,3 +63,71 @@ class RavenForCausalLM(_hf.RavenForCausalLM):
         finally:
             self._collect_maps = None
         return out
+
+    # -- older signatures ---------------------------------------------------------------------------
+    def initialize_state(self, input_embeds, deterministic=False, scale: float = 1.0):
+        """The old file took ``deterministic`` (True: an all-zero state) where the current one takes ``scale``
+        (recpre/legacy_modeling_file.py:620-626); both spellings are accepted here."""
+        if isinstance(deterministic, (int, float)) and not isinstance(deterministic, bool):
+            scale, deterministic = float(deterministic), False      # positional ``scale`` of the current API
+        if deterministic:
+            return torch.zeros_like(input_embeds)
+        return super().initialize_state(input_embeds, scale)
+
+    def compute_eager_sdpa(self, q, k, v, attn_mask=None):
+        """[B, H, S, D] operands, explicit softmax; returns (y, attention map maxed over heads), as the old file's
+        attention did when maps were requested (recpre/legacy_modeling_file.py:255-267)."""
+        y, amap = eager_causal_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                         k.shape[2] - q.shape[2])
+        return y.transpose(1, 2), amap
+
+    def get_stats(self, logits, x, latent_states, xk, input_embeds, num_steps_no_grad, num_steps_with_grad):
+        """Entropy of the prediction and (relative) distance between the last two latent states per position."""
+        probs = torch.softmax(logits.float(), dim=-1)
+        entropy = torch.where(probs > 0, -probs * probs.log(), torch.zeros_like(probs)).sum(dim=-1)
+        diff = (x - latent_states).norm(dim=-1)
+        return {"entropy": entropy, "residual_diff": diff, "rel_residual": diff / latent_states.norm(dim=-1),
+                "num_steps_no_grad": num_steps_no_grad, "num_steps_with_grad": num_steps_with_grad}
+
+
+def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0, condense_ratio: int = 1):
+    """cos / sin table ``[1, end, 1, dim / 2, 2]`` in fp32 (module-level helper of the old file)."""
+    from ..ops import reference as ref
+
+    cos, sin = ref.rope_tables(dim, end, theta, condense_ratio)
+    return ref.freqs_cis_buffer(cos, sin)
+
+
+def apply_rotary_emb_complex_like(q, k, freqs_cis):
+    """Rotate q and k ``[B, S, H, D]`` with a table from ``precompute_freqs_cis`` (already cut to S positions)."""
+    from ..ops import reference as ref
+
+    cos, sin = freqs_cis[0, :, 0, :, 0], freqs_cis[0, :, 0, :, 1]
+    return ref.rope_interleaved(q, cos, sin), ref.rope_interleaved(k, cos, sin)
+
+
+def register_auto_classes() -> None:
+    """``AutoConfig`` / ``AutoModel`` / ``AutoModelForCausalLM`` registration under ``huginn_raven`` (the old file did
+    this at import; here it is explicit because the current model file registers the same names)."""
+    from transformers import AutoConfig, AutoModel, AutoModelForCausalLM
+
+    for reg, args in ((AutoConfig, ("huginn_raven", RavenConfig)), (AutoModel, (RavenConfig, RavenForCausalLM)),
+                      (AutoModelForCausalLM, (RavenConfig, RavenForCausalLM))):
+        try:
+            reg.register(*args, exist_ok=True)
+        except TypeError:
+            try:
+                reg.register(*args)
+            except ValueError:
+                pass
+
+
+# block classes of the old file, by their old names
+def __getattr__(name: str):
+    from . import blocks
+
+    table = {"RMSNorm": blocks.RMSNorm, "CausalSelfAttention": blocks.CausalSelfAttention,
+             "GatedMLP": getattr(blocks, "GatedMLP", None), "SandwichBlock": getattr(blocks, "SandwichBlock", None)}
+    if name in table and table[name] is not None:
+        return table[name]
+    raise AttributeError(name)

@@ -12,6 +12,9 @@ broadcast, rank-0 printing, save/load helpers) with a different data path on GPU
 * ``grad_sync="p2p"``      -- hand-written kernels over NVLink peer memory on symmetric buffers: bucketed reduce-scatter
   overlapped with the backward pass, sharded optimizer state, update that stores the new bf16 weights into every rank
   (``parallel.p2p``).  One node, at most 8 ranks; anything else falls back to ``flat`` with a notice.
+* ``grad_sync="ddp"``      -- torch ``DistributedDataParallel`` around the model (bucketed all-reduce inside backward,
+  ``find_unused_parameters`` for the untracked recurrences): the reference's alternative path
+  (recpre/utils.py:1154-1155); used with ``torch.optim`` optimizers (the engine's ``torch`` mode).
 * ``grad_sync="p2p-host"`` -- the bookkeeping of ``p2p`` on ``torch.distributed`` collectives (any backend; tests).
 * ``grad_sync="zero3"``    -- as ``p2p`` with fp32 masters sharded as well and the updated bf16 weights pulled by the
   next forward pass (all-gather fused into the first consuming GEMM for the row-sharded QKV / gate-up weights).

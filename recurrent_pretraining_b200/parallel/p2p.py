@@ -6,8 +6,9 @@ gradients are complete: coda, recurrent core + adapter, prelude, and the rest (t
 The model marks these points with tensor hooks; when one fires, the bucket's reduce-scatter is launched on a side
 stream (a small number of CTAs, sharing the SMs with the GEMMs of the layers still going backward):
 
-    [per bucket]  signal "my gradients of this bucket are complete" to every peer  ->  reduce-scatter kernel that
-                  waits for all peers' signals, sums the owner's pieces from all ranks, adds to the squared-norm partial
+    [per bucket]  reduce-scatter kernel: its first CTA tells every peer "my gradients of this bucket are complete", all
+                  CTAs wait (bounded) for the peers' signals, then sum the owner's pieces from all ranks and add to the
+                  squared-norm partial
     [after backward]  barrier + exchange of the norm partials  ->  (ELLISAdam: per-tensor clipping statistics, barrier)
                   ->  update of the owned pieces (AdamW or the ELLISAdam flags) that writes the new bf16 compute copy
                   ->  barrier
@@ -198,8 +199,7 @@ class ShardedStepper:
         self.master_ptrs = [bufs[(i, "master")].ptr_array() if (i, "master") in bufs else None
                             for i in range(len(self.groups))]
         self.own_shadow_ptrs = [(C.c_void_p * 1)(bufs[(i, "shadow")].own) for i in range(len(self.groups))]
-        self.side = torch.cuda.Stream(device=f.device)
-        self.sig = torch.cuda.Stream(device=f.device)
+        self.side = torch.cuda.Stream(device=f.device, priority=-1)    # its few CTAs go first when an SM frees up
         self.gather_stream = torch.cuda.Stream(device=f.device)
         self.err = K.err_word(f.device)
 
@@ -262,16 +262,18 @@ class ShardedStepper:
         main = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(main)
-        self.sig.wait_event(ev)
-        K._check(K.lib.b200_signal(self.slot_ptrs[b.slot], self.rank, self.world, epoch,
-                                   C.c_void_p(self.sig.cuda_stream)), "signal")
+        # The "my gradients of this bucket are complete" signal is issued by the first CTA of the reduce-scatter kernel
+        # itself, never by a launch of its own: a separate signal kernel can be starved by this GPU's own waiting
+        # reduce-scatter CTAs while the peer waits for it (every rank then sits out the wait limit).  All ranks fire
+        # their buckets in the same order (hooks in graph order, the rest in BUCKET_ORDER), so waiting for the peers'
+        # kernels of the same bucket to start cannot cycle.
         self.side.wait_event(ev)
         partial = self.partials[self.reduce_count & 1]
         first = True
         for gi, tb in b.tables:
             K._check(K.lib.b200_rs_table(self.grad_ptrs[gi], self.rank, self.world, C.byref(tb),
                                          C.c_void_p(partial.data_ptr()), self.slot_ptrs[b.slot],
-                                         epoch if first else C.c_uint(0), 0, self.timeout_ms, ctas,
+                                         epoch if first else C.c_uint(0), 1, self.timeout_ms, ctas,
                                          C.c_void_p(self.err.data_ptr()), C.c_void_p(self.side.cuda_stream)),
                      "rs_table")
             first = False
@@ -309,6 +311,8 @@ class ShardedStepper:
             done.record(self.side)
             torch.cuda.current_stream().wait_event(done)
             self._barrier(sum_into=optimizer.gnorm_sq, partial_index=pi)
+            if os.environ.get("B200_DEBUG_NORM") == "1" and not bool(torch.isfinite(optimizer.gnorm_sq).all()):
+                self._report_nonfinite(pi)
         else:
             optimizer.compute_grad_norm_sq()
         first_update = optimizer.step_count == 0
@@ -340,6 +344,18 @@ class ShardedStepper:
         if self.world > 1:
             self.partials[1 - pi].zero_()
             self._barrier()
+
+    def _report_nonfinite(self, pi: int) -> None:
+        """Debug aid (B200_DEBUG_NORM=1): which of this rank's reduced pieces are not finite."""
+        bad = []
+        for gi, g in enumerate(self.groups):
+            for t in range(len(g.params)):
+                s, n = self.plans[gi].segment(t, self.rank)
+                if n and not bool(torch.isfinite(g.grad[s:s + n]).all()):
+                    bad.append(g.names[t])
+        print(f"[rank {self.rank}] non-finite norm at reduce {self.reduce_count}: own partial "
+              f"{float(self.partials[pi])}, status {int(self.err)}, non-finite pieces {bad[:8]} ({len(bad)} total)",
+              flush=True)
 
     # ------------------------------------------------------------------------------------------ zero3 gathers
     def _launch_gathers(self) -> None:
@@ -392,12 +408,16 @@ class ShardedStepper:
         torch.cuda.current_stream().wait_event(done)
         self._barrier()
         worst = 0.0
+        self.last_check = []
         for gi, (g, c) in enumerate(zip(self.groups, copies)):
             for t in range(len(g.params)):
                 s, n = self.plans[gi].segment(t, self.rank)
                 if n:
-                    d = (g.grad[s:s + n] - c[s:s + n]).norm() / (c[s:s + n].norm() + 1e-30)
-                    worst = max(worst, float(d))
+                    ref_n = float(c[s:s + n].norm())
+                    d = float((g.grad[s:s + n] - c[s:s + n]).norm()) / (ref_n + 1e-30)
+                    if d > 1e-5:
+                        self.last_check.append((g.names[t], d, float(g.grad[s:s + n].norm()), ref_n))
+                    worst = max(worst, d)
         self.partials[self.reduce_count & 1].zero_()
         self._barrier()
         for b in self.buckets.values():

@@ -77,6 +77,15 @@ class TrainEngine:
             for g in optimizer.param_groups:
                 g.setdefault("base_lr", 1.0)
             self.optimizer = optimizer
+            self.ddp = None
+            if getattr(self.fabric, "grad_sync", "") == "ddp" and self.fabric.is_distributed:
+                # the reference's alternative to its hand-rolled all-reduce: torch DistributedDataParallel with unused-
+                # parameter detection, needed because of the untracked recurrences (recpre/utils.py:1154-1155,
+                # finetuning_simple_example.py:176-179)
+                from torch.nn.parallel import DistributedDataParallel as DDP
+
+                ids = [self.device.index] if self.device.type == "cuda" else None
+                self.ddp = DDP(model, device_ids=ids, find_unused_parameters=True, gradient_as_bucket_view=True)
         self.params = [p for _, p in named]
 
     # ------------------------------------------------------------------------------------------
@@ -99,14 +108,26 @@ class TrainEngine:
             if (self.micro_step - 1 - self.window_base) % self.grad_accum == 0:
                 self._begin_window()
             self.fabric.begin_backward(model, accumulating)
-        with nvtx.range("forward"):
-            out = model(input_ids, labels=labels, **fwd_kwargs)
-        loss = out["loss"]
-        with nvtx.range("backward"):
-            if self.mode == "fused":
-                loss.backward()
-            else:
-                (loss / self.grad_accum).backward()
+        ddp = getattr(self, "ddp", None)
+        if ddp is not None:
+            import contextlib
+
+            ctx = ddp.no_sync() if accumulating else contextlib.nullcontext()
+            with ctx:
+                with nvtx.range("forward"):
+                    out = ddp(input_ids, labels=labels, **fwd_kwargs)
+                loss = out["loss"]
+                with nvtx.range("backward"):
+                    (loss / self.grad_accum).backward()      # DDP averages over ranks inside backward
+        else:
+            with nvtx.range("forward"):
+                out = model(input_ids, labels=labels, **fwd_kwargs)
+            loss = out["loss"]
+            with nvtx.range("backward"):
+                if self.mode == "fused":
+                    loss.backward()
+                else:
+                    (loss / self.grad_accum).backward()
         result = {"loss": loss.detach(), "log_ppl": out["log_ppl"], "grad_norm": None,
                   "depths": getattr(model, "last_depths", (0, 0))}
         if accumulating:
@@ -132,7 +153,8 @@ class TrainEngine:
                 self.optimizer.compute_grad_norm_sq()
             result["grad_norm"] = self.optimizer.grad_norm(scale)
         else:
-            self.fabric.all_reduce_gradients(self.params)
+            if getattr(self, "ddp", None) is None:
+                self.fabric.all_reduce_gradients(self.params)
             gn = torch.nn.utils.clip_grad_norm_(self.params, self.grad_clip if self.grad_clip > 0 else math.inf)
             finite = bool(torch.isfinite(gn))
             if do_update and finite:

@@ -18,7 +18,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from ..data import (DataScheduler, DataSchedulerTracker, ParquetStream, RandomTokens, StatefulLoader, TextRows,
+from ..data import (BufferShuffledParquet, DataScheduler, DataSchedulerTracker, ParquetStream, RandomTokens, StatefulLoader, TextRows,
                     Tokenizer, WeightedMixture, apply_tld, generic_collate_fn)
 from ..optim.schedules import get_batch_size, get_lr
 from ..parallel.fabric import Fabric
@@ -79,7 +79,12 @@ def _make_source(entry, cfg, fabric, split_dir: str, seed: int):
     if entry.type == "rngds":
         return RandomTokens(vocab, block, seed=seed, process_rank=fabric.global_rank)
     folder = entry.data_dir or split_dir
-    if entry.type in ("pqds", "pqds-pure"):
+    if entry.type == "pqds":
+        return BufferShuffledParquet(folder, seed=seed, shuffle=cfg.shuffle_blocks, num_processes=fabric.world_size,
+                                     process_rank=fabric.global_rank, prefix=entry.prefix,
+                                     shuffle_filenames=cfg.shuffle_filenames, return_data_id=entry.return_data_id,
+                                     data_id=entry.prefix)
+    if entry.type == "pqds-pure":
         return ParquetStream(folder, seed=seed, shuffle=cfg.shuffle_blocks, num_processes=fabric.world_size,
                              process_rank=fabric.global_rank, prefix=entry.prefix,
                              shuffle_filenames=cfg.shuffle_filenames, return_data_id=entry.return_data_id,

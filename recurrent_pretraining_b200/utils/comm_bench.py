@@ -1,8 +1,16 @@
-"""Communication sweep: fused NVLink kernels vs NCCL on bf16 / fp32 gradient buckets of 1 MB .. 1 GB.
+"""Communication sweep: fused NVLink kernels vs NCCL on gradient buckets of 1 MB .. 1 GB.
 
 Run under ``python -m torch.distributed.run --nproc-per-node N -m recurrent_pretraining_b200.utils.comm_bench``.
-Device-timed with CUDA events, max over ranks.  Reports algorithm bandwidth, bus bandwidth (2 (N-1)/N x bytes / t for
-an all-reduce) and the fraction of the measured 770 GB/s per-direction peer-copy bandwidth.
+Device-timed with CUDA events, max over ranks, median of 10.
+
+Default sweep (bf16 buckets drawn N(0, 1e-3^2)): for every size the one-launch fused collectives of
+``parallel/collectives.py`` -- all-reduce (bf16 in, fp32 cast + 1/N scale + squared-norm partial, result on every rank),
+reduce-scatter, all-gather, and reduce-scatter + clipped AdamW + bf16 parameter push -- each beside the NCCL call that
+the reference's path would make (``all_reduce`` on bf16 and on fp32, ``reduce_scatter_tensor``,
+``all_gather_into_tensor``).  A row's roofline time is the bytes that must cross one GPU's NVLink in the busier
+direction divided by the link bandwidth; fractions are given against the measured 770 GB/s per direction and against
+the nominal 900 GB/s.  ``--fp32`` adds the older fp32 two-shot sequence, ``--phases`` the per-phase CTA sweep, ``--ag``
+the all-gather fused into the GEMM.
 """
 from __future__ import annotations
 
@@ -17,7 +25,8 @@ import torch.distributed as dist
 from ..parallel.fabric import Fabric
 from ..parallel.symm import SymmetricBuffer
 
-LINK_GBS = 770.0
+LINK_GBS = 770.0       # measured peer copy, per direction
+LINK_NOMINAL = 900.0   # NVLink 5, per direction
 
 
 def _time(fn, device, reps=10, warmup=3):
@@ -38,13 +47,90 @@ def _time(fn, device, reps=10, warmup=3):
     return statistics.median(ts)
 
 
+def bf16_sweep(fabric, sizes_mb) -> None:
+    """bf16 buckets: fused one-launch collectives against NCCL (see the module docstring)."""
+    from ..ops import cuda as K
+    from ..parallel.collectives import FusedCollectives
+
+    dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
+    max_elems = max(sizes_mb) * 2**20 // 2
+    fc = FusedCollectives(fabric, max_elems)
+    shadow = SymmetricBuffer(fabric, fc.max_elems * 2)
+    fc.bucket.normal_(0, 1e-3)
+    nccl_bf16 = torch.empty(max_elems, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3)
+    nccl_f32 = torch.empty(max_elems, dtype=torch.float32, device=dev).normal_(0, 1e-3)
+    per_max = fc.slice_elems(max_elems)
+    p = torch.zeros(per_max, device=dev)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    torch.cuda.synchronize(dev)
+    dist.barrier(device_ids=[dev.index])
+    f = (N - 1) / N
+    for mb in sizes_mb:
+        count = mb * 2**20 // 2
+        nb = count * 2
+        lo, hi = fc.my_slice(count)
+        per = fc.slice_elems(count)
+        rows = []
+        # (name, ours, nccl, bytes over this GPU's link in the busier direction)
+        ar_bytes = f * count * 4           # out: fp32 result of the slice to N-1 peers (in: f * count * 2)
+        rows.append(("all_reduce bf16->fp32 (+scale, norm)", lambda: fc.all_reduce(count, 1.0 / N, one_shot=False),
+                     lambda: dist.all_reduce(nccl_f32[:count]), ar_bytes, "nccl all_reduce fp32"))
+        if nb <= 64 * 2**20:
+            rows.append(("all_reduce one-shot", lambda: fc.all_reduce(count, 1.0 / N, one_shot=True),
+                         lambda: dist.all_reduce(nccl_bf16[:count]), (N - 1) * nb, "nccl all_reduce bf16"))
+        rows.append(("reduce_scatter bf16->fp32 (+scale, norm)", lambda: fc.reduce_scatter(count, 1.0 / N),
+                     lambda: dist.reduce_scatter_tensor(nccl_bf16[:per], nccl_bf16[:per * N]) if per * N <= max_elems
+                     else dist.all_reduce(nccl_bf16[:count]), f * nb, "nccl reduce_scatter bf16"))
+        rows.append(("all_gather bf16 (push)", lambda: fc.all_gather_bf16(count),
+                     lambda: dist.all_gather_into_tensor(nccl_bf16[:per * N], nccl_bf16[:per]) if per * N <= max_elems
+                     else dist.all_reduce(nccl_bf16[:count]), f * nb, "nccl all_gather bf16"))
+
+        def nccl_update():
+            dist.reduce_scatter_tensor(nccl_f32[:per], nccl_f32[:per * N]) if per * N <= max_elems else None
+            g = nccl_f32[:hi - lo]
+            torch.nn.utils.clip_grad_norm_([g], 1.0) if False else g.norm()
+            m[:hi - lo].lerp_(g, 0.1)
+            v[:hi - lo].mul_(0.95).addcmul_(g, g, value=0.05)
+            p[:hi - lo].mul_(1 - 4e-5).addcdiv_(m[:hi - lo], v[:hi - lo].sqrt().add_(1e-8), value=-4e-4)
+            nccl_bf16[:hi - lo].copy_(p[:hi - lo])
+            dist.all_gather_into_tensor(nccl_bf16[:per * N], nccl_bf16[:per]) if per * N <= max_elems else None
+
+        rows.append(("reduce_scatter + clip + AdamW + bf16 push",
+                     lambda: fc.reduce_scatter_adamw(count, p[:hi - lo], m[:hi - lo], v[:hi - lo], shadow, lr=4e-4,
+                                                     step=2, scale=1.0 / N),
+                     nccl_update, f * nb, "nccl reduce_scatter fp32 + torch AdamW + all_gather bf16"))
+        for name, ours, theirs, link_bytes, nccl_name in rows:
+            t_ours = _time(ours, dev)
+            t_nccl = _time(theirs, dev)
+            gbs = link_bytes / t_ours / 1e6
+            rec = {"bucket_MB": mb, "dtype": "bf16", "n_gpus": N, "op": name, "ms": round(t_ours, 4),
+                   "link_GBps": round(gbs, 1), "frac_of_measured_link": round(gbs / LINK_GBS, 3),
+                   "frac_of_nominal_link": round(gbs / LINK_NOMINAL, 3), "nccl": nccl_name,
+                   "nccl_ms": round(t_nccl, 4), "speedup_vs_nccl": round(t_nccl / t_ours, 2)}
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+    status = K.check_device_status()
+    if rank == 0:
+        print(json.dumps({"bf16_sweep_device_status": status}), flush=True)
+    torch.cuda.synchronize(dev)
+    dist.barrier(device_ids=[dev.index])
+    shadow.close()
+    fc.close()
+
+
 def main():
     from ..ops import cuda as K
 
     fabric = Fabric.from_env(grad_sync="flat")
     dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
     sizes_mb = [1, 4, 16, 64, 256, 1024]
-    max_bytes = sizes_mb[-1] * 2**20
+    if "--sizes" in sys.argv:
+        sizes_mb = [int(x) for x in sys.argv[sys.argv.index("--sizes") + 1].split(",")]
+    max_bytes = max(sizes_mb) * 2**20
+    if "--ag-only" not in sys.argv and "--fp32-only" not in sys.argv:
+        bf16_sweep(fabric, sizes_mb)
+    if "--fp32" not in sys.argv and "--fp32-only" not in sys.argv:
+        sizes_mb = []
     if "--ag-only" in sys.argv:   # only the fused all-gather GEMM rows
         sizes_mb = []
     buf = SymmetricBuffer(fabric, max_bytes + 4096 * N)  # slack: slices are rounded up to 512 B

@@ -226,6 +226,32 @@ def sharded_step():
     fabric.shutdown()
 
 
+def ddp_alternative():
+    """torch DistributedDataParallel as the gradient sync against the hand-rolled chunked all-reduce: same losses and
+    parameters, with accumulation (no_sync) and the untracked recurrences (unused-parameter detection)."""
+    out = {}
+    runs = {}
+    for sync in ("chunked", "ddp"):
+        fabric = Fabric.from_env(backend="gloo", grad_sync=sync)
+        torch.manual_seed(0)
+        cfg = ModelConfig.from_name("tiny-raven-cpu", **OV)
+        model = cfg.construct_model()
+        eng = TrainEngine(model, fabric, lr=1e-3, mode="torch", grad_accum=2)
+        g = torch.Generator().manual_seed(11 + 1000 * fabric.global_rank)
+        losses = []
+        for i in range(6):
+            ids = torch.randint(0, cfg.padded_vocab_size, (2, 65), generator=g)
+            losses.append(eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([1, 2]))["loss"].item())
+        runs[sync] = (losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]), eng)
+    out["loss_diff"] = max(abs(a - b) for a, b in zip(runs["chunked"][0], runs["ddp"][0]))
+    out["param_diff"] = (runs["chunked"][1] - runs["ddp"][1]).abs().max().item()
+    out["wrapped"] = type(runs["ddp"][2].ddp).__name__
+    if dist.get_rank() == 0:
+        print("RESULT " + json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     {"parity": parity, "rank_failure": rank_failure, "exit_flag": exit_flag,
-     "tensor_parallel": tensor_parallel, "sharded_step": sharded_step}[sys.argv[1]]()
+     "tensor_parallel": tensor_parallel, "sharded_step": sharded_step, "ddp_alternative": ddp_alternative}[sys.argv[1]]()

@@ -83,6 +83,73 @@ def main():
             print("RESULT " + json.dumps(res))
         dist.barrier()
         dist.destroy_process_group()
+    elif mode == "collectives":
+        # one-launch fused collectives on bf16 buckets against torch sums
+        from recurrent_pretraining_b200.parallel.collectives import FusedCollectives
+        from recurrent_pretraining_b200.parallel.symm import SymmetricBuffer
+
+        fabric = Fabric.from_env(grad_sync="flat")
+        dev, rank, N = fabric.device, fabric.global_rank, fabric.world_size
+        out = {}
+        fc = FusedCollectives(fabric, 1 << 20)
+        shadow = SymmetricBuffer(fabric, fc.max_elems * 2)
+        for count in (8 * N, 40000, 1 << 20):
+            gen = torch.Generator().manual_seed(50 + count)
+            all_data = [(torch.randn(count, generator=gen) * 1e-3).bfloat16() for _ in range(N)]
+            want = sum(d.float() for d in all_data) / N
+            fc.bucket[:count].copy_(all_data[rank])
+            case = {}
+            for one_shot in (True, False):
+                res = fc.all_reduce(count, 1.0 / N, one_shot=one_shot).float().cpu()
+                torch.cuda.synchronize()
+                case[f"allreduce_oneshot{int(one_shot)}"] = (res - want).abs().max().item()
+                norm_sq = fc.partial.clone()
+                if not one_shot:
+                    dist.all_reduce(norm_sq)
+                case[f"norm_oneshot{int(one_shot)}"] = abs(norm_sq.sqrt().item() - want.norm().item()) / want.norm().item()
+            lo, hi = fc.my_slice(count)
+            rs = fc.reduce_scatter(count, 1.0 / N).float().cpu()
+            torch.cuda.synchronize()
+            case["reduce_scatter"] = (rs - want[lo:hi]).abs().max().item() if hi > lo else 0.0
+            # all-gather: every rank contributes its slice of its own bucket
+            mine = torch.full((count,), float(rank + 1)).bfloat16()
+            fc.bucket[:count].copy_(mine)
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = fc.all_gather_bf16(count).float().cpu()
+            torch.cuda.synchronize()
+            per = fc.slice_elems(count)
+            exp = torch.cat([torch.full((min(per, max(count - q * per, 0)),), float(q + 1)) for q in range(N)])
+            case["all_gather"] = (got - exp).abs().max().item()
+            # reduce-scatter + AdamW + push against torch
+            fc.bucket[:count].copy_(all_data[rank])
+            p0 = torch.randn(count, generator=torch.Generator().manual_seed(7))
+            p = p0[lo:hi].clone().to(dev)
+            m, v = torch.zeros_like(p), torch.zeros_like(p)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gn = fc.reduce_scatter_adamw(count, p, m, v, shadow, lr=1e-2, eps=1e-8, weight_decay=0.1, step=1,
+                                         max_norm=1e-3, scale=1.0 / N)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gnorm = want.norm().item()
+            clip = min(1.0, 1e-3 / (gnorm + 1e-6))
+            g = want * clip
+            mm = 0.1 * g
+            vv = 0.05 * g * g
+            pref = p0 * (1 - 1e-2 * 0.1) - 1e-2 / 0.1 * mm / (vv.sqrt() / (0.05 ** 0.5) + 1e-8)
+            sh = shadow.tensor(torch.bfloat16, count).float().cpu()
+            case["adamw_gnorm"] = abs(gn.item() - gnorm) / gnorm
+            case["adamw_shadow"] = (sh - pref).abs().max().item()
+            case["adamw_master"] = (p.cpu() - pref[lo:hi]).abs().max().item() if hi > lo else 0.0
+            out[str(count)] = case
+        status = K.check_device_status()
+        if rank == 0:
+            print("RESULT " + json.dumps({"cases": out, "status": status}))
+        dist.barrier()
+        shadow.close()
+        fc.close()
+        dist.destroy_process_group()
     elif mode == "timeout":
         # a barrier whose peer flag nobody sets must give up and report through the status word
         import ctypes as C

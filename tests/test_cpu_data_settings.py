@@ -240,3 +240,25 @@ def test_every_launch_config_parses_and_names_a_known_model(tmp_path):
         mc = ModelConfig.from_name(cfg.model_name, **(cfg.model_overwrite or {}))
         assert mc.n_embd % mc.num_attention_heads == 0 and cfg.micro_batch_size >= 1, f
         assert cfg.optimizer and cfg.fabric_strategy, f
+
+
+def test_buffer_shuffled_parquet_covers_everything_and_resumes_exactly(tmp_path):
+    from recurrent_pretraining_b200.data import BufferShuffledParquet
+
+    total = _write_shards(tmp_path, n_files=3, groups=2, rows=11)
+    make = lambda **kw: BufferShuffledParquet(str(tmp_path), seed=4, buffer_size=8, read_batch=4, **kw)  # noqa: E731
+    rows = [tuple(r.tolist()) for r in make()]
+    assert len(rows) == total and len(set(rows)) == total
+    plain = [tuple(r.tolist()) for r in make(shuffle=False, shuffle_filenames=False)]
+    assert rows != plain and sorted(rows) == sorted(plain)
+    for k in (1, 9, 20, 37):
+        ds = make()
+        it = iter(ds)
+        head = [tuple(next(it).tolist()) for _ in range(k)]
+        state = ds.state_dict()
+        again = make()
+        again.load_state_dict(state)
+        assert head + [tuple(r.tolist()) for r in again] == rows, k
+    a, b = make(num_processes=2, process_rank=0), make(num_processes=2, process_rank=1)
+    assert not set(a.parquet_files) & set(b.parquet_files)
+    assert sum(t.shape[0] for t in make().iter_batches(16)) == total

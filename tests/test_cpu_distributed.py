@@ -82,3 +82,9 @@ def test_sharded_step_matches_replicated_update():
     assert res["recut_diff"] < 1e-6, res
     assert res["zero3_shadow_diff"] < 1e-2 and res["zero3_master_diff"] < 1e-6, res
     assert res["zero3_master_numel"][0] < 0.6 * res["zero3_master_numel"][1], res
+
+
+def test_torch_ddp_alternative_matches_the_hand_rolled_all_reduce():
+    res = _result(_torchrun([os.path.join(HERE, "cpu_dp_worker.py"), "ddp_alternative"], 29635))
+    assert res["wrapped"] == "DistributedDataParallel"
+    assert res["loss_diff"] < 2e-5 and res["param_diff"] < 2e-5, res

@@ -183,3 +183,34 @@ def test_forward_with_adaptive_compute_per_position():
     assert torch.allclose(full.logits, want, atol=2e-4), (full.logits - want).abs().max()
     out = model.forward_with_adaptive_compute(ids, KLExitEvaluator(model, exit_threshold=1e9), labels=ids)
     assert out.stats["compute_steps"] == [1] * 7 and torch.isfinite(out.loss)  # the first check already fires
+
+
+def test_legacy_surface_old_signatures_and_helpers():
+    from recurrent_pretraining_b200.models import legacy
+    from recurrent_pretraining_b200.models.hf_config import RavenConfig
+    from recurrent_pretraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    cfg = RavenConfig(n_embd=64, n_heads=4, n_layers=4, block_size=32, vocab_size=128, intermediate_size=96,
+                      n_layers_in_recurrent_block=2, n_layers_in_prelude=1, n_layers_in_coda=1, mean_recurrence=2)
+    model = legacy.RavenForCausalLM(cfg).eval()
+    e = torch.randn(2, 5, 64)
+    assert float(model.initialize_state(e, deterministic=True).abs().sum()) == 0.0
+    assert model.initialize_state(e).shape == e.shape and float(model.initialize_state(e, 0.0).abs().sum()) == 0.0
+    fc = legacy.precompute_freqs_cis(16, 5, 50000.0)
+    assert fc.shape == (1, 5, 1, 8, 2)
+    q, k = torch.randn(2, 5, 4, 16), torch.randn(2, 5, 4, 16)
+    rq, rk = legacy.apply_rotary_emb_complex_like(q, k, fc)
+    cos, sin = ref.rope_tables(16, 5, 50000.0)
+    assert torch.allclose(rq, ref.rope_interleaved(q, cos, sin)) and rk.shape == k.shape
+    y, amap = model.compute_eager_sdpa(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2))
+    want = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2),
+                                                            is_causal=True)
+    assert torch.allclose(y, want, atol=1e-5) and amap.shape == (2, 5, 5)
+    st = model.get_stats(torch.randn(2, 5, 128), e, e + 0.1, None, e, 3, 1)
+    assert st["entropy"].shape == (2, 5) and st["num_steps_no_grad"] == 3 and float(st["rel_residual"].max()) < 1.0
+    assert legacy.SandwichBlock.__name__ == "SandwichBlock" and legacy.RMSNorm.__name__ == "RMSNorm"
+    legacy.register_auto_classes()
+    cache = legacy.HuginnDynamicCache()
+    cache.reset()
+    assert cache.get_seq_length() == 0

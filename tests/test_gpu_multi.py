@@ -13,12 +13,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def _run(mode: str, nproc: int = 2, port: int = 29641):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_DEBUG_NORM="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), mode]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    print("\n".join(l for l in r.stdout.splitlines() if "non-finite" in l))
+    print(line)          # shown by pytest when the test fails
     return json.loads(line[len("RESULT "):])
 
 
@@ -79,3 +81,17 @@ def test_all_gather_fused_gemm():
     for name, case in res["cases"].items():
         assert case["rel_err"] < 2e-2, (name, case)
         assert case["weight_equal"] and case["second_call_equal"], (name, case)
+
+
+@needs2
+def test_fused_one_launch_collectives_on_bf16_buckets():
+    """All-reduce (one-shot and sliced), reduce-scatter, all-gather and reduce-scatter + clipped AdamW + push, with the
+    handshakes inside the kernels, against fp32 torch sums of the same bf16 buckets."""
+    res = _run("collectives", nproc=min(torch.cuda.device_count(), 4), port=29653)
+    assert res["status"] == 0, res
+    for count, case in res["cases"].items():
+        for k in ("allreduce_oneshot0", "allreduce_oneshot1", "reduce_scatter"):
+            assert case[k] < 1e-6, (count, case)
+        assert case["norm_oneshot0"] < 1e-4 and case["norm_oneshot1"] < 1e-4, (count, case)
+        assert case["all_gather"] == 0.0, (count, case)
+        assert case["adamw_gnorm"] < 1e-4 and case["adamw_master"] < 1e-5 and case["adamw_shadow"] < 2e-2, (count, case)

