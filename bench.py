@@ -283,6 +283,8 @@ def run_ours(args):
                    "optimizer": "AdamW fused, clip 1.0",
                    "grad_sync": fabric.grad_sync if world > 1 else "none",
                    "overlap": bool(stepper is not None and stepper.overlap),
+                   "param_sync": ("pull in the next forward pass" if stepper.zero3 else "push from the update kernel")
+                   if stepper is not None else "none",
                    "l2": "working set (7.1 GB weights per recurrence) >> 126 MB L2; no explicit flush",
                    "activation_checkpointing": False},
         "clocks": r["clocks"],
@@ -297,6 +299,8 @@ def run_ours(args):
     if stepper is not None and os.environ.get("B200_BENCH_EXTRAS", "1") == "1":
         try:
             rec["persistent_bytes_per_rank"] = stepper.persistent_bytes()
+            if stepper.tracing:
+                rec["timeline_ms"] = stepper.timeline()
             rec["replicas_identical"] = stepper.replicas_identical()
             engine._begin_window()
             engine.model._phase_cb = None

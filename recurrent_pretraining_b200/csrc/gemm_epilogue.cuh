@@ -10,7 +10,13 @@ enum OutMode : int {
   OUT_BF16_T = 5,        // transposed store C[col, row] (skinny decode GEMMs computed as W x^T)
   OUT_F32_T_ATOMIC = 6,  // transposed fp32 atomic accumulate (split-K partial sums)
   OUT_BF16_ROPE = 7,     // bf16 store of a packed qkv row: q/k columns get their bias added and are rotated
+  OUT_SWIGLU_SAVE = 8,   // OUT_SWIGLU that also stores the bf16 pre-activation [gate | up] (training passes: backward
+                         // needs it); `resid` is that [M, 2I] matrix
+  OUT_DSWIGLU = 9,       // backward of the gate: the accumulator is dL/dy [M, I]; with the saved pre-activation h =
+                         // [g | u] (`resid`, [M, 2I]) the tile stores dL/dg = dy u s (1 + g (1 - s)) at C[:, col] and
+                         // dL/du = dy g s at C[:, I + col], s = sigmoid(g); C is [M, 2I]
 };
+__host__ __device__ constexpr bool is_swiglu(int mode) { return mode == OUT_SWIGLU || mode == OUT_SWIGLU_SAVE; }
 
 struct GemmParams {
   int M, N, K1, K2;
@@ -80,14 +86,67 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     }
     return;
   }
-  constexpr int CH = (MODE == OUT_SWIGLU) ? 16 : 32;  // columns per step
+  constexpr int CH = (is_swiglu(MODE) || MODE == OUT_DSWIGLU) ? 16 : 32;  // columns per step
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += CH) {
     const int col = n0 + c0;
     const int width = (BN - c0 < CH) ? (BN - c0) : CH;   // 16 for the tail of BN = 240
     const bool active = row_ok && col < p.N;
     const int nvalid = active ? min(width, p.N - col) : 0;
-    if constexpr (MODE == OUT_SWIGLU) {
+    if constexpr (MODE == OUT_DSWIGLU) {
+      // dy tile in the accumulator; g, u from the saved pre-activation; two 16-column stores (dg, du)
+      const __nv_bfloat16* hrow = p.resid + static_cast<size_t>(row) * p.ld_resid + col;
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+      const bool vec = active && nvalid == 16 && ((reinterpret_cast<uintptr_t>(hrow) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(crow) & 15) == 0) && ((p.swiglu_n & 7) == 0);
+      uint4 gq[2], uq[2];
+      if (vec) {
+        gq[0] = reinterpret_cast<const uint4*>(hrow)[0];
+        gq[1] = reinterpret_cast<const uint4*>(hrow)[1];
+        uq[0] = reinterpret_cast<const uint4*>(hrow + p.swiglu_n)[0];
+        uq[1] = reinterpret_cast<const uint4*>(hrow + p.swiglu_n)[1];
+      }
+      uint32_t v[16];
+      tmem_ld_32x16(taddr + c0, v);
+      tmem_ld_wait();
+      if (!active) continue;
+      float dg[16], du[16];
+      if (vec) {
+        const uint32_t gw[8] = {gq[0].x, gq[0].y, gq[0].z, gq[0].w, gq[1].x, gq[1].y, gq[1].z, gq[1].w};
+        const uint32_t uw[8] = {uq[0].x, uq[0].y, uq[0].z, uq[0].w, uq[1].x, uq[1].y, uq[1].z, uq[1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 g2 = unpack_bf16x2(gw[i]), u2 = unpack_bf16x2(uw[i]);
+          const float gg[2] = {g2.x, g2.y}, uu[2] = {u2.x, u2.y};
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float dy = __uint_as_float(v[2 * i + j]);
+            const float sg = 1.f / (1.f + __expf(-gg[j]));
+            dg[2 * i + j] = dy * uu[j] * sg * (1.f + gg[j] * (1.f - sg));
+            du[2 * i + j] = dy * gg[j] * sg;
+          }
+        }
+        reinterpret_cast<uint4*>(crow)[0] = make_uint4(pack_bf16x2(dg[0], dg[1]), pack_bf16x2(dg[2], dg[3]),
+                                                       pack_bf16x2(dg[4], dg[5]), pack_bf16x2(dg[6], dg[7]));
+        reinterpret_cast<uint4*>(crow)[1] = make_uint4(pack_bf16x2(dg[8], dg[9]), pack_bf16x2(dg[10], dg[11]),
+                                                       pack_bf16x2(dg[12], dg[13]), pack_bf16x2(dg[14], dg[15]));
+        reinterpret_cast<uint4*>(crow + p.swiglu_n)[0] = make_uint4(pack_bf16x2(du[0], du[1]), pack_bf16x2(du[2], du[3]),
+                                                                    pack_bf16x2(du[4], du[5]), pack_bf16x2(du[6], du[7]));
+        reinterpret_cast<uint4*>(crow + p.swiglu_n)[1] = make_uint4(pack_bf16x2(du[8], du[9]), pack_bf16x2(du[10], du[11]),
+                                                                    pack_bf16x2(du[12], du[13]), pack_bf16x2(du[14], du[15]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (i < nvalid) {
+            const float dy = __uint_as_float(v[i]);
+            const float g = bf2f(hrow[i]), u = bf2f(hrow[p.swiglu_n + i]);
+            const float sg = 1.f / (1.f + __expf(-g));
+            crow[i] = f2bf(dy * u * sg * (1.f + g * (1.f - sg)));
+            crow[p.swiglu_n + i] = f2bf(dy * g * sg);
+          }
+        }
+      }
+    } else if constexpr (is_swiglu(MODE)) {
       uint32_t v[16], u[16];
       tmem_ld_32x16(taddr + c0, v);
       tmem_ld_32x16(taddr + BN + c0, u);
@@ -109,6 +168,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           if (i < nvalid) crow[i] = f2bf(f[i]);
+      }
+      if constexpr (MODE == OUT_SWIGLU_SAVE) {
+        // the pre-activation, rounded to bf16 exactly as the unfused path stores it: [gate | up] of this row
+        __nv_bfloat16* hrow = const_cast<__nv_bfloat16*>(p.resid) + static_cast<size_t>(row) * p.ld_resid + col;
+        if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(hrow) & 15) == 0) && ((p.swiglu_n & 7) == 0)) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const uint32_t* w = hh == 0 ? v : u;
+            __nv_bfloat16* dst = hrow + hh * p.swiglu_n;
+            float t[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = __uint_as_float(w[i]);
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(pack_bf16x2(t[0], t[1]), pack_bf16x2(t[2], t[3]),
+                                                          pack_bf16x2(t[4], t[5]), pack_bf16x2(t[6], t[7]));
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(pack_bf16x2(t[8], t[9]), pack_bf16x2(t[10], t[11]),
+                                                          pack_bf16x2(t[12], t[13]), pack_bf16x2(t[14], t[15]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (i < nvalid) {
+              hrow[i] = f2bf(__uint_as_float(v[i]));
+              hrow[p.swiglu_n + i] = f2bf(__uint_as_float(u[i]));
+            }
+        }
       }
     } else if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_BF16_ROPE) {
       uint32_t v[32];
@@ -168,20 +252,50 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
           const float* ct = p.rope_cos + static_cast<size_t>(row % p.rope_S) * half;
           const float* st = p.rope_sin + static_cast<size_t>(row % p.rope_S) * half;
           int d = col % p.rope_D;     // channel of the first column of this chunk inside its head (even)
+          // Eight columns (four pairs) at a time with 16-byte loads of the tables and the bias whenever the group does
+          // not straddle a head boundary and everything is 16-byte aligned (head dims that are multiples of 8, tile
+          // starts that are multiples of 8: the flagship's 96 / 240); scalar loads otherwise.
+          const bool vec8 = ((p.rope_D & 7) == 0) && ((col & 7) == 0) && ((half & 3) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(p.rope_cos) & 15) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(p.rope_sin) & 15) == 0) &&
+                            (!p.rope_bias || (reinterpret_cast<uintptr_t>(p.rope_bias) & 15) == 0);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            if (i < width && col + i < p.rope_width) {
-              float x0 = f[i], x1 = f[i + 1];
+          for (int i0 = 0; i0 < 32; i0 += 8) {
+            if (i0 < width && col + i0 + 8 <= p.rope_width && vec8) {
+              const float4 c4 = __ldg(reinterpret_cast<const float4*>(ct + (d >> 1)));
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(st + (d >> 1)));
+              const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
               if (p.rope_bias) {
-                x0 += __ldg(p.rope_bias + col + i);
-                x1 += __ldg(p.rope_bias + col + i + 1);
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0 + 4));
+                f[i0] += b0.x; f[i0 + 1] += b0.y; f[i0 + 2] += b0.z; f[i0 + 3] += b0.w;
+                f[i0 + 4] += b1.x; f[i0 + 5] += b1.y; f[i0 + 6] += b1.z; f[i0 + 7] += b1.w;
               }
-              const float cs = __ldg(ct + (d >> 1)), sn = __ldg(st + (d >> 1));
-              f[i] = x0 * cs - x1 * sn;
-              f[i + 1] = x1 * cs + x0 * sn;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float x0 = f[i0 + 2 * j], x1 = f[i0 + 2 * j + 1];
+                f[i0 + 2 * j] = x0 * cs[j] - x1 * sn[j];
+                f[i0 + 2 * j + 1] = x1 * cs[j] + x0 * sn[j];
+              }
+              d += 8;
+              if (d >= p.rope_D) d -= p.rope_D;
+            } else {
+#pragma unroll
+              for (int i = i0; i < i0 + 8; i += 2) {
+                if (i < width && col + i < p.rope_width) {
+                  float x0 = f[i], x1 = f[i + 1];
+                  if (p.rope_bias) {
+                    x0 += __ldg(p.rope_bias + col + i);
+                    x1 += __ldg(p.rope_bias + col + i + 1);
+                  }
+                  const float cs = __ldg(ct + (d >> 1)), sn = __ldg(st + (d >> 1));
+                  f[i] = x0 * cs - x1 * sn;
+                  f[i + 1] = x1 * cs + x0 * sn;
+                }
+                d += 2;
+                if (d >= p.rope_D) d -= p.rope_D;
+              }
             }
-            d += 2;
-            if (d >= p.rope_D) d -= p.rope_D;
           }
         }
       }

@@ -27,7 +27,7 @@ template <int BN, int MODE>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;   // 16 KB
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int NB = (MODE == OUT_SWIGLU) ? 2 : 1;  // SwiGLU stages a gate tile and an up tile
+  static constexpr int NB = is_swiglu(MODE) ? 2 : 1;  // SwiGLU stages a gate tile and an up tile
   static constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
   static constexpr int STAGES = (STAGE_BYTES > 32768) ? 4 : 6;
   static constexpr int BAR_BYTES = 1024;
@@ -41,7 +41,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   using L = SmemLayout<BN, MODE>;
   constexpr int STAGES = L::STAGES;
   // accumulator width in TMEM columns: SwiGLU keeps gate and up side by side
-  constexpr int ACC_COLS = (MODE == OUT_SWIGLU) ? 2 * BN : BN;
+  constexpr int ACC_COLS = is_swiglu(MODE) ? 2 * BN : BN;
   static_assert(ACC_COLS <= 256, "accumulator too wide");
   // two accumulators; tensor memory is allocated in powers of two >= 32 columns, and only as much as they need, so
   // that a dependent kernel launched early (programmatic dependent launch) can allocate beside a resident one
@@ -162,7 +162,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (phase == 0) continue;
             if constexpr (!B_MN) {
               tma_load_2d(sb, &tmB, &full_bar[s], kbcol, n0);
-              if constexpr (MODE == OUT_SWIGLU) tma_load_2d(sb + L::B_BYTES, &tmB, &full_bar[s], kbcol, n0 + p.swiglu_n);
+              if constexpr (is_swiglu(MODE)) tma_load_2d(sb + L::B_BYTES, &tmB, &full_bar[s], kbcol, n0 + p.swiglu_n);
             } else {
 #pragma unroll
               for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[s], n0 + c * 64, kbcol);
@@ -209,7 +209,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                         : make_smem_desc(sb + k * 32, 16, 1024);
             umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb > kb0 || k) ? 1u : 0u);
-            if constexpr (MODE == OUT_SWIGLU) {
+            if constexpr (is_swiglu(MODE)) {
               const uint64_t b2 = make_smem_desc(sb + L::B_BYTES + k * 32, 16, 1024);
               umma_bf16(d_tmem + BN, adesc, b2, IDESC, (kb > kb0 || k) ? 1u : 0u);
             }
@@ -299,7 +299,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorM
                   cudaStream_t stream, int max_ctas) {
   using L = SmemLayout<BN, MODE>;
   constexpr int SMEM = L::TOTAL;
-  static_assert(MODE != OUT_SWIGLU || BN == 128, "SwiGLU epilogue uses BN = 128");
+  static_assert(!is_swiglu(MODE) || BN == 128, "SwiGLU epilogue uses BN = 128");
   auto kern = gemm_kernel<BN, A_MN, B_MN, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -366,7 +366,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   if (K2 > 0 && (a_mn || b_mn || (K1 & 7))) return -20;
   const int K = K1 + K2;
   if (bn == 0) {
-    if (out_mode == OUT_SWIGLU) bn = 128;
+    if (is_swiglu(out_mode)) bn = 128;
     else if (b_mn) bn = (N <= 128) ? 128 : 256;
     else if (N <= 128) bn = 128;
     else bn = (N % 256 != 0 && N % 240 == 0) ? 240 : 256;
@@ -382,9 +382,9 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   p.rope_cos = g_rope.cos; p.rope_sin = g_rope.sin; p.rope_bias = g_rope.bias;
   p.rope_S = g_rope.S; p.rope_D = g_rope.D; p.rope_width = g_rope.width;
   if (out_mode == OUT_BF16_ROPE && (!p.rope_cos || p.rope_D <= 0 || (p.rope_D & 1) || (p.rope_width & 1))) return -25;
-  if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240 || (out_mode == OUT_SWIGLU && !a_mn && !b_mn))) {
+  if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240 || (is_swiglu(out_mode) && !a_mn && !b_mn))) {
     // SwiGLU on the pair kernel: a 256-wide MMA tile = 128 gate columns (CTA 0's half of B) + 128 up columns (CTA 1's)
-    const int bn2 = (out_mode == OUT_SWIGLU) ? 256 : bn;
+    const int bn2 = is_swiglu(out_mode) ? 256 : bn;
     const int rc2 = gemm_2cta_dispatch(A, A2, B, p, lda, lda2, ldb, a_mn, b_mn, out_mode, bn2, max_ctas, st);
     if (rc2 != -100) return rc2;
   }
@@ -398,7 +398,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
     rc = make_tmap_2d_bf16(&ta2, A2, M, K2, lda2, BM, BK);
     if (rc) return rc;
   }
-  const int brows = (out_mode == OUT_SWIGLU) ? 2 * N : N;
+  const int brows = is_swiglu(out_mode) ? 2 * N : N;
   if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, brows, K, ldb, bn, BK);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, 64);
   if (rc) return rc;
@@ -415,6 +415,15 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   if (out_mode == OUT_SWIGLU) {
     if (a_mn || b_mn || bn != 128) return -23;
     return launch<128, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  }
+  if (out_mode == OUT_SWIGLU_SAVE) {
+    if (a_mn || b_mn || bn != 128 || !resid) return -23;
+    return launch<128, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);
+  }
+  if (out_mode == OUT_DSWIGLU) {
+    if (a_mn || !b_mn || !resid) return -26;
+    if (bn == 128) return launch<128, false, true, OUT_DSWIGLU>(ta, ta2, tb, p, st, max_ctas);
+    return launch<256, false, true, OUT_DSWIGLU>(ta, ta2, tb, p, st, max_ctas);
   }
   if (out_mode == OUT_BF16_ROPE) {
     if (a_mn || b_mn) return -24;

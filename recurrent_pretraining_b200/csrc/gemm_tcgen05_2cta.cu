@@ -128,8 +128,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   constexpr uint32_t IDESC = make_idesc_bf16(2 * BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
   // SwiGLU: the pair's 256 accumulator columns are [128 gate | 128 up] of the same 128 output columns; CTA 0 stages
   // the gate rows of B, CTA 1 the up rows (p.swiglu_n rows further down), and p.N is the OUTPUT width.
-  constexpr int BN_OUT = (MODE == OUT_SWIGLU) ? BN / 2 : BN;
-  static_assert(MODE != OUT_SWIGLU || (BN == 256 && !A_MN && !B_MN), "SwiGLU epilogue: NT GEMM with 256-wide MMA tiles");
+  constexpr int BN_OUT = is_swiglu(MODE) ? BN / 2 : BN;
+  static_assert(!is_swiglu(MODE) || (BN == 256 && !A_MN && !B_MN), "SwiGLU epilogue: NT GEMM with 256-wide MMA tiles");
   static_assert(!B_MN || (BNH % 64 == 0), "MN-major B needs 64-column chunks per CTA");
 
   extern __shared__ uint8_t smem_raw[];
@@ -206,7 +206,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int mt, nt;
         tile_mn(tile, mt, nt);
         const int m0 = mt * (2 * BM2) + static_cast<int>(rank) * BM2;
-        const int n0 = (MODE == OUT_SWIGLU) ? nt * BN_OUT + static_cast<int>(rank) * p.swiglu_n
+        const int n0 = is_swiglu(MODE) ? nt * BN_OUT + static_cast<int>(rank) * p.swiglu_n
                                             : nt * BN + static_cast<int>(rank) * BNH;
         if constexpr (AG) {
           // the weight rows of this N-tile must have landed in the local buffer (every CTA's copiers add one)
@@ -381,7 +381,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
     max_clusters = n;
   }
-  constexpr int BN_OUT = (MODE == OUT_SWIGLU) ? BN / 2 : BN;
+  constexpr int BN_OUT = is_swiglu(MODE) ? BN / 2 : BN;
   const int tiles = ((p.M + 2 * BM2 - 1) / (2 * BM2)) * ((p.N + BN_OUT - 1) / BN_OUT);
   int clusters = tiles < max_clusters ? tiles : max_clusters;
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2;
@@ -395,7 +395,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
 // Entry used by b200_gemm: returns -100 when the 2-CTA kernel does not cover the request.
 int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,
                        int a_mn, int b_mn, int out_mode, int bn, int max_ctas, cudaStream_t st) {
-  if (out_mode == OUT_SWIGLU && (a_mn || b_mn || bn != 256 || p.K2 > 0)) return -100;
+  if (is_swiglu(out_mode) && (a_mn || b_mn || bn != 256 || p.K2 > 0)) return -100;
   if (bn == 240 && b_mn) return -100;
   if (bn != 256 && bn != 240) return -100;
   const int K = p.K1 + p.K2;
@@ -409,7 +409,7 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     rc = make_tmap_2d_bf16(&ta2, A2, p.M, p.K2, lda2, BM2, BK2);
     if (rc) return rc;
   }
-  const int brows = (out_mode == OUT_SWIGLU) ? 2 * p.N : p.N;
+  const int brows = is_swiglu(out_mode) ? 2 * p.N : p.N;
   if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, brows, K, ldb, bn / 2, BK2);
   else rc = make_tmap_2d_bf16(&tb, B, K, p.N, ldb, BK2, 64);
   if (rc) return rc;
@@ -423,6 +423,11 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     default: return -100;                                                                           \
   }
   if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_SWIGLU_SAVE) return launch2<256, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_DSWIGLU) {
+    if (a_mn || !b_mn || bn != 256) return -100;
+    return launch2<256, false, true, OUT_DSWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  }
   if (out_mode == OUT_BF16_ROPE) {
     if (a_mn || b_mn) return -100;
     if (bn == 240) return launch2<240, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);

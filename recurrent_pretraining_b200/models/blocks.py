@@ -248,6 +248,9 @@ class GatedMLP(nn.Module):
     def forward(self, x):
         if self.is_silu and self.fc.bias is None and x.is_cuda and not torch.is_grad_enabled() and FUSE_SWIGLU:
             return self.proj(ops.linear_swiglu(x, self.fc.weight))  # gate applied in the GEMM epilogue
+        if self.is_silu and self.fc.bias is None and self.proj.bias is None and x.is_cuda and FUSE_SWIGLU \
+                and torch.is_grad_enabled():
+            return ops.gated_mlp(x, self.fc.weight, self.proj.weight)   # both elementwise stages in GEMM epilogues
         h = self.fc(x)
         if self.is_silu:
             return self.proj(ops.swiglu(h))

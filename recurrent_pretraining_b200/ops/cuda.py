@@ -52,6 +52,8 @@ _set_2cta = _sig("b200_gemm_set_2cta", [_i])
 
 OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_BF16_RESID, OUT_SWIGLU = range(5)
 OUT_BF16_ROPE = 7
+OUT_SWIGLU_SAVE = 8     # SwiGLU epilogue that also stores the pre-activation [gate | up] into ``resid``
+OUT_DSWIGLU = 9         # input-gradient GEMM whose epilogue applies the gate's derivative (``resid`` = pre-activation)
 _set_rope = _sig("b200_gemm_set_rope", [_vp, _vp, _vp, _i, _i, _i])
 
 
@@ -144,15 +146,23 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, 
         a2, a2r, K2, lda2 = _mat(a2)
         assert a2r == M
     assert K == K1 + K2, (K, K1, K2)
-    if out_mode == OUT_SWIGLU:
+    if out_mode in (OUT_SWIGLU, OUT_SWIGLU_SAVE):
         assert N % 2 == 0
         N //= 2
     if n_out is not None:
         N = n_out
     if out is None:
-        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU, OUT_BF16_ROPE) else torch.float32
-        out = torch.empty((M, N), dtype=dt, device=a.device)
+        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU, OUT_BF16_ROPE, OUT_SWIGLU_SAVE) \
+            else torch.float32
+        if out_mode == OUT_DSWIGLU:      # [dgate | dup]: the tile epilogue writes both halves
+            out = torch.empty((M, 2 * N), dtype=BF16, device=a.device)[:, :N]
+        else:
+            out = torch.empty((M, N), dtype=dt, device=a.device)
     assert out.dim() == 2 and out.stride(1) == 1 and out.shape[0] == M and out.shape[1] == N
+    if out_mode in (OUT_SWIGLU_SAVE, OUT_DSWIGLU):
+        assert resid is not None and resid.shape == (M, 2 * N) and resid.stride(0) == 2 * N, "pre-activation [M, 2I]"
+        if out_mode == OUT_DSWIGLU:
+            assert out.stride(0) == 2 * N and out.dtype == BF16, "the output is the first half of an [M, 2I] matrix"
     ld_resid = 0
     if resid is not None:
         assert resid.dtype == BF16 and resid.stride(1) == 1
@@ -258,6 +268,23 @@ def rope_bwd_(dqkv, cos, sin, n_head, n_kv, head_dim, has_bias, pos_ids=None):
         _check(_bias_grad(_ptr(dqkv), _ptr(dbias), B * S, W, width, _stream()), "bias_grad")
         dbias = dbias.view(2, 1, n_head, head_dim)
     return dqkv, dbias
+
+
+def linear_swiglu_save(x, w):
+    """(silu(x Wg^T) * (x Wu^T), pre-activation [M, 2I]) in one GEMM whose epilogue applies the gate and stores both."""
+    M, two_i = x.shape[0], w.shape[0]
+    h = torch.empty((M, two_i), dtype=BF16, device=x.device)
+    y = gemm(x, w, out_mode=OUT_SWIGLU_SAVE, resid=h)
+    return y, h
+
+
+def dswiglu_dgrad(dy_out, w_proj, h):
+    """dh [M, 2I] = dswiglu(dy_out @ w_proj, h): the input-gradient GEMM of the down projection with the derivative of
+    the gate in its epilogue (no [M, I] intermediate, no separate elementwise pass)."""
+    M, I = dy_out.shape[0], w_proj.shape[1]
+    dh = torch.empty((M, 2 * I), dtype=BF16, device=dy_out.device)
+    gemm(dy_out, w_proj, b_mn=True, out=dh[:, :I], out_mode=OUT_DSWIGLU, resid=h)
+    return dh
 
 
 def swiglu_fwd(h):

@@ -136,6 +136,43 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return ref.swiglu(ref.linear(x, weight))
 
 
+class _GatedMLP(torch.autograd.Function):
+    """proj(silu(x Wg^T) * (x Wu^T)) for fc = [Wg; Wu] with both elementwise stages inside GEMM epilogues: the gate-up
+    GEMM stores the gated product and the pre-activation; in backward the down projection's input-gradient GEMM applies
+    the gate's derivative in its epilogue.  Four GEMMs forward + backward pairs, no standalone SwiGLU kernels."""
+
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj):
+        C = cuda_backend()
+        x2 = x.reshape(-1, x.shape[-1])
+        y, h = sac.run_op("mm", lambda: C.linear_swiglu_save(x2, _lp(w_fc)))
+        (out,) = sac.run_op("mm", lambda: (C.gemm_nt(y, _lp(w_proj)),))
+        ctx.save_for_backward(x2, w_fc, w_proj, h, y)
+        ctx.xshape = x.shape
+        return out.view(*x.shape[:-1], w_proj.shape[0])
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = cuda_backend()
+        x2, w_fc, w_proj, h, y = ctx.saved_tensors
+        d2 = dout.reshape(-1, dout.shape[-1])
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dh = C.dswiglu_dgrad(d2, _lp(w_proj), h)
+        dw_proj = _wgrad(d2, y, w_proj) if ctx.needs_input_grad[2] else None
+        dx = C.gemm_nn(dh, _lp(w_fc)).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw_fc = _wgrad(dh, x2, w_fc) if ctx.needs_input_grad[1] else None
+        return dx, dw_fc, dw_proj
+
+
+def gated_mlp(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor) -> torch.Tensor:
+    """SwiGLU MLP without biases; the GPU path with gradients fuses both elementwise stages into GEMM epilogues."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() // x.shape[-1] >= 128 and not _ag_pending(w_fc) \
+            and (w_fc.shape[0] // 2) % 8 == 0:
+        return _GatedMLP.apply(x, w_fc, w_proj)
+    return linear(swiglu(linear(x, w_fc)), w_proj)
+
+
 class _Adapter(torch.autograd.Function):
     """y = x Ws^T + e We^T with W = [Ws | We] (no concatenation is materialised)."""
 

@@ -141,6 +141,13 @@ class Fabric:
     def shards_masters(self) -> bool:
         return self.grad_sync == "zero3" and self.uses_p2p
 
+    @property
+    def pulls_parameters(self) -> bool:
+        """Updated bf16 weights are pulled by the next forward pass (bucket by bucket on a side stream, QKV / gate-up
+        inside their first GEMM) instead of being pushed to every rank by the update kernel.  Always so when the fp32
+        masters are sharded; for the replicated mode it is a switch (``B200_PULL_PARAMS=1``)."""
+        return self.shards_masters or (self.uses_p2p and os.environ.get("B200_PULL_PARAMS", "0") == "1")
+
     def buffer_allocator(self, group_index: int):
         """Allocator for the flat buffers of optimizer group ``group_index`` (symmetric memory in p2p mode)."""
         if not self.uses_p2p:
@@ -162,9 +169,9 @@ class Fabric:
         if self.uses_p2p:
             from .p2p import AgHandle, ShardedStepper
 
-            self._p2p = ShardedStepper(self, groups, optimizer, model, zero3=self.shards_masters,
+            self._p2p = ShardedStepper(self, groups, optimizer, model, zero3=self.pulls_parameters,
                                        allocator=self._p2p_alloc)
-            if self.shards_masters:
+            if self.pulls_parameters:
                 # the big row-sharded projections are gathered by their first GEMM of a step
                 for gi, g in enumerate(groups[:1]):
                     for t, (name, p) in enumerate(zip(g.names, g.params)):

@@ -144,6 +144,10 @@ class ShardedStepper:
         self.reduce_count = 0
         self.overlap = os.environ.get("B200_OVERLAP", "1") == "1"
         self.overlap_ctas = int(os.environ.get("B200_RS_CTAS", "32"))
+        # B200_TRACE=1: CUDA-event stamps of every bucket's reduce-scatter (side stream) against the step's main-stream
+        # milestones, kept for the last step in ``self.trace`` (see ``timeline()``)
+        self.tracing = os.environ.get("B200_TRACE", "0") == "1"
+        self.trace: dict = {}
         self.plans = [getattr(g, "plan", None) or GroupShards.plan(g, self.world) for g in groups]
         optimizer.attach_plans(self.plans, self.rank, self.world)
         n_layer = getattr(getattr(model, "config", None), "n_layer", 0) if model is not None and \
@@ -213,9 +217,28 @@ class ShardedStepper:
                                         C.c_void_p(self.err.data_ptr()), C.c_void_p(K._stream())), "barrier")
 
     # ------------------------------------------------------------------------------------------ per step
+    def timeline(self) -> dict:
+        """Milliseconds relative to the start of the last traced step (B200_TRACE=1): when each bucket's reduce-scatter
+        started and ended on the side stream, when the backward pass ended on the main stream, and when the step
+        ended.  A bucket whose interval lies before ``backward_end`` ran under the backward pass."""
+        tr = self.trace
+        if not tr or "start" not in tr:
+            return {}
+        torch.cuda.synchronize(self.fabric.device)
+        t0 = tr["start"]
+        out = {"backward_end": round(t0.elapsed_time(tr["backward_end"]), 2),
+               "step_end": round(t0.elapsed_time(tr["step_end"]), 2), "buckets": {}}
+        for name, (a, b, ctas) in tr.get("buckets", {}).items():
+            out["buckets"][name] = {"start": round(t0.elapsed_time(a), 2), "end": round(t0.elapsed_time(b), 2),
+                                    "ctas": ctas or 296}
+        return out
+
     def begin_step(self, model, accumulating: bool) -> None:
         """Before the forward pass: (zero3) start pulling the other ranks' new parameter pieces; arm the model's
         phase hooks when this micro-batch ends an accumulation window."""
+        if self.tracing and self.backend == "cuda" and not accumulating:
+            self.trace = {"start": torch.cuda.Event(enable_timing=True)}
+            self.trace["start"].record()
         if self.zero3 and self.dirty and self.backend == "cuda":
             self._launch_gathers()
         if model is not None:
@@ -268,6 +291,9 @@ class ShardedStepper:
         # their buckets in the same order (hooks in graph order, the rest in BUCKET_ORDER), so waiting for the peers'
         # kernels of the same bucket to start cannot cycle.
         self.side.wait_event(ev)
+        if self.tracing:
+            t0 = torch.cuda.Event(enable_timing=True)
+            t0.record(self.side)
         partial = self.partials[self.reduce_count & 1]
         first = True
         for gi, tb in b.tables:
@@ -277,9 +303,16 @@ class ShardedStepper:
                                          C.c_void_p(self.err.data_ptr()), C.c_void_p(self.side.cuda_stream)),
                      "rs_table")
             first = False
+        if self.tracing:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record(self.side)
+            self.trace.setdefault("buckets", {})[b.name] = (t0, t1, ctas)
 
     def step(self, optimizer, max_norm: float, grad_scale: float, do_update: bool) -> None:
         """After the backward pass of the last micro-batch of a window: finish the reduction, clip, update."""
+        if self.tracing and self.backend == "cuda" and "start" in self.trace:
+            self.trace["backward_end"] = torch.cuda.Event(enable_timing=True)
+            self.trace["backward_end"].record()
         for name in BUCKET_ORDER:
             if name in self.buckets:
                 self._fire(name, 0)
@@ -287,6 +320,9 @@ class ShardedStepper:
             self._step_cuda(optimizer, max_norm, grad_scale, do_update)
         else:
             self._step_torch(optimizer, max_norm, grad_scale, do_update)
+        if self.tracing and self.backend == "cuda" and "start" in self.trace:
+            self.trace["step_end"] = torch.cuda.Event(enable_timing=True)
+            self.trace["step_end"].record()
         for b in self.buckets.values():
             b.fired = False
         self.reduce_count += 1

@@ -194,3 +194,33 @@ def test_engine_kl_exit_and_latent_reuse(small_model):
     assert all(s == [1, 1] for s in always["steps"])
     toks, reuse = eng.generate(ids, 4, criterion="kl", exit_threshold=5e-4, max_steps=8, continuous_compute=True)
     assert toks.shape == (B, P + 4) and reuse["device_status"] == 0
+
+
+def test_engine_kl_exit_matches_eager_adaptive_generation(small_model):
+    """Device-side KL exit of the engine against ``generate_with_adaptive_compute`` of the eager model on the same
+    weights and a deterministic (all-zero) start state: same per-sequence recurrence counts for every generated token and
+    the same tokens.  The threshold is put into the widest gap of the KL values seen along the way, so that bf16
+    rounding differences between the two implementations cannot flip a decision."""
+    from recurrent_pretraining_b200.engine.decode import DecodeEngine
+
+    torch.manual_seed(3)
+    B, P, new, cap = 2, 16, 6, 8
+    ids = torch.randint(0, 4000, (B, P), device="cuda")
+    common = dict(max_new_tokens=new, criterion="kl", num_steps=cap, init_scale=0.0, do_not_exit_in_prefill=True,
+                  return_dict_in_generate=True, do_sample=False)
+    probe = small_model.generate(ids, exit_threshold=1e-12, **common)
+    vals = sorted(v for tok in probe.scores["exit_values"][1:] for seq in tok for v in seq if v > 0)
+    assert len(vals) > 8
+    lo, hi = vals[len(vals) // 5], vals[-len(vals) // 5]
+    inner = [v for v in vals if lo <= v <= hi]
+    gap, thr = max((b / a, (a * b) ** 0.5) for a, b in zip(inner, inner[1:]))
+    assert gap > 1.05, "no usable gap between consecutive KL values"
+    hf = small_model.generate(ids, exit_threshold=thr, **common)
+    hf_steps = [list(s) for s in hf.scores["compute_steps"]]
+    eng = DecodeEngine(small_model, max_batch=B, max_len=P + new + 1, num_steps=cap, max_steps=cap)
+    toks, stats = eng.generate(ids, new, criterion="kl", exit_threshold=thr, max_steps=cap, init_scale=0.0, check_every=1)
+    assert stats["device_status"] == 0
+    assert hf_steps[0] == [cap] * B                       # the prompt runs the full depth in both
+    assert stats["steps"] == hf_steps[1:], (thr, stats["steps"], hf_steps)
+    assert any(s < cap for tok in stats["steps"] for s in tok), "the threshold never fired: the test would be vacuous"
+    assert torch.equal(toks, hf.sequences), (toks[:, P:], hf.sequences[:, P:])

@@ -302,3 +302,75 @@ def test_gemm_rope_epilogue(C, T, S, H, D, E):
     q, k, v = ref.qk_bias_rope(qkv, bias.view(2, 1, H, D), cos, sin, H, H, D)
     want = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
     _close(got, want, 2e-2, 2e-2 * math.sqrt(E))
+
+
+@pytest.mark.parametrize("T,E,I", [(260, 136, 256), (512, 264, 384), (1024, 5280, 1792)])
+def test_swiglu_save_and_dswiglu_epilogues(C, T, E, I):
+    """Gate-up GEMM that stores the gated product and the pre-activation; down-projection input-gradient GEMM with the
+    gate's derivative in its epilogue -- against the fp32 statement of the MLP's forward and backward."""
+    x, fc, proj = _rand(T, E), _rand(2 * I, E, scale=0.2), _rand(E, I, scale=0.2)
+    y, h = C.linear_swiglu_save(x, fc)
+    full = x.float() @ fc.float().T
+    _close(h, full, 2e-2, 0.05)
+    _close(y, torch.nn.functional.silu(full[:, :I]) * full[:, I:], 3e-2, 0.05)
+    dout = _rand(T, E, scale=0.5)
+    dh = C.dswiglu_dgrad(dout, proj, h)
+    hl = h.float().requires_grad_(True)
+    act = torch.nn.functional.silu(hl[:, :I]) * hl[:, I:]
+    (act @ proj.float().T).backward(dout.float())
+    _close(dh, hl.grad, 3e-2, 0.05 * float(hl.grad.abs().max()))
+    assert C.check_device_status() == 0
+
+
+def test_fused_gated_mlp_matches_unfused_path(C):
+    from recurrent_pretraining_b200.ops import functional as ops
+
+    T, E, I = 384, 264, 512
+    x = _rand(2, T // 2, E).requires_grad_(True)
+    fc = _rand(2 * I, E, scale=0.2).requires_grad_(True)
+    proj = _rand(E, I, scale=0.2).requires_grad_(True)
+    dout = _rand(2, T // 2, E)
+    out = ops.gated_mlp(x, fc, proj)
+    out.backward(dout)
+    got = (out.detach(), x.grad.clone(), fc.grad.clone(), proj.grad.clone())
+    for t in (x, fc, proj):
+        t.grad = None
+    ref_out = ops.linear(ops.swiglu(ops.linear(x, fc)), proj)
+    ref_out.backward(dout)
+    for a, b in zip(got, (ref_out.detach(), x.grad, fc.grad, proj.grad)):
+        _close(a, b, 3e-2, 0.03 * float(b.float().abs().max()))
+
+
+FLAGSHIP = [(4096, 5280, 17920, "nt"), (4096, 15840, 5280, "nt"), (2048, 5280, 10560, "nt"),
+            (1024, 17920, 5280, "nn"), (5280, 17920, 2048, "tn"), (512, 5280, 65536, "nn")]
+
+
+@pytest.mark.parametrize("M,N,K,kind", FLAGSHIP)
+def test_gemm_flagship_shapes(C, M, N, K, kind):
+    """Tile-tail and raster paths of the real model: N = 5280 (22 tiles of 240, 4.76 waves), N = 15840, the K = 17920
+    contraction, the dual-A adapter width, a weight gradient and the K = 65536 contraction that keeps the m-fastest
+    order.  Compared on a sample of rows against fp32 (the full fp32 product of these shapes would dominate the run)."""
+    torch.manual_seed(M + N)
+    if kind == "nt":
+        a, b = _rand(M, K, scale=0.3), _rand(N, K, scale=0.3)
+        out = C.gemm_nt(a, b)
+        rows = torch.randint(0, M, (48,), device="cuda")
+        want = a[rows].float() @ b.float().T
+        got = out[rows]
+    elif kind == "nn":
+        a, b = _rand(M, K, scale=0.3), _rand(K, N, scale=0.3)
+        out = C.gemm_nn(a, b)
+        rows = torch.randint(0, M, (48,), device="cuda")
+        want = a[rows].float() @ b.float()
+        got = out[rows]
+    else:   # weight gradient dy^T x into fp32, accumulated twice
+        dy, x = _rand(K, M, scale=0.3), _rand(K, N, scale=0.3)
+        out = torch.zeros(M, N, device="cuda")
+        C.gemm_tn(dy, x, out=out, accumulate=False)
+        C.gemm_tn(dy, x, out=out, accumulate=True)
+        rows = torch.randint(0, M, (48,), device="cuda")
+        want = 2 * (dy[:, rows].float().T @ x.float())
+        got = out[rows]
+    torch.cuda.synchronize()
+    _close(got, want, 2e-2, 0.02 * float(want.abs().max()))
+    assert C.check_device_status() == 0
