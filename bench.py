@@ -164,8 +164,10 @@ def build_engine(args, sync: str, fixed_depth: bool, grad_accum: int):
     torch.manual_seed(1337)
     with torch.device(fabric.device):
         model = cfg.construct_model()
+    flags = dict(atan2=True, update_clipping=True, running_init=True, decouple_wd=True) \
+        if args.optimizer == "ellis" else {}
     engine = TrainEngine(model, fabric, lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8, grad_clip=1.0,
-                         grad_accum=grad_accum)
+                         grad_accum=grad_accum, **flags)
     return fabric, cfg, engine
 
 
@@ -258,6 +260,7 @@ def run_steps(engine, args, device, rank, local, world, micro_per_step: int):
 def run_ours(args):
     import torch
 
+    os.environ.setdefault("B200_TRACE", "1")    # CUDA-event stamps of the bucket reductions (a few events per step)
     rank, world, local = dist_env()
     zero3 = args.mode == "zero3"
     accum = 8 if zero3 else 1
@@ -280,7 +283,8 @@ def run_ours(args):
                    "parallelism": f"dp{world}" + ("-zero3" if zero3 else ""),
                    "micro_batch": 1, "grad_accum": accum, "mean_recurrence": cfg.mean_recurrence,
                    "backprop_depth": cfg.mean_backprop_depth, "sampling": cfg.sampling_scheme,
-                   "optimizer": "AdamW fused, clip 1.0",
+                   "optimizer": "AdamW fused, clip 1.0" if args.optimizer == "adamw" else
+                   "ELLISAdam flags (update clipping, atan2, running init, decoupled decay) fused, clip 1.0",
                    "grad_sync": fabric.grad_sync if world > 1 else "none",
                    "overlap": bool(stepper is not None and stepper.overlap),
                    "param_sync": ("pull in the next forward pass" if stepper.zero3 else "push from the update kernel")
@@ -295,6 +299,9 @@ def run_ours(args):
         "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
         "device_mem_used_gb": device_mem_used_gb(device),
     }
+    from recurrent_pretraining_b200.ops import cuda as _K
+
+    rec["library_calls"] = dict(_K.LIBRARY_CALLS)     # declared library paths taken by the timed steps (none expected)
     # ---- evidence blocks outside the timed regions; a failure here never loses the headline line
     if stepper is not None and os.environ.get("B200_BENCH_EXTRAS", "1") == "1":
         try:
@@ -315,11 +322,17 @@ def run_ours(args):
     fabric_closed = False
     if world == 1 and not zero3 and os.environ.get("B200_BENCH_DECODE", "1") == "1" and args.model == MODEL:
         try:
-            del engine, r
             import gc
 
+            from recurrent_pretraining_b200.ops import cuda as C
+
+            engine.optimizer = engine.model = None       # the flat buffers, the optimizer state and the scratch
+            fabric.flat_groups = []                      # tensors go back before the KV caches are sized
+            C._ce_scratch.clear()
+            del engine, r
             gc.collect()
             torch.cuda.empty_cache()
+            rec["device_mem_used_before_decode_gb"] = device_mem_used_gb(device)
             rec["decode"] = decode_block(args, device)
         except Exception as exc:  # noqa: BLE001
             rec["decode"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
@@ -355,18 +368,22 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
         return
 
-    def build(checkpointing: bool):
+    def build(checkpointing: bool, compiled: bool = False):
         torch.manual_seed(1337)
         with torch.device(device):
             model, cfg = refload.build_train_model(args.model, gradient_checkpointing=checkpointing,
                                                    lockstep_n=True, lockstep_k=True, attn_impl="sdpa")
-        model = fabric.setup(model, compile=os.environ.get("REF_COMPILE", "0") == "1")
+        model = fabric.setup(model, compile=compiled)
         groups = optim.get_param_groups(model.named_parameters(), no_weight_decay_for_bias_and_norm_params=False)
         opt = optim.get_optimizer("AdamW")(groups, lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8)
         return model, cfg, opt
 
-    state = {"checkpointing": os.environ.get("REF_CHECKPOINT", "0") == "1"}
-    model, cfg, opt = build(state["checkpointing"])
+    # The reference's own launch configs train with ``compile_model: true`` (its fabric.setup wraps the model in
+    # torch.compile, max-autotune without CUDA graphs); that is the arm's default.  REF_COMPILE=0 gives the eager arm; a
+    # compile failure during warm-up falls back to eager and is recorded.
+    state = {"checkpointing": os.environ.get("REF_CHECKPOINT", "0") == "1",
+             "compile": os.environ.get("REF_COMPILE", "1") == "1", "compile_fallback": None}
+    model, cfg, opt = build(state["checkpointing"], state["compile"])
     total = args.warmup + args.steps
     host = make_batches(total, cfg.padded_vocab_size, 0, rank)
     dev_rows = host.to(device)
@@ -401,7 +418,17 @@ def run_reference(args):
         del model, opt
         torch.cuda.empty_cache()
         state["checkpointing"] = True
-        model, cfg, opt = build(True)
+        model, cfg, opt = build(True, state["compile"])
+        counters.update(micro=0, opt=0)
+        for i in range(args.warmup):
+            device_step(i, 0)
+    except Exception as exc:  # noqa: BLE001
+        if not state["compile"]:
+            raise
+        state["compile"], state["compile_fallback"] = False, f"{type(exc).__name__}: {exc}"[:200]
+        del model, opt
+        torch.cuda.empty_cache()
+        model, cfg, opt = build(state["checkpointing"], False)
         counters.update(micro=0, opt=0)
         for i in range(args.warmup):
             device_step(i, 0)
@@ -424,7 +451,8 @@ def run_reference(args):
         "dtype": "bf16 autocast, fp32 master weights", "data": "synthetic uniform-random tokens, random-init weights",
         "impl": "reference",
         "config": {"model": args.model, "global_batch": world, "seq_len": SEQ, "parallelism": f"dp{world}",
-                   "micro_batch": 1, "attn_impl": "sdpa", "compile": os.environ.get("REF_COMPILE", "0") == "1",
+                   "micro_batch": 1, "attn_impl": "sdpa", "compile": state["compile"],
+                   "compile_fallback": state["compile_fallback"],
                    "activation_checkpointing": state["checkpointing"],
                    "l2": "working set >> 126 MB L2; no explicit flush"},
         "clocks": clocks,
@@ -500,6 +528,8 @@ def main():
     ap.add_argument("--mode", default="dp", choices=["dp", "zero3"],
                     help="dp: the headline data-parallel config; zero3: fixed r=32, k=8, accumulation 8, parameters, "
                          "gradients and optimizer state sharded over the GPUs (needs >= 2 GPUs)")
+    ap.add_argument("--optimizer", default="adamw", choices=["adamw", "ellis"],
+                    help="adamw: the headline config; ellis: the reference's production optimizer flags on the same path")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.model == MODEL else args.warmup
     if args.impl == "reference":

@@ -15,6 +15,9 @@ enum OutMode : int {
   OUT_DSWIGLU = 9,       // backward of the gate: the accumulator is dL/dy [M, I]; with the saved pre-activation h =
                          // [g | u] (`resid`, [M, 2I]) the tile stores dL/dg = dy u s (1 + g (1 - s)) at C[:, col] and
                          // dL/du = dy g s at C[:, I + col], s = sigmoid(g); C is [M, 2I]
+  OUT_BF16_LSE = 10,     // head GEMM of the fused linear + cross-entropy: bf16 logits plus, per (row, column tile), the
+                         // online-softmax partials (max, sum exp, sum exp * logit, sum logit^2) of the scaled logits
+                         // and the target's logit; the [rows, vocab] logits never exist in fp32
 };
 __host__ __device__ constexpr bool is_swiglu(int mode) { return mode == OUT_SWIGLU || mode == OUT_SWIGLU_SAVE; }
 
@@ -37,6 +40,11 @@ struct GemmParams {
   int raster;     // m tiles per raster group (see tile_coords); 0 = m fastest
   int early_a;    // the A operand does not depend on the preceding kernel: its first tiles are requested before the
                   // programmatic-dependent-launch wait (no effect without that launch attribute)
+  // OUT_BF16_LSE: partials [M, ceil(N / BN)] float4, target logit [M], labels [M] (int64), scale applied to the logits
+  float4* lse_part;
+  float* lse_tgt;
+  const long long* lse_labels;
+  float lse_scale;
 };
 
 // Linear tile index -> (m tile, n tile), grouped: GROUP consecutive m tiles are walked across all n tiles before the
@@ -87,6 +95,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     return;
   }
   constexpr int CH = (is_swiglu(MODE) || MODE == OUT_DSWIGLU) ? 16 : 32;  // columns per step
+  // running softmax statistics of this thread's row over the tile's columns (OUT_BF16_LSE)
+  float lm = -INFINITY, ll = 0.f, le = 0.f, lq = 0.f, lt = 0.f;
+  bool lfound = false;
+  long long lab = -1;
+  if constexpr (MODE == OUT_BF16_LSE) {
+    if (row_ok) lab = p.lse_labels[row];
+  }
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += CH) {
     const int col = n0 + c0;
@@ -194,7 +209,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
             }
         }
       }
-    } else if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_BF16_ROPE) {
+    } else if constexpr (MODE == OUT_BF16 || MODE == OUT_BF16_RESID || MODE == OUT_BF16_ROPE || MODE == OUT_BF16_LSE) {
       uint32_t v[32];
       __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
       const bool vec = active && nvalid == width && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
@@ -299,6 +314,29 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
           }
         }
       }
+      if constexpr (MODE == OUT_BF16_LSE) {
+        float cm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < nvalid) cm = fmaxf(cm, f[i] * p.lse_scale);
+        if (cm > lm) {
+          const float fac = __expf(lm - cm);
+          ll *= fac;
+          le *= fac;
+          lm = cm;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i < nvalid) {
+            const float a = f[i] * p.lse_scale;
+            const float ex = __expf(a - lm);
+            ll += ex;
+            le += ex * a;
+            lq += a * a;
+            if (col + i == lab) { lt = a; lfound = true; }
+          }
+        }
+      }
       if (vec) {
 #pragma unroll
         for (int q = 0; q < 4; ++q)
@@ -358,6 +396,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
           }
         }
       }
+    }
+  }
+  if constexpr (MODE == OUT_BF16_LSE) {
+    if (row_ok) {
+      const int tiles_n = (p.N + BN - 1) / BN;
+      p.lse_part[static_cast<size_t>(row) * tiles_n + n0 / BN] = make_float4(lm, ll, le, lq);
+      if (lfound) p.lse_tgt[row] = lt;
     }
   }
 }

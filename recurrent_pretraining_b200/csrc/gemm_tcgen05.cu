@@ -359,6 +359,13 @@ B200_API void b200_gemm_set_rope(const float* cos, const float* sin, const float
   g_rope = {cos, sin, bias, S, D, width};
 }
 
+// Arguments of the next OUT_BF16_LSE call (same convention as b200_gemm_set_rope).
+struct LseArgs { void* part; float* tgt; const long long* labels; float scale; };
+static thread_local LseArgs g_lse = {nullptr, nullptr, nullptr, 1.f};
+B200_API void b200_gemm_set_lse(void* part, float* tgt, const long long* labels, float scale) {
+  g_lse = {part, tgt, labels, scale};
+}
+
 B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, const void* resid, int M, int N,
                        int K1, int K2, int lda, int lda2, int ldb, int ldc, int ld_resid, int a_mn, int b_mn,
                        int out_mode, int bn, int max_ctas, void* stream, int* err) {
@@ -381,6 +388,9 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
   p.raster = (K1 + K2 >= 32768) ? 0 : g_raster;
   p.rope_cos = g_rope.cos; p.rope_sin = g_rope.sin; p.rope_bias = g_rope.bias;
   p.rope_S = g_rope.S; p.rope_D = g_rope.D; p.rope_width = g_rope.width;
+  p.lse_part = reinterpret_cast<float4*>(g_lse.part); p.lse_tgt = g_lse.tgt; p.lse_labels = g_lse.labels;
+  p.lse_scale = g_lse.scale;
+  if (out_mode == OUT_BF16_LSE && (!p.lse_part || !p.lse_tgt || !p.lse_labels || a_mn || b_mn || bn != 256)) return -27;
   if (out_mode == OUT_BF16_ROPE && (!p.rope_cos || p.rope_D <= 0 || (p.rope_D & 1) || (p.rope_width & 1))) return -25;
   if (g_use_2cta && M >= 256 && (bn == 256 || bn == 240 || (is_swiglu(out_mode) && !a_mn && !b_mn))) {
     // SwiGLU on the pair kernel: a 256-wide MMA tile = 128 gate columns (CTA 0's half of B) + 128 up columns (CTA 1's)
@@ -416,6 +426,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
     if (a_mn || b_mn || bn != 128) return -23;
     return launch<128, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
   }
+  if (out_mode == OUT_BF16_LSE) return launch<256, false, false, OUT_BF16_LSE>(ta, ta2, tb, p, st, max_ctas);
   if (out_mode == OUT_SWIGLU_SAVE) {
     if (a_mn || b_mn || bn != 128 || !resid) return -23;
     return launch<128, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);

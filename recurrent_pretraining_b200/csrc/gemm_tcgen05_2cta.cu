@@ -424,6 +424,10 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
   }
   if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
   if (out_mode == OUT_SWIGLU_SAVE) return launch2<256, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_BF16_LSE) {
+    if (a_mn || b_mn || bn != 256) return -100;
+    return launch2<256, false, false, OUT_BF16_LSE>(ta, ta2, tb, p, st, max_ctas);
+  }
   if (out_mode == OUT_DSWIGLU) {
     if (a_mn || !b_mn || bn != 256) return -100;
     return launch2<256, false, true, OUT_DSWIGLU>(ta, ta2, tb, p, st, max_ctas);

@@ -7,7 +7,8 @@
   globbed on rank 0 and broadcast, shuffled with a seeded RNG, assigned ``rank::max(8, world)``; one row group at a
   time is read, shuffled with a per-dataset ``random.Random`` and popped from the end; the state (file index, row
   group, rows left, RNG state, fingerprint) is all-gathered on save and reloaded modulo the saved world size.
-* ``TextRows``      -- rows of a ``datasets.load_from_disk`` directory or a list of dicts (tokenised in collate).
+* ``TextRows``      -- (alias ``HuggingfaceDataset``) rows of a list of dicts, a parquet / jsonl file or a
+  ``datasets.load_from_disk`` directory, dealt out row by row over ranks x loader workers (tokenised in collate).
 """
 from __future__ import annotations
 
@@ -237,38 +238,88 @@ class BufferShuffledParquet(IterableDataset):
     load_local_state = load_state_dict
 
 
+def _load_rows(path: str):
+    """Rows of an on-disk text dataset: a parquet file or folder, a ``.jsonl`` file, or -- when the ``datasets`` package
+    is installed -- an arrow folder written by ``save_to_disk``."""
+    pth = Path(path)
+    if pth.suffix == ".jsonl":
+        import json
+
+        with open(pth) as f:
+            return [json.loads(line) for line in f if line.strip()]
+    files = [pth] if pth.suffix == ".parquet" else sorted(pth.glob("*.parquet"))
+    if files:
+        import pyarrow.parquet as pq
+
+        rows: list = []
+        for f in files:
+            rows.extend(pq.read_table(f).to_pylist())
+        return rows
+    import datasets
+
+    ds = datasets.load_from_disk(str(pth))
+    if isinstance(ds, datasets.DatasetDict):
+        raise ValueError("the dataset path must point to a single split (try adding /train)")
+    return ds
+
+
 class TextRows(IterableDataset):
-    """Raw-text rows (dicts) sharded by rank; tokenisation happens in the collate function."""
+    """The ``hfds`` source: rows (dicts) of a map-style dataset, dealt out row by row -- not file by file -- over
+    ``ranks x loader workers`` (shard ``rank * workers + worker`` takes rows ``shard::n_shards``), optionally repeated
+    ``repetitions`` times; tokenisation happens in the collate function, driven by the ``data_signature`` attached to
+    every row.  The position (``data_idx`` within this shard) is the resumable state
+    (recpre/huggingface_dataset.py:297-441)."""
 
     def __init__(self, rows_or_path, data_signature: dict, num_processes: int = 1, process_rank: int = 0,
-                 shuffle: bool = False, seed: int = 0, data_id=None):
+                 shuffle: bool = False, seed: int = 0, data_id=None, repetitions: int | None = None,
+                 return_data_id: bool | None = None):
         if isinstance(rows_or_path, (str, Path)):
-            import datasets
-
-            rows_or_path = datasets.load_from_disk(str(rows_or_path))
+            rows_or_path = _load_rows(str(rows_or_path))
         self.rows, self.sig = rows_or_path, data_signature
         self.world, self.rank, self.shuffle, self.seed, self.data_id = num_processes, process_rank, shuffle, seed, data_id
+        self.repetitions = max(1, int(repetitions or 1))
+        self.return_data_id = (data_id is not None) if return_data_id is None else return_data_id
         self._pos = 0
+        self.fingerprint, self.index_range = None, (0, 0)
 
-    def __iter__(self):
-        order = list(range(self.rank, len(self.rows), self.world))
+    def _order(self) -> list:
+        info = torch.utils.data.get_worker_info()
+        workers, worker = (info.num_workers, info.id) if info is not None else (1, 0)
+        total = len(self.rows) * self.repetitions
+        order = list(range(self.rank * workers + worker, total, self.world * workers))
+        if order:
+            self.fingerprint = hashlib.shake_128(str(order).encode()).hexdigest(4)
+            self.index_range = (order[0], order[-1])
         if self.shuffle:
             random.Random(self.seed).shuffle(order)
+        return order
+
+    def __len__(self) -> int:
+        return len(self._order())
+
+    def __iter__(self):
+        order = self._order()
+        n = len(self.rows)
         while self._pos < len(order):
-            row = dict(self.rows[order[self._pos]])
+            row = self.rows[order[self._pos] % n]
             self._pos += 1
+            keys = self.sig.get("keys") if isinstance(self.sig, dict) else None
+            row = {k: row[k] for k in keys} if keys and all(k in row for k in keys) else dict(row)
             row["data_signature"] = self.sig
-            if self.data_id is not None:
+            if self.return_data_id and self.data_id is not None:
                 row["data_id"] = self.data_id
             yield row
 
     def state_dict(self):
-        return {"pos": self._pos}
+        return {"pos": self._pos, "data_idx": self._pos}
 
     def load_state_dict(self, sd, **_):
-        self._pos = int(sd["pos"])
+        self._pos = int(sd.get("pos", sd.get("data_idx", 0)))
 
     load_local_state = load_state_dict
+
+
+HuggingfaceDataset = TextRows      # the reference's class name for this source
 
 
 class WeightedMixture(IterableDataset):

@@ -94,8 +94,15 @@ class _LMBase(nn.Module):
                     valid = labels.view(-1) != ignore
                     loss = loss + z * (lse.pow(2) * valid).sum() / valid.sum().clamp(min=1)
             else:
+                tele = None
+                if getattr(self, "monitoring", False) and x.is_cuda:
+                    tele = torch.zeros(4, dtype=torch.float32, device=x.device)
                 loss = ops.linear_cross_entropy(x, self.lm_head.weight, labels, scale, ignore,
-                                                self.objective.get("z_regularization", 0.0))
+                                                self.objective.get("z_regularization", 0.0), telemetry=tele)
+                if tele is not None:      # head statistics of this step (mean over the positions that carry a label)
+                    n = (labels != ignore).sum().clamp(min=1).float()
+                    t = (tele / n).tolist()
+                    self.head_metrics = {"logit_max": t[0], "logit_entropy": t[1], "logit_norm": t[2], "logit_z": t[3]}
             return loss, logits, loss.detach().clone()
         logits = ops.linear(x, self.lm_head.weight).float() * scale
         zero = torch.zeros((), device=x.device)
@@ -285,17 +292,17 @@ class RecurrentGPT(_LMBase):
         rope = self._rope(S, position_ids)
         with nvtx.range("prelude"):
             e = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
-            self._phase(e, "prelude")    # gradient of the embedding output: the prelude has gone backward
-            for block in self.transformer.prelude:
+            for i, block in enumerate(self.transformer.prelude):
+                self._phase(e, f"prelude.{i}")    # gradient of block i's input: blocks i.. have gone backward
                 e = block(e, rope, attention_mask)
             self._phase(e, "core")       # gradient of the prelude output: all recurrences and the adapter are done
         with nvtx.range("recurrence"):
             x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
-        self._phase(x, "coda")           # gradient of the coda input: the coda blocks are done
         x_rec = x
         in_coda = self.gradient_checkpointing and "in-coda" in cfg.activation_checkpoint_impl
         with nvtx.range("coda"):
-            for block in self.transformer.coda:
+            for i, block in enumerate(self.transformer.coda):
+                self._phase(x, f"coda.{i}")       # gradient of block i's input: coda blocks i.. have gone backward
                 if in_coda and torch.is_grad_enabled():
                     x = self._ckpt()(block, x, rope, attention_mask)
                 else:
@@ -330,6 +337,7 @@ class RecurrentGPT(_LMBase):
             "num_steps_no_grad": n,
             "num_steps_with_grad": k,
         }
+        self.latest_metrics.update(getattr(self, "head_metrics", {}))
 
 
 class GPT(_LMBase):

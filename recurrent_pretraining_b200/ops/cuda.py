@@ -3,6 +3,15 @@
 Importing this module loads the library and raises if it is missing, so a GPU run can never silently
 take a PyTorch fallback.  Every wrapper launches on the current PyTorch CUDA stream and allocates
 its outputs through the PyTorch caching allocator; nothing here synchronises the device.
+
+Declared library paths (everything else either runs an in-tree kernel or raises).  Each use is counted in
+``LIBRARY_CALLS`` and announced once per process on stderr, so a run that leaves the native kernels shows it:
+
+* ``attention_fwd`` / ``attention_bwd`` with a head dim other than 64, 96 or 128, or with
+  ``B200_NATIVE_ATTENTION=0`` / ``B200_NATIVE_ATTENTION_BWD=0`` (comparison switches of the kernel benchmarks):
+  torch's scaled-dot-product attention.  ``B200_STRICT_NATIVE=1`` turns these into errors.
+* ``attention_infer``: the eager HF model's cached decoding (``models/hf.py``; the serving engine has its own
+  flash-decoding kernel and never comes here) always uses torch's attention.
 """
 from __future__ import annotations
 
@@ -54,6 +63,9 @@ OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_BF16_RESID, OUT_SWIGLU = range(5)
 OUT_BF16_ROPE = 7
 OUT_SWIGLU_SAVE = 8     # SwiGLU epilogue that also stores the pre-activation [gate | up] into ``resid``
 OUT_DSWIGLU = 9         # input-gradient GEMM whose epilogue applies the gate's derivative (``resid`` = pre-activation)
+OUT_BF16_LSE = 10       # head GEMM: bf16 logits + per-tile softmax partials + target logit (fused linear + CE)
+_set_lse = _sig("b200_gemm_set_lse", [_vp, _vp, _vp, _f])
+_ce_finish = _sig("b200_ce_finish", [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _i, _f, _i, _vp])
 _set_rope = _sig("b200_gemm_set_rope", [_vp, _vp, _vp, _i, _i, _i])
 
 
@@ -133,7 +145,7 @@ def _mat(t: torch.Tensor):
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, resid=None, n_out=None, bn=0,
-         max_ctas=0, rope=None):
+         max_ctas=0, rope=None, lse=None):
     """C[M,N] (+)= A B^T.  ``a``: [M,K] (or [K,M] if a_mn), ``b``: [N,K] (or [K,N] if b_mn).
     ``rope`` (OUT_BF16_ROPE): (cos [S, D/2] fp32, sin, bias flat fp32 or None, S, D, width of the q+k columns)."""
     a, ar, ac, lda = _mat(a)
@@ -152,7 +164,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, 
     if n_out is not None:
         N = n_out
     if out is None:
-        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU, OUT_BF16_ROPE, OUT_SWIGLU_SAVE) \
+        dt = BF16 if out_mode in (OUT_BF16, OUT_BF16_RESID, OUT_SWIGLU, OUT_BF16_ROPE, OUT_SWIGLU_SAVE, OUT_BF16_LSE) \
             else torch.float32
         if out_mode == OUT_DSWIGLU:      # [dgate | dup]: the tile epilogue writes both halves
             out = torch.empty((M, 2 * N), dtype=BF16, device=a.device)[:, :N]
@@ -171,6 +183,12 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, 
         cos, sin, bias, S, D, width = rope
         assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[-1] * 2 == D
         _set_rope(_ptr(cos), _ptr(sin), _ptr(bias), int(S), int(D), int(width))
+    if out_mode == OUT_BF16_LSE:
+        part, tgt, labels, scale = lse     # [M, ceil(N / 256), 4] fp32, [M] fp32, [M] int64, logit scale
+        assert part.dtype == torch.float32 and part.is_contiguous() and part.shape == (M, (N + 255) // 256, 4)
+        assert tgt.numel() >= M and labels.dtype == torch.int64 and labels.is_contiguous()
+        _set_lse(_ptr(part), _ptr(tgt), _ptr(labels), float(scale))
+        bn = 256
     rc = _gemm(_ptr(a), _ptr(a2), _ptr(b), _ptr(out), _ptr(resid), M, N, K1, K2, lda, lda2, ldb, out.stride(0),
                ld_resid, int(a_mn), int(b_mn), out_mode, bn, max_ctas, _stream(), _ptr(err_word(a.device)))
     _check(rc, "b200_gemm")
@@ -361,11 +379,16 @@ def _scratch(key, shape, dtype, device):
     return t
 
 
-def linear_ce(x, w, labels, logit_scale=1.0, ignore_index=-100, z_reg=0.0, need_grad=True, chunk_rows=1024):
+def linear_ce(x, w, labels, logit_scale=1.0, ignore_index=-100, z_reg=0.0, need_grad=True, chunk_rows=1024,
+              telemetry=None, fused=None):
     """Returns (loss, dx, dw): mean CE over valid labels, and the gradients for a unit loss gradient.
 
-    Rows are processed in chunks: head GEMM -> fp32 logits chunk -> row kernel (loss, bf16 dlogits) ->
-    dX chunk = dlogits W and dW += dlogits^T x.  At most chunk_rows x V logits exist at any time."""
+    Rows are processed in chunks.  Fused form (default when the vocabulary is a multiple of 8): the head GEMM's epilogue
+    writes bf16 logits and, per (row, 256-column tile), the online-softmax partials and the target's logit; a row kernel
+    merges the partials into the log-sum-exp, adds the loss (and, if asked, telemetry: max logit, entropy, logit norm,
+    lse^2 summed over valid rows into ``telemetry[0:4]``) and rewrites the bf16 logits in place as the logit gradient;
+    then dX chunk = dlogits W and dW += dlogits^T x.  No fp32 logits exist.  ``fused=False`` keeps the older sequence
+    (fp32 logits chunk + row kernel), used as a cross-check."""
     T, E = x.shape
     V = w.shape[0]
     dev = x.device
@@ -373,19 +396,39 @@ def linear_ce(x, w, labels, logit_scale=1.0, ignore_index=-100, z_reg=0.0, need_
     loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
     n_valid = (labels != ignore_index).sum().to(torch.float32).reshape(1)
     rows = min(chunk_rows, T)
-    logits = _scratch(("logits", dev), (rows, V), torch.float32, dev)
-    dlog = _scratch(("dlogits", dev), (rows, V), BF16, dev) if need_grad else None
+    if fused is None:
+        fused = V % 8 == 0 and os.environ.get("B200_FUSED_CE", "1") == "1"
     dx = torch.empty_like(x) if need_grad else None
     dw = _scratch(("dw", dev), (V, E), torch.float32, dev) if need_grad else None
-    for i, r0 in enumerate(range(0, T, rows)):
-        r1 = min(T, r0 + rows)
-        n = r1 - r0
-        gemm(x[r0:r1], w, out=logits[:n], out_mode=OUT_F32)
-        _check(_ce_rows(_ptr(logits), _ptr(labels[r0:r1]), _ptr(dlog), _ptr(loss_sum), 0, _ptr(n_valid), n, V, V, V,
-                        float(logit_scale), int(ignore_index), float(z_reg), _stream()), "ce_rows")
-        if need_grad:
-            gemm(dlog[:n], w, b_mn=True, out=dx[r0:r1])
-            gemm(dlog[:n], x[r0:r1], a_mn=True, b_mn=True, out=dw, out_mode=OUT_F32 if i == 0 else OUT_F32_ACC)
+    if fused:
+        tiles = (V + 255) // 256
+        logits = _scratch(("logits_bf16", dev), (rows, V), BF16, dev)
+        part = _scratch(("lse_part", dev), (rows, tiles, 4), torch.float32, dev)
+        tgt = _scratch(("lse_tgt", dev), (rows,), torch.float32, dev)
+        for i, r0 in enumerate(range(0, T, rows)):
+            r1 = min(T, r0 + rows)
+            n = r1 - r0
+            lab = labels[r0:r1]
+            tgt.zero_()          # rows whose label is ignored (or out of range) keep 0; they do not enter the loss
+            gemm(x[r0:r1], w, out=logits[:n], out_mode=OUT_BF16_LSE, lse=(part[:n], tgt, lab, logit_scale))
+            _check(_ce_finish(_ptr(part), tiles, _ptr(tgt), _ptr(lab), _ptr(logits), n, V, V, _ptr(loss_sum), 0,
+                              _ptr(telemetry), _ptr(n_valid), float(logit_scale), int(ignore_index), float(z_reg),
+                              int(need_grad), _stream()), "ce_finish")
+            if need_grad:
+                gemm(logits[:n], w, b_mn=True, out=dx[r0:r1])
+                gemm(logits[:n], x[r0:r1], a_mn=True, b_mn=True, out=dw, out_mode=OUT_F32 if i == 0 else OUT_F32_ACC)
+    else:
+        logits = _scratch(("logits", dev), (rows, V), torch.float32, dev)
+        dlog = _scratch(("dlogits", dev), (rows, V), BF16, dev) if need_grad else None
+        for i, r0 in enumerate(range(0, T, rows)):
+            r1 = min(T, r0 + rows)
+            n = r1 - r0
+            gemm(x[r0:r1], w, out=logits[:n], out_mode=OUT_F32)
+            _check(_ce_rows(_ptr(logits), _ptr(labels[r0:r1]), _ptr(dlog), _ptr(loss_sum), 0, _ptr(n_valid), n, V, V, V,
+                            float(logit_scale), int(ignore_index), float(z_reg), _stream()), "ce_rows")
+            if need_grad:
+                gemm(dlog[:n], w, b_mn=True, out=dx[r0:r1])
+                gemm(dlog[:n], x[r0:r1], a_mn=True, b_mn=True, out=dw, out_mode=OUT_F32 if i == 0 else OUT_F32_ACC)
     loss = (loss_sum / n_valid.clamp(min=1.0)).reshape(())
     return loss, dx, dw
 
@@ -400,6 +443,20 @@ def _views(qkv_r, n_head, n_kv, D):
     k = qkv_r[..., wq:wq + wk].view(B, S, n_kv, D)
     v = qkv_r[..., wq + wk:].view(B, S, n_kv, D)
     return q, k, v
+
+
+LIBRARY_CALLS: dict = {}
+
+
+def _library(op: str, why: str, strict: bool = True) -> None:
+    """Account for a call that leaves the in-tree kernels."""
+    if strict and os.environ.get("B200_STRICT_NATIVE", "0") == "1":
+        raise RuntimeError(f"{op}: {why}, and B200_STRICT_NATIVE=1 forbids the library path")
+    if op not in LIBRARY_CALLS:
+        import sys
+
+        print(f"[b200] {op}: library path ({why})", file=sys.stderr, flush=True)
+    LIBRARY_CALLS[op] = LIBRARY_CALLS.get(op, 0) + 1
 
 
 def _sdpa(q, k, v, scale, causal=True):
@@ -417,6 +474,7 @@ def attention_fwd(qkv_r, n_head, n_kv, D, scale):
 
     if A.native_supported(D, S):
         return A.fwd(qkv_r, n_head, n_kv, D, scale)
+    _library("attention_fwd", f"head dim {D} has no native kernel" if A.ENABLED else "B200_NATIVE_ATTENTION=0")
     q, k, v = _views(qkv_r, n_head, n_kv, D)
     o = _sdpa(q, k, v, scale)
     return o.reshape(B, S, n_head * D), torch.empty(0, device=qkv_r.device)
@@ -426,6 +484,7 @@ def _attention_bwd_library(do, qkv_r, n_head, n_kv, D, scale):
     """Backward through the library attention (recomputes its forward); used for head dims the native kernels do
     not cover."""
     B, S, W = qkv_r.shape
+    _library("attention_bwd", f"head dim {D} has no native kernel or the native backward is switched off")
     with torch.enable_grad():
         leaf = qkv_r.detach().requires_grad_(True)
         q, k, v = _views(leaf, n_head, n_kv, D)
@@ -446,6 +505,7 @@ def attention_bwd(do, qkv_r, o, lse, n_head, n_kv, D, scale):
 def attention_infer(q, k, v, scale, q_offset=0):
     """Inference attention: q [B,Sq,H,D] against cached k,v [B,Sk,Hk,D]; query i sits at position q_offset+i."""
     Sq, Sk = q.shape[1], k.shape[1]
+    _library("attention_infer", "eager HF model with a KV cache", strict=False)
     # the library attention is only ever given densely packed operands (a strided batch view of a static cache
     # made its kernel fault)
     if k.shape[0] > 1 and k.stride(0) != k.shape[1] * k.stride(1):

@@ -503,12 +503,13 @@ class _LinearCE(torch.autograd.Function):
     (the scheme of recpre/ops.py:1034-1040); backward only scales them by the incoming gradient."""
 
     @staticmethod
-    def forward(ctx, x, weight, labels, logit_scale, ignore_index, z_reg):
+    def forward(ctx, x, weight, labels, logit_scale, ignore_index, z_reg, telemetry=None):
         C = cuda_backend()
         x2 = x.reshape(-1, x.shape[-1])
         lab = labels.reshape(-1)
         need_grad = x.requires_grad or weight.requires_grad
-        loss, dx, dw = C.linear_ce(x2, _lp(weight), lab, logit_scale, ignore_index, z_reg, need_grad=need_grad)
+        loss, dx, dw = C.linear_ce(x2, _lp(weight), lab, logit_scale, ignore_index, z_reg, need_grad=need_grad,
+                                   telemetry=telemetry)
         ctx.weight = weight
         if need_grad:
             ctx.save_for_backward(dx, dw)
@@ -525,13 +526,17 @@ class _LinearCE(torch.autograd.Function):
                 torch.mul(dw, dloss.to(dw.dtype), out=weight.grad)
             else:
                 weight.grad.addcmul_(dw, dloss.to(dw.dtype))
-            return dx, None, None, None, None, None
-        return dx, (dw * dloss).to(weight.dtype), None, None, None, None
+            return dx, None, None, None, None, None, None
+        return dx, (dw * dloss).to(weight.dtype), None, None, None, None, None
 
 
-def linear_cross_entropy(x, weight, labels, logit_scale: float = 1.0, ignore_index: int = -100, z_reg: float = 0.0):
+def linear_cross_entropy(x, weight, labels, logit_scale: float = 1.0, ignore_index: int = -100, z_reg: float = 0.0,
+                         telemetry: torch.Tensor | None = None):
+    """Mean cross entropy of ``x W^T * logit_scale`` without materialising the logits.  ``telemetry`` (CUDA path; four
+    fp32 zeros) receives the sums over valid rows of the maximal logit, the entropy of the prediction, the L2 norm of
+    the logits and lse^2 -- the head statistics the reference's fused head reports (recpre/ops.py:1120-1127)."""
     if x.is_cuda:
-        return _LinearCE.apply(x, weight, labels, logit_scale, ignore_index, z_reg)
+        return _LinearCE.apply(x, weight, labels, logit_scale, ignore_index, z_reg, telemetry)
     return ref.linear_cross_entropy(x, weight, labels, logit_scale, ignore_index, z_reg)
 
 

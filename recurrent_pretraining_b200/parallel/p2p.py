@@ -33,7 +33,7 @@ import torch
 import torch.distributed as dist
 
 from ..utils import nvtx
-from .segments import BUCKET_ORDER, GATHER_ORDER, GroupShards, bucket_of
+from .segments import MAX_BUCKETS, GroupShards, bucket_of, gather_key, readiness_key
 from .symm import SymmetricBuffer
 
 ALIGN = 128
@@ -153,20 +153,32 @@ class ShardedStepper:
         n_layer = getattr(getattr(model, "config", None), "n_layer", 0) if model is not None and \
             type(model).__name__ == "GPT" else 0
         # buckets -------------------------------------------------------------------------------
+        def assign(coarse: bool) -> dict:
+            found: dict = {}
+            for gi, g in enumerate(groups):
+                kind = GROUP_KINDS[gi] if gi < len(GROUP_KINDS) else "weight"
+                for t, (name, p) in enumerate(zip(g.names, g.params)):
+                    found.setdefault(bucket_of(name, kind, n_layer, coarse), []).append((gi, t, p))
+            return found
+
+        found = assign(False)
+        if len(found) > MAX_BUCKETS:          # very deep prelude / coda: one bucket for each of them
+            found = assign(True)
+        self.order = sorted(found, key=readiness_key)            # completion order of the gradients
+        self.gather_order = sorted(found, key=gather_key)        # order in which the forward pass needs the weights
         self.buckets: dict = {}
-        self.stat_base = []
-        base = 0
-        for gi, (g, plan) in enumerate(zip(groups, self.plans)):
-            self.stat_base.append(base)
-            kind = GROUP_KINDS[gi] if gi < len(GROUP_KINDS) else "weight"
-            for t, (name, p) in enumerate(zip(g.names, g.params)):
-                bname = bucket_of(name, kind, n_layer)
-                b = self.buckets.get(bname)
-                if b is None:
-                    b = self.buckets[bname] = _Bucket(bname, 1 + BUCKET_ORDER.index(bname))
+        for slot, bname in enumerate(self.order, start=1):
+            b = self.buckets[bname] = _Bucket(bname, slot)
+            for gi, t, p in found[bname]:
                 b.tensors.setdefault(gi, []).append(t)
                 b.params.append(p)
                 p._bucket = b
+        # a bucket fired by a hook shares the SMs with the backward pass of the layers before it and gets few CTAs; the
+        # buckets whose hook comes when (almost) nothing is left to run get the whole machine
+        self.full_width = set(self.order[-2:]) if len(self.order) > 1 else set(self.order)
+        self.stat_base, base = [], 0
+        for g in groups:
+            self.stat_base.append(base)
             base += len(g.params)
         self.n_stats = base
         for b in self.buckets.values():
@@ -196,7 +208,7 @@ class ShardedStepper:
         self.stat_ptrs = self.stats_buf.ptr_array()
         self.partials = [self.ctrl.tensor(torch.float32, 1, PARTIAL_OFF + 64 * i) for i in range(2)]
         self.partial_ptrs = [self.ctrl.ptr_array(PARTIAL_OFF + 64 * i) for i in range(2)]
-        self.slot_ptrs = [self.ctrl.ptr_array(SLOT_BYTES * s) for s in range(8)]
+        self.slot_ptrs = [self.ctrl.ptr_array(SLOT_BYTES * s) for s in range(MAX_BUCKETS + 2)]
         bufs = self.alloc.buffers
         self.grad_ptrs = [bufs[(i, "grad")].ptr_array() for i in range(len(self.groups))]
         self.shadow_ptrs = [bufs[(i, "shadow")].ptr_array() for i in range(len(self.groups))]
@@ -247,7 +259,7 @@ class ShardedStepper:
     def on_phase(self, name: str) -> None:
         """Called from a tensor hook during backward: the gradients of bucket ``name`` are complete on this rank."""
         if name in self.buckets:
-            self._fire(name, self.overlap_ctas)
+            self._fire(name, 0 if name in self.full_width else self.overlap_ctas)
 
     def _fix_unwritten(self, b: _Bucket) -> None:
         """Gradient buffers are not cleared between steps (the first contribution of a window stores); a tensor that
@@ -288,7 +300,7 @@ class ShardedStepper:
         # The "my gradients of this bucket are complete" signal is issued by the first CTA of the reduce-scatter kernel
         # itself, never by a launch of its own: a separate signal kernel can be starved by this GPU's own waiting
         # reduce-scatter CTAs while the peer waits for it (every rank then sits out the wait limit).  All ranks fire
-        # their buckets in the same order (hooks in graph order, the rest in BUCKET_ORDER), so waiting for the peers'
+        # their buckets in the same order (hooks in graph order, the rest in the same completion order), so waiting for the peers'
         # kernels of the same bucket to start cannot cycle.
         self.side.wait_event(ev)
         if self.tracing:
@@ -313,9 +325,8 @@ class ShardedStepper:
         if self.tracing and self.backend == "cuda" and "start" in self.trace:
             self.trace["backward_end"] = torch.cuda.Event(enable_timing=True)
             self.trace["backward_end"].record()
-        for name in BUCKET_ORDER:
-            if name in self.buckets:
-                self._fire(name, 0)
+        for name in self.order:
+            self._fire(name, 0)
         if self.backend == "cuda":
             self._step_cuda(optimizer, max_norm, grad_scale, do_update)
         else:
@@ -331,11 +342,9 @@ class ShardedStepper:
 
     # ------------------------------------------------------------------------------------------ cuda step
     def _launch_tables(self):
-        for name in BUCKET_ORDER:
-            b = self.buckets.get(name)
-            if b is not None:
-                for gi, tb in b.tables:
-                    yield gi, tb
+        for name in self.order:
+            for gi, tb in self.buckets[name].tables:
+                yield gi, tb
 
     def _step_cuda(self, optimizer, max_norm, grad_scale, do_update) -> None:
         K = self.K
@@ -404,10 +413,8 @@ class ShardedStepper:
         ev.record(main)
         self.gather_stream.wait_event(ev)
         st = C.c_void_p(self.gather_stream.cuda_stream)
-        for name in GATHER_ORDER:
-            b = self.buckets.get(name)
-            if b is None:
-                continue
+        for name in self.gather_order:
+            b = self.buckets[name]
             for gi, ids in b.tensors.items():
                 g, plan = self.groups[gi], self.plans[gi]
                 pull = []
@@ -436,9 +443,8 @@ class ShardedStepper:
         copies = [g.grad.clone() for g in self.groups]
         for c in copies:
             dist.all_reduce(c)
-        for name in BUCKET_ORDER:
-            if name in self.buckets:
-                self._fire(name, 0)
+        for name in self.order:
+            self._fire(name, 0)
         done = torch.cuda.Event()
         done.record(self.side)
         torch.cuda.current_stream().wait_event(done)

@@ -99,17 +99,20 @@ class GroupShards:
         return out
 
 
-def bucket_of(name: str, group_kind: str, n_layer: int = 0) -> str:
-    """Readiness bucket of a parameter.  The small fp32 group (norm scales, biases) always goes last: its gradients
-    pass through autograd's accumulation nodes, whose position in the backward order is not pinned down."""
+def bucket_of(name: str, group_kind: str, n_layer: int = 0, coarse: bool = False) -> str:
+    """Readiness bucket of a parameter: one per prelude block and per coda block (``coarse``: one for all of them), one
+    for the recurrent core with the adapter, ``upper`` for the top half of a plain GPT stack, ``last`` for the rest.
+    The small fp32 group (norm scales, biases) always goes last: its gradients pass through autograd's accumulation
+    nodes, whose position in the backward order is not pinned down."""
     if group_kind == "norm":
         return "last"
-    if ".coda." in name:
-        return "coda"
+    for part in ("coda", "prelude"):
+        tag = f".{part}."
+        if tag in name:
+            idx = name.split(tag)[1].split(".")[0]
+            return f"{part}.{0 if coarse or not idx.isdigit() else int(idx)}"
     if ".core_block." in name or ".adapter." in name or "step_embedding" in name:
         return "core"
-    if ".prelude." in name:
-        return "prelude"
     if ".h." in name and n_layer > 1:
         try:
             idx = int(name.split(".h.")[1].split(".")[0])
@@ -119,5 +122,22 @@ def bucket_of(name: str, group_kind: str, n_layer: int = 0) -> str:
     return "last"
 
 
-BUCKET_ORDER = ("coda", "upper", "core", "prelude", "last")       # order in which gradients complete
-GATHER_ORDER = ("last", "prelude", "upper", "core", "coda")        # order in which the forward pass needs weights
+def _split(bucket: str) -> tuple[str, int]:
+    head, _, idx = bucket.partition(".")
+    return head, int(idx) if idx.isdigit() else 0
+
+
+def readiness_key(bucket: str) -> tuple:
+    """Sort key: the order in which the buckets' gradients complete during backward (the coda's last block first, then
+    down to its first block, the core, the prelude from its last block down, and the rest at the very end)."""
+    head, idx = _split(bucket)
+    return ({"coda": 0, "upper": 1, "core": 2, "prelude": 3}.get(head, 9), -idx)
+
+
+def gather_key(bucket: str) -> tuple:
+    """Sort key: the order in which the forward pass needs the buckets' weights."""
+    head, idx = _split(bucket)
+    return ({"last": 0, "prelude": 1, "upper": 2, "core": 3, "coda": 4}.get(head, 5), idx)
+
+
+MAX_BUCKETS = 30

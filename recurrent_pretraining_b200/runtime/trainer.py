@@ -92,7 +92,8 @@ def _make_source(entry, cfg, fabric, split_dir: str, seed: int):
     if entry.type == "hfds":
         sig = entry.data_signature or cfg.data_signature
         return TextRows(os.path.join(folder, entry.prefix), sig, fabric.world_size, fabric.global_rank,
-                        shuffle=cfg.shuffle_blocks, seed=seed, data_id=entry.prefix)
+                        shuffle=cfg.shuffle_blocks, seed=seed, data_id=entry.prefix,
+                        repetitions=getattr(entry, "repetitions", None), return_data_id=entry.return_data_id)
     raise ValueError(f"Unsupported dataset type {entry.type}")
 
 
@@ -220,6 +221,8 @@ def startup(cfg, fabric: Fabric) -> dict:
             engine.optimizer_step = state["optimizer_step"]
             fabric.print(f"Resumed from {path} at micro-batch step {state['microbatch_step']}")
     fabric.barrier()
+    path = "fused flat-buffer kernels" if engine.mode == "fused" else "torch optimizer on unflattened parameters"
+    fabric.print(f"optimizer {cfg.optimizer} runs on the {path}; gradient sync: {fabric.grad_sync}")
     fabric.print(f"start-up took {time.time() - t0:.1f}s; {sum(p.numel() for p in model.parameters()):,} parameters")
     return state
 

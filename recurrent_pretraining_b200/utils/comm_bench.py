@@ -7,8 +7,8 @@ Default sweep (bf16 buckets drawn N(0, 1e-3^2)): for every size the one-launch f
 ``parallel/collectives.py`` -- all-reduce (bf16 in, fp32 cast + 1/N scale + squared-norm partial, result on every rank),
 reduce-scatter, all-gather, and reduce-scatter + clipped AdamW + bf16 parameter push -- each beside the NCCL call that
 the reference's path would make (``all_reduce`` on bf16 and on fp32, ``reduce_scatter_tensor``,
-``all_gather_into_tensor``).  A row's roofline time is the bytes that must cross one GPU's NVLink in the busier
-direction divided by the link bandwidth; fractions are given against the measured 770 GB/s per direction and against
+``all_gather_into_tensor``).  A row's roofline time is the bytes that must cross one GPU's NVLink in one direction
+(its own traffic plus what it serves to its peers) divided by the link bandwidth; fractions are given against the measured 770 GB/s per direction and against
 the nominal 900 GB/s.  ``--fp32`` adds the older fp32 two-shot sequence, ``--phases`` the per-phase CTA sweep, ``--ag``
 the all-gather fused into the GEMM.
 """
@@ -71,8 +71,10 @@ def bf16_sweep(fabric, sizes_mb) -> None:
         lo, hi = fc.my_slice(count)
         per = fc.slice_elems(count)
         rows = []
-        # (name, ours, nccl, bytes over this GPU's link in the busier direction)
-        ar_bytes = f * count * 4           # out: fp32 result of the slice to N-1 peers (in: f * count * 2)
+        # (name, ours, nccl, bytes over this GPU's link per direction).  Every direction carries both what this GPU
+        # asks for and what its peers ask of it: the all-reduce sends its fp32 slice results out (f * count * 4) while
+        # serving the peers' reads of its bf16 bucket (f * count * 2), and receives the mirror image.
+        ar_bytes = f * count * 6
         rows.append(("all_reduce bf16->fp32 (+scale, norm)", lambda: fc.all_reduce(count, 1.0 / N, one_shot=False),
                      lambda: dist.all_reduce(nccl_f32[:count]), ar_bytes, "nccl all_reduce fp32"))
         if nb <= 64 * 2**20:
@@ -98,7 +100,7 @@ def bf16_sweep(fabric, sizes_mb) -> None:
         rows.append(("reduce_scatter + clip + AdamW + bf16 push",
                      lambda: fc.reduce_scatter_adamw(count, p[:hi - lo], m[:hi - lo], v[:hi - lo], shadow, lr=4e-4,
                                                      step=2, scale=1.0 / N),
-                     nccl_update, f * nb, "nccl reduce_scatter fp32 + torch AdamW + all_gather bf16"))
+                     nccl_update, 2 * f * nb, "nccl reduce_scatter fp32 + torch AdamW + all_gather bf16"))
         for name, ours, theirs, link_bytes, nccl_name in rows:
             t_ours = _time(ours, dev)
             t_nccl = _time(theirs, dev)

@@ -262,3 +262,39 @@ def test_buffer_shuffled_parquet_covers_everything_and_resumes_exactly(tmp_path)
     a, b = make(num_processes=2, process_rank=0), make(num_processes=2, process_rank=1)
     assert not set(a.parquet_files) & set(b.parquet_files)
     assert sum(t.shape[0] for t in make().iter_batches(16)) == total
+
+
+def test_text_rows_are_dealt_over_ranks_and_workers_and_resume(tmp_path):
+    """The row-sharded text source: shard ``rank * workers + worker`` of ``ranks * workers`` takes every n-th row of the
+    (repeated) table, keeps only the signature's keys, and resumes at its saved row (recpre/huggingface_dataset.py:341-441)."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from torch.utils.data import DataLoader
+
+    from recurrent_pretraining_b200.data import HuggingfaceDataset, TextRows
+
+    assert HuggingfaceDataset is TextRows
+    rows = [{"text": f"row {i}", "extra": i} for i in range(23)]
+    pq.write_table(pa.Table.from_pylist(rows), tmp_path / "part.parquet")
+    sig = {"keys": ["text"], "format_fn": "pass_text"}
+    seen = []
+    for rank in range(2):
+        ds = TextRows(str(tmp_path), sig, num_processes=2, process_rank=rank, repetitions=2, data_id="d")
+        assert len(ds) == 23
+        got = list(ds)
+        assert all(set(r) == {"text", "data_signature", "data_id"} for r in got)
+        seen += [r["text"] for r in got]
+        assert ds.fingerprint is not None and ds.index_range[0] == rank
+    assert sorted(seen) == sorted([f"row {i}" for i in range(23)] * 2)          # two repetitions, nothing lost
+    # with loader workers the table is dealt over ranks * workers shards
+    ds = TextRows(rows, sig, num_processes=2, process_rank=1)
+    via_workers = [r for batch in DataLoader(ds, batch_size=None, num_workers=2) for r in [batch["text"]]]
+    assert sorted(via_workers) == sorted(f"row {i}" for i in range(23) if i % 4 in (2, 3))
+    # resume
+    a = TextRows(rows, sig, num_processes=2, process_rank=0)
+    it = iter(a)
+    head = [next(it)["text"] for _ in range(5)]
+    state = a.state_dict()
+    b = TextRows(rows, sig, num_processes=2, process_rank=0)
+    b.load_state_dict(state)
+    assert head + [r["text"] for r in b] == [f"row {i}" for i in range(0, 23, 2)]

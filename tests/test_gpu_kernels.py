@@ -223,6 +223,37 @@ def test_linear_ce(C):
     _close(dw, wl.grad, 5e-2, 2e-4)
 
 
+@pytest.mark.parametrize("T,E,V,chunk", [(300, 136, 1000, 128), (700, 264, 4096, 512), (1024, 528, 65536, 1024)])
+def test_fused_linear_ce_epilogue_form(C, T, E, V, chunk):
+    """Head GEMM with the online-softmax partials in its epilogue + the row kernel that merges them (bf16 logits only):
+    loss, z term, both gradients and the telemetry sums against the fp32 statement, and against the older fp32-logits
+    sequence."""
+    x, w = _rand(T, E), _rand(V, E, scale=0.2)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    tele = torch.zeros(4, device="cuda")
+    loss, dx, dw = C.linear_ce(x, w, labels, logit_scale=0.5, z_reg=1e-3, chunk_rows=chunk, telemetry=tele, fused=True)
+    loss, dx, dw = loss.clone(), dx.clone(), dw.clone()
+    old_loss, old_dx, old_dw = C.linear_ce(x, w, labels, logit_scale=0.5, z_reg=1e-3, chunk_rows=chunk, fused=False)
+    xl, wl = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    logits = (xl @ wl.T) * 0.5
+    valid = labels != -100
+    lse = torch.logsumexp(logits, -1)
+    want = torch.nn.functional.cross_entropy(logits, labels, ignore_index=-100) + 1e-3 * (lse[valid] ** 2).mean()
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-3 * max(1.0, abs(want.item()))
+    assert abs(loss.item() - old_loss.item()) < 2e-3 * max(1.0, abs(want.item()))
+    _close(dx, xl.grad, 5e-2, 3e-2 * float(xl.grad.abs().max()))
+    _close(dw, wl.grad, 5e-2, 3e-2 * float(wl.grad.abs().max()))
+    _close(dx, old_dx, 5e-2, 3e-2 * float(xl.grad.abs().max()))
+    lg = logits.detach()[valid]
+    p = torch.softmax(lg, -1)
+    ent = -(p * torch.log_softmax(lg, -1)).sum(-1)
+    want_t = torch.stack([lg.max(-1).values.sum(), ent.sum(), lg.norm(dim=-1).sum(), (lse.detach()[valid] ** 2).sum()])
+    assert torch.allclose(tele, want_t, rtol=2e-2, atol=1e-2 * float(want_t.abs().max())), (tele, want_t)
+    assert C.check_device_status() == 0
+
+
 def _packed_qkv(B, S, H, Hkv, D):
     return _rand(B, S, (H + 2 * Hkv) * D, scale=0.7)
 

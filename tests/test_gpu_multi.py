@@ -46,7 +46,8 @@ def test_p2p_sharded_step_matches_nccl_allreduce(mode):
     two-micro-batch accumulation window."""
     res = _run(mode)
     _check_parity(res)
-    assert res["overlap_fired"] == ["coda", "core", "last", "prelude"], res
+    kinds = sorted({b.split(".")[0] for b in res["overlap_fired"]})
+    assert kinds == ["coda", "core", "last", "prelude"], res
 
 
 @needs2
