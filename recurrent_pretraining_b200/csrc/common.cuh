@@ -24,6 +24,7 @@ enum ErrCode : int {
   ERR_WAIT_PEER_FLAG = 5,
   ERR_BAD_ARGS = 6,
   ERR_WAIT_ATTN = 7,
+  ERR_BAD_INDEX = 8,      // a token id or label outside its table (the access was skipped)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -361,14 +361,23 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
 }
 
 // out[t, :] = w[ids[t], :] * scale
+// An id outside [0, V) is recorded in the status word (ERR_BAD_INDEX) and its row reads as zero / is skipped: a bad token
+// id must not become a wild address.
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
-                                     __nv_bfloat16* __restrict__ out, size_t T, int E, float scale) {
+                                     __nv_bfloat16* __restrict__ out, size_t T, int E, float scale, long long V,
+                                     int* __restrict__ err) {
   const int vpr = E >> 3;
   const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (gid >= T * vpr) return;
   const size_t t = gid / vpr;
   const int c = static_cast<int>(gid % vpr);
-  const uint4 q = reinterpret_cast<const uint4*>(w + static_cast<size_t>(ids[t]) * E)[c];
+  const long long id = ids[t];
+  if (id < 0 || id >= V) {
+    if (err && c == 0) atomicCAS(err, 0, ERR_BAD_INDEX);
+    reinterpret_cast<uint4*>(out + t * E)[c] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4 q = reinterpret_cast<const uint4*>(w + static_cast<size_t>(id) * E)[c];
   const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
   uint32_t o[4];
 #pragma unroll
@@ -381,15 +390,21 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __
 
 // grad[ids[t], :] += dy[t, :] * scale   (fp32 atomics: a token id may repeat)
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
-                                     float* __restrict__ grad, size_t T, int E, float scale) {
+                                     float* __restrict__ grad, size_t T, int E, float scale, long long V,
+                                     int* __restrict__ err) {
   const int vpr = E >> 3;
   const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (gid >= T * vpr) return;
   const size_t t = gid / vpr;
   const int c = static_cast<int>(gid % vpr);
+  const long long id = ids[t];
+  if (id < 0 || id >= V) {
+    if (err && c == 0) atomicCAS(err, 0, ERR_BAD_INDEX);
+    return;
+  }
   const uint4 q = reinterpret_cast<const uint4*>(dy + t * E)[c];
   const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
-  float* dst = grad + static_cast<size_t>(ids[t]) * E + c * 8;
+  float* dst = grad + static_cast<size_t>(id) * E + c * 8;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float2 f = unpack_bf16x2(qs[j]);
@@ -539,21 +554,21 @@ B200_API int b200_swiglu_bwd(const void* dy, const void* h, void* dh, long long 
 }
 
 B200_API int b200_embedding_fwd(const long long* ids, const void* w, void* out, long long T, int E, float scale,
-                                void* stream) {
+                                long long V, int* err, void* stream) {
   if (E % 8) return -1;
   const size_t n = static_cast<size_t>(T) * (E / 8);
   embedding_fwd_kernel<<<blocks_for(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       ids, reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out), static_cast<size_t>(T), E,
-      scale);
+      scale, V, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 B200_API int b200_embedding_bwd(const long long* ids, const void* dy, float* grad, long long T, int E, float scale,
-                                void* stream) {
+                                long long V, int* err, void* stream) {
   if (E % 8) return -1;
   const size_t n = static_cast<size_t>(T) * (E / 8);
   embedding_bwd_kernel<<<blocks_for(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ids, reinterpret_cast<const __nv_bfloat16*>(dy), grad, static_cast<size_t>(T), E, scale);
+      ids, reinterpret_cast<const __nv_bfloat16*>(dy), grad, static_cast<size_t>(T), E, scale, V, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -249,7 +249,7 @@ class GatedMLP(nn.Module):
         if self.is_silu and self.fc.bias is None and x.is_cuda and not torch.is_grad_enabled() and FUSE_SWIGLU:
             return self.proj(ops.linear_swiglu(x, self.fc.weight))  # gate applied in the GEMM epilogue
         if self.is_silu and self.fc.bias is None and self.proj.bias is None and x.is_cuda and FUSE_SWIGLU \
-                and torch.is_grad_enabled():
+                and torch.is_grad_enabled() and type(self.proj) is Linear:   # a row-parallel proj reduces in its forward
             return ops.gated_mlp(x, self.fc.weight, self.proj.weight)   # both elementwise stages in GEMM epilogues
         h = self.fc(x)
         if self.is_silu:

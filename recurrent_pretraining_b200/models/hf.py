@@ -87,6 +87,15 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
         self.gradient_checkpointing = False
         self.post_init()
 
+    def _apply(self, fn, recurse=True):
+        """The rotary table stays fp32 whatever the model is cast to; device moves still apply."""
+        keep = self._buffers.get("freqs_cis")
+        out = super()._apply(fn, recurse)
+        cur = self._buffers.get("freqs_cis")
+        if keep is not None and cur is not None and cur.dtype != torch.float32:
+            self._buffers["freqs_cis"] = keep.to(device=cur.device, dtype=torch.float32)
+        return out
+
     # -- HF plumbing ---------------------------------------------------------------------------------
     def get_input_embeddings(self):
         return self.transformer.wte

@@ -63,6 +63,16 @@ class _LMBase(nn.Module):
             fn = self._ckpt_fn = checkpoint_fn(self.config.activation_checkpoint_impl)
         return fn
 
+    def _apply(self, fn, recurse=True):
+        """The rotary table stays fp32 whatever the module is cast to (``.bfloat16()`` would otherwise round cos / sin
+        to three digits); device moves still apply."""
+        keep = self._buffers.get("freqs_cis")
+        out = super()._apply(fn, recurse)
+        cur = self._buffers.get("freqs_cis")
+        if keep is not None and cur is not None and cur.dtype != torch.float32:
+            self._buffers["freqs_cis"] = keep.to(device=cur.device, dtype=torch.float32)
+        return out
+
     def _setup_rope(self, config) -> None:
         length = config.randomize_positions_from or config.block_size
         cos, sin = ref.rope_tables(config.head_size, length, config.rope_settings.rope_base,

@@ -49,8 +49,8 @@ _rope = _sig("b200_rope", [_vp] * 6 + [_i] * 6 + [_vp])
 _bias_grad = _sig("b200_bias_grad", [_vp, _vp, _i, _i, _i, _vp])
 _swiglu_fwd = _sig("b200_swiglu_fwd", [_vp, _vp, _ll, _i, _vp])
 _swiglu_bwd = _sig("b200_swiglu_bwd", [_vp, _vp, _vp, _ll, _i, _vp])
-_emb_fwd = _sig("b200_embedding_fwd", [_vp, _vp, _vp, _ll, _i, _f, _vp])
-_emb_bwd = _sig("b200_embedding_bwd", [_vp, _vp, _vp, _ll, _i, _f, _vp])
+_emb_fwd = _sig("b200_embedding_fwd", [_vp, _vp, _vp, _ll, _i, _f, _ll, _vp, _vp])
+_emb_bwd = _sig("b200_embedding_bwd", [_vp, _vp, _vp, _ll, _i, _f, _ll, _vp, _vp])
 _trunc_normal = _sig("b200_trunc_normal", [_vp, _ll, _f, _ull, _vp])
 _sumsq = _sig("b200_sumsq", [_vp, _ll, _vp, _vp])
 _adamw = _sig("b200_adamw", [_vp] * 5 + [_ll, _vp] + [_f] * 9 + [_i, _i, _vp])
@@ -181,7 +181,9 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_mode=OUT_BF16, a2=None, 
         ld_resid = resid.stride(0)
     if out_mode == OUT_BF16_ROPE:
         cos, sin, bias, S, D, width = rope
-        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[-1] * 2 == D
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape[-1] * 2 == D and cos.shape[0] >= S and sin.shape == cos.shape, (cos.shape, S, D)
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() >= width)
         _set_rope(_ptr(cos), _ptr(sin), _ptr(bias), int(S), int(D), int(width))
     if out_mode == OUT_BF16_LSE:
         part, tgt, labels, scale = lse     # [M, ceil(N / 256), 4] fp32, [M] fp32, [M] int64, logit scale
@@ -262,9 +264,16 @@ def rmsnorm_bwd(dy, x, weight, rstd, need_dw=True):
 # ------------------------------------------------------------------------------------------------
 # rope / attention / swiglu
 # ------------------------------------------------------------------------------------------------
+def _table32(t):
+    """The rotary kernels read fp32 tables; a table that followed its module into bf16 is converted (never reinterpreted)."""
+    return t if t.dtype == torch.float32 and t.is_contiguous() else t.float().contiguous()
+
+
 def rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, pos_ids=None):
     """Packed [B,S,(H+2Hkv)*D] -> packed, q and k biased + rotated, v copied."""
     B, S, W = qkv.shape
+    cos, sin = _table32(cos), _table32(sin)
+    assert cos.shape[-1] * 2 == head_dim and (pos_ids is not None or cos.shape[0] >= S), (cos.shape, S, head_dim)
     qkv = qkv.contiguous()
     out = torch.empty_like(qkv)
     bias = None if qk_bias is None else qk_bias.detach().float().contiguous()
@@ -276,6 +285,8 @@ def rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, pos_ids=None):
 def rope_bwd_(dqkv, cos, sin, n_head, n_kv, head_dim, has_bias, pos_ids=None):
     """In-place inverse rotation of the q/k parts of a packed gradient; returns (dqkv, dbias or None)."""
     B, S, W = dqkv.shape
+    cos, sin = _table32(cos), _table32(sin)
+    assert cos.shape[-1] * 2 == head_dim and (pos_ids is not None or cos.shape[0] >= S), (cos.shape, S, head_dim)
     _check(_rope(_ptr(dqkv), _ptr(dqkv), 0, _ptr(cos), _ptr(sin), _ptr(pos_ids), B * S, S, n_head, n_kv, head_dim, 1,
                  _stream()), "rope_bwd")
     dbias = None
@@ -327,15 +338,17 @@ def embedding_fwd(ids, w_bf16, scale):
     ids = ids.contiguous()
     E = w_bf16.shape[1]
     out = torch.empty(*ids.shape, E, dtype=BF16, device=w_bf16.device)
-    _check(_emb_fwd(_ptr(ids), _ptr(w_bf16), _ptr(out), ids.numel(), E, float(scale), _stream()), "embedding_fwd")
+    _check(_emb_fwd(_ptr(ids), _ptr(w_bf16), _ptr(out), ids.numel(), E, float(scale), w_bf16.shape[0],
+                    _ptr(err_word(w_bf16.device)), _stream()), "embedding_fwd")
     return out
 
 
 def embedding_bwd(dy, ids, grad_f32, scale):
     E = grad_f32.shape[1]
     assert grad_f32.dtype == torch.float32 and grad_f32.is_contiguous()
-    _check(_emb_bwd(_ptr(ids.contiguous()), _ptr(dy), _ptr(grad_f32), ids.numel(), E, float(scale), _stream()),
-           "embedding_bwd")
+    ids = ids.contiguous()
+    _check(_emb_bwd(_ptr(ids), _ptr(dy), _ptr(grad_f32), ids.numel(), E, float(scale), grad_f32.shape[0],
+                    _ptr(err_word(grad_f32.device)), _stream()), "embedding_bwd")
 
 
 def trunc_normal(shape, std, seed, dtype=BF16, device=None):

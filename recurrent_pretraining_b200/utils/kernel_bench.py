@@ -1,5 +1,5 @@
 """Micro-benchmarks of the hot kernels on the flagship shapes, reported against the library GEMM and the measured
-machine peaks.  ``python -m recurrent_pretraining_b200.utils.kernel_bench [gemm|swiglu|norm|attn|skinny [shape [batch]]|all]``.
+machine peaks.  ``python -m recurrent_pretraining_b200.utils.kernel_bench [gemm|swiglu|norm|attn|ce|skinny [shape [batch]]|all]``.
 
 Timing: CUDA events on the launching stream after warm-up, L2 flushed between timed launches by writing a 256 MB
 buffer, median of the repeats.
@@ -105,6 +105,37 @@ def bench_swiglu(M=4096, E=5280, I=17920):
     fl = 2.0 * M * 2 * I * E
     print(json.dumps({"kernel": "gate-up GEMM + SwiGLU", "fused_ms": round(t_fused, 3),
                       "fused_tflops": round(fl / t_fused / 1e9, 1), "gemm_then_swiglu_ms": round(t_pair, 3)}))
+    # training forms: the forward also stores the bf16 pre-activation; the down projection's input-gradient GEMM applies
+    # the gate's derivative in its epilogue
+    t_save = time_fn(lambda: C.linear_swiglu_save(x, w), flush=flush)
+    print(json.dumps({"kernel": "gate-up GEMM + SwiGLU + pre-activation store (training forward)",
+                      "fused_ms": round(t_save, 3), "fused_tflops": round(fl / t_save / 1e9, 1),
+                      "gemm_then_swiglu_ms": round(t_pair, 3)}))
+    y, h = C.linear_swiglu_save(x, w)
+    wp = (torch.randn(E, I, device="cuda") * 0.02).bfloat16()
+    dy = torch.randn(M, E, device="cuda").bfloat16()
+    t_d = time_fn(lambda: C.dswiglu_dgrad(dy, wp, h), flush=flush)
+    t_dpair = time_fn(lambda: C.swiglu_bwd(C.gemm_nn(dy, wp), h), flush=flush)
+    fl2 = 2.0 * M * I * E
+    print(json.dumps({"kernel": "down-proj dgrad GEMM + dSwiGLU epilogue", "fused_ms": round(t_d, 3),
+                      "fused_tflops": round(fl2 / t_d / 1e9, 1), "gemm_then_swiglu_bwd_ms": round(t_dpair, 3)}))
+    assert C.check_device_status() == 0
+
+
+def bench_ce(T=4096, E=5280, V=65536):
+    """Head: linear + cross-entropy with the softmax partials from the head GEMM's epilogue (bf16 logits chunk) against
+    the older form (fp32 logits chunk + row kernel).  Both include the two gradient GEMMs."""
+    from ..ops import cuda as C
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    x = torch.randn(T, E, device="cuda").bfloat16()
+    w = (torch.randn(V, E, device="cuda") * 0.02).bfloat16()
+    lab = torch.randint(0, V, (T,), device="cuda")
+    fl = 3 * 2.0 * T * V * E
+    for tag, fused in (("epilogue partials + ce_finish", True), ("fp32 logits chunk + ce_rows", False)):
+        t = time_fn(lambda: C.linear_ce(x, w, lab, 1.0, -100, 0.0, need_grad=True, fused=fused), flush=flush)
+        print(json.dumps({"kernel": "linear + cross-entropy, forward + both gradients", "form": tag, "ms": round(t, 3),
+                          "tflops": round(fl / t / 1e9, 1)}))
     assert C.check_device_status() == 0
 
 
@@ -182,5 +213,7 @@ if __name__ == "__main__":
         bench_norm()
     if what in ("attn", "all"):
         bench_attn()
+    if what in ("ce", "all"):
+        bench_ce()
     if what in ("skinny", "all"):
         bench_skinny(only=sys.argv[2] if len(sys.argv) > 2 else None, B=int(sys.argv[3]) if len(sys.argv) > 3 else 1)

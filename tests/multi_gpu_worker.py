@@ -83,6 +83,49 @@ def main():
             print("RESULT " + json.dumps(res))
         dist.barrier()
         dist.destroy_process_group()
+    elif mode == "tensor_parallel":
+        # two-way tensor parallel blocks on the CUDA kernels (NCCL all-reduces) against the unsharded model
+        from recurrent_pretraining_b200.parallel.tensor_parallel import tensor_parallelize
+
+        fabric = Fabric.from_env(grad_sync="flat")
+        dev, rank, tp = fabric.device, fabric.global_rank, fabric.world_size
+        torch.manual_seed(0)
+        cfg = ModelConfig.from_name("smoke-raven-96", n_embd=384, num_attention_heads=4, num_key_value_heads=4, intermediate_size=1024)
+        full = cfg.construct_model()
+        sharded = tensor_parallelize(copy.deepcopy(full))
+        full, sharded = full.to(dev).bfloat16(), sharded.to(dev).bfloat16()
+        ids = torch.randint(0, cfg.padded_vocab_size, (2, 129), generator=torch.Generator().manual_seed(5)).to(dev)
+        state = (torch.randn(2, 128, cfg.n_embd, generator=torch.Generator().manual_seed(6)) * 0.6).to(dev).bfloat16()
+        pair = torch.tensor([1, 2])
+        a = full(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair, input_states=state)["loss"]
+        b = sharded(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair, input_states=state)["loss"]
+        a.backward()
+        b.backward()
+        torch.cuda.synchronize()
+        fp, sp = dict(full.named_parameters()), dict(sharded.named_parameters())
+
+        def rel(x, y):
+            return ((x.float() - y.float()).norm() / (y.float().norm() + 1e-12)).item()
+
+        name = "transformer.core_block.0.attn.Wqkv.weight"
+        H, D, E = cfg.n_head, cfg.n_embd // cfg.n_head, cfg.n_embd
+        h = H // tp
+        want = torch.cat([fp[name].grad[sec * H * D:(sec + 1) * H * D].view(H, D, E)[rank * h:(rank + 1) * h]
+                          .reshape(h * D, E) for sec in range(3)], 0)
+        name2 = "transformer.core_block.1.mlp.proj.weight"
+        i = cfg.intermediate_size // tp
+        res = {"loss_full": a.item(), "loss_tp": b.item(), "g_qkv": rel(sp[name].grad, want),
+               "g_proj": rel(sp[name2].grad, fp[name2].grad[:, rank * i:(rank + 1) * i]),
+               "g_norm": rel(sp["transformer.ln_f.weight"].grad, fp["transformer.ln_f.weight"].grad),
+               "g_emb": rel(sp["transformer.wte.weight"].grad, fp["transformer.wte.weight"].grad),
+               "status": K.check_device_status()}
+        worst = torch.tensor([res["g_qkv"], res["g_proj"], res["g_norm"], res["g_emb"]], device=dev)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        res["g_qkv"], res["g_proj"], res["g_norm"], res["g_emb"] = worst.tolist()
+        if rank == 0:
+            print("RESULT " + json.dumps(res))
+        dist.barrier()
+        dist.destroy_process_group()
     elif mode == "collectives":
         # one-launch fused collectives on bf16 buckets against torch sums
         from recurrent_pretraining_b200.parallel.collectives import FusedCollectives

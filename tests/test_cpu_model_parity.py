@@ -189,3 +189,18 @@ def test_embed_step_and_noise_schedules():
                     num_steps_pair=torch.tensor([1, 1]))
         out["loss"].backward()
         assert torch.isfinite(out["loss"])
+
+
+def test_rotary_table_stays_fp32_under_dtype_casts():
+    """``model.bfloat16()`` casts parameters but must leave the fp32 cos / sin table alone: the rotary kernels read fp32,
+    and bf16 would round the angles of late positions to three digits."""
+    from recurrent_pretraining_b200.config import ModelConfig
+
+    cfg = ModelConfig.from_name("tiny-raven-cpu")
+    model = cfg.construct_model()
+    before = model.freqs_cis.clone()
+    model = model.bfloat16()
+    assert model.transformer.wte.weight.dtype == torch.bfloat16
+    assert model.freqs_cis.dtype == torch.float32 and torch.equal(model.freqs_cis, before)
+    cos, sin = model._rope(8, None)
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32

@@ -268,7 +268,7 @@ def _attention_reference(qkv, H, Hkv, D, scale):
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
-                                         (1, 1024, 2, 2, 96)])
+                                         (1, 1024, 2, 2, 96), (2, 128, 5, 5, 96), (1, 4096, 3, 3, 96)])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_flash_attention_forward(C, B, S, H, Hkv, D, variant):
     from recurrent_pretraining_b200.ops import attention as A
@@ -292,7 +292,7 @@ def test_flash_attention_forward(C, B, S, H, Hkv, D, variant):
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 256, 5, 5, 96), (1, 200, 3, 3, 64), (1, 512, 2, 2, 128), (1, 384, 4, 2, 96),
-                                         (1, 1024, 2, 2, 96)])
+                                         (1, 1024, 2, 2, 96), (2, 128, 5, 5, 96), (1, 4096, 3, 3, 96)])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_flash_attention_backward(C, B, S, H, Hkv, D, variant):
     from recurrent_pretraining_b200.ops import attention as A

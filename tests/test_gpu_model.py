@@ -34,13 +34,15 @@ def test_loss_and_grads_match_fp32_reference(name):
                       input_states=state.cuda().bfloat16())
     out_g["loss"].backward()
     torch.cuda.synchronize()
-    assert abs(out_g["loss"].item() - out_c["loss"].item()) < 0.03 * abs(out_c["loss"].item())
+    # measured on B200: loss within 4e-5 relative, worst per-parameter gradient error 1.4 % (bf16 activations against the
+    # fp32 statement of the model)
+    assert abs(out_g["loss"].item() - out_c["loss"].item()) < 0.002 * abs(out_c["loss"].item())
     ref = dict(cpu_model.named_parameters())
     worst = {}
     for n, p in gpu_model.named_parameters():
         err = _rel(p.grad, ref[n].grad)
         worst[n] = err
-    bad = {n: e for n, e in worst.items() if e > 0.08}
+    bad = {n: e for n, e in worst.items() if e > 0.03}
     assert not bad, f"gradient mismatch: {sorted(bad.items(), key=lambda kv: -kv[1])[:8]}"
     assert eng.optimizer is not None
 

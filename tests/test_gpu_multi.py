@@ -96,3 +96,14 @@ def test_fused_one_launch_collectives_on_bf16_buckets():
         assert case["norm_oneshot0"] < 1e-4 and case["norm_oneshot1"] < 1e-4, (count, case)
         assert case["all_gather"] == 0.0, (count, case)
         assert case["adamw_gnorm"] < 1e-4 and case["adamw_master"] < 1e-5 and case["adamw_shadow"] < 2e-2, (count, case)
+
+
+@needs2
+def test_tensor_parallel_blocks_on_the_cuda_kernels():
+    """Two-way tensor parallelism (heads and MLP channels split, NCCL all-reduces) on the bf16 CUDA path: loss and
+    gradient shards agree with the unsharded model on the same kernels."""
+    res = _run("tensor_parallel", nproc=2, port=29655)
+    assert res["status"] == 0, res
+    assert abs(res["loss_tp"] - res["loss_full"]) < 5e-3 * abs(res["loss_full"]), res
+    for k in ("g_qkv", "g_proj", "g_norm", "g_emb"):
+        assert res[k] < 3e-2, res

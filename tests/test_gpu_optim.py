@@ -82,4 +82,12 @@ def test_table_update_equals_plain_adamw_kernel():
     torch.cuda.synchronize()
     assert torch.allclose(ga.master, gb.master, rtol=1e-6, atol=1e-8)
     assert torch.equal(ga.shadow, gb.shadow)
-    assert torch.allclose(ga.state["v"], gb.state["v"], rtol=1e-5, atol=1e-10)   # the two kernels contract FMAs differently
+    # the table kernel keeps its state packed per tensor (no alignment gaps); compare tensor by tensor
+    from recurrent_pretraining_b200.parallel.segments import GroupShards
+
+    plan = GroupShards.plan(gb, 1)
+    for off, so, n in zip(plan.offs, plan.state_offsets(0), plan.numels):
+        for key in ("m", "v"):
+            a, b = ga.state[key][off:off + n], gb.state[key][so:so + n]
+            # m sums signed terms (cancellation: absolute bound at its 1e-3 scale); v is a sum of squares
+            assert torch.allclose(a, b, rtol=1e-4, atol=1e-8 if key == "m" else 1e-12), (key, (a - b).abs().max().item())
