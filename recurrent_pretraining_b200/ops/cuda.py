@@ -228,6 +228,7 @@ def _w32(w):
 
 def rmsnorm_fwd(x, weight, eps):
     M, E = x.shape
+    assert x.dtype == BF16, x.dtype
     x = x.contiguous()
     y = torch.empty_like(x)
     rstd = torch.empty(M, dtype=torch.float32, device=x.device)
@@ -238,6 +239,7 @@ def rmsnorm_fwd(x, weight, eps):
 
 def add_rmsnorm_fwd(a, x, weight, eps):
     M, E = x.shape
+    assert x.dtype == BF16 and a.dtype == BF16 and a.shape == x.shape, (a.dtype, x.dtype, a.shape, x.shape)
     a, x = a.contiguous(), x.contiguous()
     y, s = torch.empty_like(x), torch.empty_like(x)
     rstd = torch.empty(M, dtype=torch.float32, device=x.device)
@@ -248,6 +250,8 @@ def add_rmsnorm_fwd(a, x, weight, eps):
 
 def rmsnorm_bwd(dy, x, weight, rstd, need_dw=True):
     M, E = x.shape
+    assert dy.dtype == BF16 and x.dtype == BF16 and x.is_contiguous() and rstd.dtype == torch.float32 \
+        and rstd.numel() == M and dy.shape == x.shape, (dy.dtype, x.dtype, rstd.dtype, dy.shape, x.shape)
     dy = dy.contiguous()
     dx = torch.empty_like(x)
     w = _w32(weight)
@@ -272,6 +276,7 @@ def _table32(t):
 def rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, pos_ids=None):
     """Packed [B,S,(H+2Hkv)*D] -> packed, q and k biased + rotated, v copied."""
     B, S, W = qkv.shape
+    assert qkv.dtype == BF16 and W == (n_head + 2 * n_kv) * head_dim, (qkv.dtype, qkv.shape)
     cos, sin = _table32(cos), _table32(sin)
     assert cos.shape[-1] * 2 == head_dim and (pos_ids is not None or cos.shape[0] >= S), (cos.shape, S, head_dim)
     qkv = qkv.contiguous()
@@ -285,6 +290,7 @@ def rope_fwd(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim, pos_ids=None):
 def rope_bwd_(dqkv, cos, sin, n_head, n_kv, head_dim, has_bias, pos_ids=None):
     """In-place inverse rotation of the q/k parts of a packed gradient; returns (dqkv, dbias or None)."""
     B, S, W = dqkv.shape
+    assert dqkv.dtype == BF16 and dqkv.is_contiguous() and W == (n_head + 2 * n_kv) * head_dim, (dqkv.dtype, dqkv.shape)
     cos, sin = _table32(cos), _table32(sin)
     assert cos.shape[-1] * 2 == head_dim and (pos_ids is not None or cos.shape[0] >= S), (cos.shape, S, head_dim)
     _check(_rope(_ptr(dqkv), _ptr(dqkv), 0, _ptr(cos), _ptr(sin), _ptr(pos_ids), B * S, S, n_head, n_kv, head_dim, 1,
@@ -335,6 +341,7 @@ def swiglu_bwd(dy, h):
 # embedding / state init
 # ------------------------------------------------------------------------------------------------
 def embedding_fwd(ids, w_bf16, scale):
+    assert ids.dtype == torch.int64 and w_bf16.dtype == BF16 and w_bf16.is_contiguous(), (ids.dtype, w_bf16.dtype)
     ids = ids.contiguous()
     E = w_bf16.shape[1]
     out = torch.empty(*ids.shape, E, dtype=BF16, device=w_bf16.device)
@@ -346,6 +353,7 @@ def embedding_fwd(ids, w_bf16, scale):
 def embedding_bwd(dy, ids, grad_f32, scale):
     E = grad_f32.shape[1]
     assert grad_f32.dtype == torch.float32 and grad_f32.is_contiguous()
+    assert ids.dtype == torch.int64 and dy.dtype == BF16 and dy.is_contiguous() and dy.numel() == ids.numel() * E
     ids = ids.contiguous()
     _check(_emb_bwd(_ptr(ids), _ptr(dy), _ptr(grad_f32), ids.numel(), E, float(scale), grad_f32.shape[0],
                     _ptr(err_word(grad_f32.device)), _stream()), "embedding_bwd")
@@ -405,6 +413,8 @@ def linear_ce(x, w, labels, logit_scale=1.0, ignore_index=-100, z_reg=0.0, need_
     T, E = x.shape
     V = w.shape[0]
     dev = x.device
+    assert x.dtype == BF16 and w.dtype == BF16 and x.is_contiguous() and w.is_contiguous() and w.shape[1] == E
+    assert labels.dtype == torch.int64 and labels.numel() == T, (labels.dtype, labels.shape, T)
     labels = labels.contiguous()
     loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
     n_valid = (labels != ignore_index).sum().to(torch.float32).reshape(1)

@@ -46,6 +46,23 @@ def main():
     print(f"total kernel time {total / 1e3:.1f} ms")
     for e in rows[:40]:
         print(f"{e.device_time_total / 1e3:9.2f} ms {100 * e.device_time_total / total:5.1f}%  x{e.count:5d}  {e.key[:110]}")
+    # idle time between consecutive kernels: where the device waited for the host
+    kern = sorted((e for e in prof.events() if e.device_type.name == "CUDA" and e.device_time_total > 0),
+                  key=lambda e: e.time_range.start)
+    if kern:
+        span = (kern[-1].time_range.end - kern[0].time_range.start) / 1e3
+        gaps = []
+        end = kern[0].time_range.end
+        prev = kern[0]
+        for e in kern[1:]:
+            if e.time_range.start > end:
+                gaps.append(((e.time_range.start - end) / 1e3, prev.name[:60], e.name[:60]))
+            if e.time_range.end > end:
+                end, prev = e.time_range.end, e
+        idle = sum(g[0] for g in gaps)
+        print(f"first-to-last kernel span {span:.1f} ms, idle inside it {idle:.2f} ms in {len(gaps)} gaps")
+        for g in sorted(gaps, reverse=True)[:8]:
+            print(f"  gap {g[0]:7.3f} ms after {g[1]} before {g[2]}")
 
 
 if __name__ == "__main__":
