@@ -230,6 +230,8 @@ struct OptArgs {
   float max_norm, grad_scale;
   int atan2_mode, update_clip, state_init, zero_grad;
   int n_push, push_master, master_sharded, n_ranks;
+  int max_ctas;                         // 0: as many CTAs as the work fills; else a cap (an update that runs beside the
+                                        // next step's forward pass leaves the SMs to its GEMMs)
 };
 
 __device__ __forceinline__ float clip_scale(const float* gnorm_sq, const OptArgs& a, bool& skip) {
@@ -466,7 +468,7 @@ B200_API int b200_ag_table(void* const* buf_ptrs, int rank, int N, const void* t
 
 struct OptHost {
   float lr, beta1, beta2, eps, decay, bc1, bc2, max_norm, grad_scale;
-  int atan2_mode, update_clip, state_init, zero_grad, n_push, push_master, master_sharded, n_ranks;
+  int atan2_mode, update_clip, state_init, zero_grad, n_push, push_master, master_sharded, n_ranks, max_ctas;
 };
 
 B200_API int b200_opt_stats(const float* g, const float* v, const void* table, int rank, const float* gnorm_sq,
@@ -491,7 +493,7 @@ B200_API int b200_opt_table(float* p, float* g, float* m, float* v, void* const*
   if (a.n_push > MAX_RANKS_T || a.n_ranks > MAX_RANKS_T) return -1;
   const long long nvec = owned_total(tb, rank) >> 2;
   if (nvec == 0) return 0;
-  const int grid = grid_cap(nvec, 256, 148 * 8);
+  const int grid = grid_cap(nvec, 256, a.max_ctas > 0 ? a.max_ctas : 148 * 8);
   opt_tab_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       p, g, m, v, mk(shadow_ptrs, a.n_push), mk(master_ptrs, a.n_push), mk(stat_ptrs, a.n_ranks), *tb, rank, gnorm_sq, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -43,6 +43,15 @@ class _LMBase(nn.Module):
     # during backward as soon as the gradient of a phase-boundary tensor exists, i.e. when every layer after that
     # boundary has finished its backward pass and its weight gradients are complete (parallel/p2p.py).
     _phase_cb = None
+    # Set by the data-parallel stepper when part of the previous optimizer update still runs beside this forward pass:
+    # ``cb(name)`` is called before the first use of the weights of phase ``name`` ("core", "coda") and makes the
+    # current stream wait for that part of the update (parallel/p2p.py: on_forward).
+    _fwd_cb = None
+
+    def _fwd_point(self, name: str) -> None:
+        cb = self._fwd_cb
+        if cb is not None:
+            cb(name)
 
     def _phase(self, t: torch.Tensor, name: str) -> torch.Tensor:
         cb = self._phase_cb
@@ -307,10 +316,12 @@ class RecurrentGPT(_LMBase):
                 e = block(e, rope, attention_mask)
             self._phase(e, "core")       # gradient of the prelude output: all recurrences and the adapter are done
         with nvtx.range("recurrence"):
+            self._fwd_point("core")
             x, n, k, xk = self.iterate_forward(e, rope, attention_mask, num_steps_pair, input_states)
         x_rec = x
         in_coda = self.gradient_checkpointing and "in-coda" in cfg.activation_checkpoint_impl
         with nvtx.range("coda"):
+            self._fwd_point("coda")
             for i, block in enumerate(self.transformer.coda):
                 self._phase(x, f"coda.{i}")       # gradient of block i's input: coda blocks i.. have gone backward
                 if in_coda and torch.is_grad_enabled():

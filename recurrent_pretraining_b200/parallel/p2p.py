@@ -47,7 +47,7 @@ class OptArgsC(C.Structure):
     _fields_ = [(n, C.c_float) for n in ("lr", "beta1", "beta2", "eps", "decay", "bc1", "bc2", "max_norm",
                                          "grad_scale")] + \
                [(n, C.c_int) for n in ("atan2_mode", "update_clip", "state_init", "zero_grad", "n_push", "push_master",
-                                       "master_sharded", "n_ranks")]
+                                       "master_sharded", "n_ranks", "max_ctas")]
 
 
 def shard_range(numel: int, rank: int, world: int) -> tuple[int, int]:
@@ -73,7 +73,7 @@ class P2PAllocator:
 
 
 def _opt_args(opt, h, *, max_norm, grad_scale, first_update, n_push, push_master, master_sharded, n_ranks,
-              zero_grad=False) -> OptArgsC:
+              zero_grad=False, max_ctas=0) -> OptArgsC:
     b1, b2 = h["betas"]
     t = max(opt.step_count, 1)
     a = OptArgsC()
@@ -85,6 +85,7 @@ def _opt_args(opt, h, *, max_norm, grad_scale, first_update, n_push, push_master
     a.state_init = int(opt.running_init and first_update)
     a.zero_grad, a.n_push, a.push_master = int(zero_grad), n_push, int(push_master)
     a.master_sharded, a.n_ranks = int(master_sharded), n_ranks
+    a.max_ctas = int(max_ctas)
     return a
 
 
@@ -187,6 +188,19 @@ class ShardedStepper:
                     b.tables.append((gi, tb))
         self.master_sharded = [bool(getattr(g, "master_sharded", False)) for g in groups]
         self.dirty = False         # zero3: owners hold newer pieces than the local copies
+        # Deferred update (replicated-parameter mode): the weights of the recurrent core and of the coda are needed by
+        # the next forward pass only after the prelude, so their update + push runs on the side stream beside the next
+        # step's first layers instead of in the exposed tail of this step.  The forward pass waits at the model's
+        # "core" / "coda" points (``on_forward``); every other reader of parameters calls ``finish_deferred``.
+        self.defer = (os.environ.get("B200_DEFER_UPDATE", "1") == "1" and self.world > 1 and not zero3
+                      and self.backend == "cuda" and "core" in self.buckets
+                      and any(n.startswith("coda") for n in self.buckets))
+        # the core's update must be over when the prelude's forward pass is (a few ms): full width, its CTAs share the
+        # SMs with the prelude GEMMs; the coda's has the whole recurrence to hide in: few CTAs
+        self.defer_ctas = {"core": int(os.environ.get("B200_DEFER_CTAS_CORE", "0")),
+                           "coda": int(os.environ.get("B200_DEFER_CTAS_CODA", "32"))}
+        self.deferred_events: dict = {}
+        self.defer_epoch = 0
         if self.backend == "cuda":
             self._setup_cuda()
         if self.world > 1 and dist.is_initialized():
@@ -219,6 +233,25 @@ class ShardedStepper:
         self.gather_stream = torch.cuda.Stream(device=f.device)
         self.err = K.err_word(f.device)
 
+    def _side_barrier(self) -> None:
+        """Barrier of the deferred phase: its own flag slot and epoch counter, launched on the side stream."""
+        K = self.K
+        self.defer_epoch += 1
+        K._check(K.lib.b200_barrier_sum(self.slot_ptrs[MAX_BUCKETS + 1], self.rank, self.world,
+                                        C.c_uint(self.defer_epoch), self.timeout_ms, None, 0, None,
+                                        C.c_void_p(self.err.data_ptr()), C.c_void_p(self.side.cuda_stream)), "barrier")
+
+    def on_forward(self, name: str) -> None:
+        """Called by the model's forward pass before it touches the weights of phase ``name`` ("core", "coda")."""
+        ev = self.deferred_events.pop(name, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def finish_deferred(self) -> None:
+        """Every reader of parameters other than the model's forward pass: wait for the deferred updates."""
+        for name in list(self.deferred_events):
+            self.on_forward(name)
+
     def _barrier(self, sum_into=None, partial_index: int = 0) -> None:
         K = self.K
         self.epoch += 1
@@ -243,6 +276,9 @@ class ShardedStepper:
         for name, (a, b, ctas) in tr.get("buckets", {}).items():
             out["buckets"][name] = {"start": round(t0.elapsed_time(a), 2), "end": round(t0.elapsed_time(b), 2),
                                     "ctas": ctas or 296}
+        for name, (a, b, ctas) in tr.get("deferred", {}).items():   # update + push that ran beside the next forward
+            out.setdefault("deferred_update", {})[name] = {"start": round(t0.elapsed_time(a), 2),
+                                                           "end": round(t0.elapsed_time(b), 2), "ctas": ctas}
         return out
 
     def begin_step(self, model, accumulating: bool) -> None:
@@ -255,6 +291,9 @@ class ShardedStepper:
             self._launch_gathers()
         if model is not None:
             model._phase_cb = self.on_phase if (not accumulating and self.overlap and self.world > 1) else None
+            model._fwd_cb = self.on_forward if self.defer else None
+        elif self.defer:
+            self.finish_deferred()
 
     def on_phase(self, name: str) -> None:
         """Called from a tensor hook during backward: the gradients of bucket ``name`` are complete on this rank."""
@@ -379,16 +418,51 @@ class ShardedStepper:
                                                   C.c_void_p(self.stats.data_ptr()), st), "opt_stats")
                 if self.world > 1:
                     self._barrier()
-            for gi, tb in self._launch_tables():
-                g, a = self.groups[gi], args[gi]
+            def launch(gi, tb, a, stream):
+                g = self.groups[gi]
                 shadows = self.own_shadow_ptrs[gi] if a.n_push == 1 and self.world > 1 else self.shadow_ptrs[gi]
                 K._check(K.lib.b200_opt_table(
                     C.c_void_p(g.master.data_ptr()), C.c_void_p(g.grad.data_ptr()), C.c_void_p(g.state["m"].data_ptr()),
                     C.c_void_p(g.state["v"].data_ptr()), shadows, self.master_ptrs[gi] if a.push_master else None,
-                    self.stat_ptrs, C.byref(tb), self.rank, gn, C.byref(a), st), "opt_table")
+                    self.stat_ptrs, C.byref(tb), self.rank, gn, C.byref(a), stream), "opt_table")
+
+            later = {"core": [], "coda": []}
+            for name in self.order:
+                phase = name.split(".")[0]
+                for gi, tb in self.buckets[name].tables:
+                    if self.defer and phase in later and not args[gi].push_master:
+                        later[phase].append((gi, tb))
+                    else:
+                        launch(gi, tb, args[gi], st)
+            if self.defer and (later["core"] or later["coda"]):
+                self._launch_deferred(later, args, launch)
         if self.world > 1:
             self.partials[1 - pi].zero_()
             self._barrier()
+
+    def _launch_deferred(self, later: dict, args: list, launch) -> None:
+        """Update + push of the core and coda weights on the side stream, after everything the main stream has issued
+        so far (the norm is known, the immediate part of the update owns the link first).  Each phase ends with a
+        cross-rank barrier of its own and an event the next forward pass waits on."""
+        self.finish_deferred()                      # a step that came without a forward pass in between
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.side.wait_event(ev)
+        side = C.c_void_p(self.side.cuda_stream)
+        for phase in ("core", "coda"):
+            if self.tracing:
+                t0 = torch.cuda.Event(enable_timing=True)
+                t0.record(self.side)
+            for gi, tb in later[phase]:
+                a = OptArgsC.from_buffer_copy(args[gi])
+                a.max_ctas = self.defer_ctas[phase]
+                launch(gi, tb, a, side)
+            self._side_barrier()
+            done = torch.cuda.Event(enable_timing=self.tracing)
+            done.record(self.side)
+            self.deferred_events[phase] = done
+            if self.tracing:
+                self.trace.setdefault("deferred", {})[phase] = (t0, done, self.defer_ctas[phase])
 
     def _report_nonfinite(self, pi: int) -> None:
         """Debug aid (B200_DEBUG_NORM=1): which of this rank's reduced pieces are not finite."""
@@ -440,6 +514,7 @@ class ShardedStepper:
         """Diagnostic (collective): sums the gradients now in the local buffers twice -- NCCL all-reduce on copies and
         the bucket kernels in place -- and returns the largest relative difference over this rank's pieces."""
         assert self.backend == "cuda" and self.world > 1
+        self.finish_deferred()
         copies = [g.grad.clone() for g in self.groups]
         for c in copies:
             dist.all_reduce(c)
@@ -480,6 +555,7 @@ class ShardedStepper:
     def sync_parameters(self) -> None:
         """Make the local bf16 copies complete now (parameter-sharded mode; before validation, export or comparison).
         Every rank must call it at the same point: the owners' pieces must not change while peers read them."""
+        self.finish_deferred()
         if not (self.zero3 and self.dirty and self.backend == "cuda"):
             return
         self._launch_gathers()
@@ -565,6 +641,7 @@ class ShardedStepper:
     @torch.no_grad()
     def gather_master(self) -> None:
         """Make every rank's replicated fp32 master copies complete (owners broadcast their pieces)."""
+        self.finish_deferred()
         if self.world == 1 or not dist.is_initialized():
             return
         for gi, g in enumerate(self.groups):
