@@ -20,6 +20,7 @@ Optimizer state can be sharded: ``attach_plans`` gives every group a ``GroupShar
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -67,6 +68,8 @@ class FusedAdamW:
             g.state["m"] = torch.zeros(max(hi - lo, 4), dtype=torch.float32, device=dev)
             g.state["v"] = torch.zeros(max(hi - lo, 4), dtype=torch.float32, device=dev)
             g.state["range"] = (lo, hi)
+
+    defer_ranges = None
 
     def attach_plans(self, plans, rank: int, world: int) -> None:
         """Per-tensor sharding: this rank keeps the moments of its own piece of every tensor (``plans[i]`` is the
@@ -148,15 +151,29 @@ class FusedAdamW:
                     self.zero_grad()
                 return
             clip = min(1.0, max_norm / (gn + 1e-6)) if max_norm > 0 else 1.0
-        for g, h in zip(self.groups, self.param_groups):
+        later = []
+        for gi, (g, h) in enumerate(zip(self.groups, self.param_groups)):
             lr = float(h["lr"])
             b1, b2 = h["betas"]
             if on_gpu:
                 from ..ops import cuda as C
 
-                C.adamw_(g.master, g.grad, g.state["m"], g.state["v"], g.shadow, self.gnorm_sq, lr=lr, beta1=b1,
-                         beta2=b2, eps=h["eps"], wd=h["weight_decay"], step=self.step_count, max_norm=max_norm,
-                         grad_scale=grad_scale, zero_grad=zero_grad, atan2=self.atan2)
+                def run(lo, hi, g=g, h=h, lr=lr, b1=b1, b2=b2):
+                    sl = slice(lo, hi)
+                    C.adamw_(g.master[sl], g.grad[sl], g.state["m"][sl], g.state["v"][sl],
+                             g.shadow[sl] if g.shadow is not None else None, self.gnorm_sq, lr=lr, beta1=b1,
+                             beta2=b2, eps=h["eps"], wd=h["weight_decay"], step=self.step_count, max_norm=max_norm,
+                             grad_scale=grad_scale, zero_grad=zero_grad, atan2=self.atan2)
+
+                ranges = self.defer_ranges.get(gi) if self.defer_ranges else None
+                if not ranges:
+                    run(0, g.master.numel())
+                    continue
+                for phase, lo, hi in ranges:
+                    if phase is None:
+                        run(lo, hi)
+                    else:
+                        later.append((phase, lo, hi, run))
                 continue
             if self.plain_adamw and not self.atan2:
                 ref.adamw_step(g.master, g.grad, g.state["m"], g.state["v"], lr, b1, b2, h["eps"], h["weight_decay"],
@@ -174,6 +191,65 @@ class FusedAdamW:
                 g.shadow.copy_(g.master)
             if zero_grad:
                 g.grad.zero_()
+        if later:
+            self._run_deferred(later)
+
+    # -- deferred part of the single-GPU update ------------------------------------------------
+    def enable_deferred(self, model) -> bool:
+        """One GPU, plain AdamW: update the weights the next forward pass needs late (recurrent core, coda) on a side
+        stream beside that pass's first layers; the update is bound by HBM, those layers by the tensor cores.  The model
+        waits at its ``core`` / ``coda`` points (``on_forward``); other readers call ``finish_deferred``.  Needs the
+        core and the coda tensors to be contiguous runs of the flat weight group (module order gives that)."""
+        from ..parallel.segments import bucket_of
+
+        self.defer_ranges = None
+        if self.plans is not None or not self.plain_adamw or not self.groups[0].master.is_cuda \
+                or not hasattr(model, "_fwd_point") or os.environ.get("B200_DEFER_UPDATE", "1") != "1":
+            return False
+        g = self.groups[0]
+        runs = []                                  # (phase or None, lo, hi) in buffer order
+        for name, off, p in sorted(zip(g.names, g.offsets, g.params), key=lambda x: x[1]):
+            head = bucket_of(name, "weight").split(".")[0]
+            phase = head if head in ("core", "coda") else None
+            if runs and runs[-1][0] == phase:
+                runs[-1][2] = off + p.numel()
+            else:
+                runs.append([phase, off, off + p.numel()])
+        phases = [r[0] for r in runs if r[0]]
+        if sorted(phases) != ["coda", "core"]:     # each must be ONE contiguous run
+            return False
+        # cover alignment gaps: every run ends where the next begins, the last at the end of the buffer
+        for a, b in zip(runs, runs[1:]):
+            a[2] = b[1]
+        runs[0][1], runs[-1][2] = 0, g.master.numel()
+        self.defer_ranges = {0: [tuple(r) for r in runs]}
+        self._side = torch.cuda.Stream(device=g.master.device, priority=-1)
+        self._deferred_events = {}
+        model._fwd_cb = self.on_forward
+        return True
+
+    def _run_deferred(self, later) -> None:
+        self.finish_deferred()
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self._side.wait_event(ev)
+        order = {"core": 0, "coda": 1}
+        with torch.cuda.stream(self._side):
+            for phase, lo, hi, run in sorted(later, key=lambda x: order[x[0]]):
+                run(lo, hi)
+                done = torch.cuda.Event()
+                done.record(self._side)
+                self._deferred_events[phase] = done
+
+    def on_forward(self, name: str) -> None:
+        ev = self._deferred_events.pop(name, None) if self.defer_ranges else None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def finish_deferred(self) -> None:
+        if self.defer_ranges:
+            for name in list(self._deferred_events):
+                self.on_forward(name)
 
     def grad_norm(self, grad_scale: float = 1.0) -> torch.Tensor:
         return self.gnorm_sq.sqrt() * grad_scale
@@ -184,6 +260,7 @@ class FusedAdamW:
 
     # -- checkpoint --------------------------------------------------------------------------
     def state_dict(self):
+        self.finish_deferred()
         groups = []
         for gi, (g, h) in enumerate(zip(self.groups, self.param_groups)):
             entry = {"m": g.state["m"], "v": g.state["v"], "range": g.state["range"], "names": g.names,

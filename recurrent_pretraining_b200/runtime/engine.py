@@ -68,6 +68,9 @@ class TrainEngine:
                                         decouple_wd=decouple_wd)
             self.fabric.register_flat_groups(self.flat_groups, model, self.optimizer)
             self._fused_params = [p for g in self.flat_groups for p in g.params if getattr(p, "_fused_grad", False)]
+            if not self.fabric.is_distributed:
+                # one GPU: the core / coda part of the update runs beside the next forward pass (optim/fused.py)
+                self.optimizer.enable_deferred(model)
         else:
             if optimizer is None:
                 for g in groups:
@@ -241,6 +244,8 @@ class TrainEngine:
         st = self._stepper()
         if st is not None:
             st.gather_master()
+        if hasattr(self.optimizer, "finish_deferred"):
+            self.optimizer.finish_deferred()
         sharded = self._sharded_index()
         out = {}
         for k, v in self.model.state_dict(keep_vars=True).items():
@@ -255,6 +260,10 @@ class TrainEngine:
         own = self.model.state_dict(keep_vars=True)
         sharded = self._sharded_index()
         st = self._stepper()
+        if st is not None:
+            st.finish_deferred()
+        if hasattr(self.optimizer, "finish_deferred"):
+            self.optimizer.finish_deferred()
         for k, v in sd.items():
             if k not in own:
                 if strict and k != "lm_head.weight":
