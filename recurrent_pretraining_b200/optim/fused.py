@@ -27,6 +27,28 @@ import torch
 from ..ops import reference as ref
 
 
+def deferred_runs(names, offsets, numels, total: int):
+    """Cut a flat weight group into contiguous runs ``(phase, lo, hi)`` in buffer order, ``phase`` being ``"core"`` /
+    ``"coda"`` for the tensors the forward pass needs late and ``None`` for the rest.  Returns None unless the core and
+    the coda are ONE run each.  Alignment gaps are covered: every run ends where the next begins."""
+    from ..parallel.segments import bucket_of
+
+    runs: list = []
+    for name, off, n in sorted(zip(names, offsets, numels), key=lambda x: x[1]):
+        head = bucket_of(name, "weight").split(".")[0]
+        phase = head if head in ("core", "coda") else None
+        if runs and runs[-1][0] == phase:
+            runs[-1][2] = off + n
+        else:
+            runs.append([phase, off, off + n])
+    if sorted(r[0] for r in runs if r[0]) != ["coda", "core"]:
+        return None
+    for a, b in zip(runs, runs[1:]):
+        a[2] = b[1]
+    runs[0][1], runs[-1][2] = 0, total
+    return [tuple(r) for r in runs]
+
+
 class FusedAdamW:
     def __init__(self, flat_groups, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, atan2=False,
                  update_clipping=False, running_init=False, decouple_wd=False):
@@ -200,29 +222,15 @@ class FusedAdamW:
         stream beside that pass's first layers; the update is bound by HBM, those layers by the tensor cores.  The model
         waits at its ``core`` / ``coda`` points (``on_forward``); other readers call ``finish_deferred``.  Needs the
         core and the coda tensors to be contiguous runs of the flat weight group (module order gives that)."""
-        from ..parallel.segments import bucket_of
-
         self.defer_ranges = None
         if self.plans is not None or not self.plain_adamw or not self.groups[0].master.is_cuda \
                 or not hasattr(model, "_fwd_point") or os.environ.get("B200_DEFER_UPDATE", "1") != "1":
             return False
         g = self.groups[0]
-        runs = []                                  # (phase or None, lo, hi) in buffer order
-        for name, off, p in sorted(zip(g.names, g.offsets, g.params), key=lambda x: x[1]):
-            head = bucket_of(name, "weight").split(".")[0]
-            phase = head if head in ("core", "coda") else None
-            if runs and runs[-1][0] == phase:
-                runs[-1][2] = off + p.numel()
-            else:
-                runs.append([phase, off, off + p.numel()])
-        phases = [r[0] for r in runs if r[0]]
-        if sorted(phases) != ["coda", "core"]:     # each must be ONE contiguous run
+        runs = deferred_runs(g.names, g.offsets, [p.numel() for p in g.params], g.master.numel())
+        if runs is None:
             return False
-        # cover alignment gaps: every run ends where the next begins, the last at the end of the buffer
-        for a, b in zip(runs, runs[1:]):
-            a[2] = b[1]
-        runs[0][1], runs[-1][2] = 0, g.master.numel()
-        self.defer_ranges = {0: [tuple(r) for r in runs]}
+        self.defer_ranges = {0: runs}
         self._side = torch.cuda.Stream(device=g.master.device, priority=-1)
         self._deferred_events = {}
         model._fwd_cb = self.on_forward

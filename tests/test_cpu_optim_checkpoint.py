@@ -259,3 +259,30 @@ def test_interval_saves_wait_for_the_accumulation_boundary_and_resume_realigns(t
     assert eng2.is_accumulating()        # first micro-batch of the realigned window
     out = eng2.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=torch.tensor([0, 1]))
     assert out["grad_norm"] is not None and not eng2.is_accumulating()
+
+
+def test_deferred_update_runs_cover_the_weight_group_once():
+    """The part of the update that runs beside the next forward pass: the recurrent core (with the adapter) and the coda
+    must be one contiguous run each of the flat weight group, and the runs must tile the buffer without gaps."""
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.optim.fused import deferred_runs
+    from recurrent_pretraining_b200.optim.groups import get_param_groups
+
+    model = ModelConfig.from_name("tiny-raven-cpu").construct_model()
+    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    g = get_param_groups(named, False, with_names=True)[0]
+    offsets, off = [], 0
+    for p in g["params"]:
+        offsets.append(off)
+        off += (p.numel() + 127) // 128 * 128
+    runs = deferred_runs(g["names"], offsets, [p.numel() for p in g["params"]], off)
+    assert [r[0] for r in runs] == [None, "core", "coda"]
+    assert runs[0][1] == 0 and runs[-1][2] == off
+    assert all(a[2] == b[1] for a, b in zip(runs, runs[1:]))
+    for name, o in zip(g["names"], offsets):
+        phase = next(r[0] for r in runs if r[1] <= o < r[2])
+        want = "core" if (".core_block." in name or ".adapter." in name) else ("coda" if ".coda." in name else None)
+        assert phase == want, (name, phase)
+    # a layout in which the coda is split by other tensors is refused
+    assert deferred_runs(["transformer.coda.0.a", "transformer.prelude.0.a", "transformer.coda.1.a",
+                          "transformer.core_block.0.a"], [0, 128, 256, 384], [128] * 4, 512) is None
