@@ -376,7 +376,7 @@ B200_API int b200_gemm(const void* A, const void* A2, const void* B, void* C, co
     if (is_swiglu(out_mode)) bn = 128;
     else if (b_mn) bn = (N <= 128) ? 128 : 256;
     else if (N <= 128) bn = 128;
-    else bn = (N % 256 != 0 && N % 240 == 0) ? 240 : 256;
+    else bn = (!a_mn && N % 256 != 0 && N % 240 == 0) ? 240 : 256;   // 240-wide tiles exist for the NT layout only
   }
   if (b_mn && bn == 240) return -21;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -396,7 +396,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
 int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmParams& p, int lda, int lda2, int ldb,
                        int a_mn, int b_mn, int out_mode, int bn, int max_ctas, cudaStream_t st) {
   if (is_swiglu(out_mode) && (a_mn || b_mn || bn != 256 || p.K2 > 0)) return -100;
-  if (bn == 240 && b_mn) return -100;
+  if (bn == 240 && (a_mn || b_mn)) return -100;   // the 240-wide instantiation is NT only
   if (bn != 256 && bn != 240) return -100;
   const int K = p.K1 + p.K2;
   CUtensorMap ta, ta2, tb;

@@ -217,6 +217,34 @@ def gemm_tn(dy, x, out=None, accumulate=False, out_dtype=torch.float32):
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_mode=mode)
 
 
+def split_bf16(x: torch.Tensor):
+    """fp32 matrix -> (hi, lo) bf16 with hi + lo = x to ~16 bits of mantissa."""
+    hi = x.to(BF16)
+    lo = (x - hi.float()).to(BF16)
+    return hi, lo
+
+
+def matmul_f32(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
+    """fp32-accurate product of two fp32 matrices on the bf16 tensor cores: each operand is split into a bf16 head and a
+    bf16 remainder and ``hi*hi + hi*lo + lo*hi`` is accumulated in fp32 by three tcgen05 GEMMs (the dropped ``lo*lo``
+    term is ~2^-16 relative).  Operand conventions as in ``gemm``: C[M,N] = A B^T with ``a`` [M,K] (or [K,M] with
+    ``a_mn``) and ``b`` [N,K] (or [K,N] with ``b_mn``).  Used by the preconditioner products of SOAP / Shampoo, which
+    would otherwise run as fp32 SIMT GEMMs."""
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.dim() == 2 and b.dim() == 2
+    ah, al = split_bf16(a.contiguous())
+    bh, bl = split_bf16(b.contiguous())
+    out = gemm(ah, bh, a_mn=a_mn, b_mn=b_mn, out_mode=OUT_F32)
+    gemm(ah, bl, a_mn=a_mn, b_mn=b_mn, out=out, out_mode=OUT_F32_ACC)
+    gemm(al, bh, a_mn=a_mn, b_mn=b_mn, out=out, out_mode=OUT_F32_ACC)
+    return out
+
+
+def matmul_f32_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Shapes the tensor-core path takes: CUDA fp32 matrices whose every extent is a multiple of 8 and at least 128."""
+    return (a.is_cuda and b.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32 and a.dim() == 2
+            and b.dim() == 2 and all(d % 8 == 0 and d >= 128 for d in (*a.shape, *b.shape)))
+
+
 # ------------------------------------------------------------------------------------------------
 # norms
 # ------------------------------------------------------------------------------------------------

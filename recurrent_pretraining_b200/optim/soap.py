@@ -4,13 +4,52 @@ Per 2-D parameter: accumulate ``L = E[G G^T]`` and ``R = E[G^T G]`` for every di
 ``max_precond_dim`` (so the 15840/17920/35840/65536-wide sides of the flagship stay un-preconditioned), keep their
 eigenvectors ``Q_L, Q_R`` (``eigh`` at the first step, one power-iteration + QR refresh every ``precondition_frequency``
 steps), run Adam on the rotated gradient ``Q_L^T G Q_R`` and rotate the update back.  The first step only initialises
-the preconditioners.  The GG-accumulation and projection GEMMs go through ``torch.matmul``; they are not on a hot path
-named by the benchmark (one optimizer step per ~0.7 s training step).
+the preconditioners.
+
+The products are fp32 x fp32: Gram matrices ``G^T G``, the three rotations per step and the power iteration.  On the
+flagship they are ~150 TFLOP per optimizer step, seconds as fp32 SIMT GEMMs.  On CUDA tensors with tensor-core
+friendly extents they run as three bf16 tcgen05 GEMMs each with fp32 accumulation on split operands
+(``ops/cuda.py: matmul_f32``, ~2^-16 relative error); ``eigh`` and ``qr`` stay on the library.  ``B200_SOAP_TENSOR_CORES=0``
+keeps ``torch.tensordot``.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 from torch.optim import Optimizer
+
+_TC = os.environ.get("B200_SOAP_TENSOR_CORES", "1") == "1"
+
+
+def _contract_first(x: torch.Tensor, mat: torch.Tensor, back: bool) -> torch.Tensor:
+    """``tensordot(x, mat, dims=[[0], [1 if back else 0]])`` for 2-D operands: x^T mat (x^T mat^T when ``back``)."""
+    if _TC and x.dim() == 2 and x.is_cuda:
+        from ..ops import cuda as C
+
+        if C.matmul_f32_supported(x, mat):
+            return C.matmul_f32(x, mat, a_mn=True, b_mn=not back)
+    return torch.tensordot(x, mat, dims=[[0], [1 if back else 0]])
+
+
+def _gram(g: torch.Tensor, keep: int) -> torch.Tensor:
+    """Sum over every dimension but ``keep`` of the outer product of g with itself."""
+    if _TC and g.dim() == 2 and g.is_cuda:
+        from ..ops import cuda as C
+
+        if C.matmul_f32_supported(g, g):
+            return C.matmul_f32(g, g) if keep == 0 else C.matmul_f32(g, g, a_mn=True, b_mn=True)
+    dims = [j for j in range(g.dim()) if j != keep]
+    return torch.tensordot(g, g, dims=[dims, dims])
+
+
+def _mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    if _TC and a.is_cuda:
+        from ..ops import cuda as C
+
+        if C.matmul_f32_supported(a, b):
+            return C.matmul_f32(a, b, b_mn=True)
+    return a @ b
 
 
 class SOAP(Optimizer):
@@ -52,7 +91,7 @@ class SOAP(Optimizer):
     def _project(g, Q, back=False):
         for mat in Q:
             if len(mat) > 0:
-                g = torch.tensordot(g, mat, dims=[[0], [1 if back else 0]])
+                g = _contract_first(g, mat, back)
             else:
                 g = g.permute(list(range(1, g.dim())) + [0])
         return g
@@ -61,9 +100,7 @@ class SOAP(Optimizer):
         beta = st["shampoo_beta"]
         for i, m in enumerate(st["GG"]):
             if len(m) > 0:
-                dims = [j for j in range(g.dim()) if j != i]
-                outer = torch.tensordot(g, g, dims=[dims, dims])
-                m.lerp_(outer, 1 - beta)
+                m.lerp_(_gram(g, i), 1 - beta)
 
     @staticmethod
     def _eigh_basis(mats):
@@ -87,11 +124,11 @@ class SOAP(Optimizer):
             if len(m) == 0:
                 new_q.append([])
                 continue
-            est = torch.diag(q.T @ m @ q)
+            mq = _mm(m, q)
+            est = (q * mq).sum(0)              # diag(q^T m q)
             order = torch.argsort(est, descending=True)
             exp_avg_sq = exp_avg_sq.index_select(i, order)
-            q = q[:, order]
-            power = m @ q
+            power = mq[:, order]               # m @ q[:, order]
             q_new, _ = torch.linalg.qr(power)
             new_q.append(q_new)
         st["exp_avg_sq"] = exp_avg_sq

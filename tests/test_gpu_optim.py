@@ -91,3 +91,47 @@ def test_table_update_equals_plain_adamw_kernel():
             a, b = ga.state[key][off:off + n], gb.state[key][so:so + n]
             # m sums signed terms (cancellation: absolute bound at its 1e-3 scale); v is a sum of squares
             assert torch.allclose(a, b, rtol=1e-4, atol=1e-8 if key == "m" else 1e-12), (key, (a - b).abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1000, 136, 264), (5280, 5280, 1024)])
+def test_fp32_products_on_split_bf16_tensor_cores(M, N, K):
+    """fp32 x fp32 on three bf16 tcgen05 GEMMs (hi*hi + hi*lo + lo*hi): all four operand layouts against float64."""
+    from recurrent_pretraining_b200.ops import cuda as C
+
+    gen = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=gen).cuda()
+    b = torch.randn(N, K, generator=gen).cuda()
+    want = (a.double() @ b.double().T)
+    scale = want.abs().max().item()
+    for a_mn in (False, True):
+        for b_mn in (False, True):
+            aa = a.T.contiguous() if a_mn else a
+            bb = b.T.contiguous() if b_mn else b
+            got = C.matmul_f32(aa, bb, a_mn=a_mn, b_mn=b_mn)
+            err = (got.double() - want).abs().max().item() / scale
+            assert err < 3e-5, (a_mn, b_mn, err)
+    # one bf16 GEMM alone is two orders of magnitude worse: the split is what buys the accuracy
+    one = C.gemm(a.bfloat16(), b.bfloat16(), out_mode=C.OUT_F32)
+    assert (one.double() - want).abs().max().item() / scale > 3e-4
+    assert C.check_device_status() == 0
+
+
+def test_soap_step_on_tensor_cores_matches_cpu():
+    """SOAP on CUDA parameters (its Gram matrices and rotations on the split-bf16 GEMMs) against the same optimizer on
+    the CPU (torch.tensordot): same parameters after a few steps."""
+    from recurrent_pretraining_b200.optim.soap import SOAP
+
+    gen = torch.Generator().manual_seed(0)
+    # square: both Gram matrices of a random gradient have full rank, so the eigenbases are determined up to signs
+    # (which the update does not depend on)
+    w0 = torch.randn(256, 256, generator=gen) * 0.1
+    grads = [torch.randn(256, 256, generator=gen) * 0.05 for _ in range(4)]
+    outs = []
+    for dev in ("cpu", "cuda"):
+        p = torch.nn.Parameter(w0.clone().to(dev))
+        opt = SOAP([p], lr=1e-2, precondition_frequency=2, weight_decay=0.0)
+        for g in grads:
+            p.grad = g.to(dev)
+            opt.step()
+        outs.append(p.detach().cpu())
+    assert (outs[0] - outs[1]).abs().max().item() < 5e-3 * outs[0].abs().max().item()
