@@ -95,23 +95,104 @@ class StepTimer:
         return out
 
 
+def adam_effective_lr(grad: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, eps: float) -> torch.Tensor:
+    """Per-element ratio of the Adam direction to the raw gradient, ``m / (sqrt(v) + eps) / g`` (``/ eps`` where the
+    gradient is below eps): how much the optimizer amplifies or damps each coordinate, without bias correction and
+    without the scheduled learning rate (recpre/monitor.py:24-36)."""
+    g = grad.float()
+    direction = exp_avg.float() / (exp_avg_sq.float().sqrt() + eps)
+    return torch.where(g.abs() > eps, direction / g, direction / eps)
+
+
+def _moments(optimizer, p):
+    """(exp_avg, exp_avg_sq, eps) of one parameter for torch-style optimizers and for the flat fused optimizer (full-size
+    state only; sharded state holds pieces and is skipped)."""
+    st = getattr(optimizer, "state", None)
+    if isinstance(st, dict) or hasattr(st, "get"):
+        ps = st.get(p) if hasattr(st, "get") else None
+        if ps and "exp_avg" in ps and "exp_avg_sq" in ps:
+            eps = next((g["eps"] for g in optimizer.param_groups if any(q is p for q in g["params"])), 1e-8)
+            return ps["exp_avg"], ps["exp_avg_sq"], eps
+    groups = getattr(optimizer, "groups", None)
+    if groups is not None and getattr(optimizer, "plans", None) is None:
+        if hasattr(optimizer, "finish_deferred"):
+            optimizer.finish_deferred()
+        for g, h in zip(groups, optimizer.param_groups):
+            for q, off in zip(g.params, g.offsets):
+                if q is p:
+                    n = p.numel()
+                    return (g.state["m"][off:off + n].view(p.shape), g.state["v"][off:off + n].view(p.shape),
+                            h["eps"])
+    return None
+
+
 @torch.no_grad()
 def optimizer_telemetry(model, optimizer) -> dict:
-    """Gradient / parameter norms of selected layers (recpre/monitor.py:39-137): q-projection and second FFN matrix
-    gradient norms per block, global L1/L2 parameter norms."""
-    out, l1, l2 = {}, 0.0, 0.0
+    """Optimizer-side telemetry of one step (recpre/monitor.py:39-137, same metric names): query / second-FFN gradient
+    norms per layer, RMS of ``g^2 / v`` per parameter (mean over parameters, and for the embedding), effective Adam
+    learning rates of the q / k / v rows and of the second FFN matrix, mean local L1 gradient norm, and parameter norms
+    (all, core block, embedding, everything but the embedding)."""
+    cfg = getattr(model, "config", None)
+    E = getattr(cfg, "n_embd", None)
+    kv = getattr(cfg, "head_size", 0) * getattr(cfg, "n_query_groups", 0) if cfg is not None else 0
+    wte = getattr(getattr(model, "transformer", None), "wte", None)
+    out: dict = {}
+    qkv_i = ffn_i = 0
+    rms_sum, rms_n, l1_grads = 0.0, 0, []
+    sq_all = sq_core = sq_wte = sq_rest = 0.0
+    l1_params = []
     for name, p in model.named_parameters():
         pf = p.detach().float()
-        l1 += pf.abs().sum().item()
-        l2 += pf.pow(2).sum().item()
-        if p.grad is None:
+        sq = pf.pow(2).sum().item()
+        sq_all += sq
+        l1_params.append(pf.abs().sum().item())
+        if ".core_block." in name:
+            sq_core += sq
+        if ".wte." in name:
+            sq_wte += sq
+        else:
+            sq_rest += sq
+        g = p.grad
+        if g is None:
             continue
-        if name.endswith("attn.Wqkv.weight"):
-            E = p.shape[1]
-            out[f"grad_norm_q/{name}"] = p.grad[:E].float().norm().item()
-        elif name.endswith("mlp.proj.weight"):
-            out[f"grad_norm_ffn2/{name}"] = p.grad.float().norm().item()
-    out["param_l1"], out["param_l2"] = l1, math.sqrt(l2)
+        is_qkv = "qkv" in name.lower() and name.endswith("weight")
+        is_ffn2 = ".mlp." in name and "proj" in name and name.endswith("weight")
+        finite = bool(torch.isfinite(g).all())
+        if is_qkv:
+            if not finite:
+                out[f"query_grad_{qkv_i}"] = float("nan")
+            elif E and g.dim() == 2 and g.shape[1] == E:
+                out[f"query_grad_{qkv_i}"] = g[:E].float().norm().item()
+        if is_ffn2:
+            out[f"ffn2_grad_{ffn_i}"] = g.float().norm().item() if finite else float("nan")
+        if finite:
+            l1_grads.append(g.float().abs().sum().item())
+            mom = _moments(optimizer, p)
+            if mom is not None and mom[1].shape == g.shape:
+                m, v, eps = mom
+                rms = (g.float().pow(2) / v.float().clamp(min=eps ** 2)).mean().sqrt().item()
+                rms_sum += rms
+                rms_n += 1
+                if wte is not None and p is wte.weight:
+                    out["embed_RMS"] = rms
+                if is_qkv and E and g.dim() == 2 and g.shape[1] == E:
+                    lr = adam_effective_lr(g, m, v, eps)
+                    out[f"q_effective_lr_{qkv_i}"] = lr[:E].mean().item()
+                    out[f"k_effective_lr_{qkv_i}"] = lr[E:E + kv].mean().item()
+                    out[f"v_effective_lr_{qkv_i}"] = lr[E + kv:].mean().item()
+                if is_ffn2:
+                    out[f"ffn2_effective_lr_{ffn_i}"] = adam_effective_lr(g, m, v, eps).mean().item()
+        qkv_i += int(is_qkv)
+        ffn_i += int(is_ffn2)
+    if rms_n:
+        out["avg_RMS"] = rms_sum / rms_n
+    if l1_grads:
+        out["local_l1_grad_norm"] = sum(l1_grads) / len(l1_grads)
+    out["l2_param_norm"] = math.sqrt(sq_all)
+    out["l1_param_norm"] = sum(l1_params) / max(len(l1_params), 1)
+    out["core_block_l2_param_norm"] = math.sqrt(sq_core)
+    out["word_embed_l2_param_norm"] = math.sqrt(sq_wte)
+    out["model_l2_param_norm"] = math.sqrt(sq_rest)
     return out
 
 

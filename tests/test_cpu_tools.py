@@ -3,6 +3,7 @@ import os
 import sys
 
 import torch
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -166,3 +167,52 @@ def test_utils_extras(tmp_path):
     assert red["em/2/3"] == 0.5 and red["em/y/2/3"] == 0.0 and red["em/natural_suffix/unmasked"] == 0.5
     assert extras.flops_per_param(4, 2, 8, 100) == 2 * 100 * 4 + 2 * 4 * 8 * 16
     assert extras.gptneox_tflops(1.0, 1, 1, 8, 2, 16, 32, True) > extras.gptneox_tflops(1.0, 1, 1, 8, 2, 16, 32, False)
+
+
+def test_optimizer_telemetry_names_and_values():
+    """The optimizer-side telemetry (gradient norms per layer, g^2/v RMS, effective Adam learning rates, parameter norms)
+    for a torch optimizer and for the flat fused optimizer on the same model and step: same metric names as the
+    reference's ``track_gradient_metrics`` and the same numbers from both state layouts."""
+    import torch
+
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.runtime.engine import TrainEngine
+    from recurrent_pretraining_b200.runtime.monitor import adam_effective_lr, optimizer_telemetry
+
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("tiny-raven-cpu")
+    ids = torch.randint(0, cfg.padded_vocab_size, (2, 33))
+    pair = torch.tensor([1, 2])
+    found = {}
+    for mode in ("torch", "fused"):
+        torch.manual_seed(1)
+        model = cfg.construct_model()
+        eng = TrainEngine(model, lr=1e-3, mode=mode, skip_first_step=False)
+        for _ in range(2):
+            eng.train_step(ids[:, :-1], ids[:, 1:], num_steps_pair=pair)
+        if mode == "fused":
+            eng._begin_window()            # the flat gradient buffers are not cleared between steps: start a window
+        else:
+            eng.optimizer.zero_grad(set_to_none=False)
+        model(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=pair)["loss"].backward()   # fresh gradients to look at
+        found[mode] = optimizer_telemetry(model, eng.optimizer)
+    t = found["torch"]
+    n_blocks = cfg.n_layers_in_prelude + cfg.n_layers_in_recurrent_block + cfg.n_layers_in_coda
+    for i in range(n_blocks):
+        for key in (f"query_grad_{i}", f"ffn2_grad_{i}", f"q_effective_lr_{i}", f"k_effective_lr_{i}",
+                    f"v_effective_lr_{i}", f"ffn2_effective_lr_{i}"):
+            assert key in t, key
+    for key in ("avg_RMS", "embed_RMS", "local_l1_grad_norm", "l2_param_norm", "l1_param_norm",
+                "core_block_l2_param_norm", "word_embed_l2_param_norm", "model_l2_param_norm"):
+        assert key in t and t[key] == t[key], key
+    assert t["l2_param_norm"] ** 2 == pytest.approx(t["word_embed_l2_param_norm"] ** 2 + t["model_l2_param_norm"] ** 2,
+                                                    rel=1e-5)
+    f = found["fused"]
+    assert set(f) == set(t)
+    for key in ("avg_RMS", "embed_RMS", "l2_param_norm", "query_grad_0", "ffn2_grad_1"):
+        assert f[key] == pytest.approx(t[key], rel=2e-3, abs=1e-6), (key, f[key], t[key])
+    assert f["ffn2_effective_lr_1"] == f["ffn2_effective_lr_1"]     # a mean of ratios with heavy tails: finite, not compared
+    # the effective learning rate of a coordinate whose moments equal its gradient statistics is 1 / |g|
+    g = torch.tensor([0.5, -2.0, 1e-12])
+    lr = adam_effective_lr(g, g.clone(), g * g, 1e-8)
+    assert lr[0].item() == pytest.approx(2.0, rel=1e-4) and lr[1].item() == pytest.approx(0.5, rel=1e-4)
