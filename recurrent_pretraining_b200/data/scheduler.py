@@ -51,6 +51,16 @@ class DataSchedulerTracker:
     def get_data_weights(self):
         return self.weights
 
+    def get_sample_count(self):
+        return self.sample_count
+
+    def get_epoch_count(self):
+        return self.epoch_count
+
+    def __repr__(self):
+        return (f"DataSchedulerTracker: {self.weights} | sample_count: {self.sample_count} | "
+                f"epoch_count: {self.epoch_count}")
+
 
 class DataScheduler:
     def __init__(self, tracker: DataSchedulerTracker, data_config: list, max_steps: int):
@@ -82,6 +92,15 @@ class DataScheduler:
 
     def get_data_weights(self):
         return self.tracker.weights
+
+    def get_sample_count(self):
+        return self.tracker.sample_count
+
+    def get_epoch_count(self):
+        return self.tracker.epoch_count
+
+    def __repr__(self):
+        return f"DataScheduler(weights={self.tracker.weights}, max_epochs={self.max_epochs}, base={self.base_id})"
 
     def set_one_hot_schedule(self, idx: int) -> None:
         self._fns = [(lambda s: 0) for _ in self._fns]

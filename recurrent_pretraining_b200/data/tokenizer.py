@@ -74,5 +74,13 @@ class Tokenizer:
     def state_dict(self):
         return {"dir": str(self.checkpoint_dir)}
 
+    def load_state_dict(self, state_dict):
+        """The tokenizer recorded in a checkpoint, or this one when its folder no longer exists."""
+        try:
+            return Tokenizer(state_dict["dir"])
+        except Exception as exc:  # noqa: BLE001
+            print(f"Warning: could not reload the checkpoint's tokenizer ({exc}); keeping the configured one.")
+            return self
+
     def __reduce__(self):
         return (self.__class__, (self.checkpoint_dir,))

@@ -20,6 +20,7 @@ from typing import Optional, Union
 
 import torch
 import torch.nn as nn
+import torch.utils.checkpoint
 from transformers import GenerationMixin, PreTrainedModel
 from transformers.utils import ModelOutput
 
@@ -118,10 +119,48 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
             fc = fc[:seq_len]
         return fc[..., 0].contiguous(), fc[..., 1].contiguous()
 
+    _attn_mask = None      # boolean [B, 1, Sq, Sk] of the forward pass in flight, or None (plain causal attention)
+    # The reference's forward builds no mask at all (its call of compile_mask is commented out,
+    # recpre/raven_modeling_minimal.py:683), so padded rows of a batch attend to their padding.  False keeps that
+    # behaviour (bit-level parity of logits); True applies compile_mask, which is what padded batches need.
+    apply_padding_mask = False
+
+    def compile_mask(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                     past_key_values=None, pad_token_id: int = 65509) -> Optional[torch.Tensor]:
+        """Attention mask of a (pre)fill over ``input_ids``: causal, keys that hold the padding token are hidden, and an
+        optional ``attention_mask`` is applied on top ([B, Sq, Sk] boolean as in the reference, or the usual [B, Sk] key
+        mask).  None when there is nothing to hide, and for single-token steps on a cache (as in
+        recpre/raven_modeling_minimal.py:593-636, which returns a flex-attention block mask; here a dense boolean
+        [B, 1, Sq, Sk] tensor)."""
+        B, S = input_ids.shape
+        has_pad = bool((input_ids == pad_token_id).any())
+        if attention_mask is None and not has_pad:
+            return None
+        if past_key_values is not None and S == 1:
+            return None
+        seen = past_key_values.get_seq_length() if past_key_values is not None else 0
+        if seen:                       # a chunk with history: keys of earlier chunks are not described by input_ids
+            return None
+        keep = torch.ones(S, S, dtype=torch.bool, device=input_ids.device).tril()[None, None]
+        keep = keep & (input_ids != pad_token_id)[:, None, None, :]
+        if attention_mask is not None:
+            am = attention_mask.to(torch.bool)
+            keep = keep & (am[:, None, None, :] if am.dim() == 2 else am[:, None])
+        return keep
+
     def _attention(self, attn, x, rope, step_idx: int, cache):
         B, S, E = x.shape
         cos, sin = rope
         qkv = attn.Wqkv(x)
+        mask = self._attn_mask
+        if mask is not None and mask.shape[-2] == S:
+            q, k, v = ops.qk_bias_rope(qkv, attn.qk_bias, cos, sin, attn.n_head, attn.n_kv, attn.head_dim)
+            if cache is not None:
+                k, v = cache.update(k, v, step_idx)
+            if k.shape[1] == mask.shape[-1]:
+                return attn.proj(ops.masked_attention(q, k, v, mask).reshape(B, S, E))
+            y = ops.causal_attention(q, k, v, None, k.shape[1] - q.shape[1])
+            return attn.proj(y.reshape(B, S, E))
         if x.is_cuda and x.dtype == torch.bfloat16 and S > 1 and not torch.is_grad_enabled():
             y = self._native_prefill_attention(attn, qkv, cos, sin, step_idx, cache)
             if y is not None:
@@ -197,6 +236,13 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
         x = x * (1 - f) + torch.randn_like(x) * f
         return self.transformer.core_block[-1].norm_4(x) if renorm else x
 
+    def _maybe_checkpoint_core_block(self, *args):
+        """One recurrence, recomputed in backward when ``gradient_checkpointing`` is on (finetuning)."""
+        if self.gradient_checkpointing and torch.is_grad_enabled():
+            return torch.utils.checkpoint.checkpoint(self.core_block_forward, *args, use_reentrant=False,
+                                                     preserve_rng_state=False, determinism_check="none")
+        return self.core_block_forward(*args)
+
     def core_block_forward(self, x, input_embeds, rope, cache, block_idx: int, current_step: int = 0):
         x = self._maybe_inject_noise(x, current_step)
         x = ops.adapter(x, input_embeds.to(x.dtype), self.transformer.adapter.weight)
@@ -245,6 +291,16 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
                 init_scale: float = 1.0, **kwargs) -> CausalLMOutputRecurrentLatents:
         S = input_ids.shape[1] if input_ids is not None else input_embeds.shape[1]
         rope = self._rope(S, position_ids, cache_position)
+        self._attn_mask = self.compile_mask(input_ids, attention_mask, past_key_values) \
+            if (self.apply_padding_mask and input_ids is not None) else None
+        try:
+            return self._forward(input_ids, input_embeds, input_states, rope, labels, num_steps, past_key_values,
+                                 output_details, use_cache, init_scale)
+        finally:
+            self._attn_mask = None
+
+    def _forward(self, input_ids, input_embeds, input_states, rope, labels, num_steps, past_key_values, output_details,
+                 use_cache, init_scale) -> CausalLMOutputRecurrentLatents:
         if input_embeds is None:
             input_embeds = ops.embedding(input_ids, self.transformer.wte.weight, self.emb_scale)
         elif self.emb_scale != 1:

@@ -152,3 +152,70 @@ class RecurrentKVCache:
 
 
 HuginnDynamicCache = RecurrentKVCache
+
+
+class StaticRecurrentCache:
+    """Preallocated cache for the HF-style model (``HuginnStaticCache`` of recpre/raven_modeling_minimal.py:311-437):
+    one [batch, max_length, kv heads, head dim] key and value block per step index, written in place, so decoding
+    allocates nothing.  Step indices follow the model (prelude 0.., recurrence ``2 + 4 j + b``, coda -1, -2 counted
+    from the end of the table); ``compress-s<N>`` / ``compress-r<N>`` fold the recurrence indices into N (resp. every N)
+    slots.  Only the ``full`` lookup (every step reads its own entries) and its compressed forms are defined on the
+    static layout; the partial-history strategies live in ``RecurrentKVCache``."""
+
+    def __init__(self, max_length: int, max_num_steps: int, num_heads: int, hidden_dim: int, batch_size: int = 1,
+                 lookup_strategy: str = "full", device=None, dtype: torch.dtype = torch.float32):
+        self.max_length, self.lookup_strategy, self._seen_tokens = max_length, lookup_strategy, 0
+        self.stage, self.modulo = 0, False
+        if "compress-" in lookup_strategy:
+            tag = lookup_strategy.split("compress-")[1]
+            self.modulo, self.stage = tag[0] == "s", int(tag[1:].split("-")[0])
+            steps = 4 + self.stage if self.modulo else 4 + (max_num_steps - 4 + self.stage - 1) // self.stage
+        else:
+            steps = max_num_steps
+        if not lookup_strategy.startswith(("full", "compress-")):
+            raise NotImplementedError(f"lookup strategy {lookup_strategy!r} needs the dynamic cache")
+        self.max_num_steps = steps
+        shape = (steps, batch_size, max_length, num_heads, hidden_dim)
+        self.key_cache = torch.zeros(shape, dtype=dtype, device=device)
+        self.value_cache = torch.zeros(shape, dtype=dtype, device=device)
+        self.valid_mask = torch.zeros(steps, max_length, dtype=torch.bool, device=device)
+
+    def fold(self, step_idx: int) -> int:
+        step_idx = int(step_idx)
+        if self.stage and step_idx > 1:
+            return (step_idx - 2) % self.stage + 2 if self.modulo else (step_idx - 2) // self.stage + 2
+        return step_idx
+
+    def update(self, k: torch.Tensor, v: torch.Tensor, step_idx: int, lookup_strategy: str | None = None):
+        """k, v: [B, S_new, Hkv, D] of the newest positions; returns the step's keys and values of all positions."""
+        n = k.shape[1]
+        if int(step_idx) == 0:
+            self._seen_tokens += n
+        assert self._seen_tokens <= self.max_length, "static cache is full"
+        slot = self.fold(step_idx)
+        lo = self._seen_tokens - n
+        B = k.shape[0]
+        self.key_cache[slot, :B, lo:lo + n].copy_(k)
+        self.value_cache[slot, :B, lo:lo + n].copy_(v)
+        self.valid_mask[slot, lo:lo + n] = True
+        return self.key_cache[slot, :B, :self._seen_tokens], self.value_cache[slot, :B, :self._seen_tokens]
+
+    def reset(self) -> None:
+        self._seen_tokens = 0
+        self.key_cache.zero_()
+        self.value_cache.zero_()
+        self.valid_mask.zero_()
+
+    def clear_last_k_entries(self, k: int = 0) -> None:
+        assert self._seen_tokens >= k
+        self._seen_tokens -= k
+        self.valid_mask[:, self._seen_tokens:] = False
+
+    def get_seq_length(self, step_idx: int = 0) -> int:
+        return self._seen_tokens
+
+    def get_memory_usage(self) -> float:
+        return (self.key_cache.nelement() + self.value_cache.nelement()) * self.key_cache.element_size() / (1024 * 1024)
+
+
+HuginnStaticCache = StaticRecurrentCache

@@ -446,6 +446,14 @@ def causal_attention(q, k, v, scale: float | None = None, q_offset: int = 0):
     return ref.causal_attention(q, k, v, scale, q_offset)
 
 
+def masked_attention(q, k, v, mask, scale: float | None = None):
+    """Attention under an explicit boolean mask [B,1,Sq,Sk] (padding / block masks of the eager HF-style model).  The
+    fp32 statement on every device: this path serves masked prefill of padded batches, not the training step."""
+    if q.is_cuda:
+        cuda_backend()._library("attention_masked", "explicit attention mask (eager HF-style model)", strict=False)
+    return ref.masked_attention(q, k, v, mask, scale)
+
+
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h):

@@ -86,6 +86,24 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     return torch.matmul(p, vf).transpose(1, 2).to(q.dtype).contiguous()
 
 
+def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor,
+                     scale: float | None = None) -> torch.Tensor:
+    """softmax(q k^T * scale, restricted to ``mask``) v with q,k,v as [B,S,H,hd] and a boolean ``mask`` [B,1,Sq,Sk]
+    (True = may attend).  A query row that may attend to nothing (a padding position) returns zeros."""
+    B, Sq, H, D = q.shape
+    Hk = k.shape[2]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+    if Hk != H:
+        kf = kf.repeat_interleave(H // Hk, dim=1)
+        vf = vf.repeat_interleave(H // Hk, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)
+    return torch.matmul(p, vf).transpose(1, 2).to(q.dtype).contiguous()
+
+
 def swiglu(h: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up with ``h = [gate | up]`` along the last dim (recpre/model_dynamic.py:776-780)."""
     a, b = h.float().chunk(2, dim=-1)

@@ -19,13 +19,106 @@ PEAK_FLOPS = {"B200": 2.25e15, "H200": 989e12, "H100": 989e12, "A100": 312e12, "
               "A6000": 155e12, "L40": 181e12, "4090": 165e12}
 
 
-def peak_flops(device_name: str | None = None) -> float:
+def peak_flops(device_name: str | None = None, precision: str = "bf16") -> float:
+    """Nominal dense tensor peak of the device for the run's precision string (``"bf16-mixed"``, ``"32-true"``, ...):
+    halved for fp32, quartered for fp64, doubled for 8-bit, as in recpre/monitor.py:195-245 -- but with entries for the
+    GPUs that table does not know (it raises on a B200)."""
     if device_name is None:
         device_name = torch.cuda.get_device_name() if torch.cuda.is_available() else "cpu"
+    mult = 0.5 if "32" in precision else 0.25 if "64" in precision else 2.0 if "8" in precision else 1.0
     for key, val in PEAK_FLOPS.items():
         if key.lower() in device_name.lower():
-            return val
+            return val * mult
     return float("nan")
+
+
+def num_params(model, only_trainable: bool = False) -> int:
+    return sum(p.numel() for p in model.parameters() if p.requires_grad or not only_trainable)
+
+
+def estimate_flops_per_token(n_params: int, cfg) -> int:
+    """The reference's closed-form estimate (recpre/monitor.py:152-160): ``3 * (6 P + 12 L H Q T)``."""
+    heads = getattr(cfg, "n_heads", None) or cfg.num_attention_heads
+    return 3 * (6 * n_params + 12 * cfg.n_layer * heads * cfg.head_size * cfg.block_size)
+
+
+def measure_flops(cfg, micro_batch_size: int = 1, gradient_checkpointing: bool = False) -> float:
+    """FLOPs of one forward + backward pass over ``micro_batch_size`` sequences of ``block_size`` tokens, counted by
+    torch's FLOP counter on a meta-device copy of the model (the measurement behind the reference's MFU,
+    recpre/monitor.py:163-192).  Falls back to the analytic count when the model cannot run on meta tensors."""
+    import copy
+
+    from torch.utils.flop_counter import FlopCounterMode
+
+    try:
+        with torch.device("meta"):
+            meta = copy.deepcopy(cfg).construct_model(gradient_checkpointing=gradient_checkpointing)
+            x = torch.randint(0, cfg.padded_vocab_size, (micro_batch_size, cfg.block_size))
+            counter = FlopCounterMode(display=False)
+            with counter:
+                meta(x, labels=x)["loss"].backward()
+        depths = getattr(meta, "last_depths", None)
+        return float(counter.get_total_flops()), depths
+    except Exception:  # noqa: BLE001  (any op without a meta kernel)
+        n, k = (cfg.mean_recurrence - cfg.mean_backprop_depth, cfg.mean_backprop_depth) if cfg.is_recurrent else (0, 0)
+        return cfg.flops_per_token(cfg.block_size, n, k, gradient_checkpointing) * cfg.block_size * micro_batch_size, (n, k)
+
+
+_mfu_cache: dict = {}
+
+
+def mfu_metrics(tokens_per_second: float, world_size: int, model, precision: str = "bf16-mixed",
+                measure: bool = True, device_name: str | None = None):
+    """(FLOPs per token, achieved TFLOP/s of the whole job, MFU per device) -- the triple of the reference's
+    ``get_MFU_metrics`` (recpre/monitor.py:248-266); model constants are cached per model object."""
+    c = _mfu_cache.get(id(model))
+    if c is None:
+        n = num_params(model)
+        cfg = model.config
+        if measure:
+            total, _ = measure_flops(cfg, 1, getattr(model, "gradient_checkpointing", False))
+            per_token = total / cfg.block_size
+        else:
+            per_token = estimate_flops_per_token(n, cfg)
+        c = _mfu_cache[id(model)] = {"num_params": n, "num_flop_per_token": per_token,
+                                     "peak_flops": peak_flops(device_name, precision)}
+    flops = c["num_flop_per_token"] * tokens_per_second
+    return c["num_flop_per_token"], flops / 1e12, flops / world_size / c["peak_flops"]
+
+
+def measure_peak_flops(sizes=(2048, 4096, 8192), batch: int = 8, runs: int = 20) -> list:
+    """Achieved dense bf16 matmul rate of this GPU: the library's batched GEMM and the in-tree tcgen05 GEMM on square
+    problems, timed with CUDA events (the counterpart of recpre/monitor.py:269-336, which compares against an A100 peak).
+    ``python -m recurrent_pretraining_b200.runtime.monitor`` prints the table."""
+    from ..ops import cuda as C
+
+    nominal = peak_flops()
+    rows = []
+    for n in sizes:
+        a = torch.randn(batch, n, n, device="cuda").bfloat16()
+        b = torch.randn(batch, n, n, device="cuda").bfloat16()
+
+        def timed(fn):
+            fn()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(runs):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) / 1e3)
+            ts.sort()
+            return ts[len(ts) // 2]
+
+        t_lib = timed(lambda: torch.bmm(a, b))
+        t_own = timed(lambda: [C.gemm(a[i], b[i], b_mn=True) for i in range(batch)])
+        fl = 2.0 * n ** 3 * batch
+        rows.append({"n": n, "batch": batch, "library_tflops": fl / t_lib / 1e12, "tcgen05_tflops": fl / t_own / 1e12,
+                     "library_frac_of_nominal": fl / t_lib / nominal, "tcgen05_frac_of_nominal": fl / t_own / nominal})
+        print(rows[-1], flush=True)
+    return rows
 
 
 class RunningMean:
@@ -209,3 +302,7 @@ def harvest_metrics(model) -> dict:
         if lm:
             out.update(lm)
     return out
+
+
+if __name__ == "__main__":
+    measure_peak_flops()

@@ -108,6 +108,23 @@ def create_dataloader(cfg, fabric, tokenizer, entries, split_dir, seed, schedule
     return StatefulLoader(ds, cfg.micro_batch_size, collate, prefetch=prefetch)
 
 
+def derive_precision(precision: str, all_reduce_dtype: Optional[str] = None) -> dict:
+    """Dtypes that a precision string stands for (train.py:802-822 of the reference builds torch-FSDP's MixedPrecision
+    from the same rule): compute copy of the parameters, gradient reduction, buffers."""
+    param = torch.bfloat16 if "bf16" in precision else torch.float16 if "16" in precision else torch.float32
+    reduce = torch.float32 if "mixed" in precision else param
+    if all_reduce_dtype is not None:
+        reduce = torch.float16 if all_reduce_dtype in ("16", "fp16", "fp16-mixed") else \
+            torch.bfloat16 if all_reduce_dtype in ("bf16", "bf16-mixed") else torch.float32
+    return {"param_dtype": param, "reduce_dtype": reduce, "buffer_dtype": torch.float32}
+
+
+def get_attention_mask(input_ids, tokenizer=None, cache_attn: bool = True, doc_block_attn: bool = True):
+    """Pretraining packs documents without a block mask and without explicit positions: (mask, position_ids) =
+    (None, None), as in the reference (train.py:825-827); the models then run plain causal attention."""
+    return None, None
+
+
 def warmup_or_early_fail_allreduce(fabric) -> None:
     """Growing all-reduces so that a broken fabric fails before any real work (train.py:965-982)."""
     if not fabric.is_distributed:

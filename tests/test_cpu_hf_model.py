@@ -214,3 +214,61 @@ def test_legacy_surface_old_signatures_and_helpers():
     cache = legacy.HuginnDynamicCache()
     cache.reset()
     assert cache.get_seq_length() == 0
+
+
+def test_padding_mask_is_optional_and_hides_padding_when_on():
+    """``compile_mask``: causal + padding keys hidden + optional custom mask.  Off by default (the reference's forward
+    builds no mask); when on, a left-padded row gives the logits of the unpadded row, and a custom [B, Sq, Sk] mask
+    changes exactly the rows it restricts."""
+    model = _ours()
+    PAD = 65509
+    torch.manual_seed(1)
+    row = torch.randint(0, 1000, (1, 10))
+    padded = torch.cat([torch.full((1, 6), PAD), row], 1)
+    with torch.no_grad():
+        plain = model(row, num_steps=3, init_scale=0.0).logits
+        off = model(padded, num_steps=3, init_scale=0.0).logits[:, 6:]
+        model.apply_padding_mask = True
+        on = model(padded, num_steps=3, init_scale=0.0).logits[:, 6:]
+        mask = model.compile_mask(padded)
+        assert mask.shape == (1, 1, 16, 16) and not mask[0, 0, :, :6].any() and mask[0, 0, 15, 6:].all()
+        assert model.compile_mask(row) is None                                     # nothing to hide
+        assert model.compile_mask(padded[:, -1:], past_key_values=object()) is None  # single-token step on a cache
+        am = torch.ones(1, 10, 10, dtype=torch.bool).tril()
+        am[0, 7:, 2] = False                                                      # queries 7.. may not see key 2
+        restricted = model(row, attention_mask=am, num_steps=3, init_scale=0.0).logits
+    assert (on - plain).abs().max().item() < 1e-4          # padding hidden: same as the unpadded row
+    assert (off - plain).abs().max().item() > 1e-3         # default (reference behaviour): padding is attended to
+    assert (restricted[:, :7] - plain[:, :7]).abs().max().item() < 1e-5
+    assert (restricted[:, 7:] - plain[:, 7:]).abs().max().item() > 1e-4
+
+
+def test_static_cache_gives_the_dynamic_cache_logits():
+    """Prefill + token-by-token decoding on the preallocated cache equals the same on the dynamic cache (lookup ``full``
+    and the folded ``compress-s4`` form)."""
+    from recurrent_pretraining_b200.models.kv_cache import HuginnStaticCache, StaticRecurrentCache
+
+    assert HuginnStaticCache is StaticRecurrentCache
+    model = _ours()
+    cfg = model.config
+    steps = 5
+    torch.manual_seed(2)
+    ids = torch.randint(0, 1000, (2, 9))
+    for strategy in ("full", "compress-s4"):
+        dyn = RecurrentKVCache(strategy)
+        sta = StaticRecurrentCache(max_length=16, max_num_steps=4 + 4 * steps, num_heads=cfg.num_key_value_heads,
+                                   hidden_dim=cfg.n_embd // cfg.num_attention_heads, batch_size=2,
+                                   lookup_strategy=strategy)
+        with torch.no_grad():
+            for cache in (dyn, sta):
+                out = model(ids[:, :6], num_steps=steps, init_scale=0.0, past_key_values=cache, use_cache=True)
+                rows = [out.logits[:, -1]]
+                for t in range(6, 9):
+                    out = model(ids[:, t:t + 1], num_steps=steps, init_scale=0.0, past_key_values=cache, use_cache=True,
+                                cache_position=torch.tensor([t]))
+                    rows.append(out.logits[:, -1])
+                cache.result = torch.stack(rows, 1)
+        assert (dyn.result - sta.result).abs().max().item() < 1e-4, strategy
+        assert sta.get_seq_length() == 9 and sta.get_memory_usage() > 0
+    sta.reset()
+    assert sta.get_seq_length() == 0 and not sta.valid_mask.any()

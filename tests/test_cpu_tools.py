@@ -216,3 +216,96 @@ def test_optimizer_telemetry_names_and_values():
     g = torch.tensor([0.5, -2.0, 1e-12])
     lr = adam_effective_lr(g, g.clone(), g * g, 1e-8)
     assert lr[0].item() == pytest.approx(2.0, rel=1e-4) and lr[1].item() == pytest.approx(0.5, rel=1e-4)
+
+
+def test_flop_accounting_and_mfu():
+    """The analytic FLOP count of the config equals what torch's FLOP counter measures on a meta-device copy of the
+    model (the reference's MFU measurement); peak table with the precision multiplier and a B200 entry; MFU triple."""
+    from recurrent_pretraining_b200.config import ModelConfig
+    from recurrent_pretraining_b200.runtime import monitor as M
+
+    cfg = ModelConfig.from_name("tiny-raven-cpu")
+    model = cfg.construct_model()
+    total, (n, k) = M.measure_flops(cfg, micro_batch_size=1)
+    assert total == pytest.approx(cfg.flops_per_token(cfg.block_size, n, k) * cfg.block_size, rel=1e-6)
+    assert M.peak_flops("NVIDIA B200", "bf16-mixed") == 2.25e15
+    assert M.peak_flops("NVIDIA B200", "32-true") == 2.25e15 / 2
+    assert M.peak_flops("NVIDIA H100 80GB HBM3") == 989e12
+    per_token, tflops, mfu = M.mfu_metrics(1000.0, 2, model, "bf16-mixed", True, "NVIDIA B200")
+    assert per_token == pytest.approx(total / cfg.block_size)
+    assert tflops == pytest.approx(per_token * 1000.0 / 1e12) and mfu == pytest.approx(per_token * 1000.0 / 2 / 2.25e15)
+    est = M.estimate_flops_per_token(M.num_params(model), cfg)
+    assert est == 3 * (6 * M.num_params(model) + 12 * cfg.n_layer * cfg.num_attention_heads * cfg.head_size * cfg.block_size)
+
+
+def test_small_helpers(tmp_path, monkeypatch):
+    """Rounding / counting / directory conventions / remapping / cycling / closed-form count / abacus groups / loss head."""
+    import dataclasses
+
+    import torch.nn as nn
+
+    from recurrent_pretraining_b200.utils import helpers as H
+
+    assert H.find_multiple(65, 64) == 128 and H.find_multiple(128, 64) == 128
+    lin = nn.Linear(4, 3)
+    lin.bias.requires_grad_(False)
+    assert H.num_parameters(lin) == 15 and H.num_parameters(lin, True) == 12 and H.num_parameters(lin, False) == 3
+    seq = nn.Sequential(nn.Linear(4, 4), nn.ReLU())
+    before = seq[0].weight.clone()
+    H.reset_parameters(seq)
+    assert not torch.equal(before, seq[0].weight)
+    # checkpoint directory conventions
+    monkeypatch.chdir(tmp_path)
+    (tmp_path / "checkpoints" / "org" / "model").mkdir(parents=True)
+    assert H.extend_checkpoint_dir("org/model") == (tmp_path / "checkpoints" / "org" / "model").relative_to(tmp_path)
+    with pytest.raises(SystemExit):
+        H.check_valid_checkpoint_dir(tmp_path / "checkpoints" / "org" / "model")
+    d = tmp_path / "checkpoints" / "org" / "model"
+    for name in ("lit_model.pth", "model_config.yaml", "tokenizer.json", "tokenizer_config.json"):
+        (d / name).write_text("x")
+    H.check_valid_checkpoint_dir(d)
+    out = tmp_path / "out"
+    out.mkdir()
+    H.copy_config_files(d, out)
+    assert sorted(p.name for p in out.iterdir()) == ["model_config.yaml", "tokenizer.json", "tokenizer_config.json"]
+    assert H.flatten_dict({"a": {"b": 1, "c": {"d": 2}}, "e": 3}) == {"a_b": 1, "a_c_d": 2, "e": 3}
+
+    @dataclasses.dataclass
+    class S:
+        lr: float = 0.1
+        name: str = "x"
+
+    def f(alpha=1, cfg=S(), other=[1, 2]):
+        return H.capture_hparams()
+
+    hp = f()
+    assert hp["alpha"] == 1 and hp["cfg"] == {"lr": 0.1, "name": "x"} and hp["other"] == "[1, 2]"
+    H.save_hyperparameters(S(), out)
+    assert "lr: 0.1" in (out / "hyperparameters.yaml").read_text()
+    assert H.parse_devices(3) == 3 and H.parse_devices("auto") >= 1
+    with pytest.raises(ValueError):
+        H.parse_devices(0)
+    assert H.get_default_supported_precision(True) in ("bf16-mixed", "16-mixed")
+    sd = H.map_old_state_dict_weights({"m.old": 1, "m.keep": 2}, {"old": "new"}, "m.")
+    assert sd == {"m.new": 1, "m.keep": 2}
+    logits = torch.arange(12.0).view(2, 6)
+    lg, tg = H.slice_logits_remap_labels(logits, torch.tensor([5, -1]), [1, 3, 5])
+    assert lg.tolist() == [[1.0, 3.0, 5.0], [7.0, 9.0, 11.0]] and tg.tolist() == [2, -1]
+    it = H.CycleIterator([1, 2, 3])
+    assert [next(it) for _ in range(7)] == [1, 2, 3, 1, 2, 3, 1] and it.epoch == 2
+    # closed-form count against a real module stack of the same description
+    from recurrent_pretraining_b200.config import ModelConfig
+
+    cfg = ModelConfig.from_name("tiny-raven-cpu")
+    est = H.param_count_estimator(cfg.n_embd, 1, cfg.padded_vocab_size, cfg.n_head, cfg.head_size, cfg.n_query_groups,
+                                  cfg.intermediate_size)
+    E, I, V = cfg.n_embd, cfg.intermediate_size, cfg.padded_vocab_size
+    assert est == (3 * E * E + E * E + 3 * E * I + 2 * E) + 2 * V * E + E
+    groups = H.get_abacus_param_groups([("abacus.weight", nn.Parameter(torch.zeros(2))), ("w", nn.Parameter(torch.zeros(2))),
+                                        ("norm.weight", nn.Parameter(torch.zeros(2)))], 0.1, True, 4.0)
+    assert [len(g["params"]) for g in groups] == [1, 1, 1] and groups[1]["weight_decay"] == 0.0
+    assert groups[2]["lr"] == pytest.approx(0.4)
+    head = H.LinearCrossEntropyLoss(8, 16)
+    x, y = torch.randn(5, 8), torch.tensor([1, 2, -100, 4, 15])
+    want = torch.nn.functional.cross_entropy(head(x), y, ignore_index=-100)
+    assert head(x, y).item() == pytest.approx(want.item(), rel=1e-5)
