@@ -21,10 +21,15 @@ AUTO_THRESHOLDS = {"entropy-diff": 1e-3, "latent-diff": 0.03, "kl": 1e-3, "minp-
 class AdaptiveComputeLM(RecurrentLM):
     def __init__(self, model, tokenizer, criterion: str = "entropy-diff", exit_threshold="auto",
                  lookup_strategy: str = "full", continuous_compute: bool = False, max_steps: Optional[int] = None,
-                 **kw):
+                 exit_evaluator=None, **kw):
         super().__init__(model, tokenizer, **kw)
         if not self._hf:
             raise TypeError("adaptive generation needs the HF-style model (RavenForCausalLM)")
+        # a ready-made evaluator object (e.g. ``NumStepsGenerator`` with a schedule of depths per token) overrides the
+        # named criterion, as in evaluate_raven/misc_benchmark_variants/eval_alternate_loops.py
+        self.exit_evaluator = exit_evaluator
+        if exit_evaluator is not None:
+            criterion = "none"
         if criterion not in AUTO_THRESHOLDS:
             raise ValueError(f"unknown exit criterion {criterion!r}; one of {sorted(AUTO_THRESHOLDS)}")
         self.criterion = criterion
@@ -35,7 +40,9 @@ class AdaptiveComputeLM(RecurrentLM):
 
     def gen_kwargs(self) -> dict:
         kw = dict(num_steps=self.max_steps, cache_lookup_strategy=self.lookup_strategy)
-        if self.criterion != "none":
+        if self.exit_evaluator is not None:
+            kw["exit_evaluator"] = self.exit_evaluator
+        elif self.criterion != "none":
             kw.update(criterion=self.criterion, exit_threshold=self.exit_threshold)
         if self.continuous_compute:
             kw["continuous_compute"] = True

@@ -108,14 +108,20 @@ class Identity(nn.Identity):
 def make_norm(config, dim: int | None = None) -> nn.Module:
     dim = config.n_embd if dim is None else dim
     name = config.norm_class_name
-    if name in ("RMSNorm", "RMSNorm_llama", "FusedRMSNorm"):
+    # every RMS form of the reference (recpre/norms.py:18-152: its own, the llama and gemma-like casts, torch's, the
+    # Triton one) is the same function up to where the cast happens; here the statistics are always fp32
+    if name in ("RMSNorm", "RMSNorm_llama", "FusedRMSNorm", "TorchRMSNorm", "GemmalikeRMS"):
         return RMSNorm(dim, eps=config.norm_eps, add_unit_offset="Gemma" in config.name)
     if name == "UnparametrizedRMSNorm":
         return RMSNorm(dim, eps=config.norm_eps, learnable=False)
     if name == "LayerNorm":
         return LayerNorm(dim, eps=config.norm_eps)
+    if name == "OlmoLayerNorm":                      # layer norm without scale and shift
+        return LayerNorm(dim, eps=config.norm_eps, elementwise_affine=False)
     if name == "Identity":
         return Identity()
+    if hasattr(nn, name):                            # any other torch.nn norm by name, as the reference falls back to
+        return _PlainNorm(getattr(nn, name)(dim, eps=config.norm_eps))
     raise ValueError(f"unknown norm class {name!r}")
 
 
@@ -197,6 +203,11 @@ class CausalSelfAttention(nn.Module):
         if self.monitoring:
             self._monitor(q, k)
         return self.proj(y.reshape(B, S, E))
+
+    def monitor_layer(self, q, k, mask=None):
+        """The reference's name for the attention telemetry (q, k as [B, S, H, hd])."""
+        self._monitor(q, k)
+        return self.latest_metrics
 
     @torch.no_grad()
     def _monitor(self, q, k):

@@ -141,3 +141,20 @@ def test_saturation_eval_and_pass_at_k(tmp_path):
     assert pk.build_predictions_instruct([["    return 1\n```\nthanks"]], docs)[0][0].endswith("return 1\n")
     assert parse_kv("pretrained=x/y,mean_recurrence=32,exit_threshold=1e-2,flag=true") == \
         {"pretrained": "x/y", "mean_recurrence": 32, "exit_threshold": 0.01, "flag": True}
+
+
+def test_adaptive_compute_wrapper_with_a_scripted_depth_schedule():
+    """An evaluator object instead of a named criterion: ``NumStepsGenerator`` alternating 2 and 4 recurrences per
+    generated token (the reference's eval_alternate_loops example); the recorded steps follow the schedule."""
+    from recurrent_pretraining_b200.evaluate.adaptive_eval import AdaptiveComputeLM
+    from recurrent_pretraining_b200.models.exit_criteria import NumStepsGenerator
+    from recurrent_pretraining_b200.models.hf import RavenForCausalLM
+    from recurrent_pretraining_b200.models.hf_config import RavenConfig
+
+    torch.manual_seed(0)
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **TINY)
+    model = RavenForCausalLM(RavenConfig.from_model_config(cfg)).eval()
+    lm = AdaptiveComputeLM(model, ByteTok(), exit_evaluator=NumStepsGenerator(lambda i: 2 if i % 2 == 0 else 4),
+                           max_steps=6, max_gen_toks=4, device="cpu")
+    lm.generate_until([("hello", {"max_gen_toks": 4})])
+    assert lm.step_log and lm.step_log[0][:4] == [2, 4, 2, 4][:len(lm.step_log[0])], lm.step_log

@@ -186,3 +186,18 @@ def test_loop_probe_learns_depth_on_a_tiny_model():
     assert res["chance"] == 0.25 and res["accuracy"][-1] > res["accuracy"][0]
     pair = loop_probe.train_probe(model, [ids] * 5, 4, classes=torch.tensor([0, 3]))
     assert pair["chance"] == 0.5 and len(pair["accuracy"]) == 5
+
+
+def test_category_report_sums_and_shares():
+    from recurrent_pretraining_b200.data.prepare.count_tokens import category_report, format_category_report
+    from recurrent_pretraining_b200.data.prepare.unify_filter import DataSource
+
+    sources = {"web-a": DataSource("org/web-a", category="generic-web"), "web-b": DataSource("org/web-b", category="generic-web"),
+               "code": DataSource("org/code", category="code"), "empty": DataSource("org/none", category="math")}
+    rep = category_report(sources, {"web-a": (600, 800), "web-b": (200, 200), "code": (200, 250)})
+    assert rep["total_kept"] == 1000
+    assert rep["categories"]["generic-web"]["kept"] == 800 and rep["categories"]["generic-web"]["share_pct"] == 80.0
+    assert rep["categories"]["generic-web"]["datasets"] == ["web-a", "web-b"]
+    assert rep["datasets"]["web-a"]["dropped_pct"] == 25.0 and rep["datasets"]["empty"]["kept"] == 0
+    text = format_category_report(rep)
+    assert "generic-web" in text and "Total tokens" in text
