@@ -148,10 +148,38 @@ def _split_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim):
     return ref.qk_bias_rope(qkv, qk_bias, cos, sin, n_head, n_kv, head_dim)
 
 
-def _dense_attention(q, k, v):
+def _dense_attention(q, k, v, softcap: float = 0.0):
+    """fp32 statement of causal attention on [B,S,H,hd] tensors; ``softcap`` > 0 squashes the logits to
+    ``softcap * tanh(logit / softcap)`` before the softmax (the ``flex-attention-soft-cap`` provider of the reference,
+    recpre/attention_backends/flex_attentions.py:66-97, cap 20)."""
     from ..ops import reference as ref
 
-    return ref.causal_attention(q, k, v)
+    if softcap <= 0:
+        return ref.causal_attention(q, k, v)
+    B, S, H, D = q.shape
+    Hk = k.shape[2]
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+    if Hk != H:
+        kf, vf = kf.repeat_interleave(H // Hk, dim=1), vf.repeat_interleave(H // Hk, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(D)
+    s = softcap * torch.tanh(s / softcap)
+    s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    return (torch.softmax(s, dim=-1) @ vf).transpose(1, 2).to(q.dtype).contiguous()
+
+
+def _center_debias(y, v, n_head: int, center: bool, debias: bool):
+    """Post-operations of the reference's attention providers on y, v as [B,S,H,hd] (recpre/attention_backends/
+    pytorch.py:22-29): ``center`` adds the token's own value (attention matrix + identity), ``debias`` subtracts the
+    causal running mean of the values (attention matrix - uniform causal attention)."""
+    if v.shape[2] != n_head:
+        v = v.repeat_interleave(n_head // v.shape[2], dim=2)
+    if center:
+        y = y + v
+    if debias:
+        S = y.shape[1]
+        steps = torch.arange(1, S + 1, device=y.device, dtype=torch.float32)[None, :, None, None]
+        y = y - (v.float().cumsum(dim=1) / steps).to(y.dtype)
+    return y
 
 
 class CausalSelfAttention(nn.Module):
@@ -177,8 +205,11 @@ class CausalSelfAttention(nn.Module):
     def forward(self, x, rope, mask=None):
         B, S, E = x.shape
         cos, sin = rope
-        plain = not (self.config.qk_norm or self.monitoring or self.config.attn_impl == "debug-skip")
-        if (plain and FUSE_ROPE and x.is_cuda and self.config.clip_qkv is None and self.Wqkv.bias is None
+        cfg = self.config
+        post = cfg.center_attention or cfg.debias_attention
+        softcap = 20.0 if cfg.attn_impl == "flex-attention-soft-cap" else 0.0
+        plain = not (cfg.qk_norm or self.monitoring or cfg.attn_impl == "debug-skip" or softcap)
+        if (plain and not post and FUSE_ROPE and x.is_cuda and self.config.clip_qkv is None and self.Wqkv.bias is None
                 and self.config.rope_settings.use_rope):
             # bias + rotation ride in the epilogue of the QKV GEMM
             y = ops.qkv_rope_attention(x, self.Wqkv.weight, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
@@ -188,18 +219,26 @@ class CausalSelfAttention(nn.Module):
             qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
         if not self.config.rope_settings.use_rope:
             cos, sin = torch.ones_like(cos), torch.zeros_like(sin)
-        plain = not (self.config.qk_norm or self.monitoring or self.config.attn_impl == "debug-skip")
         if plain:
             y = ops.rope_attention(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+            if post:     # the providers' post-operations need the (un-rotated) values beside the attention output
+                wq, wk = self.n_head * self.head_dim, self.n_kv * self.head_dim
+                v = qkv[..., wq + wk:].reshape(B, S, self.n_kv, self.head_dim)
+                y = _center_debias(y.reshape(B, S, self.n_head, self.head_dim), v, self.n_head, cfg.center_attention,
+                                   cfg.debias_attention).reshape(B, S, E)
             return self.proj(y)
         q, k, v = _split_rope(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
         if self.config.qk_norm:
             q = F.rms_norm(q, (q.shape[-1],))
             k = F.rms_norm(k, (k.shape[-1],))
         if self.config.attn_impl == "debug-skip":
-            y = q  # attention bypass for pure-GEMM sanity models
+            # attention bypass for pure-GEMM sanity models: the values pass through (recpre/attention_backends/
+            # interface.py:37-39)
+            y = v if self.n_kv == self.n_head else v.repeat_interleave(self.n_head // self.n_kv, dim=2)
         else:
-            y = _dense_attention(q, k, v)
+            y = _dense_attention(q, k, v, softcap)
+            if post:
+                y = _center_debias(y, v, self.n_head, cfg.center_attention, cfg.debias_attention)
         if self.monitoring:
             self._monitor(q, k)
         return self.proj(y.reshape(B, S, E))

@@ -17,6 +17,26 @@ import yaml
 
 
 @dataclass
+class HuggingfaceConfig:
+    """A stock Hugging Face architecture as the training model (``model_impl: huggingface`` in the reference,
+    recpre/settings.py:14-43): built from its config (``checkpoint`` folder or hub ``name``), random weights.  It trains
+    through the engine's ``torch`` mode (library kernels); the native kernels serve the recurrent model family."""
+    name: str
+    checkpoint: Optional[str] = None
+    block_size: Optional[int] = None
+    strategy: Optional[str] = None
+    abacus_ids: list = field(default_factory=lambda: list(range(10)))
+
+    def construct_model(self, objective=None, gradient_checkpointing: bool = False, **kwargs):
+        from transformers import AutoConfig, AutoModelForCausalLM
+
+        model = AutoModelForCausalLM.from_config(AutoConfig.from_pretrained(self.checkpoint or self.name))
+        if gradient_checkpointing:
+            model.gradient_checkpointing_enable()
+        return model
+
+
+@dataclass
 class DataEntry:
     type: str = "rngds"  # hfds | pqds | pqds-pure | rngds
     prefix: str = ""

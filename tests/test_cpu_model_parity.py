@@ -204,3 +204,50 @@ def test_rotary_table_stays_fp32_under_dtype_casts():
     assert model.freqs_cis.dtype == torch.float32 and torch.equal(model.freqs_cis, before)
     cos, sin = model._rope(8, None)
     assert cos.dtype == torch.float32 and sin.dtype == torch.float32
+
+
+@needs_ref
+@pytest.mark.parametrize("extra", [dict(center_attention=True), dict(debias_attention=True),
+                                   dict(center_attention=True, debias_attention=True), dict(attn_impl="debug-skip")])
+def test_attention_provider_options_match_reference(extra):
+    """The attention providers' options: value centering, causal-mean debiasing, and the attention bypass of the
+    pure-GEMM sanity models -- same loss and gradients as the reference's ``sdpa`` provider with those options."""
+    torch.manual_seed(0)
+    kw = dict(TINY, **extra)
+    ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **kw)
+    model = ModelConfig.from_name("nebel-raven-3.5b", **kw).construct_model()
+    model.load_state_dict(ref_model.state_dict())
+    ids, labels = torch.randint(0, 512, (2, 64)), torch.randint(0, 512, (2, 64))
+    ref_model.config.state_init = model.config.state_init = "zero"
+    pair = torch.tensor([1, 2])
+    a = ref_model(ids, labels=labels, num_steps_pair=pair)
+    b = model(ids, labels=labels, num_steps_pair=pair)
+    assert torch.allclose(a["loss"], b["loss"], rtol=1e-5, atol=1e-6), (a["loss"].item(), b["loss"].item())
+    a["loss"].backward()
+    b["loss"].backward()
+    theirs = dict(ref_model.named_parameters())
+    for n, p in model.named_parameters():
+        if theirs[n].grad is None:
+            assert p.grad is None or p.grad.abs().max() == 0, n
+            continue
+        assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-4, atol=1e-7), n
+
+
+def test_soft_capped_attention_logits():
+    """``attn_impl: flex-attention-soft-cap``: logits squashed to 20 tanh(logit / 20) before the softmax."""
+    from recurrent_pretraining_b200.models.blocks import _dense_attention
+    from recurrent_pretraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 16, 2, 8) * s for s in (6.0, 6.0, 1.0))
+    capped = _dense_attention(q, k, v, softcap=20.0)
+    s = (q.transpose(1, 2) @ k.transpose(1, 2).transpose(-1, -2)) / math.sqrt(8)
+    s = 20.0 * torch.tanh(s / 20.0)
+    s = s.masked_fill(torch.ones(16, 16, dtype=torch.bool).triu(1), float("-inf"))
+    want = (torch.softmax(s, -1) @ v.transpose(1, 2)).transpose(1, 2)
+    assert torch.allclose(capped, want, atol=1e-5)
+    assert not torch.allclose(capped, ref.causal_attention(q, k, v), atol=1e-3)   # large logits: the cap matters
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **dict(TINY, attn_impl="flex-attention-soft-cap"))
+    model = cfg.construct_model()
+    ids = torch.randint(0, 512, (1, 33))
+    assert torch.isfinite(model(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=torch.tensor([1, 1]))["loss"])
