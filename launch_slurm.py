@@ -42,6 +42,46 @@ def nccl_environment(disable_net_gdr: bool = False, debug: bool = False) -> dict
     return env
 
 
+def snapshot_working_tree(dest_dir: str | None = None, name: str = "repo_snapshot") -> str:
+    """Freeze the code a queued job will run: tar the tracked and untracked-but-not-ignored files of this repository
+    (``git ls-files``) into ``<dest_dir>/<name>.tar.gz`` under a top-level folder ``<name>/`` (the reference's
+    ``compress_working_dir``, launch_frontier.py:88-101).  Later edits do not reach the job."""
+    import subprocess
+    import tarfile
+
+    dest_dir = dest_dir or os.environ.get("WRKSPC", os.path.expanduser("~"))
+    os.makedirs(dest_dir, exist_ok=True)
+    out = os.path.join(dest_dir, f"{name}.tar.gz")
+    listing = subprocess.run(["git", "ls-files", "--cached", "--others", "--exclude-standard"], cwd=HERE,
+                             capture_output=True, text=True, check=True).stdout.splitlines()
+    with tarfile.open(out, "w:gz") as tar:
+        for rel in listing:
+            full = os.path.join(HERE, rel)
+            if os.path.isfile(full):
+                tar.add(full, arcname=os.path.join(name, rel))
+    return out
+
+
+def stage_archives_script(archives, local_dir: str = "/tmp/${USER}/${SLURM_JOB_ID}", interval: int = 5) -> str:
+    """Shell lines for the batch script that copy ``.tar.gz`` archives (code snapshot, packed environment) to
+    node-local storage on every node with ``sbcast``, unpack them once per node and hold the other tasks of the node at
+    a file barrier until that is done (launch_frontier.py:104-156)."""
+    archives = [a for a in (archives or []) if a]
+    if not archives:
+        return ""
+    for a in archives:
+        if not a.endswith(".tar.gz"):
+            raise ValueError(f"archive {a!r} is not a .tar.gz file")
+    lines = [f'STAGE_DIR="{local_dir}"', 'srun --ntasks-per-node=1 mkdir -p "$STAGE_DIR"',
+             f'echo "$(date -u) copying {",".join(os.path.basename(a) for a in archives)} to every node"']
+    for a in archives:
+        lines.append(f'sbcast -pf {shlex.quote(a)} "$STAGE_DIR/{os.path.basename(a)}" || {{ echo "sbcast failed"; exit 1; }}')
+    unpack = " && ".join(f'tar -xzf "$STAGE_DIR/{os.path.basename(a)}" -C "$STAGE_DIR"' for a in archives)
+    lines.append(f"srun --ntasks-per-node=1 bash -c '{unpack} && touch \"$STAGE_DIR/.unpacked\"'")
+    lines.append(f'while [ ! -f "$STAGE_DIR/.unpacked" ]; do sleep {interval}; done')
+    return "\n".join(lines) + "\n"
+
+
 @dataclass
 class SlurmJob:
     run_name: str
@@ -60,6 +100,8 @@ class SlurmJob:
     custom_invocation: str | None = None
     dependency: str | None = None
     rebuild_kernels: bool = True
+    archives: list = field(default_factory=list)     # .tar.gz files staged to node-local storage before the run
+    run_from_snapshot: str | None = None             # top-level folder of the staged code snapshot to cd into
 
     @property
     def log_dir(self) -> str:
@@ -98,9 +140,11 @@ class SlurmJob:
         exports = "\n".join(f"export {k}={shlex.quote(str(v))}" for k, v in self.env.items())
         build = (f"srun --nodes=1 --ntasks=1 python -c 'import __graft_entry__ as g; g.build()'\n"
                  if self.rebuild_kernels else "")
+        stage = stage_archives_script(self.archives)
+        workdir = f'"$STAGE_DIR/{self.run_from_snapshot}"' if (stage and self.run_from_snapshot) else shlex.quote(HERE)
         body = f"""
 set -euo pipefail
-cd {shlex.quote(HERE)}
+{stage}cd {workdir}
 {exports}
 export MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)
 export MASTER_PORT=$((20000 + SLURM_JOB_ID % 20000))
@@ -189,6 +233,9 @@ def parse_and_execute(argv=None):
     ap.add_argument("--nccl_debug", action="store_true")
     ap.add_argument("--use_chain", action="store_true", help="chain jobs with afterany instead of a job array")
     ap.add_argument("--no_rebuild", action="store_true", help="skip the kernel library build step")
+    ap.add_argument("--snapshot", action="store_true",
+                    help="freeze the working tree into a tar.gz, stage it to node-local storage and run from there")
+    ap.add_argument("--archives", nargs="*", default=[], help="further .tar.gz files to stage on every node")
     args = ap.parse_args(argv)
 
     name = args.run_name + (f"_{secrets.token_hex(3)}" if args.uuid else "")
@@ -201,7 +248,13 @@ def parse_and_execute(argv=None):
                    partition=args.partition, account=args.account, qos="debug" if args.debug_qos else args.qos,
                    email=args.email, output_dir=args.output_dir or os.path.join(HERE, "outputs"), env=env,
                    custom_invocation=args.custom_invocation, dependency=args.dependency,
-                   rebuild_kernels=not args.no_rebuild)
+                   rebuild_kernels=not args.no_rebuild, archives=list(args.archives))
+    if args.snapshot:
+        snap = f"{name}_code"
+        path = snapshot_working_tree(os.path.join(job.output_dir, name), snap) if not args.dryrun else \
+            os.path.join(job.output_dir, name, f"{snap}.tar.gz")
+        job.archives.insert(0, path)
+        job.run_from_snapshot = snap
     if args.interactive:
         print(interactive(job))
         return job

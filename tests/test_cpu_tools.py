@@ -309,3 +309,23 @@ def test_small_helpers(tmp_path, monkeypatch):
     x, y = torch.randn(5, 8), torch.tensor([1, 2, -100, 4, 15])
     want = torch.nn.functional.cross_entropy(head(x), y, ignore_index=-100)
     assert head(x, y).item() == pytest.approx(want.item(), rel=1e-5)
+
+
+def test_launcher_snapshot_and_staging(tmp_path):
+    """Code snapshot of the working tree and the batch-script lines that stage archives on every node."""
+    import tarfile
+
+    import launch_slurm as L
+
+    snap = L.snapshot_working_tree(str(tmp_path), "snap")
+    names = tarfile.open(snap).getnames()
+    assert "snap/bench.py" in names and "snap/recurrent_pretraining_b200/ops/cuda.py" in names
+    assert not any("_lib/" in n or n.startswith("snap/_work") for n in names)          # ignored files stay out
+    script = L.stage_archives_script([snap, None])
+    assert "sbcast -pf" in script and "tar -xzf" in script and ".unpacked" in script
+    with pytest.raises(ValueError):
+        L.stage_archives_script(["env.zip"])
+    job = L.parse_and_execute(["--config", "launch_configs/nebel_dp_8xb200.yaml", "--nodes", "2", "--snapshot", "--dryrun",
+                               "--output_dir", str(tmp_path / "out"), "--run_name", "t"])
+    text = job.sbatch_text()
+    assert 'cd "$STAGE_DIR/t_code"' in text and "sbcast" in text
