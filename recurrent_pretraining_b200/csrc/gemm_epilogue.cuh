@@ -40,6 +40,8 @@ struct GemmParams {
   int raster;     // m tiles per raster group (see tile_coords); 0 = m fastest
   int early_a;    // the A operand does not depend on the preceding kernel: its first tiles are requested before the
                   // programmatic-dependent-launch wait (no effect without that launch attribute)
+  int tma_c;      // fp32 output modes of the pair kernel: the tile leaves through shared memory and bulk tensor
+                  // stores / reductions (tensor map of C passed beside the operand maps) instead of per-thread accesses
   // OUT_BF16_LSE: partials [M, ceil(N / BN)] float4, target logit [M], labels [M] (int64), scale applied to the logits
   float4* lse_part;
   float* lse_tgt;
@@ -404,6 +406,42 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       p.lse_part[static_cast<size_t>(row) * tiles_n + n0 / BN] = make_float4(lm, ll, le, lq);
       if (lfound) p.lse_tgt[row] = lt;
     }
+  }
+}
+
+// fp32 store / accumulate of one accumulator tile through shared memory: each epilogue warp stages 32 rows x 32 columns
+// (4 KB, 128-byte swizzle) and one lane issues ONE bulk tensor store (OUT_F32) or reduction (OUT_F32_ACC: the add happens
+// at the memory side, the old values never travel to the SM).  Per-thread accesses to a row-per-lane tile touch 32
+// different cache lines per instruction -- with the read-modify-write of the weight gradients they kept the LSU data
+// pipe 44 % busy beside the tensor cores' shared-memory reads; the bulk form moves whole 128-byte rows.
+// ``stage``: this warp's two 4 KB buffers (1024-byte aligned); ``buf`` alternates between them across calls.
+// row0: first global row of this warp's 32 rows.  All 32 lanes must call.
+template <int BN, int MODE>
+__device__ __forceinline__ void epilogue_tile_tma_f32(const GemmParams& p, const CUtensorMap* tmC, uint32_t taddr, int row0,
+                                                      int n0, uint8_t* stage, int lane, int& buf) {
+  static_assert(MODE == OUT_F32 || MODE == OUT_F32_ACC, "fp32 output modes");
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c0, v);
+    tmem_ld_wait();
+    const int col = n0 + c0;
+    if (col >= p.N || row0 >= p.M) continue;   // uniform over the warp; partial boxes are clipped by the copy engine
+    uint8_t* tile = stage + buf * 4096;
+    if (lane == 0) bulk_wait_read_but_one();   // the operation issued two chunks ago has finished reading this buffer
+    __syncwarp();
+    uint8_t* rowp = tile + lane * 128;
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if constexpr (MODE == OUT_F32_ACC) tma_reduce_add_2d(tmC, tile, col, row0);
+      else tma_store_2d(tmC, tile, col, row0);
+      bulk_commit_group();
+    }
+    buf ^= 1;
   }
 }
 

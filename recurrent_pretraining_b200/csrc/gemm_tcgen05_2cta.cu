@@ -16,6 +16,8 @@
 // the pair synchronises with the cluster barrier before tensor memory is released.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -23,6 +25,7 @@ namespace b200 {
 
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                       uint32_t box_rows, uint32_t box_cols);
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows);
 int num_sms();
 
 constexpr int BM2 = 128;   // rows per CTA (256 per pair)
@@ -114,13 +117,18 @@ struct Smem2 {
   static constexpr int B_BYTES = (BN / 2) * BK2 * 2;   // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int C_STAGE_OFFSET = BAR_OFFSET + 1024;          // fp32 output modes: 4 warps x 2 x 4 KB
+  static constexpr int C_STAGE_BYTES = 4 * 2 * 4096;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+  static constexpr int TOTAL_F32 = TOTAL + C_STAGE_BYTES;
 };
 
 template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? 320 : 192, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
-             const __grid_constant__ CUtensorMap tmB, const GemmParams p, const __grid_constant__ AgParams ag) {
+             const __grid_constant__ CUtensorMap tmB, const GemmParams p, const __grid_constant__ AgParams ag,
+             const __grid_constant__ CUtensorMap tmC) {
   using L = Smem2<BN>;
   constexpr int STAGES = L::STAGES;
   constexpr int ACC_STRIDE = 256;
@@ -337,6 +345,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // ------------------------------------------------------------------ epilogue (both CTAs, warps 2..5)
     const int quad = warp & 3;
     uint32_t tcount = 0;
+    constexpr bool F32_MODE = MODE == OUT_F32 || MODE == OUT_F32_ACC;
+    uint8_t* c_stage = smem + L::C_STAGE_OFFSET + quad * 8192;   // only backed by memory in the fp32 output modes
+    int c_buf = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
@@ -347,10 +358,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_STRIDE + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      if constexpr (F32_MODE) {
+        if (p.tma_c) epilogue_tile_tma_f32<BN_OUT, MODE>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
+        else epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      } else {
+        epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+    }
+    if constexpr (F32_MODE) {
+      if (p.tma_c && lane == 0) bulk_wait_all();   // this lane's stores / reductions have reached memory
     }
   }
 
@@ -367,16 +386,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
 template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, const GemmParams& p,
-                   cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr) {
+                   cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr, const CUtensorMap* tcp = nullptr) {
   using L = Smem2<BN>;
   auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE, AG>;
+  constexpr int SMEM = (MODE == OUT_F32 || MODE == OUT_F32_ACC) ? L::TOTAL_F32 : L::TOTAL;
   static int max_clusters = -1;
   if (max_clusters < 0) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_sms() & ~1, 1, 1);
     cfg.blockDim = dim3(AG ? 320 : 192, 1, 1);
-    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.dynamicSmemBytes = SMEM;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
     max_clusters = n;
@@ -388,7 +408,9 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
   if (clusters <= 0) return 0;
   AgParams ag = {};
   if (agp) ag = *agp;
-  kern<<<2 * clusters, AG ? 320 : 192, L::TOTAL, stream>>>(ta, ta2, tb, p, ag);
+  GemmParams pp = p;
+  if (!tcp) pp.tma_c = 0;
+  kern<<<2 * clusters, AG ? 320 : 192, SMEM, stream>>>(ta, ta2, tb, pp, ag, tcp ? *tcp : ta);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -414,11 +436,23 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
   else rc = make_tmap_2d_bf16(&tb, B, K, p.N, ldb, BK2, 64);
   if (rc) return rc;
 
+  // fp32 output of 256-wide tiles leaves through bulk tensor stores / reductions when C can be described by a tensor
+  // map (16-byte aligned base and row pitch); B200_GEMM_TMA_C=0 keeps the per-thread epilogue
+  CUtensorMap tc;
+  const CUtensorMap* tcp = nullptr;
+  GemmParams pc = p;
+  pc.tma_c = 0;
+  static const bool tma_c_on = [] { const char* e = getenv("B200_GEMM_TMA_C"); return !(e && e[0] == '0'); }();
+  if ((out_mode == OUT_F32 || out_mode == OUT_F32_ACC) && bn == 256 && tma_c_on &&
+      make_tmap_2d_f32(&tc, p.C, p.M, p.N, p.ldc, 32) == 0) {
+    tcp = &tc;
+    pc.tma_c = 1;
+  }
 #define DISPATCH2(BN_, AMN_, BMN_)                                                                  \
   switch (out_mode) {                                                                               \
     case OUT_BF16: return launch2<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, p, st, max_ctas);         \
-    case OUT_F32: return launch2<BN_, AMN_, BMN_, OUT_F32>(ta, ta2, tb, p, st, max_ctas);           \
-    case OUT_F32_ACC: return launch2<BN_, AMN_, BMN_, OUT_F32_ACC>(ta, ta2, tb, p, st, max_ctas);   \
+    case OUT_F32: return launch2<BN_, AMN_, BMN_, OUT_F32>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);         \
+    case OUT_F32_ACC: return launch2<BN_, AMN_, BMN_, OUT_F32_ACC>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp); \
     case OUT_BF16_RESID: return launch2<BN_, AMN_, BMN_, OUT_BF16_RESID>(ta, ta2, tb, p, st, max_ctas); \
     default: return -100;                                                                           \
   }

@@ -405,3 +405,22 @@ def test_gemm_flagship_shapes(C, M, N, K, kind):
     torch.cuda.synchronize()
     _close(got, want, 2e-2, 0.02 * float(want.abs().max()))
     assert C.check_device_status() == 0
+
+
+@pytest.mark.parametrize("T,N,K", [(512, 1000, 264), (300, 5280, 520), (4096, 776, 1096)])
+def test_gemm_tn_fp32_tiles_through_bulk_stores(C, T, N, K):
+    """Weight-gradient GEMM on the pair kernel (M >= 256): fp32 tiles leave through shared memory and bulk tensor stores
+    (first contribution) / reductions (accumulation).  Ragged extents in both dimensions, a column-slice output view
+    (row pitch larger than the width, as the adapter halves), and values that were there before."""
+    dy, x = _rand(T, N), _rand(T, K)
+    want = dy.float().T @ x.float()
+    tol = 1e-2 * math.sqrt(T)
+    full = torch.full((N, 2 * K + 8), 3.0, device="cuda")
+    view = full[:, 8:8 + K]
+    C.gemm_tn(dy, x, out=view, accumulate=False)
+    _close(view, want, 1e-2, tol)
+    assert torch.all(full[:, :8] == 3.0) and torch.all(full[:, 8 + K:] == 3.0)     # nothing outside the view
+    C.gemm_tn(dy, x, out=view, accumulate=True)
+    _close(view, 2 * want, 1e-2, 2 * tol)
+    assert torch.all(full[:, :8] == 3.0) and torch.all(full[:, 8 + K:] == 3.0)
+    assert C.check_device_status() == 0
