@@ -70,6 +70,63 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   ni = r / rows;
 }
 
+// q/k bias + rotation of one chunk of up to 32 accumulator columns (``f``, fp32) of global row ``row`` starting at
+// global column ``col``: interleaved pairs (2j, 2j+1) of every q/k head, (x0, x1) -> (x0 cos - x1 sin, x1 cos + x0 sin)
+// after the bias; columns at or beyond rope_width (the v part) are left alone.
+__device__ __forceinline__ void rope_chunk(const GemmParams& p, int row, int col, int width, float (&f)[32]) {
+  if (col < p.rope_width) {
+    const int half = p.rope_D >> 1;
+    const float* ct = p.rope_cos + static_cast<size_t>(row % p.rope_S) * half;
+    const float* st = p.rope_sin + static_cast<size_t>(row % p.rope_S) * half;
+    int d = col % p.rope_D;     // channel of the first column of this chunk inside its head (even)
+    // Eight columns (four pairs) at a time with 16-byte loads of the tables and the bias whenever the group does
+    // not straddle a head boundary and everything is 16-byte aligned (head dims that are multiples of 8, tile
+    // starts that are multiples of 8: the flagship's 96 / 240); scalar loads otherwise.
+    const bool vec8 = ((p.rope_D & 7) == 0) && ((col & 7) == 0) && ((half & 3) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.rope_cos) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.rope_sin) & 15) == 0) &&
+                      (!p.rope_bias || (reinterpret_cast<uintptr_t>(p.rope_bias) & 15) == 0);
+#pragma unroll
+    for (int i0 = 0; i0 < 32; i0 += 8) {
+      if (i0 < width && col + i0 + 8 <= p.rope_width && vec8) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(ct + (d >> 1)));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(st + (d >> 1)));
+        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+        if (p.rope_bias) {
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0));
+          const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0 + 4));
+          f[i0] += b0.x; f[i0 + 1] += b0.y; f[i0 + 2] += b0.z; f[i0 + 3] += b0.w;
+          f[i0 + 4] += b1.x; f[i0 + 5] += b1.y; f[i0 + 6] += b1.z; f[i0 + 7] += b1.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float x0 = f[i0 + 2 * j], x1 = f[i0 + 2 * j + 1];
+          f[i0 + 2 * j] = x0 * cs[j] - x1 * sn[j];
+          f[i0 + 2 * j + 1] = x1 * cs[j] + x0 * sn[j];
+        }
+        d += 8;
+        if (d >= p.rope_D) d -= p.rope_D;
+      } else {
+#pragma unroll
+        for (int i = i0; i < i0 + 8; i += 2) {
+          if (i < width && col + i < p.rope_width) {
+            float x0 = f[i], x1 = f[i + 1];
+            if (p.rope_bias) {
+              x0 += __ldg(p.rope_bias + col + i);
+              x1 += __ldg(p.rope_bias + col + i + 1);
+            }
+            const float cs = __ldg(ct + (d >> 1)), sn = __ldg(st + (d >> 1));
+            f[i] = x0 * cs - x1 * sn;
+            f[i + 1] = x1 * cs + x0 * sn;
+          }
+          d += 2;
+          if (d >= p.rope_D) d -= p.rope_D;
+        }
+      }
+    }
+  }
+}
+
 // taddr: TMEM address of (this warp's lane quadrant, first accumulator column); row: global row of this thread;
 // n0: first global column of the tile.  All 32 lanes must call (tcgen05.ld is warp-collective).
 template <int BN, int MODE>
@@ -262,60 +319,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
             if (i < nvalid) f[i] += bf2f(rrow[i]);
         }
       }
-      if constexpr (MODE == OUT_BF16_ROPE) {
-        // interleaved pairs (2j, 2j+1) of every q/k head: (x0, x1) -> (x0 cos - x1 sin, x1 cos + x0 sin) after the bias
-        if (col < p.rope_width) {
-          const int half = p.rope_D >> 1;
-          const float* ct = p.rope_cos + static_cast<size_t>(row % p.rope_S) * half;
-          const float* st = p.rope_sin + static_cast<size_t>(row % p.rope_S) * half;
-          int d = col % p.rope_D;     // channel of the first column of this chunk inside its head (even)
-          // Eight columns (four pairs) at a time with 16-byte loads of the tables and the bias whenever the group does
-          // not straddle a head boundary and everything is 16-byte aligned (head dims that are multiples of 8, tile
-          // starts that are multiples of 8: the flagship's 96 / 240); scalar loads otherwise.
-          const bool vec8 = ((p.rope_D & 7) == 0) && ((col & 7) == 0) && ((half & 3) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(p.rope_cos) & 15) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(p.rope_sin) & 15) == 0) &&
-                            (!p.rope_bias || (reinterpret_cast<uintptr_t>(p.rope_bias) & 15) == 0);
-#pragma unroll
-          for (int i0 = 0; i0 < 32; i0 += 8) {
-            if (i0 < width && col + i0 + 8 <= p.rope_width && vec8) {
-              const float4 c4 = __ldg(reinterpret_cast<const float4*>(ct + (d >> 1)));
-              const float4 s4 = __ldg(reinterpret_cast<const float4*>(st + (d >> 1)));
-              const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-              if (p.rope_bias) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0));
-                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.rope_bias + col + i0 + 4));
-                f[i0] += b0.x; f[i0 + 1] += b0.y; f[i0 + 2] += b0.z; f[i0 + 3] += b0.w;
-                f[i0 + 4] += b1.x; f[i0 + 5] += b1.y; f[i0 + 6] += b1.z; f[i0 + 7] += b1.w;
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float x0 = f[i0 + 2 * j], x1 = f[i0 + 2 * j + 1];
-                f[i0 + 2 * j] = x0 * cs[j] - x1 * sn[j];
-                f[i0 + 2 * j + 1] = x1 * cs[j] + x0 * sn[j];
-              }
-              d += 8;
-              if (d >= p.rope_D) d -= p.rope_D;
-            } else {
-#pragma unroll
-              for (int i = i0; i < i0 + 8; i += 2) {
-                if (i < width && col + i < p.rope_width) {
-                  float x0 = f[i], x1 = f[i + 1];
-                  if (p.rope_bias) {
-                    x0 += __ldg(p.rope_bias + col + i);
-                    x1 += __ldg(p.rope_bias + col + i + 1);
-                  }
-                  const float cs = __ldg(ct + (d >> 1)), sn = __ldg(st + (d >> 1));
-                  f[i] = x0 * cs - x1 * sn;
-                  f[i + 1] = x1 * cs + x0 * sn;
-                }
-                d += 2;
-                if (d >= p.rope_D) d -= p.rope_D;
-              }
-            }
-          }
-        }
-      }
+      if constexpr (MODE == OUT_BF16_ROPE) rope_chunk(p, row, col, width, f);
       if constexpr (MODE == OUT_BF16_LSE) {
         float cm = -INFINITY;
 #pragma unroll
@@ -439,6 +443,191 @@ __device__ __forceinline__ void epilogue_tile_tma_f32(const GemmParams& p, const
     if (lane == 0) {
       if constexpr (MODE == OUT_F32_ACC) tma_reduce_add_2d(tmC, tile, col, row0);
       else tma_store_2d(tmC, tile, col, row0);
+      bulk_commit_group();
+    }
+    buf ^= 1;
+  }
+}
+
+// bf16 store of one accumulator tile through shared memory: 64 columns (one 128-byte row per lane) at a time, one bulk
+// tensor store per 32 x 64 box; a tile width that is not a multiple of 64 (240 = 3 x 64 + 48) finishes with per-thread
+// stores.  Same staging buffers and rules as epilogue_tile_tma_f32.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma_bf16(const GemmParams& p, const CUtensorMap* tmC, uint32_t taddr, int row0,
+                                                       int n0, uint8_t* stage, int lane, int& buf) {
+  constexpr int FULL = BN / 64 * 64;
+#pragma unroll 1
+  for (int c0 = 0; c0 < FULL; c0 += 64) {
+    uint32_t v[32], w[32];
+    tmem_ld_32x32(taddr + c0, v);
+    tmem_ld_32x32(taddr + c0 + 32, w);
+    tmem_ld_wait();
+    const int col = n0 + c0;
+    if (col >= p.N || row0 >= p.M) continue;
+    uint8_t* tile = stage + buf * 4096;
+    if (lane == 0) bulk_wait_read_but_one();
+    __syncwarp();
+    uint8_t* rowp = tile + lane * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+          make_uint4(pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                     pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                     pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                     pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+      *reinterpret_cast<uint4*>(rowp + (((q + 4) ^ (lane & 7)) << 4)) =
+          make_uint4(pack_bf16x2(__uint_as_float(w[8 * q]), __uint_as_float(w[8 * q + 1])),
+                     pack_bf16x2(__uint_as_float(w[8 * q + 2]), __uint_as_float(w[8 * q + 3])),
+                     pack_bf16x2(__uint_as_float(w[8 * q + 4]), __uint_as_float(w[8 * q + 5])),
+                     pack_bf16x2(__uint_as_float(w[8 * q + 6]), __uint_as_float(w[8 * q + 7])));
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmC, tile, col, row0);
+      bulk_commit_group();
+    }
+    buf ^= 1;
+  }
+  if constexpr (FULL < BN) {
+    // the remaining BN - FULL columns (48 of a 240-wide tile): per-thread 16-byte stores
+    const int row = row0 + lane;
+#pragma unroll 1
+    for (int c0 = FULL; c0 < BN; c0 += 16) {
+      uint32_t v[16];
+      tmem_ld_32x16(taddr + c0, v);
+      tmem_ld_wait();
+      const int col = n0 + c0;
+      if (row >= p.M || col >= p.N) continue;
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+      const int nvalid = min(16, p.N - col);
+      if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          reinterpret_cast<uint4*>(crow)[q] =
+              make_uint4(pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                         pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                         pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                         pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < nvalid) crow[i] = f2bf(__uint_as_float(v[i]));
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void stage_row_bf16x64(uint8_t* tile, int lane, const uint32_t (&lo)[16], const uint32_t (&hi)[16]) {
+  uint8_t* rowp = tile + lane * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = make_uint4(lo[4 * q], lo[4 * q + 1], lo[4 * q + 2], lo[4 * q + 3]);
+    *reinterpret_cast<uint4*>(rowp + (((q + 4) ^ (lane & 7)) << 4)) =
+        make_uint4(hi[4 * q], hi[4 * q + 1], hi[4 * q + 2], hi[4 * q + 3]);
+  }
+}
+
+// QKV projection: bias + rotation in registers, then the staged bf16 store (64 columns per box; the 48-column rest of a
+// 240-wide tile by per-thread stores).
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma_rope(const GemmParams& p, const CUtensorMap* tmC, uint32_t taddr, int row0,
+                                                       int n0, uint8_t* stage, int lane, int& buf) {
+  constexpr int FULL = BN / 64 * 64;
+  const int row = row0 + lane;
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c0 = 0; c0 < FULL; c0 += 64) {
+    uint32_t packed[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c0 + 32 * hh, v);
+      tmem_ld_wait();
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+      const int col = n0 + c0 + 32 * hh;
+      if (row_ok && col < p.N) rope_chunk(p, row, col, 32, f);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) packed[hh][i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
+    }
+    const int col = n0 + c0;
+    if (col >= p.N || row0 >= p.M) continue;
+    uint8_t* tile = stage + buf * 4096;
+    if (lane == 0) bulk_wait_read_but_one();
+    __syncwarp();
+    stage_row_bf16x64(tile, lane, packed[0], packed[1]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmC, tile, col, row0);
+      bulk_commit_group();
+    }
+    buf ^= 1;
+  }
+  if constexpr (FULL < BN) {
+#pragma unroll 1
+    for (int c0 = FULL; c0 < BN; c0 += 16) {
+      uint32_t v[16];
+      tmem_ld_32x16(taddr + c0, v);
+      tmem_ld_wait();
+      const int col = n0 + c0;
+      if (!row_ok || col >= p.N) continue;
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+#pragma unroll
+      for (int i = 16; i < 32; ++i) f[i] = 0.f;
+      rope_chunk(p, row, col, 16, f);
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+      const int nvalid = min(16, p.N - col);
+      if (nvalid == 16 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          reinterpret_cast<uint4*>(crow)[q] = make_uint4(pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
+                                                         pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < nvalid) crow[i] = f2bf(f[i]);
+      }
+    }
+  }
+}
+
+// Gate-up projection without stored pre-activation: silu(gate) * up of 64 output columns at a time (gate in accumulator
+// columns [0, BN), up in [BN, 2 BN)), staged and stored as one box.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma_swiglu(const GemmParams& p, const CUtensorMap* tmC, uint32_t taddr, int row0,
+                                                         int n0, uint8_t* stage, int lane, int& buf) {
+  static_assert(BN % 64 == 0, "SwiGLU tiles are 128 output columns wide");
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 64) {
+    uint32_t packed[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(taddr + c0 + 32 * hh, g);
+      tmem_ld_32x32(taddr + BN + c0 + 32 * hh, u);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+        packed[hh][i] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * __uint_as_float(u[2 * i]),
+                                    g1 / (1.f + __expf(-g1)) * __uint_as_float(u[2 * i + 1]));
+      }
+    }
+    const int col = n0 + c0;
+    if (col >= p.N || row0 >= p.M) continue;
+    uint8_t* tile = stage + buf * 4096;
+    if (lane == 0) bulk_wait_read_but_one();
+    __syncwarp();
+    stage_row_bf16x64(tile, lane, packed[0], packed[1]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmC, tile, col, row0);
       bulk_commit_group();
     }
     buf ^= 1;

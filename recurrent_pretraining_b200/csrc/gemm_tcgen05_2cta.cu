@@ -346,6 +346,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int quad = warp & 3;
     uint32_t tcount = 0;
     constexpr bool F32_MODE = MODE == OUT_F32 || MODE == OUT_F32_ACC;
+    // modes with a shared-memory staged epilogue
+    constexpr bool STAGED = (F32_MODE || MODE == OUT_BF16 || MODE == OUT_BF16_ROPE || MODE == OUT_SWIGLU) && !AG;
     uint8_t* c_stage = smem + L::C_STAGE_OFFSET + quad * 8192;   // only backed by memory in the fp32 output modes
     int c_buf = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
@@ -361,6 +363,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       if constexpr (F32_MODE) {
         if (p.tma_c) epilogue_tile_tma_f32<BN_OUT, MODE>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
         else epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+      } else if constexpr (STAGED) {
+        if (!p.tma_c) epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
+        else if constexpr (MODE == OUT_BF16_ROPE)
+          epilogue_tile_tma_rope<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
+        else if constexpr (MODE == OUT_SWIGLU)
+          epilogue_tile_tma_swiglu<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
+        else epilogue_tile_tma_bf16<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
       } else {
         epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
       }
@@ -368,7 +377,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
     }
-    if constexpr (F32_MODE) {
+    if constexpr (STAGED) {
       if (p.tma_c && lane == 0) bulk_wait_all();   // this lane's stores / reductions have reached memory
     }
   }
@@ -389,7 +398,8 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
                    cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr, const CUtensorMap* tcp = nullptr) {
   using L = Smem2<BN>;
   auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE, AG>;
-  constexpr int SMEM = (MODE == OUT_F32 || MODE == OUT_F32_ACC) ? L::TOTAL_F32 : L::TOTAL;
+  constexpr int SMEM = ((MODE == OUT_F32 || MODE == OUT_F32_ACC || MODE == OUT_BF16 || MODE == OUT_BF16_ROPE ||
+                         MODE == OUT_SWIGLU) && !AG) ? L::TOTAL_F32 : L::TOTAL;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
@@ -448,15 +458,21 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     tcp = &tc;
     pc.tma_c = 1;
   }
+  static const bool tma_c16_on = [] { const char* e = getenv("B200_GEMM_TMA_C16"); return !(e && e[0] == '0'); }();
+  if ((out_mode == OUT_BF16 || out_mode == OUT_BF16_ROPE || out_mode == OUT_SWIGLU) && tma_c_on && tma_c16_on &&
+      make_tmap_2d_bf16(&tc, p.C, p.M, p.N, p.ldc, 32, 64) == 0) {
+    tcp = &tc;
+    pc.tma_c = 1;
+  }
 #define DISPATCH2(BN_, AMN_, BMN_)                                                                  \
   switch (out_mode) {                                                                               \
-    case OUT_BF16: return launch2<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, p, st, max_ctas);         \
+    case OUT_BF16: return launch2<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);       \
     case OUT_F32: return launch2<BN_, AMN_, BMN_, OUT_F32>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);         \
     case OUT_F32_ACC: return launch2<BN_, AMN_, BMN_, OUT_F32_ACC>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp); \
     case OUT_BF16_RESID: return launch2<BN_, AMN_, BMN_, OUT_BF16_RESID>(ta, ta2, tb, p, st, max_ctas); \
     default: return -100;                                                                           \
   }
-  if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);
   if (out_mode == OUT_SWIGLU_SAVE) return launch2<256, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);
   if (out_mode == OUT_BF16_LSE) {
     if (a_mn || b_mn || bn != 256) return -100;
@@ -468,8 +484,8 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
   }
   if (out_mode == OUT_BF16_ROPE) {
     if (a_mn || b_mn) return -100;
-    if (bn == 240) return launch2<240, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
-    return launch2<256, false, false, OUT_BF16_ROPE>(ta, ta2, tb, p, st, max_ctas);
+    if (bn == 240) return launch2<240, false, false, OUT_BF16_ROPE>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);
+    return launch2<256, false, false, OUT_BF16_ROPE>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);
   }
   if (!a_mn && !b_mn) {
     if (bn == 256) { DISPATCH2(256, false, false) }
