@@ -634,4 +634,125 @@ __device__ __forceinline__ void epilogue_tile_tma_swiglu(const GemmParams& p, co
   }
 }
 
+__device__ __forceinline__ void staged_store_bf16x64(const CUtensorMap* tm, uint8_t* stage, int& buf, int lane, int x, int y,
+                                                     const uint32_t (&lo)[16], const uint32_t (&hi)[16]) {
+  uint8_t* tile = stage + buf * 4096;
+  if (lane == 0) bulk_wait_read_but_one();
+  __syncwarp();
+  stage_row_bf16x64(tile, lane, lo, hi);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tm, tile, x, y);
+    bulk_commit_group();
+  }
+  buf ^= 1;
+}
+
+// Gate-up projection of the training forward pass: the gated product (tmC: [M, I]) and the bf16 pre-activation
+// [gate | up] of 64 output columns at a time (tmG / tmU: the two [M, I] halves of the [M, 2 I] buffer as tensors of their
+// own, so that a box at the right edge of the gate half is clipped there and cannot reach into the up half).  Three passes over the accumulator columns keep the
+// register footprint of one output at a time; tensor-memory reads are cheap next to per-thread global stores.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma_swiglu_save(const GemmParams& p, const CUtensorMap* tmC, const CUtensorMap* tmG,
+                                                              const CUtensorMap* tmU, uint32_t taddr, int row0, int n0,
+                                                              uint8_t* stage, int lane, int& buf) {
+  static_assert(BN % 64 == 0, "SwiGLU tiles are 128 output columns wide");
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 64) {
+    const int col = n0 + c0;
+    const bool live = col < p.N && row0 < p.M;       // uniform over the warp
+    uint32_t packed[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(taddr + c0 + 32 * hh, g);
+      tmem_ld_32x32(taddr + BN + c0 + 32 * hh, u);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+        packed[hh][i] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * __uint_as_float(u[2 * i]),
+                                    g1 / (1.f + __expf(-g1)) * __uint_as_float(u[2 * i + 1]));
+      }
+    }
+    if (live) staged_store_bf16x64(tmC, stage, buf, lane, col, row0, packed[0], packed[1]);
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {           // 0: gate, 1: up
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + part * BN + c0 + 32 * hh, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[hh][i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      }
+      if (live) staged_store_bf16x64(part == 0 ? tmG : tmU, stage, buf, lane, col, row0, packed[0], packed[1]);
+    }
+  }
+}
+
+// Down-projection input gradient with the gate's derivative: dy in the accumulator, g / u from the saved pre-activation
+// (per-thread 16-byte loads), dg and du staged and stored as boxes of the two [M, I] halves of the output (tmG, tmU).
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma_dswiglu(const GemmParams& p, const CUtensorMap* tmG, const CUtensorMap* tmU,
+                                                          uint32_t taddr, int row0, int n0, uint8_t* stage, int lane,
+                                                          int& buf) {
+  static_assert(BN % 64 == 0, "256-wide tiles");
+  const int row = row0 + lane;
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 64) {
+    const int col = n0 + c0;
+    const bool live = col < p.N && row0 < p.M;
+    uint32_t pg[2][16], pu[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int c = col + 32 * hh;
+      const __nv_bfloat16* hrow = p.resid + static_cast<size_t>(row_ok ? row : 0) * p.ld_resid + c;
+      const bool in = row_ok && c + 32 <= p.N;
+      uint4 gq[4], uq[4];
+      if (in) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          gq[q] = reinterpret_cast<const uint4*>(hrow)[q];
+          uq[q] = reinterpret_cast<const uint4*>(hrow + p.swiglu_n)[q];
+        }
+      }
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c0 + 32 * hh, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t gw[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w}, uw[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 g2 = make_float2(0.f, 0.f), u2 = make_float2(0.f, 0.f);
+          if (in) {
+            g2 = unpack_bf16x2(gw[i]);
+            u2 = unpack_bf16x2(uw[i]);
+          } else if (row_ok) {                        // ragged right edge: element-wise
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int cc = c + 8 * q + 2 * i + j;
+              if (cc < p.N) {
+                const float gv = bf2f(p.resid[static_cast<size_t>(row) * p.ld_resid + cc]);
+                const float uv = bf2f(p.resid[static_cast<size_t>(row) * p.ld_resid + p.swiglu_n + cc]);
+                if (j == 0) { g2.x = gv; u2.x = uv; } else { g2.y = gv; u2.y = uv; }
+              }
+            }
+          }
+          const float dy0 = __uint_as_float(v[8 * q + 2 * i]), dy1 = __uint_as_float(v[8 * q + 2 * i + 1]);
+          const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+          pg[hh][4 * q + i] = pack_bf16x2(dy0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), dy1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+          pu[hh][4 * q + i] = pack_bf16x2(dy0 * g2.x * s0, dy1 * g2.y * s1);
+        }
+      }
+    }
+    if (!live) continue;
+    staged_store_bf16x64(tmG, stage, buf, lane, col, row0, pg[0], pg[1]);
+    staged_store_bf16x64(tmU, stage, buf, lane, col, row0, pu[0], pu[1]);
+  }
+}
+
 }  // namespace b200

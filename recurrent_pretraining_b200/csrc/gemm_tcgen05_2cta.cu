@@ -128,7 +128,8 @@ template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? 320 : 192, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
              const __grid_constant__ CUtensorMap tmB, const GemmParams p, const __grid_constant__ AgParams ag,
-             const __grid_constant__ CUtensorMap tmC) {
+             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
+             const __grid_constant__ CUtensorMap tmC3) {
   using L = Smem2<BN>;
   constexpr int STAGES = L::STAGES;
   constexpr int ACC_STRIDE = 256;
@@ -347,7 +348,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint32_t tcount = 0;
     constexpr bool F32_MODE = MODE == OUT_F32 || MODE == OUT_F32_ACC;
     // modes with a shared-memory staged epilogue
-    constexpr bool STAGED = (F32_MODE || MODE == OUT_BF16 || MODE == OUT_BF16_ROPE || MODE == OUT_SWIGLU) && !AG;
+    constexpr bool STAGED = (F32_MODE || MODE == OUT_BF16 || MODE == OUT_BF16_ROPE || MODE == OUT_SWIGLU ||
+                             MODE == OUT_SWIGLU_SAVE || MODE == OUT_DSWIGLU) && !AG;
     uint8_t* c_stage = smem + L::C_STAGE_OFFSET + quad * 8192;   // only backed by memory in the fp32 output modes
     int c_buf = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
@@ -369,6 +371,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           epilogue_tile_tma_rope<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
         else if constexpr (MODE == OUT_SWIGLU)
           epilogue_tile_tma_swiglu<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
+        else if constexpr (MODE == OUT_SWIGLU_SAVE)
+          epilogue_tile_tma_swiglu_save<BN_OUT>(p, &tmC, &tmC2, &tmC3, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
+        else if constexpr (MODE == OUT_DSWIGLU)
+          epilogue_tile_tma_dswiglu<BN_OUT>(p, &tmC, &tmC2, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
         else epilogue_tile_tma_bf16<BN_OUT>(p, &tmC, taddr, m0 + quad * 32, n0, c_stage, lane, c_buf);
       } else {
         epilogue_tile<BN_OUT, MODE>(p, taddr, m0 + quad * 32 + lane, n0);
@@ -395,11 +401,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
 template <int BN, bool A_MN, bool B_MN, int MODE, bool AG = false>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tb, const GemmParams& p,
-                   cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr, const CUtensorMap* tcp = nullptr) {
+                   cudaStream_t stream, int max_ctas, const AgParams* agp = nullptr, const CUtensorMap* tcp = nullptr,
+                   const CUtensorMap* tcp2 = nullptr, const CUtensorMap* tcp3 = nullptr) {
   using L = Smem2<BN>;
   auto kern = gemm2_kernel<BN, A_MN, B_MN, MODE, AG>;
   constexpr int SMEM = ((MODE == OUT_F32 || MODE == OUT_F32_ACC || MODE == OUT_BF16 || MODE == OUT_BF16_ROPE ||
-                         MODE == OUT_SWIGLU) && !AG) ? L::TOTAL_F32 : L::TOTAL;
+                         MODE == OUT_SWIGLU || MODE == OUT_SWIGLU_SAVE || MODE == OUT_DSWIGLU) && !AG)
+                            ? L::TOTAL_F32 : L::TOTAL;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
@@ -420,7 +428,8 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensor
   if (agp) ag = *agp;
   GemmParams pp = p;
   if (!tcp) pp.tma_c = 0;
-  kern<<<2 * clusters, AG ? 320 : 192, SMEM, stream>>>(ta, ta2, tb, pp, ag, tcp ? *tcp : ta);
+  kern<<<2 * clusters, AG ? 320 : 192, SMEM, stream>>>(ta, ta2, tb, pp, ag, tcp ? *tcp : ta, tcp2 ? *tcp2 : ta,
+                                                       tcp3 ? *tcp3 : ta);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -464,6 +473,27 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     tcp = &tc;
     pc.tma_c = 1;
   }
+  // SwiGLU with stored pre-activation: y [M, I] plus the gate and up halves of h [M, 2 I]; dSwiGLU: the dg and du
+  // halves of the [M, 2 I] output.  Each half is a tensor of its own (clipping at its right edge).
+  CUtensorMap tc2, tc3;
+  const CUtensorMap *tcp2 = nullptr, *tcp3 = nullptr;
+  static const bool tma_h_on = [] { const char* e = getenv("B200_GEMM_TMA_H"); return !(e && e[0] == '0'); }();
+  if (tma_c_on && tma_c16_on && tma_h_on && bn == 256 && (p.swiglu_n & 7) == 0) {
+    const __nv_bfloat16* h = p.resid;
+    if (out_mode == OUT_SWIGLU_SAVE && h &&
+        make_tmap_2d_bf16(&tc, p.C, p.M, p.N, p.ldc, 32, 64) == 0 &&
+        make_tmap_2d_bf16(&tc2, h, p.M, p.N, p.ld_resid, 32, 64) == 0 &&
+        make_tmap_2d_bf16(&tc3, h + p.swiglu_n, p.M, p.N, p.ld_resid, 32, 64) == 0) {
+      tcp = &tc; tcp2 = &tc2; tcp3 = &tc3;
+      pc.tma_c = 1;
+    }
+    if (out_mode == OUT_DSWIGLU && h && (reinterpret_cast<uintptr_t>(h) & 15) == 0 && (p.ld_resid & 7) == 0 &&
+        make_tmap_2d_bf16(&tc, p.C, p.M, p.N, p.ldc, 32, 64) == 0 &&
+        make_tmap_2d_bf16(&tc2, reinterpret_cast<const __nv_bfloat16*>(p.C) + p.swiglu_n, p.M, p.N, p.ldc, 32, 64) == 0) {
+      tcp = &tc; tcp2 = &tc2;
+      pc.tma_c = 1;
+    }
+  }
 #define DISPATCH2(BN_, AMN_, BMN_)                                                                  \
   switch (out_mode) {                                                                               \
     case OUT_BF16: return launch2<BN_, AMN_, BMN_, OUT_BF16>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);       \
@@ -473,14 +503,15 @@ int gemm_2cta_dispatch(const void* A, const void* A2, const void* B, const GemmP
     default: return -100;                                                                           \
   }
   if (out_mode == OUT_SWIGLU) return launch2<256, false, false, OUT_SWIGLU>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp);
-  if (out_mode == OUT_SWIGLU_SAVE) return launch2<256, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, p, st, max_ctas);
+  if (out_mode == OUT_SWIGLU_SAVE)
+    return launch2<256, false, false, OUT_SWIGLU_SAVE>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp, tcp2, tcp3);
   if (out_mode == OUT_BF16_LSE) {
     if (a_mn || b_mn || bn != 256) return -100;
     return launch2<256, false, false, OUT_BF16_LSE>(ta, ta2, tb, p, st, max_ctas);
   }
   if (out_mode == OUT_DSWIGLU) {
     if (a_mn || !b_mn || bn != 256) return -100;
-    return launch2<256, false, true, OUT_DSWIGLU>(ta, ta2, tb, p, st, max_ctas);
+    return launch2<256, false, true, OUT_DSWIGLU>(ta, ta2, tb, pc, st, max_ctas, nullptr, tcp, tcp2);
   }
   if (out_mode == OUT_BF16_ROPE) {
     if (a_mn || b_mn) return -100;
