@@ -36,6 +36,73 @@ def _make(spec, default_weight, max_steps):
     raise NotImplementedError(f"unknown weight schedule {kind!r}")
 
 
+class _Weight:
+    """A weight schedule as an object with ``get_weight(step)``: the form in which the reference exposes its schedules
+    (recpre/data_scheduler_utils.py:5-123).  The arithmetic is that of ``_make``; these classes only name it."""
+
+    kind = ""
+
+    def __init__(self, *args, max_steps: int = 0, default_weight=0):
+        self.args = list(args)
+        self._fn = _make([self.kind, *args], default_weight, max_steps)
+
+    def get_weight(self, current_step: int):
+        return self._fn(current_step)
+
+    def __repr__(self):
+        return f"{type(self).__name__}: {', '.join(str(a) for a in self.args)}"
+
+
+class ConstWeight(_Weight):
+    kind = "const"                                   # ConstWeight(weight)
+
+
+class StepWeight(_Weight):
+    kind = "step"                                    # StepWeight(initial_weight, step_size, gamma)
+
+
+class LinearWeight(_Weight):
+    kind = "linear"                                  # LinearWeight(initial_weight, end_weight, total_steps)
+
+
+class CosineAnnealingWeight(_Weight):
+    kind = "cosine"                                  # CosineAnnealingWeight(initial_weight, eta_min, T_max)
+
+
+class BaseWeight(_Weight):
+    kind = "base"                                    # the source that takes what the others leave of 100
+
+    def get_weight(self, current_step: int):
+        return 0
+
+
+class PiecewiseWeight:
+    """``[[start_step, spec], ...]``: each piece runs on its own clock from its start step."""
+
+    def __init__(self, scheduler_configs, default_weight, max_steps: int = 0):
+        self.scheduler_configs, self.default_weight = scheduler_configs, default_weight
+        self._fn = _make(scheduler_configs, default_weight, max_steps)
+
+    def get_weight(self, current_step: int):
+        return self._fn(current_step)
+
+    def __repr__(self):
+        return f"PiecewiseWeight: {self.scheduler_configs}"
+
+
+def GetScheduler(scheduler_config, default_weight, max_steps: int = 0):
+    """Schedule object for one source's ``scheduler`` entry (None: constant at ``default_weight``)."""
+    if scheduler_config is None:
+        return ConstWeight(default_weight)
+    if isinstance(scheduler_config[0], (list, tuple)):
+        return PiecewiseWeight(scheduler_config, default_weight, max_steps)
+    cls = {"const": ConstWeight, "step": StepWeight, "linear": LinearWeight, "cosine": CosineAnnealingWeight,
+           "base": BaseWeight, "base-renorm": BaseWeight}.get(scheduler_config[0])
+    if cls is None:
+        raise NotImplementedError(f"unknown weight schedule {scheduler_config[0]!r}")
+    return cls(*scheduler_config[1:], max_steps=max_steps, default_weight=default_weight)
+
+
 class DataSchedulerTracker:
     def __init__(self, weights):
         self.weights = list(weights)

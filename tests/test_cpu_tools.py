@@ -329,3 +329,37 @@ def test_launcher_snapshot_and_staging(tmp_path):
                                "--output_dir", str(tmp_path / "out"), "--run_name", "t"])
     text = job.sbatch_text()
     assert 'cd "$STAGE_DIR/t_code"' in text and "sbcast" in text
+
+
+def test_every_listed_reference_symbol_resolves_to_an_object_of_this_package():
+    """The reference-name table is the porting index: every target must import, and bare names must be unambiguous."""
+    from recurrent_pretraining_b200 import reference_names as ref
+
+    assert len(ref.REFERENCE_NAMES) > 150
+    for key in ref.REFERENCE_NAMES:
+        obj = ref.resolve(key)
+        assert obj is not None, key
+        assert ref.where(key).startswith("recurrent_pretraining_b200.")
+    from recurrent_pretraining_b200.data.datasets import ParquetStream
+    from recurrent_pretraining_b200.optim.soap import SOAP
+
+    assert ref.ParquetStreamPure is ParquetStream and ref.SOAP is SOAP
+    with pytest.raises(AttributeError):
+        ref.RavenForCausalLM        # two reference files define it (current and legacy): ask by dotted path
+    with pytest.raises(KeyError):
+        ref.resolve("recpre.nothing.Here")
+
+
+def test_named_weight_schedules_match_the_mixture_scheduler():
+    from recurrent_pretraining_b200.data import scheduler as S
+
+    assert S.GetScheduler(None, 7).get_weight(3) == 7
+    assert S.GetScheduler(["step", 8, 10, 0.5], 5).get_weight(25) == 2.0
+    assert S.GetScheduler(["linear", 10, 20, 100], 5).get_weight(50) == 15.0
+    assert S.GetScheduler(["linear", 10, 20, 100], 5).get_weight(500) == 20.0
+    assert abs(S.GetScheduler(["cosine", 10, 0, 100], 0).get_weight(50) - 5.0) < 1e-9
+    assert S.GetScheduler([[0, ["const", 3]], [10, ["linear", 3, 9, 10]]], 1).get_weight(15) == 6.0
+    assert S.GetScheduler(["base"], 1).get_weight(4) == 0
+    assert repr(S.StepWeight(8, 10, 0.5)) == "StepWeight: 8, 10, 0.5"
+    with pytest.raises(NotImplementedError):
+        S.GetScheduler(["spline", 1], 1)
