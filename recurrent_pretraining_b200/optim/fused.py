@@ -155,6 +155,7 @@ class FusedAdamW:
         hold the squared norm of the *stored* gradients (before ``grad_scale``) unless clipping is off; it is computed
         here when ``norm_ready`` is False."""
         assert self.plans is None, "sharded state is stepped by parallel.p2p.ShardedStepper"
+        self.finish_deferred()       # a step that follows another without a forward pass in between
         if not norm_ready:
             self.compute_grad_norm_sq()
         first_update = self.step_count == 0
@@ -263,6 +264,7 @@ class FusedAdamW:
         return self.gnorm_sq.sqrt() * grad_scale
 
     def zero_grad(self, set_to_none: bool = False):
+        self.finish_deferred()       # the deferred part of the last update still reads its gradients
         for g in self.groups:
             g.grad.zero_()
 

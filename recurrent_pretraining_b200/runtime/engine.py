@@ -173,9 +173,15 @@ class TrainEngine:
         embedding and head backward; known from ``_gemm_written`` once it happened) is marked unwritten, so its first
         contribution stores.  Every other gradient is accumulated by autograd and is cleared here (norm scales, biases:
         a few hundred KB)."""
-        for g in self.flat_groups:
+        deferred = getattr(self.optimizer, "defer_ranges", None) or {}
+        st = self._stepper()
+        if st is not None and getattr(st, "defer", False):
+            deferred = dict.fromkeys(range(len(self.flat_groups) - 1))     # every group but the fp32 one
+        for gi, g in enumerate(self.flat_groups):
             fused = [p for p in g.params if getattr(p, "_fused_grad", False)]
             if fused and not any(getattr(p, "_gemm_written", False) for p in fused):
+                if gi in deferred:
+                    self._finish_deferred()             # the late part of the last update still reads these gradients
                 g.grad.zero_()                      # one launch for a whole group of autograd-accumulated gradients
                 for p in fused:
                     p._written = 3
@@ -184,8 +190,17 @@ class TrainEngine:
                 if getattr(p, "_gemm_written", False):
                     p._written = 0
                 else:
+                    if gi in deferred:
+                        self._finish_deferred()
                     p.grad.zero_()
                     p._written = 3
+
+    def _finish_deferred(self) -> None:
+        st = self._stepper()
+        if st is not None:
+            st.finish_deferred()
+        if hasattr(self.optimizer, "finish_deferred"):
+            self.optimizer.finish_deferred()
 
     def _finish_window(self) -> None:
         """A tensor that received no gradient in this window must read as zero (nothing else clears the buffers)."""
