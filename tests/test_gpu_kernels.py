@@ -424,3 +424,89 @@ def test_gemm_tn_fp32_tiles_through_bulk_stores(C, T, N, K):
     _close(view, 2 * want, 1e-2, 2 * tol)
     assert torch.all(full[:, :8] == 3.0) and torch.all(full[:, 8 + K:] == 3.0)
     assert C.check_device_status() == 0
+
+
+def _guarded(rows, cols, pitch, dtype=torch.bfloat16, pad=4096, sentinel=512.0):
+    """A [rows, cols] view with row pitch ``pitch`` inside a larger buffer filled with a sentinel value."""
+    big = torch.full((pad + rows * pitch + pad,), sentinel, dtype=dtype, device="cuda")
+    return big, big[pad:pad + rows * pitch].view(rows, pitch)[:, :cols]
+
+
+def _guards_intact(big, rows, cols, pitch, pad=4096, sentinel=512.0):
+    body = big[pad:pad + rows * pitch].view(rows, pitch)
+    return bool((big[:pad] == sentinel).all()) and bool((big[pad + rows * pitch:] == sentinel).all()) and \
+        (cols == pitch or bool((body[:, cols:] == sentinel).all()))
+
+
+def test_bf16_epilogues_write_nothing_outside_their_output(C):
+    """Canary check of the staged bf16 epilogues on ragged extents (rows not a multiple of 32, columns not a multiple
+    of 64, row pitch wider than the matrix): the bulk stores are clipped by the tensor map, so the sentinel values in
+    front of, behind and between the rows of the output must survive -- and the values inside must be right."""
+    M, E, I = 260, 136, 200
+    x, w = _rand(M, E), _rand(I, E, scale=0.3)
+    big, out = _guarded(M, I, I + 8)                                   # plain NT
+    C.gemm_nt(x, w, out=out)
+    _close(out, x.float() @ w.float().T, 2e-2, 2e-2 * math.sqrt(E))
+    assert _guards_intact(big, M, I, I + 8)
+    dy = _rand(M, I)
+    big, out = _guarded(M, E, E + 24)                                  # NN (input gradient)
+    C.gemm_nn(dy, w, out=out)
+    _close(out, dy.float() @ w.float(), 2e-2, 2e-2 * math.sqrt(I))
+    assert _guards_intact(big, M, E, E + 24)
+    fc, proj = _rand(2 * I, E, scale=0.2), _rand(E, I, scale=0.2)      # gated MLP, training forms
+    big_y, y = _guarded(M, I, I + 8)
+    big_h, h = _guarded(M, 2 * I, 2 * I)
+    C.gemm(x, fc, out=y, out_mode=C.OUT_SWIGLU_SAVE, resid=h)
+    full = x.float() @ fc.float().T
+    _close(h, full, 2e-2, 0.05)
+    _close(y, torch.nn.functional.silu(full[:, :I]) * full[:, I:], 3e-2, 0.05)
+    assert _guards_intact(big_y, M, I, I + 8) and _guards_intact(big_h, M, 2 * I, 2 * I)
+    big_d, dh = _guarded(M, 2 * I, 2 * I)
+    dout = _rand(M, E, scale=0.5)
+    C.gemm(dout, proj, b_mn=True, out=dh[:, :I], out_mode=C.OUT_DSWIGLU, resid=h)
+    hl = h.float().requires_grad_(True)
+    (torch.nn.functional.silu(hl[:, :I]) * hl[:, I:] @ proj.float().T).backward(dout.float())
+    _close(dh, hl.grad, 3e-2, 0.05 * float(hl.grad.abs().max()))
+    assert _guards_intact(big_d, M, 2 * I, 2 * I)
+    H, D, S = 2, 96, 130                                               # q/k bias + rotation
+    T, W = 2 * S, 3 * H * D
+    xq, wq = _rand(T, E), _rand(W, E, scale=0.3)
+    bias = torch.randn(2 * H * D, device="cuda") * 0.1
+    cos, sin = (t.cuda().contiguous() for t in ref.rope_tables(D, S))
+    big, out = _guarded(T, W, W + 16)
+    C.gemm(xq, wq, out=out, out_mode=C.OUT_BF16_ROPE, rope=(cos, sin, bias, S, D, 2 * H * D))
+    qkv = (xq.float() @ wq.float().T).view(T // S, S, W)
+    q, k, v = ref.qk_bias_rope(qkv, bias.view(2, 1, H, D), cos, sin, H, H, D)
+    _close(out, torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1), 2e-2, 2e-2 * math.sqrt(E))
+    assert _guards_intact(big, T, W, W + 16)
+    assert C.check_device_status() == 0
+
+
+def test_atomics_free_kernels_repeat_bit_for_bit(C):
+    """Kernels that use no floating-point atomics give the same bits on every run: GEMMs of every layout (each output
+    tile has one writer, the k loop runs in one order), the gated-MLP forms, the norm kernels (the weight gradient is a
+    two-stage column sum in a fixed order) and the attention forward pass."""
+    M, E, I = 1100, 264, 512
+    x, w, dy = _rand(M, E), _rand(I, E, scale=0.3), _rand(M, I)
+    fc = _rand(2 * I, E, scale=0.2)
+    nw = torch.rand(E, device="cuda") + 0.5
+    H, D, S = 3, 96, 384
+    qkv = _rand(2, S, 3 * H * D, scale=0.5)
+    dyn = _rand(M, E)
+
+    def run():
+        out = [C.gemm_nt(x, w), C.gemm_nn(dy, w), C.gemm_tn(dy, x)]
+        out += list(C.linear_swiglu_save(x, fc))
+        y, rstd = C.rmsnorm_fwd(x, nw, 1e-6)
+        out += [y, rstd]
+        out += list(C.rmsnorm_bwd(dyn, x, nw, rstd))
+        o, lse = C.attention_fwd(qkv, H, H, D, 1.0 / math.sqrt(D))
+        out += [o, lse]
+        torch.cuda.synchronize()
+        return [t.clone() for t in out if t is not None]
+
+    first, second = run(), run()
+    assert len(first) == len(second) >= 10
+    for i, (a, b) in enumerate(zip(first, second)):
+        assert torch.equal(a, b), f"output {i} differs between two runs"
+    assert C.check_device_status() == 0
