@@ -22,7 +22,8 @@ from torch.utils.data import IterableDataset
 
 
 class RandomTokens(IterableDataset):
-    def __init__(self, vocab_size: int, block_size: int, seed: int = 233, process_rank: int = 0, length: int = 10**6):
+    def __init__(self, vocab_size: int = 1024, block_size: int = 4096, seed: int = 233, process_rank: int = 0,
+                 length: int = 10**6):
         self.vocab_size, self.block_size, self.seed, self.rank, self.length = vocab_size, block_size, seed, process_rank, length
         self._pos = 0
 
@@ -45,7 +46,12 @@ class ParquetStream(IterableDataset):
     def __init__(self, dataset_folder_path: str = "", seed: int = 12345, shuffle: bool = True, num_processes: int = 1,
                  process_rank: int = 0, prefix: str = "", shuffle_filenames: bool = True, column: str = "input_ids",
                  broadcast_glob: bool = True, stateful: bool = True, plan_for_later_rank_expansion_to: int = 8,
-                 return_data_id: bool = False, data_id=None):
+                 return_data_id: bool = False, data_id=None, verbose: bool = False, data_signature: dict | None = None,
+                 repetitions=None):
+        # ``data_signature`` ({"keys": [column]}), ``repetitions`` and ``verbose`` are the reference's argument names
+        # (recpre/huggingface_dataset.py:128-145); as there, the token streams do not repeat
+        if data_signature is not None and data_signature.get("keys"):
+            column = data_signature["keys"][0]
         files = None
         distributed = dist.is_available() and dist.is_initialized()
         if not (broadcast_glob and distributed) or process_rank == 0:
@@ -151,7 +157,10 @@ class BufferShuffledParquet(IterableDataset):
     def __init__(self, dataset_folder_path: str = "", seed: int = 12345, shuffle: bool = True, num_processes: int = 1,
                  process_rank: int = 0, prefix: str = "", shuffle_filenames: bool = True, column: str = "input_ids",
                  buffer_size: int = 1024, read_batch: int = 256, return_data_id: bool = False, data_id=None,
-                 broadcast_glob: bool = True):
+                 broadcast_glob: bool = True, data_signature: dict | None = None, repetitions=None,
+                 verbose: bool = True, stateful: bool = True):
+        if data_signature is not None and data_signature.get("keys"):     # the reference's name for the column choice
+            column = data_signature["keys"][0]
         files = None
         distributed = dist.is_available() and dist.is_initialized()
         if not (broadcast_glob and distributed) or process_rank == 0:
@@ -270,9 +279,13 @@ class TextRows(IterableDataset):
     every row.  The position (``data_idx`` within this shard) is the resumable state
     (recpre/huggingface_dataset.py:297-441)."""
 
-    def __init__(self, rows_or_path, data_signature: dict, num_processes: int = 1, process_rank: int = 0,
-                 shuffle: bool = False, seed: int = 0, data_id=None, repetitions: int | None = None,
-                 return_data_id: bool | None = None):
+    def __init__(self, rows_or_path=None, data_signature: dict | None = None, num_processes: int = 1,
+                 process_rank: int = 0, shuffle: bool = False, seed: int = 12345, data_id=None,
+                 repetitions: int | None = None, return_data_id: bool | None = None, ds_name_or_path=None):
+        rows_or_path = ds_name_or_path if rows_or_path is None else rows_or_path     # the reference's argument name
+        assert rows_or_path is not None, "rows (a sequence of dicts) or the path of a saved dataset"
+        if data_signature is None:
+            data_signature = {"keys": ["text"], "format_fn": "pass_text"}
         if isinstance(rows_or_path, (str, Path)):
             rows_or_path = _load_rows(str(rows_or_path))
         self.rows, self.sig = rows_or_path, data_signature
@@ -325,8 +338,19 @@ HuggingfaceDataset = TextRows      # the reference's class name for this source
 class WeightedMixture(IterableDataset):
     """Draws the next row from one of several sources according to (scheduled) weights."""
 
-    def __init__(self, sources: list, weights: list, seed: int = 0, scheduler=None):
+    def __init__(self, sources: list | None = None, weights=None, seed=0, scheduler=None, *, datasets: list | None = None,
+                 data_telemetry: bool = False):
+        """``WeightedMixture(sources, weights, seed, scheduler)``; the reference's call
+        ``HuggingfaceCombinedDataset(datasets, seed, weights=None, data_telemetry=False)`` is accepted as well
+        (recpre/huggingface_dataset.py:444-481): an integer in second place is the seed, missing weights are uniform,
+        telemetry prints the source of the first draws."""
+        sources = datasets if sources is None else sources
+        if isinstance(weights, int) and not isinstance(weights, bool):       # (datasets, seed, weights)
+            weights, seed = (seed if isinstance(seed, (list, tuple)) else None), weights
+        if weights is None:
+            weights = [1.0 / len(sources)] * len(sources)
         self.sources, self.weights, self.scheduler = sources, list(weights), scheduler
+        self.data_telemetry, self._draws = data_telemetry, 0
         self._rng = random.Random(seed)
 
     def __iter__(self):
@@ -338,6 +362,11 @@ class WeightedMixture(IterableDataset):
             if sum(w) <= 0:
                 return
             i = self._rng.choices(range(len(iters)), weights=w)[0]
+            self._draws += 1
+            if self.data_telemetry and self._draws <= 5:
+                src = self.sources[i]
+                print(f"draw {self._draws}: source {i} ({getattr(src, 'data_id', None)}:"
+                      f"{getattr(src, 'fingerprint', None)})" if self._draws < 5 else "data telemetry off ...", flush=True)
             try:
                 yield next(iters[i])
             except StopIteration:

@@ -92,6 +92,7 @@ class PiecewiseWeight:
 
 def GetScheduler(scheduler_config, default_weight, max_steps: int = 0):
     """Schedule object for one source's ``scheduler`` entry (None: constant at ``default_weight``)."""
+    max_steps = int(getattr(max_steps, "max_steps", max_steps))      # the reference passes its settings object
     if scheduler_config is None:
         return ConstWeight(default_weight)
     if isinstance(scheduler_config[0], (list, tuple)):
@@ -130,7 +131,15 @@ class DataSchedulerTracker:
 
 
 class DataScheduler:
-    def __init__(self, tracker: DataSchedulerTracker, data_config: list, max_steps: int):
+    def __init__(self, tracker: DataSchedulerTracker = None, data_config: list = None, max_steps: int = 0, *,
+                 data_scheduler_tracker: DataSchedulerTracker = None, args=None):
+        """``DataScheduler(tracker, data_config, max_steps)``; the reference's keywords ``data_scheduler_tracker`` and
+        ``args`` (an object with ``max_steps``) are accepted too (recpre/data_scheduler_utils.py:150-170)."""
+        tracker = data_scheduler_tracker if tracker is None else tracker
+        if not isinstance(max_steps, int):               # (tracker, data_config, args) passed positionally
+            args, max_steps = max_steps, 0
+        if args is not None:
+            max_steps = int(getattr(args, "max_steps", max_steps))
         self.tracker = tracker
         self.base_id, self._renorm = None, False
         self.max_epochs, self._fns = [], []

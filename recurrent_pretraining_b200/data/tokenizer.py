@@ -16,7 +16,10 @@ HUGINN_IDS = {"bos": 65504, "eos": 65505, "end_turn": 65508, "pad": 65509}
 
 
 class Tokenizer:
-    def __init__(self, checkpoint_dir: Union[Path, str, None], allow_missing: bool = True):
+    def __init__(self, checkpoint_dir: Union[Path, str, None], allow_missing: bool = True,
+                 broken_state_load_fallback: Optional[bool] = None):
+        if broken_state_load_fallback is not None:       # the reference's name for the same switch
+            allow_missing = bool(broken_state_load_fallback)
         self.checkpoint_dir = Path(checkpoint_dir) if checkpoint_dir else None
         self.processor = None
         self.backend = None

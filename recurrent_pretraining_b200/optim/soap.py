@@ -53,9 +53,12 @@ def _mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 class SOAP(Optimizer):
-    def __init__(self, params, lr: float = 3e-3, betas=(0.95, 0.95), shampoo_beta: float = -1, eps: float = 1e-8,
+    def __init__(self, params, lr: float = 3e-3, betas=(0.9, 0.95), shampoo_beta: float = -1, eps: float = 1e-8,
                  weight_decay: float = 0.01, precondition_frequency: int = 10, max_precond_dim: int = 10000,
-                 merge_dims: bool = False, precondition_1d: bool = False, correct_bias: bool = True):
+                 merge_dims: bool = False, precondition_1d: bool = False, data_format: str = "channels_first",
+                 correct_bias: bool = True):
+        assert data_format in ("channels_first", "channels_last")
+        self._data_format = data_format       # 4-D weights stored NHWC are merged in NCHW order (recpre/soap.py:96-103)
         defaults = dict(lr=lr, betas=tuple(betas), shampoo_beta=shampoo_beta, eps=eps, weight_decay=weight_decay,
                         precondition_frequency=precondition_frequency, max_precond_dim=max_precond_dim,
                         merge_dims=merge_dims, precondition_1d=precondition_1d, correct_bias=correct_bias)
@@ -145,6 +148,10 @@ class SOAP(Optimizer):
                 g = p.grad.float()
                 st = self.state[p]
                 shape = g.shape
+                nhwc = group["merge_dims"] and g.dim() == 4 and self._data_format == "channels_last"
+                if nhwc:
+                    g = g.permute(0, 3, 1, 2).contiguous()
+                    shape = g.shape
                 if group["merge_dims"] and g.dim() > 1:
                     g = g.reshape(self._merge(g.shape, group["max_precond_dim"]))
                 if "step" not in st:
@@ -165,7 +172,10 @@ class SOAP(Optimizer):
                 if group["correct_bias"]:
                     step_size = step_size * ((1 - b2 ** st["step"]) ** 0.5) / (1 - b1 ** st["step"])
                 upd = self._project(mp / denom, st["Q"], back=True)
-                p.add_(upd.reshape(shape).to(p.dtype), alpha=-float(step_size))
+                upd = upd.reshape(shape)
+                if nhwc:
+                    upd = upd.permute(0, 2, 3, 1)
+                p.add_(upd.to(p.dtype), alpha=-float(step_size))
                 if group["weight_decay"] > 0:
                     p.add_(p, alpha=-float(group["lr"]) * group["weight_decay"])
                 self._update_gg(g, st)

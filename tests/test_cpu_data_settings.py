@@ -298,3 +298,43 @@ def test_text_rows_are_dealt_over_ranks_and_workers_and_resume(tmp_path):
     b = TextRows(rows, sig, num_processes=2, process_rank=0)
     b.load_state_dict(state)
     assert head + [r["text"] for r in b] == [f"row {i}" for i in range(0, 23, 2)]
+
+
+def test_data_classes_accept_the_reference_constructor_keywords(tmp_path):
+    """Scripts written against the reference pass its argument names (recpre/huggingface_dataset.py:35-51,128-145,
+    298-309,445; recpre/data_scheduler_utils.py:131; recpre/tokenizer.py:11)."""
+    import types
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from recurrent_pretraining_b200.data.datasets import (BufferShuffledParquet, ParquetStream, RandomTokens, TextRows,
+                                                          WeightedMixture)
+    from recurrent_pretraining_b200.data.scheduler import DataScheduler, DataSchedulerTracker, GetScheduler
+    from recurrent_pretraining_b200.data.tokenizer import Tokenizer
+    from recurrent_pretraining_b200.settings import DataEntry
+
+    pq.write_table(pa.table({"tokens": [[1, 2, 3, 4], [5, 6, 7, 8]]}), tmp_path / "a_0.parquet")
+    kw = dict(dataset_folder_path=str(tmp_path), seed=1, shuffle=False, num_processes=1, process_rank=0, prefix="a_",
+              verbose=False, shuffle_filenames=True, data_signature={"keys": ["tokens"]}, repetitions=None,
+              return_data_id=False, data_id=None, broadcast_glob=False, stateful=True)
+    rows = [list(map(int, r)) for r in ParquetStream(plan_for_later_rank_expansion_to=0, **kw)]
+    assert sorted(rows) == [[1, 2, 3, 4], [5, 6, 7, 8]]
+    assert sorted(list(map(int, r)) for r in BufferShuffledParquet(**kw)) == sorted(rows)
+    text = TextRows(ds_name_or_path=[{"text": "a"}, {"text": "b"}, {"text": "c"}], num_processes=1, process_rank=0)
+    assert [r["text"] for r in text] == ["a", "b", "c"] and text.sig["format_fn"] == "pass_text" and text.seed == 12345
+    assert RandomTokens().block_size == 4096 and RandomTokens().vocab_size == 1024
+    mix = WeightedMixture(datasets=[[1, 1, 1], [2, 2, 2]], seed=3)                # uniform weights
+    assert sorted(mix) == [1, 1, 1, 2, 2, 2] and mix.weights == [0.5, 0.5]
+    mix = WeightedMixture([[1], [2]], 7, [1.0, 0.0])                               # (datasets, seed, weights)
+    assert mix.weights == [1.0, 0.0] and list(mix) == [1]
+    entries = [DataEntry(type="rngds", prefix="", weight=60, scheduler=["linear", 60, 20]),
+               DataEntry(type="rngds", prefix="", weight=40)]
+    tracker = DataSchedulerTracker([60, 40])
+    sched = DataScheduler(data_scheduler_tracker=tracker, data_config=entries, args=types.SimpleNamespace(max_steps=10))
+    sched.step(5)
+    assert tracker.weights == [40.0, 40]
+    assert GetScheduler(["linear", 60, 20], 0, types.SimpleNamespace(max_steps=10)).get_weight(10) == 20
+    assert Tokenizer(tmp_path / "missing", broken_state_load_fallback=True).processor is None
+    with pytest.raises(NotADirectoryError):
+        Tokenizer(tmp_path / "missing", broken_state_load_fallback=False)

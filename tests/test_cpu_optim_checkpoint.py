@@ -286,3 +286,86 @@ def test_deferred_update_runs_cover_the_weight_group_once():
     # a layout in which the coda is split by other tensors is refused
     assert deferred_runs(["transformer.coda.0.a", "transformer.prelude.0.a", "transformer.coda.1.a",
                           "transformer.core_block.0.a"], [0, 128, 256, 384], [128] * 4, 512) is None
+
+
+def _run_three(cls, kw, steps=6, sampled=False):
+    """A matrix, a vector and a 'vocabulary-sized' matrix under a fixed stream of gradients."""
+    torch.manual_seed(1)
+    ps = [torch.nn.Parameter(torch.randn(12, 8)), torch.nn.Parameter(torch.randn(6)),
+          torch.nn.Parameter(torch.randn(32, 8))]
+    opt = cls(ps, **kw)
+    targets = [torch.randn_like(p) for p in ps]
+    for i in range(steps):
+        if sampled:                                   # variational optimizers draw the weights they evaluate
+            torch.manual_seed(100 + i)
+            with opt.sampled_params(train=True):
+                for p in ps:
+                    p.grad = None
+                sum(((p - t) ** 2).sum() for p, t in zip(ps, targets)).backward()
+        else:
+            for p in ps:
+                p.grad = torch.randn_like(p) * (i + 1) * 0.1
+            if i % 2 == 0 and hasattr(opt, "update_hessian"):
+                opt.update_hessian()                  # Sophia: the Hessian estimate is refreshed every k steps
+        opt.step()
+    return [p.detach().clone() for p in ps]
+
+
+@needs_ref
+@pytest.mark.parametrize("name,kw,sampled", [
+    ("SophiaG", dict(lr=1e-2, betas=(0.9, 0.95), rho=0.05, weight_decay=0.1), False),
+    ("SophiaG", dict(lr=1e-2, betas=(0.9, 0.95), rho=1e-4, weight_decay=0.0, maximize=True), False),
+    ("Lilith", dict(lr=1e-2), False),
+    ("IVON", dict(lr=1e-2, ess=100.0), True),
+    ("ZeroShampooWithAdamGraftingOptimizer", dict(lr=1e-2, block_size=4, start_preconditioning=2), False),
+    ("OrthogonalNesterov", dict(lr=1e-2, vocab_dim=32, weight_decay=0.1), False),
+])
+def test_other_optimizers_match_reference_classes(name, kw, sampled):
+    """Step-for-step against the reference's own optimizer classes (recpre/optim.py), same constructor keywords.
+    The reference's OrthogonalNesterov never accumulates the moments of its AdamW branch; ``frozen_moments`` selects
+    that arithmetic for the comparison (the default here accumulates them)."""
+    from recurrent_pretraining_b200.optim import others, research
+
+    mine = getattr(others, name, None) or getattr(research, name)
+    with torch.compiler.set_stance("force_eager"):                 # the reference decorates helpers with torch.compile
+        want = _run_three(getattr(refload.module("optim"), name), kw, sampled=sampled)
+    got = _run_three(mine, dict(kw, frozen_moments=True) if name == "OrthogonalNesterov" else kw, sampled=sampled)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, rtol=1e-5, atol=2e-6), float((a - b).abs().max())
+
+
+def test_orthogonal_nesterov_trains_the_adam_branch_by_default():
+    from recurrent_pretraining_b200.optim.others import OrthogonalNesterov
+
+    torch.manual_seed(0)
+    w, e, b = (torch.nn.Parameter(torch.randn(8, 16)), torch.nn.Parameter(torch.randn(32, 16)),
+               torch.nn.Parameter(torch.randn(16)))
+    before = [p.detach().clone() for p in (w, e, b)]
+    opt = OrthogonalNesterov([w, e, b], lr=0.1, vocab_dim=32, weight_decay=0.0, zeropower_iters=5)
+    for p in (w, e, b):
+        p.grad = torch.randn_like(p)
+    opt.step()
+    # matrix branch: the step has norm 0.1 * lr * sqrt(numel); Adam branch: first step moves every entry by ~lr
+    assert abs(float((w - before[0]).norm()) - 0.1 * 0.1 * (w.numel() ** 0.5)) < 1e-4
+    assert abs(float((e - before[1]).abs().mean()) - 0.1) < 1e-3 and abs(float((b - before[2]).abs().mean()) - 0.1) < 1e-3
+    assert "momentum_buffer" in opt.state[w] and "exp_avg_sq" in opt.state[e]
+
+
+def test_lion_update_matches_its_definition_and_reports_update_alignment():
+    from recurrent_pretraining_b200.optim.others import LionW
+
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(5, 7))
+    opt = LionW([p], lr=1e-2, betas=(0.9, 0.99), weight_decay=0.1, fused=True)      # unknown keywords are tolerated
+    assert opt.param_groups[0]["initial_lr"] == 1e-2 and opt.get_post_step_metrics() == {}
+    w, m = p.detach().clone(), torch.zeros(5, 7)
+    for _ in range(3):
+        g = torch.randn(5, 7)
+        p.grad = g.clone()
+        opt.step()
+        u = 0.9 * m + 0.1 * g
+        w = w * (1 - 1e-2 * 0.1) - 1e-2 * torch.sign(u)
+        m = 0.99 * m + 0.01 * g
+        assert torch.allclose(p.detach(), w, atol=1e-6)
+    cos = opt.get_post_step_metrics()["update_cos_sim"]
+    assert abs(float(cos) - float((u * u.sign()).sum() / (u.norm() * u.sign().norm()))) < 1e-5
