@@ -29,23 +29,31 @@ class Linear(nn.Module):
     """Bias-optional linear layer whose weight is initialised by a role-aware initialiser
     (recpre/config_dynamic.py:450-467)."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = False, init=None):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None,
+                 init_method=None, init=None):
+        """``init_method`` (the reference's keyword) or ``init``: callable that fills the weight in place; without one
+        the weight is drawn from a normal of std 1/sqrt(in_features) truncated at three std (recpre/init.py:511-516)."""
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
-        self.weight = nn.Parameter(torch.empty(out_features, in_features))
-        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
-        self._init = init
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
+        self._init = init_method if init_method is not None else init
         self.reset_parameters()
+
+    @property
+    def init_method(self):
+        return self._init
 
     def reset_parameters(self) -> None:
         if self._init is not None:
             self._init(self.weight)
         else:
-            nn.init.trunc_normal_(self.weight, std=1 / math.sqrt(self.in_features))
+            std = 1 / math.sqrt(self.in_features)
+            nn.init.trunc_normal_(self.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
         if self.bias is not None:
             nn.init.zeros_(self.bias)
 
-    def forward(self, x):
+    def forward(self, x, **kwargs):                  # extra arguments of tensor-parallel wrappers are ignored
         y = ops.linear(x, self.weight)
         return y if self.bias is None else y + self.bias.to(y.dtype)
 
@@ -126,8 +134,14 @@ def make_norm(config, dim: int | None = None) -> nn.Module:
 
 
 class Relu2(nn.Module):
+    """0.5 * relu(x)^2 (the factor is the reference's, recpre/config_dynamic.py:470-476)."""
+
+    def __init__(self, inplace: bool = False):
+        super().__init__()
+        self.inplace = inplace
+
     def forward(self, x):
-        return F.relu(x).square()
+        return F.relu(x, inplace=self.inplace).square().mul(0.5)
 
 
 def make_nonlin(name: str) -> nn.Module:

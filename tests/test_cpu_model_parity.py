@@ -251,3 +251,48 @@ def test_soft_capped_attention_logits():
     model = cfg.construct_model()
     ids = torch.randint(0, 512, (1, 33))
     assert torch.isfinite(model(ids[:, :-1], labels=ids[:, 1:], num_steps_pair=torch.tensor([1, 1]))["loss"])
+
+
+@needs_ref
+@pytest.mark.parametrize("extra", [dict(mlp_class_name="BaseMLP", nonlin_name="ReLU2"),
+                                   dict(mlp_class_name="BaseMLP", nonlin_name="GELU"), dict(nonlin_name="ReLU2"),
+                                   dict(norm_class_name="LayerNorm"), dict(norm_class_name="GemmalikeRMS"),
+                                   dict(norm_class_name="UnparametrizedRMSNorm"), dict(norm_class_name="Identity"),
+                                   dict(bias=True), dict(qk_norm=True), dict(clip_qkv=0.5), dict(tie_embeddings=False),
+                                   dict(lm_head_bias=True)], ids=lambda e: "-".join(f"{k}={v}" for k, v in e.items()))
+def test_config_options_match_reference(extra):
+    """Nonlinearity (ReLU2 carries the reference's factor 0.5), MLP class, norm class, biases, qk norm, qkv clipping,
+    untied head: same state-dict keys, same loss and gradients as the reference model built from the same overrides."""
+    torch.manual_seed(0)
+    over = dict(TINY, attn_impl="sdpa", **extra)
+    ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **over)
+    model = ModelConfig.from_name("nebel-raven-3.5b", **over).construct_model()
+    sd = ref_model.state_dict()
+    assert set(sd) == set(model.state_dict()), set(sd) ^ set(model.state_dict())
+    model.load_state_dict(sd)
+    ids, labels = torch.randint(0, 512, (2, 64)), torch.randint(0, 512, (2, 64))
+    ref_model.config.state_init = model.config.state_init = "zero"
+    a = ref_model(ids, labels=labels, num_steps_pair=torch.tensor([1, 2]))
+    b = model(ids, labels=labels, num_steps_pair=torch.tensor([1, 2]))
+    assert torch.allclose(a["loss"], b["loss"], rtol=2e-5, atol=1e-6), (a["loss"], b["loss"])
+    a["loss"].backward()
+    b["loss"].backward()
+    theirs = dict(ref_model.named_parameters())
+    for n, p in model.named_parameters():
+        if theirs[n].grad is None:
+            assert p.grad is None or float(p.grad.abs().max()) == 0.0, n
+        else:
+            assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-3, atol=1e-6), n
+
+
+def test_linear_default_init_is_a_three_sigma_truncated_normal():
+    from recurrent_pretraining_b200.models.blocks import Linear, Relu2
+
+    torch.manual_seed(0)
+    lin = Linear(256, 512)                                   # reference signature: bias defaults to True
+    std = 1 / 16
+    assert lin.bias is not None and float(lin.bias.abs().max()) == 0.0
+    assert float(lin.weight.abs().max()) <= 3 * std + 1e-6 and abs(float(lin.weight.std()) - std) < 0.05 * std
+    marked = Linear(8, 8, bias=False, init_method=lambda w: torch.nn.init.constant_(w, 0.25))
+    assert marked.bias is None and float(marked.weight.min()) == 0.25 and marked.init_method is not None
+    assert torch.equal(Relu2()(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0]))
