@@ -223,7 +223,11 @@ class CausalSelfAttention(nn.Module):
         post = cfg.center_attention or cfg.debias_attention
         softcap = 20.0 if cfg.attn_impl == "flex-attention-soft-cap" else 0.0
         plain = not (cfg.qk_norm or self.monitoring or cfg.attn_impl == "debug-skip" or softcap)
-        if (plain and not post and FUSE_ROPE and x.is_cuda and self.config.clip_qkv is None and self.Wqkv.bias is None
+        # grouped keys with a q/k bias: the reference repeats k (and v) to all query heads and THEN adds the bias, which
+        # has one row per query head (recpre/model_dynamic.py:357-366), so the keys differ inside a group
+        expand = self.qk_bias is not None and self.n_kv != self.n_head
+        n_kv = self.n_head if expand else self.n_kv
+        if (plain and not post and not expand and FUSE_ROPE and x.is_cuda and self.config.clip_qkv is None and self.Wqkv.bias is None
                 and self.config.rope_settings.use_rope):
             # bias + rotation ride in the epilogue of the QKV GEMM
             y = ops.qkv_rope_attention(x, self.Wqkv.weight, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
@@ -231,24 +235,30 @@ class CausalSelfAttention(nn.Module):
         qkv = self.Wqkv(x)
         if self.config.clip_qkv is not None:
             qkv = qkv.clamp(min=-self.config.clip_qkv, max=self.config.clip_qkv)
+        if expand:
+            wq, wk, rep = self.n_head * self.head_dim, self.n_kv * self.head_dim, self.n_head // self.n_kv
+            q, k, v = qkv.split([wq, wk, wk], dim=-1)
+            k, v = (t.reshape(B, S, self.n_kv, 1, self.head_dim).expand(B, S, self.n_kv, rep, self.head_dim)
+                    .reshape(B, S, wq) for t in (k, v))
+            qkv = torch.cat([q, k, v], dim=-1)
         if not self.config.rope_settings.use_rope:
             cos, sin = torch.ones_like(cos), torch.zeros_like(sin)
         if plain:
-            y = ops.rope_attention(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+            y = ops.rope_attention(qkv, self.qk_bias, cos, sin, self.n_head, n_kv, self.head_dim)
             if post:     # the providers' post-operations need the (un-rotated) values beside the attention output
-                wq, wk = self.n_head * self.head_dim, self.n_kv * self.head_dim
-                v = qkv[..., wq + wk:].reshape(B, S, self.n_kv, self.head_dim)
+                wq, wk = self.n_head * self.head_dim, n_kv * self.head_dim
+                v = qkv[..., wq + wk:].reshape(B, S, n_kv, self.head_dim)
                 y = _center_debias(y.reshape(B, S, self.n_head, self.head_dim), v, self.n_head, cfg.center_attention,
                                    cfg.debias_attention).reshape(B, S, E)
             return self.proj(y)
-        q, k, v = _split_rope(qkv, self.qk_bias, cos, sin, self.n_head, self.n_kv, self.head_dim)
+        q, k, v = _split_rope(qkv, self.qk_bias, cos, sin, self.n_head, n_kv, self.head_dim)
         if self.config.qk_norm:
             q = F.rms_norm(q, (q.shape[-1],))
             k = F.rms_norm(k, (k.shape[-1],))
         if self.config.attn_impl == "debug-skip":
             # attention bypass for pure-GEMM sanity models: the values pass through (recpre/attention_backends/
             # interface.py:37-39)
-            y = v if self.n_kv == self.n_head else v.repeat_interleave(self.n_head // self.n_kv, dim=2)
+            y = v if n_kv == self.n_head else v.repeat_interleave(self.n_head // n_kv, dim=2)
         else:
             y = _dense_attention(q, k, v, softcap)
             if post:

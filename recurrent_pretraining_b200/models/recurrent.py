@@ -236,9 +236,15 @@ class RecurrentGPT(_LMBase):
             elif c.geom_noise_injection == "line":
                 top = max(int(getattr(c, "maximal_recurrence", None) or c.mean_recurrence), 1)
                 f = max(noise, (top - step) / top)
+            elif c.geom_noise_injection == "chi":
+                # as in the reference (recpre/model_dynamic.py:1227-1228): a noise level is drawn and not applied;
+                # the draw is kept so that the random stream stays the same
+                torch.rand(1, device=x.device, dtype=x.dtype)
+                f = None
             else:
                 f = noise
-            x = x * (1 - f) + torch.randn_like(x) * f
+            if f is not None:
+                x = x * (1 - f) + torch.randn_like(x) * f
         per_block = self.gradient_checkpointing and "per-block" in c.activation_checkpoint_impl
         if self._modulated_core:
             for block in self.transformer.core_block:
@@ -261,6 +267,9 @@ class RecurrentGPT(_LMBase):
             pair = [int(v) for v in torch.as_tensor(num_steps_pair).reshape(-1).tolist()]
             n, k = (pair[0], pair[1]) if len(pair) > 1 else (pair[0], 0)
         self.last_depths = (n, k)
+        offset = 0
+        if getattr(self.config, "randomize_embed_step", False):     # recpre/model_dynamic.py:1175-1178
+            offset = int(torch.randint(0, self.config.mean_recurrence * 8, (1,), device=e.device))
         xk = x
         inj = None
         if (HOIST_ADAPTER and self.config.injection_type == "linear" and e.is_cuda and n + k > 1
@@ -269,14 +278,14 @@ class RecurrentGPT(_LMBase):
         with torch.no_grad():
             for step in range(n):
                 xk = x
-                x = self.core_block_forward(x, e, rope, mask, step, inj)
+                x = self.core_block_forward(x, e, rope, mask, step + offset, inj)
         per_iter = self.gradient_checkpointing and "per-iteration" in self.config.activation_checkpoint_impl
         for step in range(k):
             xk = x
             if per_iter and torch.is_grad_enabled():
-                x = self._ckpt()(self.core_block_forward, x, e, rope, mask, n + step, inj)
+                x = self._ckpt()(self.core_block_forward, x, e, rope, mask, n + step + offset, inj)
             else:
-                x = self.core_block_forward(x, e, rope, mask, n + step, inj)
+                x = self.core_block_forward(x, e, rope, mask, n + step + offset, inj)
         return self.transformer.ln_f(x), n, k, xk.detach()
 
     def _hoists_adapter(self) -> bool:

@@ -259,20 +259,36 @@ def test_soft_capped_attention_logits():
                                    dict(norm_class_name="LayerNorm"), dict(norm_class_name="GemmalikeRMS"),
                                    dict(norm_class_name="UnparametrizedRMSNorm"), dict(norm_class_name="Identity"),
                                    dict(bias=True), dict(qk_norm=True), dict(clip_qkv=0.5), dict(tie_embeddings=False),
-                                   dict(lm_head_bias=True)], ids=lambda e: "-".join(f"{k}={v}" for k, v in e.items()))
+                                   dict(lm_head_bias=True), dict(num_key_value_heads=2),
+                                   dict(num_key_value_heads=1, qk_norm=True), dict(num_key_value_heads=2, qk_bias=False),
+                                   dict(embed_step=True, randomize_embed_step=True),
+                                   dict(intermediate_noise_injection=0.1, geom_noise_injection="chi"),
+                                   dict(intermediate_noise_injection=0.1, geom_noise_injection="sqrt"),
+                                   dict(attn_impl="debug-skip"), dict(num_key_value_heads=2, center_attention=True),
+                                   dict(debias_attention=True), dict(injection_type="gate"), dict(injection_type="ffn"),
+                                   dict(mcleish_throttle=True), dict(elbayad_weighing=True, elbayad_exponent=2.0)],
+                         ids=lambda e: "-".join(f"{k}={v}" for k, v in e.items()))
 def test_config_options_match_reference(extra):
     """Nonlinearity (ReLU2 carries the reference's factor 0.5), MLP class, norm class, biases, qk norm, qkv clipping,
-    untied head: same state-dict keys, same loss and gradients as the reference model built from the same overrides."""
+    untied head, grouped keys (with the q/k bias the reference adds the k bias per query head, after repeating k), step
+    embedding with a random offset, state noise (the ``chi`` form draws a level and applies nothing), attention
+    providers, injection types, loss weightings: same state-dict keys, same loss and gradients as the reference model
+    built from the same overrides, under the same random stream."""
     torch.manual_seed(0)
-    over = dict(TINY, attn_impl="sdpa", **extra)
+    over = dict(TINY, **{"attn_impl": "sdpa", **extra})
     ref_model, _ = refload.build_train_model("nebel-raven-3.5b", **over)
     model = ModelConfig.from_name("nebel-raven-3.5b", **over).construct_model()
     sd = ref_model.state_dict()
     assert set(sd) == set(model.state_dict()), set(sd) ^ set(model.state_dict())
+    for n, p in ref_model.named_parameters():
+        if "qk_bias" in n:
+            sd[n].normal_()                       # a zero bias would hide how it is applied
     model.load_state_dict(sd)
     ids, labels = torch.randint(0, 512, (2, 64)), torch.randint(0, 512, (2, 64))
     ref_model.config.state_init = model.config.state_init = "zero"
+    torch.manual_seed(5)
     a = ref_model(ids, labels=labels, num_steps_pair=torch.tensor([1, 2]))
+    torch.manual_seed(5)
     b = model(ids, labels=labels, num_steps_pair=torch.tensor([1, 2]))
     assert torch.allclose(a["loss"], b["loss"], rtol=2e-5, atol=1e-6), (a["loss"], b["loss"])
     a["loss"].backward()
@@ -282,7 +298,7 @@ def test_config_options_match_reference(extra):
         if theirs[n].grad is None:
             assert p.grad is None or float(p.grad.abs().max()) == 0.0, n
         else:
-            assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-3, atol=1e-6), n
+            assert torch.allclose(p.grad, theirs[n].grad, rtol=1e-3, atol=1e-6, equal_nan=True), n
 
 
 def test_linear_default_init_is_a_three_sigma_truncated_normal():
