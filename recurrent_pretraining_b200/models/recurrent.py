@@ -128,6 +128,21 @@ class _LMBase(nn.Module):
         return zero, logits, zero
 
 
+def _accept_transposed_head(module: nn.Module) -> None:
+    """The reference's Triton head keeps ``lm_head.weight`` as [E, V] (untied ``full-triton`` head of the recurrent model,
+    every GPT baseline: recpre/ops.py:1084-1088); here the head is always [V, E].  Checkpoints in the other layout are
+    transposed while they load."""
+
+    def hook(state_dict, prefix, *_):
+        key = prefix + "lm_head.weight"
+        w = state_dict.get(key)
+        want = module.lm_head.weight.shape
+        if w is not None and w.dim() == 2 and tuple(w.shape) != tuple(want) and tuple(w.shape) == tuple(want)[::-1]:
+            state_dict[key] = w.t().contiguous()
+
+    module._register_load_state_dict_pre_hook(hook)
+
+
 class RecurrentGPT(_LMBase):
     def __init__(self, config, objective: Optional[dict] = None, gradient_checkpointing: bool = False, **_):
         super().__init__()
@@ -154,6 +169,7 @@ class RecurrentGPT(_LMBase):
                               init=lambda w: init.init_weight_(w, "head"))
         if config.tie_embeddings:
             self.lm_head.weight = self.transformer.wte.weight
+        _accept_transposed_head(self)
         if getattr(config, "embed_step", False):
             from .variants import TimestepEmbedder
 
@@ -384,6 +400,7 @@ class GPT(_LMBase):
             ln_f=make_norm(config)))
         self.lm_head = Linear(config.n_embd, config.padded_vocab_size, bias=config.lm_head_bias,
                               init=lambda w: init.init_weight_(w, "head"))
+        _accept_transposed_head(self)
         self.emb_scale = math.sqrt(config.n_embd) if config.scale_embeddings else init.embedding_scale
         self.gradient_checkpointing = gradient_checkpointing
         self.max_seq_length = config.block_size

@@ -312,3 +312,29 @@ def test_linear_default_init_is_a_three_sigma_truncated_normal():
     marked = Linear(8, 8, bias=False, init_method=lambda w: torch.nn.init.constant_(w, 0.25))
     assert marked.bias is None and float(marked.weight.min()) == 0.25 and marked.init_method is not None
     assert torch.equal(Relu2()(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0]))
+
+
+@needs_ref
+@pytest.mark.parametrize("name", ["baby-llama-200m", "baby-snake-200m", "gpt2-124m", "brick-200m", "big-brick-200m",
+                                  "tiny-llama-1.1b"])
+def test_gpt_baselines_load_reference_checkpoints_and_give_the_same_logits(name):
+    """The non-recurrent baselines.  The reference keeps their head weight transposed ([E, V], for its Triton head);
+    it is turned while loading.  Logits of the evaluation path agree (the reference's training path needs its Triton
+    kernel and a GPU)."""
+    small = dict(block_size=64, vocab_size=4096, padding_multiple=4096, n_embd=256, num_attention_heads=4,
+                 num_key_value_heads=4, intermediate_size=320, n_layer=2)
+    if name_to_config[name].get("num_key_value_heads", 0) != name_to_config[name].get("num_attention_heads", 0):
+        small["num_key_value_heads"] = 2
+    torch.manual_seed(0)
+    ref_model, _ = refload.build_train_model(name, **small)
+    model = ModelConfig.from_name(name, **small).construct_model()
+    sd = ref_model.state_dict()
+    assert set(sd) == set(model.state_dict())
+    assert tuple(sd["lm_head.weight"].shape) == (256, 4096) and tuple(model.lm_head.weight.shape) == (4096, 256)
+    model.load_state_dict(sd)
+    ids = torch.randint(0, 4096, (2, 64))
+    ref_model.eval(), model.eval()
+    with torch.no_grad():
+        a = ref_model(ids, return_logits=True)["logits"]
+        b = model(ids, return_logits=True)["logits"]
+    assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), float((a - b).abs().max())
