@@ -1,8 +1,16 @@
 """Goldfish loss: deterministic token-loss dropout on the labels (recpre/utils.py:1395-1517).
 
-Strategies: ``static`` (every k-th position), ``seeded_random``, ``hash-table`` (a fixed table of uniforms indexed by
-the product of the previous ``context_width`` labels mod a prime) and ``hash-avalanche`` (Thomas Wang's 64-bit integer
-hash of that product, truncated to 32 bits).  Dropped labels are replaced by ``ignore_index``.
+Strategies: ``static`` (every k-th position), ``seeded_random`` / ``pure_random`` (each position with probability 1/k
+from the global / a time-seeded generator), ``random_but_consisent_for_given_micro_batch`` (generator seeded by the sum
+of the labels), ``hash-table`` (a fixed table of uniforms indexed by the product of the previous ``context_width``
+labels mod a prime), ``hash-avalanche`` (Thomas Wang's 64-bit integer hash of that product, truncated to 32 bits) and
+``hash-legacy`` (one generator draw per position, seeded by the product; slow, for cross-checks).  Dropped labels are
+replaced by ``ignore_index``.
+
+The random strategies and ``hash-legacy`` apply their 0/1 draw as a boolean mask over positions.  The reference indexes
+with the 0/1 integers instead (recpre/utils.py:1450-1480), which blanks rows 0 and 1 of the batch whatever was drawn,
+and its ``hash-legacy`` never hands its seeded generator to the draw; the hash strategies that the shipped runs use
+(``hash-table``, ``hash-avalanche``) and ``static`` are the same in both.
 """
 from __future__ import annotations
 
@@ -48,8 +56,26 @@ def apply_tld(labels: torch.Tensor, settings, ignore_index: int = -100):
         idx = torch.arange(S, device=labels.device)[start::k]
         out[:, idx] = ignore_index
         return out, idx
-    if strategy in ("seeded_random", "pure_random"):
-        drop = torch.randint(1, k + 1, labels.shape, device=labels.device) == k
+    if strategy in ("seeded_random", "pure_random", "random_but_consisent_for_given_micro_batch"):
+        gen = None
+        if strategy == "pure_random":
+            import time
+
+            gen = torch.Generator().manual_seed(int(time.time()))
+        elif strategy != "seeded_random":
+            gen = torch.Generator().manual_seed(int(labels.sum().item()))
+        drop = (torch.randint(1, k + 1, labels.shape, generator=gen) == k).to(labels.device)
+        out[drop] = ignore_index
+        return out, drop.int()
+    if strategy == "hash-legacy":
+        drop = torch.zeros(B, S, dtype=torch.bool)
+        gen = torch.Generator()
+        host = labels.cpu()
+        for b in range(B):
+            for pos in range(width, S):
+                gen.manual_seed(int(host[b, pos - width:pos].prod().item()) % (2 ** 63 - 1))
+                drop[b, pos] = bool(torch.rand((1,), generator=gen) < 1.0 / k)
+        drop = drop.to(labels.device)
         out[drop] = ignore_index
         return out, drop.int()
     keys = labels.unfold(1, width, 1).prod(dim=-1)

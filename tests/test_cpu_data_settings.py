@@ -338,3 +338,35 @@ def test_data_classes_accept_the_reference_constructor_keywords(tmp_path):
     assert Tokenizer(tmp_path / "missing", broken_state_load_fallback=True).processor is None
     with pytest.raises(NotADirectoryError):
         Tokenizer(tmp_path / "missing", broken_state_load_fallback=False)
+
+
+def test_goldfish_strategies_against_the_reference_and_their_definitions():
+    """``static`` and ``hash-table`` equal the reference's masks bit for bit; the random strategies drop about 1/k of
+    the positions of EVERY row (the reference blanks rows 0 and 1 instead); ``hash-legacy`` and the micro-batch-seeded
+    form are functions of the labels alone."""
+    import refload
+
+    from recurrent_pretraining_b200.data.goldfish import apply_tld
+    from recurrent_pretraining_b200.settings import GoldfishConfig
+
+    torch.manual_seed(0)
+    labels = torch.randint(1, 500, (4, 96))
+    if refload.available():
+        ref_tld = refload.module("utils").apply_tld
+        for strat in ("static", "hash-table"):
+            for k, start, ctx in ((2, 0, 3), (4, 5, 13), (3, 1, 4)):
+                cfg = GoldfishConfig(strategy=strat, k_token_loss_dropout=k, start_position=start, context_width=ctx)
+                want, _ = ref_tld(labels.clone(), cfg, ignore_index=-100)
+                got, _ = apply_tld(labels.clone(), cfg, ignore_index=-100)
+                assert torch.equal(got, want), (strat, k, start, ctx)
+    for strat in ("seeded_random", "pure_random", "random_but_consisent_for_given_micro_batch", "hash-legacy"):
+        cfg = GoldfishConfig(strategy=strat, k_token_loss_dropout=4, context_width=3)
+        out, drop = apply_tld(labels, cfg)
+        frac = (out == -100).float().mean(dim=1)
+        assert bool(((frac > 0.05) & (frac < 0.5)).all()), (strat, frac)
+        assert torch.equal((out == -100), drop.bool()) and torch.equal(out[out != -100], labels[out != -100])
+    for strat in ("random_but_consisent_for_given_micro_batch", "hash-legacy", "hash-avalanche"):
+        cfg = GoldfishConfig(strategy=strat, k_token_loss_dropout=3, context_width=3)
+        assert torch.equal(apply_tld(labels, cfg)[0], apply_tld(labels.clone(), cfg)[0])
+    with pytest.raises(NotImplementedError):
+        apply_tld(labels, GoldfishConfig(strategy="nope"))
