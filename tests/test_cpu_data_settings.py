@@ -370,3 +370,82 @@ def test_goldfish_strategies_against_the_reference_and_their_definitions():
         assert torch.equal(apply_tld(labels, cfg)[0], apply_tld(labels.clone(), cfg)[0])
     with pytest.raises(NotImplementedError):
         apply_tld(labels, GoldfishConfig(strategy="nope"))
+
+
+def test_collate_matches_the_reference_collate_function():
+    """Tensor rows (fast and general path, pad replaced by eos in the inputs only) and text rows with every format
+    function, against recpre/data_loading_utils.py:generic_collate_fn on the same batches."""
+    import copy
+
+    import refload
+
+    if not refload.available():
+        pytest.skip("reference not installed under baseline/_ref")
+    ref_collate = refload.module("data_loading_utils").generic_collate_fn
+    from recurrent_pretraining_b200.data.collate import generic_collate_fn
+
+    class Tok:
+        pad_id, eos_id, bos_id = 0, 2, 1
+
+        def encode(self, s, bos=False, eos=False, device=None, max_length=-1):
+            ids = [3 + (ord(c) % 50) for c in s]
+            ids = ([self.bos_id] if bos else []) + ids + ([self.eos_id] if eos else [])
+            return torch.tensor(ids[:max_length] if max_length > 0 else ids, dtype=torch.int)
+
+    def same(x, y):
+        if torch.is_tensor(x):
+            return torch.is_tensor(y) and x.shape == y.shape and torch.equal(x.long(), y.long())
+        if isinstance(x, (list, tuple)):
+            return len(x) == len(y) and all(same(i, j) for i, j in zip(x, y))
+        return x == y
+
+    tok = Tok()
+    torch.manual_seed(0)
+    rows = [torch.randint(3, 60, (17,)) for _ in range(3)]
+    rows[0][5] = 0
+    batches = [(rows, kw) for kw in (dict(block_size=16, all_block_size_tensors=True),
+                                     dict(block_size=16, pad_to_block_size=True), dict(block_size=16))]
+    for fmt, keys in (("pass_text", ["text"]), ("concat_input_target", ["input", "target"]),
+                      ("condition_input_supervise_target", ["input", "target"])):
+        sig = {"keys": keys, "format_fn": fmt}
+        text = [dict({k: ("hello world " * (i + 1))[:7 * (i + 1) + j] for j, k in enumerate(keys)}, data_signature=sig)
+                for i in range(3)]
+        batches += [(text, kw) for kw in (dict(block_size=24, pad_to_block_size=True), dict(block_size=24),
+                                          dict(block_size=12, add_bos=False))]
+    for batch, kw in batches:
+        want = ref_collate(copy.deepcopy(batch), tok, **kw)
+        got = generic_collate_fn(copy.deepcopy(batch), tok, **kw)
+        assert same(want, got), kw
+
+
+def test_parquet_stream_yields_rows_in_the_reference_order(tmp_path, capsys):
+    """File shuffle, per-rank file striding (with the later-expansion plan) and the per-row-group shuffle give the same
+    row sequence as recpre/huggingface_dataset.py:ParquetStreamPure on the same shards."""
+    import random
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    import refload
+
+    if not refload.available():
+        pytest.skip("reference not installed under baseline/_ref")
+    ref_cls = refload.module("huggingface_dataset").ParquetStreamPure
+    from recurrent_pretraining_b200.data.datasets import ParquetStream
+
+    rng = random.Random(0)
+    for f in range(40):
+        rows = [[f * 1000 + g * 100 + i, rng.randrange(100)] for g in range(3) for i in range(7)]
+        pq.write_table(pa.table({"input_ids": rows}), tmp_path / f"train_{f:03d}.parquet", row_group_size=7)
+
+    def take(ds, n):
+        it = iter(ds)
+        return [[int(v) for v in next(it)] for _ in range(n)]
+
+    base = dict(dataset_folder_path=str(tmp_path), seed=7, prefix="train_", broadcast_glob=False)
+    for kw in (dict(num_processes=1, process_rank=0), dict(num_processes=2, process_rank=1),
+               dict(num_processes=2, process_rank=0, shuffle=False),
+               dict(num_processes=1, process_rank=0, shuffle_filenames=False),
+               dict(num_processes=3, process_rank=2, plan_for_later_rank_expansion_to=0),
+               dict(num_processes=16, process_rank=9)):
+        assert take(ref_cls(**base, **kw), 30) == take(ParquetStream(**base, **kw), 30), kw
+    capsys.readouterr()
