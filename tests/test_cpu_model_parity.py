@@ -338,3 +338,56 @@ def test_gpt_baselines_load_reference_checkpoints_and_give_the_same_logits(name)
         a = ref_model(ids, return_logits=True)["logits"]
         b = model(ids, return_logits=True)["logits"]
     assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), float((a - b).abs().max())
+
+
+@needs_ref
+def test_every_init_strategy_matches_the_reference_initialiser():
+    """All 25 strategies of recpre/init.py, with and without the orthogonal variant and a muP factor: the scalar queries
+    (which the reference evaluates with its arguments one place off) and the tensors produced for every layer role are
+    the same, bit for bit under the same seed.  Left out on purpose: zero deviations (the reference divides by zero
+    there, here the tensor is zero-filled) and the untruncated mode on fused tensors (the reference passes the deviation
+    as the mean)."""
+    from recurrent_pretraining_b200.models import init as mine
+
+    ref_init = refload.module("init")
+    strategies = list(ref_init.get_factor_table(256, 640, 32, 0, 8))
+    assert len(strategies) == 25 and set(strategies) <= set(mine.STRATEGIES)
+    roles = (("qkv", (256 + 2 * 64, 256)), ("qkv-diagonal", (3 * 256, 256)), ("out_attn", (256, 256)),
+             ("glu", (2 * 640, 256)), ("w1", (640, 256)), ("w2", (256, 640)), ("mlp", (640, 256)), ("v", (256, 256)),
+             ("head", (512, 256)), ("embedding", (512, 256)), ("in_proj", (256, 512)), ("out_proj", (256, 640)),
+             ("normalization", (256,)), ("unnamed_layer", (64, 256)))
+    checked = 0
+    for st in strategies:
+        for mu, orth in ((1, False), (2, False), (1, True)):
+            r = ref_init.Init(st, 256, 640, 32, 8, mu, orthogonal=orth, verbose=False)
+            m = mine.Init(st, 256, 640, 32, 8, mu, orthogonal=orth)
+            assert r.embedding_scale == m.embedding_scale and r.logit_scale == m.logit_scale, st
+            for li in (-1, 3):
+                assert r.get_scales(li) == m.get_scales(li), (st, li)
+                for role in ("embedding", "head", "out_attn", "w1", "q", "mlp", "anything"):
+                    try:
+                        want = r.get_std(role, li)
+                    except KeyError:
+                        with pytest.raises(ValueError):
+                            m.get_std(role, li)
+                        continue
+                    assert want == m.get_std(role, li), (st, role, li)
+            for role, shape in roles:
+                for li in (0, 5):
+                    a, b = torch.empty(shape), torch.empty(shape)
+                    torch.manual_seed(0)
+                    try:
+                        r.fn(role, li)(a)
+                    except ZeroDivisionError:            # deviation 0.0 in the reference's truncated normal
+                        m.fn(role, li)(b)
+                        assert float(b.abs().max()) == 0.0
+                        continue
+                    except ValueError:
+                        with pytest.raises(ValueError):
+                            m.fn(role, li)(b)
+                        continue
+                    torch.manual_seed(0)
+                    m.fn(role, li)(b)
+                    assert torch.equal(a, b), (st, mu, orth, role, li)
+                    checked += 1
+    assert checked > 1500
