@@ -192,6 +192,10 @@ class CLISettings:
             self.gradient_accumulation_steps = 1
         self.replicas = self.devices * self.num_nodes
         self.dataset_names = [e.prefix for e in self.data_config["train_data"]]
+        self.train_dataset_prefixes = list(self.dataset_names)
+        self.val_dataset_prefixes = [e.prefix for e in self.data_config.get("val_data", [])]
+        # filled in by the trainer at start-up (recpre/settings.py:226-228)
+        self.global_total_time, self.max_tokens_per_device, self.tokens_per_step = 0, 0, 0
         self._validate_args()
         from .config import ModelConfig
 
@@ -201,8 +205,10 @@ class CLISettings:
         self.model_config = ModelConfig.from_name(self.model_name, **overrides)
         self.model_config.strategy = self.fabric_strategy
         if self.max_steps is None:
-            tokens_per_step = self.world_batch_size * self.block_size
-            self.max_steps = max(int(self.max_tokens // tokens_per_step), 1) * self.gradient_accumulation_steps
+            # micro-steps per device, as the reference derives them at start-up (train.py:268-271)
+            self.max_tokens_per_device = self.max_tokens // max(self.replicas, 1)
+            self.tokens_per_step = self.micro_batch_size * self.block_size
+            self.max_steps = max(int(self.max_tokens_per_device // self.tokens_per_step), 1)
 
     def _validate_args(self):
         if not ((self.max_steps is not None) ^ (self.max_tokens > 0)):
@@ -222,7 +228,9 @@ class CLISettings:
     def _parse_environment_variables(self):
         env = os.getenv
         self.SLURM_JOB_ID = int(env("SLURM_JOB_ID", 0))
+        self.SLURM_ARRAY_JOB_ID = int(env("SLURM_ARRAY_JOB_ID", 0))
         self.SLURM_ARRAY_TASK_ID = int(env("SLURM_ARRAY_TASK_ID", 0))
+        self.SLURM_ARRAY_TASK_COUNT = int(env("SLURM_ARRAY_TASK_COUNT", 1))
         self.MASTER_ADDR = env("MASTER_ADDR", "127.0.0.1")
         self.MASTER_PORT = int(env("MASTER_PORT", 0))
         self.WORLD_SIZE = int(env("SLURM_NTASKS", env("WORLD_SIZE", 1)))

@@ -449,3 +449,61 @@ def test_parquet_stream_yields_rows_in_the_reference_order(tmp_path, capsys):
                dict(num_processes=16, process_rank=9)):
         assert take(ref_cls(**base, **kw), 30) == take(ParquetStream(**base, **kw), 30), kw
     capsys.readouterr()
+
+
+@pytest.mark.parametrize("name", ["recurrent.yaml", "frontier_nebel_512_nodes.yaml", "frontier_baseline_256_nodes.yaml"])
+def test_derived_settings_match_the_reference_settings_class(name, monkeypatch):
+    """The reference's launch configs through the reference's ``CLISettings`` and through ours, under the same SLURM
+    environment: every derived attribute (batch arithmetic, loader block size, dataset prefixes, environment fields)
+    and every field both classes have agree."""
+    import dataclasses
+
+    import refload
+    import yaml
+
+    if not refload.available():
+        pytest.skip("reference not installed under baseline/_ref")
+    theirs_mod = refload.module("settings")
+    from recurrent_pretraining_b200 import settings as ours_mod
+
+    for k, v in {"SLURM_JOB_NUM_NODES": "4", "SLURM_NTASKS": "32", "SLURM_NTASKS_PER_NODE": "8", "WORLD_SIZE": "32",
+                 "SLURM_JOB_ID": "77", "SLURM_ARRAY_TASK_ID": "2", "SLURM_ARRAY_TASK_COUNT": "5",
+                 "SLURM_ARRAY_JOB_ID": "70", "SLURM_PROCID": "3", "MASTER_ADDR": "node0", "MASTER_PORT": "29400",
+                 "OUTPUT_DIR": "/tmp/out"}.items():
+        monkeypatch.setenv(k, v)
+    path = os.path.join(os.path.dirname(__file__), "..", "launch_configs", name)
+
+    def build(mod):
+        y = yaml.safe_load(open(path))
+        if "fabric" in y:
+            y["fabric"] = mod.FabricConfig(**y["fabric"])
+        if "goldfish" in y:
+            y["goldfish"] = mod.GoldfishConfig(**y["goldfish"])
+        if isinstance(y.get("data_config"), dict):
+            y["data_config"] = {k: [mod.DataEntry(**e) for e in v] for k, v in y["data_config"].items()}
+        return mod.CLISettings(**y)
+
+    a, b = build(theirs_mod), build(ours_mod)
+    def plain(v):
+        if dataclasses.is_dataclass(v):
+            return dataclasses.asdict(v)
+        if isinstance(v, dict):
+            return {k: plain(x) for k, x in v.items()}
+        if isinstance(v, (list, tuple)):
+            return [plain(x) for x in v]
+        return v
+
+    # derived later over there / a site-specific default path
+    skipped = {"model_config", "max_steps", "max_tokens_per_device", "tokens_per_step", "tokenizer_path"}
+    for key, want in vars(a).items():
+        if key in skipped:
+            continue
+        assert hasattr(b, key), key
+        assert plain(getattr(b, key)) == plain(want), (key, getattr(b, key), want)
+    # the step budget the reference derives at start-up (train.py:268-271)
+    world = a.devices * a.num_nodes
+    assert b.max_steps == (a.max_tokens // world) // (a.micro_batch_size * a.block_size)
+    for key in ("n_embd", "intermediate_size", "mean_recurrence", "mean_backprop_depth", "sampling_scheme",
+                "injection_type", "block_class_name", "norm_class_name", "init_strategy", "padded_vocab_size"):
+        if hasattr(a.model_config, key):
+            assert getattr(b.model_config, key) == getattr(a.model_config, key), key
