@@ -363,3 +363,30 @@ def test_named_weight_schedules_match_the_mixture_scheduler():
     assert repr(S.StepWeight(8, 10, 0.5)) == "StepWeight: 8, 10, 0.5"
     with pytest.raises(NotImplementedError):
         S.GetScheduler(["spline", 1], 1)
+
+
+def test_schedules_take_the_reference_call_forms():
+    """``get_lr(step, max_steps, cfg)`` / ``get_batch_size(step, cfg)`` as in the reference's train.py:831-862 beside the
+    scalar forms; values from the piecewise definition."""
+    import math
+    import types
+
+    from recurrent_pretraining_b200.optim.schedules import get_batch_size, get_lr
+
+    cfg = types.SimpleNamespace(optim_config={"lr": 3e-3}, warmup_steps=10, cooldown_steps=20, lr_schedule="cosine",
+                                min_lr=1e-4, batch_size_ramp=30, batch_size=50, micro_batch_size=4)
+    for step in (0, 5, 10, 40, 80, 81, 95, 100):
+        a = get_lr(step, 100, cfg)
+        assert a == get_lr(3e-3, step, 10, 100, 20, "cosine", 1e-4)
+        if step < 10:
+            want = 3e-3 * step / 10
+        elif step > 80:
+            want = max(3e-3 * (100 - step) / 20, 1e-4)
+        else:
+            want = 1e-4 + 0.5 * (1 + math.cos(math.pi * (step - 10) / 90)) * (3e-3 - 1e-4)
+        assert abs(a - want) < 1e-15, step
+    assert get_lr(120, 100, types.SimpleNamespace(**{**vars(cfg), "cooldown_steps": 0})) == 1e-4   # past the end
+    cfg.lr_schedule = "linear"
+    assert abs(get_lr(55, 100, cfg) - (3e-3 - 0.5 * (3e-3 - 1e-4))) < 1e-15
+    assert [get_batch_size(s, cfg) for s in (1, 15, 30, 31, 500)] == [1, math.ceil(0.5 * 12.5), 13, 12, 12]
+    assert [get_batch_size(s, 30, 12) for s in (0, 15, 30, 31)] == [1, 6, 12, 12]
