@@ -134,24 +134,24 @@ def reduce_memorization_metrics(stats_list: Sequence[dict], fabric=None, dataset
 def chunked_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, chunk_size: int = 128,
                           ignore_indices: Sequence[Optional[int]] = (-1,), reduction: Optional[str] = None,
                           training: bool = True, z_loss_eps: float = 0.0,
-                          target_range: Optional[tuple[int, int]] = None):
+                          target_range: Optional[Sequence[int]] = None, return_logits_targets: bool = False):
     """Mean cross entropy over non-ignored positions, evaluated ``chunk_size`` rows at a time so that the softmax
-    temporaries of the whole [tokens, vocab] matrix never exist at once; several ignore ids are folded into the first;
-    ``target_range = (lo, hi)`` restricts the softmax to that slice of the vocabulary (labels outside it are ignored);
-    optional z-loss ``eps * mean(logsumexp^2)`` in training."""
-    ignore = ignore_indices[0] if ignore_indices and ignore_indices[0] not in (None, 0) else -100
-    targets = targets.reshape(-1).clone()
+    temporaries of the whole [tokens, vocab] matrix never exist at once (recpre/utils.py:536-597).  The first entry of
+    ``ignore_indices`` is the ignore value (a zero or None there means -100), further entries are folded into it;
+    ``target_range`` is a sorted list of vocabulary ids to which the classification is restricted (logits keep those
+    columns, the i-th id becomes class i); optional z-loss ``eps * mean(logsumexp^2)`` in training.  With
+    ``return_logits_targets`` the logits and targets of the non-ignored rows are returned beside the loss."""
+    ignore = ignore_indices[0] or -100
+    targets = targets.clone()
     for extra in list(ignore_indices)[1:]:
         if extra is not None and extra != ignore:
             targets[targets == extra] = ignore
-    if ignore_indices and ignore_indices[0] not in (None, 0):
-        targets[targets == ignore_indices[0]] = ignore
-    logits = logits.reshape(-1, logits.shape[-1])
+    logits = logits.reshape(-1, logits.size(-1))
+    targets = targets.reshape(-1)
     if target_range is not None:
-        lo, hi = target_range
-        outside = (targets < lo) | (targets >= hi)
-        logits = logits[:, lo:hi]
-        targets = torch.where(outside | (targets == ignore), torch.full_like(targets, ignore), targets - lo)
+        from .helpers import slice_logits_remap_labels
+
+        logits, targets = slice_logits_remap_labels(logits, targets, target_range, list(ignore_indices))
     if chunk_size == 0:
         loss = F.cross_entropy(logits, targets, ignore_index=ignore, **({"reduction": reduction} if reduction else {}))
     else:
@@ -161,7 +161,10 @@ def chunked_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, chunk_siz
         loss = total / (targets != ignore).sum().clamp(min=1)
     if z_loss_eps > 0.0 and training:
         loss = loss + z_loss_eps * torch.logsumexp(logits, dim=-1).pow(2).mean()
-    return loss
+    if not return_logits_targets:
+        return loss
+    keep = targets != ignore
+    return loss, logits[keep, :], targets[keep]
 
 
 # ------------------------------------------------------------------------------------------------------

@@ -152,9 +152,16 @@ def test_utils_extras(tmp_path):
     want = F.cross_entropy(logits.view(-1, 50), torch.where(tg == 49, -100, tg).view(-1), ignore_index=-100)
     assert torch.allclose(extras.chunked_cross_entropy(logits, tg, 16, ignore_indices=[-100, 49]), want, atol=1e-6)
     assert torch.allclose(extras.chunked_cross_entropy(logits, tg, 0, ignore_indices=[-100, 49]), want, atol=1e-6)
-    sl = extras.chunked_cross_entropy(logits, tg, 8, ignore_indices=[-100], target_range=(10, 30))
-    keep = (tg >= 10) & (tg < 30)
-    assert torch.allclose(sl, F.cross_entropy(logits[keep][:, 10:30], tg[keep] - 10), atol=1e-6)
+    # a restricted vocabulary: the listed ids become classes 0, 1, 2 (recpre/utils.py:489-533)
+    few = torch.tensor([[3, 7, 9, -1, 7, 3]])
+    lg6 = torch.randn(1, 6, 50)
+    sl = extras.chunked_cross_entropy(lg6, few, 4, ignore_indices=[-1], target_range=[3, 7, 9])
+    keep = few[0] != -1
+    remapped = torch.tensor([0, 1, 2, 1, 0])
+    assert torch.allclose(sl, F.cross_entropy(lg6[0][keep][:, [3, 7, 9]], remapped), atol=1e-6)
+    loss, kept_logits, kept_targets = extras.chunked_cross_entropy(logits, tg, 16, ignore_indices=[-100, 49],
+                                                                   return_logits_targets=True)
+    assert torch.allclose(loss, want, atol=1e-6) and kept_logits.shape == (2 * 37 - 5, 50) and kept_targets.numel() == 69
     # exact-match statistics
     V, pad = 11, 10
     labels = torch.tensor([[1, 2, 3, 4, 5, pad], [1, 2, 3, 4, 5, 6]])
