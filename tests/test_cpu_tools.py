@@ -161,7 +161,8 @@ def test_utils_extras(tmp_path):
     assert torch.allclose(sl, F.cross_entropy(lg6[0][keep][:, [3, 7, 9]], remapped), atol=1e-6)
     loss, kept_logits, kept_targets = extras.chunked_cross_entropy(logits, tg, 16, ignore_indices=[-100, 49],
                                                                    return_logits_targets=True)
-    assert torch.allclose(loss, want, atol=1e-6) and kept_logits.shape == (2 * 37 - 5, 50) and kept_targets.numel() == 69
+    n_kept = int((tg != 49).sum())
+    assert torch.allclose(loss, want, atol=1e-6) and kept_logits.shape == (n_kept, 50) and kept_targets.numel() == n_kept
     # exact-match statistics
     V, pad = 11, 10
     labels = torch.tensor([[1, 2, 3, 4, 5, pad], [1, 2, 3, 4, 5, 6]])
