@@ -78,7 +78,14 @@ class RavenGenerationMixin:
             if "max_length" in model_kwargs:
                 max_new = min(max_new, model_kwargs["max_length"] - input_ids.shape[1])
         else:
-            max_new = model_kwargs.get("max_length", gc.max_length) - input_ids.shape[1]
+            total = model_kwargs.get("max_length", getattr(gc, "max_length", None))
+            new = getattr(gc, "max_new_tokens", None)
+            if new is not None:                       # a generation config that names the number of new tokens
+                max_new = new if total is None else min(new, total - input_ids.shape[1])
+            elif total is not None:
+                max_new = total - input_ids.shape[1]
+            else:
+                max_new = 20                              # the library's default length budget
         model_kwargs.pop("max_length", None)
         model_kwargs.pop("cache_implementation", None)
         model_kwargs["past_key_values"] = RecurrentKVCache(
@@ -183,12 +190,12 @@ class RavenGenerationMixin:
             return logits.squeeze(1) if original_logits.shape[0] == input_ids.shape[0] else logits.squeeze(0)
         return logits
 
-    def _finish(self, input_ids, gc, model_kwargs, streamer, scores=None):
+    def _finish(self, input_ids, gc, model_kwargs, streamer, scores=None, hidden_states=None):
         if streamer:
             streamer.end()
         if gc.return_dict_in_generate:
             return GenerateOutput(sequences=input_ids, scores=scores or {}, logits=None, attentions=None,
-                                  hidden_states=None, past_key_values=model_kwargs.get("past_key_values"))
+                                  hidden_states=hidden_states, past_key_values=model_kwargs.get("past_key_values"))
         return input_ids
 
     def _update_unfinished(self, unfinished, next_token, stops, model_kwargs, input_ids):
@@ -425,13 +432,18 @@ class RavenGenerationMixin:
                                  inner_recurrence: int = 4, num_steps: int = 32, freeze_strategy: str = "latent-diff",
                                  headway: int = 1, dampened_state_mixer: bool = True, sqrt_mixer: bool = False,
                                  continuous_compute: bool = False, exit_t: float = 0.03, max_wavefront: int = 128,
-                                 max_diffusion_steps: int = 4096, **model_kwargs):
+                                 max_diffusion_steps: int = 4096, return_analysis_tablets: bool = False,
+                                 return_full_state_tablet: bool = False, **model_kwargs):
         """Diffusion-style sampling (batch 1): a wavefront of not-yet-frozen positions is refined together, each sweep
         running ``inner_recurrence`` core iterations over the whole front, proposing tokens for every position and
         extending the front by ``headway`` positions; positions freeze (left to right) once their latent stops moving
         (``latent-diff`` < ``exit_t``) or their token has been stable for ``num_steps / inner_recurrence`` sweeps
         (``token-stability``).  Equivalent to ordinary decoding for ``headway = 1, inner_recurrence = num_steps``
-        (recpre/raven_modeling_minimal.py:1234-1549)."""
+        (recpre/raven_modeling_minimal.py:1234-1549).  Freeze strategies: ``latent-diff`` (relative change of the
+        latent), ``latent-acceleration-1`` / ``-2`` (relative second difference over the last two / three sweeps),
+        ``token-stability``, ``fixed``.  ``return_analysis_tablets`` records, per sweep and on the CPU, the proposed and
+        frozen tokens, the recurrence and stability counters (and with ``return_full_state_tablet`` the bf16 latents)
+        and returns them as ``hidden_states`` of the output."""
         assert input_ids.shape[0] == 1, "Only batch_size=1 supported"
         model_kwargs, gc, max_new = self._prep_generate_args(input_ids, generation_config, cache_lookup_strategy,
                                                              model_kwargs)
@@ -444,7 +456,14 @@ class RavenGenerationMixin:
         stable = torch.zeros(1, size, dtype=torch.long, device=dev)
         like = self.transformer.wte.weight.new_zeros(1, 1, E) if self.transformer.wte.weight.dtype != torch.float32 \
             else torch.zeros(1, 1, E, device=dev)
-        stats = {"core_passes": 0, "tokens_forward": 0, "cache_clears": 0}
+        stats = {"core_passes": 0, "tokens_forward": 0, "cache_clears": 0, "standing_waves": 0}
+        tablets = None
+        if return_analysis_tablets:
+            rows = (max_new + headway) * 2
+            tablets = {name: torch.zeros(rows, size, dtype=torch.long) for name in ("token_tablet", "frozen_tablet",
+                                                                                    "counter_tablet", "stability_tablet")}
+            tablets["state_tablet"] = torch.zeros(rows, size, E, dtype=torch.bfloat16) if return_full_state_tablet \
+                else None
         if full_prefill:
             inputs = self.prepare_inputs_for_generation(input_ids, **model_kwargs)
             out = self(**inputs, init_scale=init_scale, num_steps=num_steps)
@@ -459,6 +478,7 @@ class RavenGenerationMixin:
                 raise ValueError("prompt longer than max_wavefront; use full_prefill or raise max_wavefront")
         old_embeds = self.embed_inputs(current)[0] if ema_embeds > 0 else None
         prev_states, old_index, sweeps = states.clone(), 0, 0
+        prev_delta, prev_prev_states, old_old_index = torch.zeros_like(states).float(), torch.zeros_like(states), 0
         while frozen.shape[1] - prompt_len < max_new and current.shape[1] <= self.config.block_size \
                 and sweeps < max_diffusion_steps:
             sweeps += 1
@@ -498,14 +518,33 @@ class RavenGenerationMixin:
                 head = max_wavefront - (states.shape[1] - headway)
                 states = states[:, :max_wavefront]
                 current = current[:, : idx + max_wavefront]
+                stats["standing_waves"] += 1
             k = None
             if "latent" in freeze_strategy:
                 match_prev = prev_states[:, idx - old_index:]
                 cur = states[:, : match_prev.shape[1]]
-                crit = (cur - match_prev[:, : cur.shape[1]]).float().norm(dim=-1) / cur.float().norm(dim=-1)
+                match_prev = match_prev[:, : cur.shape[1]]
+                first = idx                                   # absolute position of the criterion's first entry
+                if freeze_strategy == "latent-diff":
+                    crit = (cur - match_prev).float().norm(dim=-1) / cur.float().norm(dim=-1)
+                elif freeze_strategy == "latent-acceleration-1":
+                    delta = (cur - match_prev).float()
+                    m = min(delta.shape[1], prev_delta.shape[1])
+                    crit = (delta[:, :m] - prev_delta[:, :m]).norm(dim=-1) / cur[:, :m].float().norm(dim=-1)
+                    prev_delta = delta.clone()
+                elif freeze_strategy == "latent-acceleration-2":
+                    first = max(idx, old_index, old_old_index)
+                    last = min(idx + states.shape[1], old_index + prev_states.shape[1],
+                               old_old_index + prev_prev_states.shape[1])
+                    a = states[:, first - idx: last - idx].float()
+                    b = prev_states[:, first - old_index: last - old_index].float()
+                    c = prev_prev_states[:, first - old_old_index: last - old_old_index].float()
+                    crit = ((a - b) - (b - c)).norm(dim=-1) / (a.norm(dim=-1) + 1e-6)
+                else:
+                    raise ValueError(f"unknown freeze_strategy {freeze_strategy!r}")
                 done = (crit < exit_t).nonzero()
                 if len(done) > 0:
-                    k = idx + int(done[-1][1]) + 1
+                    k = first + int(done[-1][1]) + 1
             elif freeze_strategy == "token-stability":
                 done = (stable > num_steps // inner_recurrence).nonzero()
                 if len(done) > 0:
@@ -516,7 +555,17 @@ class RavenGenerationMixin:
                     k = int(done[-1][1]) + 1
             else:
                 raise ValueError(f"unknown freeze_strategy {freeze_strategy!r}")
+            prev_prev_states, old_old_index = prev_states, old_index
             prev_states, old_index = states.clone(), idx
+            if tablets is not None and sweeps - 1 < tablets["token_tablet"].shape[0]:
+                row = sweeps - 1
+                tablets["token_tablet"][row, : current.shape[1]] = current[0].cpu()
+                tablets["frozen_tablet"][row, : frozen.shape[1]] = frozen[0].cpu()
+                tablets["counter_tablet"][row] = rec_count[0].cpu()
+                tablets["stability_tablet"][row] = stable[0].cpu()
+                if tablets["state_tablet"] is not None:
+                    width = min(states.shape[1], size - idx)
+                    tablets["state_tablet"][row, idx: idx + width] = states[0, :width].to(torch.bfloat16).cpu()
             if k is not None and k > frozen.shape[1] - 1 and k > idx:
                 k = min(k, current.shape[1] - head)
                 clear = current.shape[1] - head - k + 1
@@ -537,4 +586,14 @@ class RavenGenerationMixin:
                 frozen = frozen[:, : prompt_len + int(hits[0]) + 1]
                 break
         out_ids = frozen[:, : prompt_len + max_new]
-        return self._finish(out_ids, gc, model_kwargs, streamer, stats)
+        # the reference's names for the same counters (recpre/raven_modeling_minimal.py:1528-1538)
+        stats.update(num_core_forward_passes=stats["core_passes"], num_tokens_forward=stats["tokens_forward"],
+                     num_cache_clears=stats["cache_clears"], num_standing_waves=stats["standing_waves"],
+                     diffusion_steps=sweeps, gen_seq_length=current.shape[1], len_prefill=prompt_len,
+                     recurrence_per_position=rec_count[:, : frozen.shape[1]].cpu(),
+                     token_stable_per_position=stable[:, : frozen.shape[1]].cpu())
+        analysis = None
+        if tablets is not None:
+            analysis = dict(last_step=sweeps, last_recurrence=sweeps * inner_recurrence, longest_token=current.shape[1],
+                            **tablets)
+        return self._finish(out_ids, gc, model_kwargs, streamer, stats, hidden_states=analysis)

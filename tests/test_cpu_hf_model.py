@@ -272,3 +272,49 @@ def test_static_cache_gives_the_dynamic_cache_logits():
         assert sta.get_seq_length() == 9 and sta.get_memory_usage() > 0
     sta.reset()
     assert sta.get_seq_length() == 0 and not sta.valid_mask.any()
+
+
+def test_diffusion_style_sampler_strategies_statistics_and_analysis_tablets():
+    """Every freeze strategy of the wavefront sampler runs within its length budget; with no randomness in the state
+    (init_scale 0, no noise mixing, no embedding EMA) the run is repeatable; the summary carries the reference's counter
+    names and the analysis tablets have one row per sweep."""
+    from transformers import GenerationConfig
+
+    m = _ours(5)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 60000, (1, 10))
+    gc = GenerationConfig(max_new_tokens=6, do_sample=False, return_dict_in_generate=True)   # no max_length given
+    kw = dict(generation_config=gc, init_scale=0.0, ema_embeds=0.0, state_noise_mixing=0.0, inner_recurrence=2,
+              num_steps=4, exit_t=0.5)
+    seen = {}
+    for strategy in ("latent-diff", "latent-acceleration-1", "latent-acceleration-2", "token-stability", "fixed"):
+        for headway in (1, 2):
+            out = m.generate_diffusion_style(ids, freeze_strategy=strategy, headway=headway, **kw)
+            seq = out.sequences
+            assert seq.shape[0] == 1 and 10 < seq.shape[1] <= 16 and torch.equal(seq[:, :10], ids), (strategy, headway)
+            for key in ("num_core_forward_passes", "num_tokens_forward", "num_cache_clears", "num_standing_waves",
+                        "diffusion_steps", "gen_seq_length", "len_prefill", "recurrence_per_position",
+                        "token_stable_per_position"):
+                assert key in out.scores, key
+            assert out.scores["len_prefill"] == 10 and out.scores["num_core_forward_passes"] == \
+                2 * out.scores["diffusion_steps"]
+            assert out.scores["recurrence_per_position"].shape == (1, seq.shape[1]) or \
+                out.scores["recurrence_per_position"].shape[1] >= seq.shape[1]
+            seen[(strategy, headway)] = seq
+    again = m.generate_diffusion_style(ids, freeze_strategy="latent-acceleration-2", headway=2, **kw)
+    assert torch.equal(again.sequences, seen[("latent-acceleration-2", 2)])
+    with pytest.raises(ValueError):
+        m.generate_diffusion_style(ids, freeze_strategy="latent-nonsense", **kw)
+    narrow = m.generate_diffusion_style(ids, freeze_strategy="token-stability", headway=3, max_wavefront=4, **kw)
+    assert narrow.scores["num_standing_waves"] > 0
+    full = m.generate_diffusion_style(ids, freeze_strategy="latent-diff", headway=2, return_analysis_tablets=True,
+                                      return_full_state_tablet=True, **kw)
+    tab = full.hidden_states
+    steps = tab["last_step"]
+    assert steps == full.scores["diffusion_steps"] and tab["last_recurrence"] == 2 * steps
+    assert tab["token_tablet"].shape == tab["frozen_tablet"].shape == tab["counter_tablet"].shape
+    assert tab["state_tablet"].dtype == torch.bfloat16 and tab["state_tablet"].shape[:2] == tab["token_tablet"].shape
+    used = min(steps, tab["token_tablet"].shape[0])
+    assert bool((tab["token_tablet"][:used, :10] == ids[0]).all())             # every sweep starts from the prompt
+    assert int(tab["token_tablet"][used:].abs().sum()) == 0                      # rows past the last sweep stay empty
+    assert int(tab["counter_tablet"][used - 1].max()) >= 4
