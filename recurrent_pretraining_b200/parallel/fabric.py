@@ -38,6 +38,7 @@ class Fabric:
         self.grad_sync = grad_sync
         self.precision = precision
         self.flat_groups = []
+        self._loggers: list = []
         self._p2p = None
         self._p2p_alloc = None
         self.no_sync = False
@@ -88,7 +89,9 @@ class Fabric:
             else:
                 dist.barrier()
 
-    def all_reduce(self, t: torch.Tensor, reduce_op: str = "mean") -> torch.Tensor:
+    def all_reduce(self, t, reduce_op: str = "mean") -> torch.Tensor:
+        if not torch.is_tensor(t):                    # plain numbers (and lists of them) are accepted, as there
+            t = torch.as_tensor(t, dtype=torch.float32, device=self.device)
         if not self.is_distributed:
             return t
         t = t.clone()
@@ -109,28 +112,154 @@ class Fabric:
         dist.broadcast_object_list(box, src)
         return box[0]
 
-    def print(self, *a, **k) -> None:
-        if self.global_rank == 0:
+    def print(self, *a, ranks=(0,), **k) -> None:
+        if self.global_rank in ranks:
             print(*a, **k, flush=True)
 
-    def seed_everything(self, seed: int) -> None:
+    def seed_everything(self, seed: int | None = None, workers: bool = False) -> int:
         import random
 
         import numpy as np
 
+        if seed is None:
+            seed = int(os.environ.get("PL_GLOBAL_SEED", 0))
+        seed = int(seed) % (2 ** 32)
+        os.environ["PL_GLOBAL_SEED"] = str(seed)
+        os.environ["PL_SEED_WORKERS"] = str(int(workers))
         random.seed(seed)
-        np.random.seed(seed % (2**32))
+        np.random.seed(seed)
         torch.manual_seed(seed)
         if torch.cuda.is_available():
             torch.cuda.manual_seed_all(seed)
+        return seed
 
     @contextmanager
-    def no_backward_sync(self, enabled: bool = True):
-        prev, self.no_sync = self.no_sync, enabled
+    def no_backward_sync(self, model=None, enabled: bool = True):
+        """``with fabric.no_backward_sync(model, enabled=accumulating):`` -- gradients of the micro-batches inside stay
+        local (``no_backward_sync(flag)`` without a model is accepted too)."""
+        if isinstance(model, bool):
+            model, enabled = None, model
+        prev, self.no_sync = self.no_sync, bool(enabled)
         try:
             yield
         finally:
             self.no_sync = prev
+
+    # -- the hand-written-loop interface of the reference's fabric (recpre/utils.py:1072-1289) --------------------------
+    # For loops that own their model and a torch.optim optimizer:  model = fabric.setup(model); ...;
+    # fabric.backward(loss, model=model); fabric.clip_gradients(model, opt, max_norm=1.0); opt.step().  The fused engine
+    # (runtime.engine.TrainEngine) does not go through these.
+    verbose = False
+
+    def launch(self) -> None:
+        pass
+
+    @property
+    def rank(self) -> int:
+        return self.global_rank
+
+    @property
+    def local_device(self) -> torch.device:
+        return self.device
+
+    @property
+    def strategy(self) -> str:
+        return self.strategy_name
+
+    @property
+    def strategy_name(self) -> str:
+        return {"p2p": "B200P2P", "zero3": "B200Sharded", "ddp": "DDP"}.get(self.grad_sync, "SimpleDDP")
+
+    @property
+    def local_devices(self) -> int:
+        per_node = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("SLURM_NTASKS_PER_NODE", self.world_size)))
+        return max(min(per_node, self.world_size), 1)
+
+    @property
+    def logger(self):
+        return self._loggers[0]
+
+    def log_dict(self, metrics: dict, step: int | None = None) -> None:
+        """Rank 0 hands the metrics (tensors turned into numbers) to every logger's ``log_metrics``."""
+        if self.global_rank != 0:
+            return
+        plain = {k: (v.item() if torch.is_tensor(v) and v.numel() == 1 else v) for k, v in metrics.items()}
+        for logger in self._loggers:
+            logger.log_metrics(metrics=plain, step=step)
+
+    def log_to_summary(self, dict_of_values: dict) -> None:
+        if self.global_rank == 0 and self._loggers:
+            summary = getattr(getattr(self.logger, "experiment", None), "summary", None)
+            if summary is not None:
+                for key, value in dict_of_values.items():
+                    summary[key] = value
+            elif hasattr(self.logger, "log_metrics"):
+                self.logger.log_metrics(metrics={f"summary/{k}": v for k, v in dict_of_values.items()}, step=None)
+
+    def log_chart(self, dict_of_charts: dict) -> None:
+        if self.global_rank == 0 and self._loggers and hasattr(getattr(self.logger, "experiment", None), "log"):
+            self.logger.experiment.log(dict_of_charts)
+
+    def setup_dataloaders(self, train_dataloader, val_dataloader=None):
+        return train_dataloader, val_dataloader
+
+    def setup(self, model, compile: bool = False):
+        """Move the model to this rank's device (and remember it for ``no_backward_sync`` / ``backward``).  ``compile``
+        is accepted and ignored: the kernels behind the model's ops are compiled ahead of time."""
+        self.model_ref = model.to(self.device)
+        return self.model_ref
+
+    def setup_optimizers(self, optimizers):
+        return optimizers
+
+    def backward(self, loss, model=None) -> None:
+        """``loss.backward()`` and, outside ``no_backward_sync``, the averaging of the gradients over the ranks."""
+        loss.backward()
+        model = model if model is not None else getattr(self, "model_ref", None)
+        if not self.no_sync and self.is_distributed and model is not None:
+            self.all_reduce_gradients([p for p in model.parameters()])
+
+    def clip_gradients(self, model, optimizer=None, max_norm: float = 1.0, error_if_nonfinite: bool = False):
+        return torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm, norm_type=2.0,
+                                              error_if_nonfinite=error_if_nonfinite)
+
+    def get_prefix_for_checkpoint(self) -> str:
+        from ..runtime.checkpoint import PREFIX
+
+        return PREFIX
+
+    def save(self, checkpoint_file_location: str, state: dict, overwrite: bool = True, strict: bool = False) -> None:
+        """``{location}_{local_rank}.pth`` written by the ranks of the first node; ``model``, ``optimizer`` and the
+        train loader entries are stored as their ``state_dict()`` (formed on every rank: they may be collective)."""
+        payload = {}
+        for key, value in state.items():
+            payload[key] = value.state_dict() if (key in ("optimizer", "model") or "train_dataloader" in key) else value
+        if self.global_rank >= self.local_devices:
+            return
+        folder = os.path.dirname(checkpoint_file_location)
+        if folder:
+            os.makedirs(folder, exist_ok=True)
+        path = f"{checkpoint_file_location}_{self.local_rank}.pth"
+        if os.path.exists(path) and not overwrite:
+            raise ValueError(f"Checkpoint {path} already exists")
+        tmp = path + ".tmp"
+        torch.save(payload, tmp)
+        os.replace(tmp, path)
+        if self.verbose:
+            print(f"Rank {self.global_rank} - local {self.local_rank} saved {path}.", flush=True)
+
+    def load(self, checkpoint_file_location: str, state: dict, strict: bool = False) -> None:
+        path = f"{checkpoint_file_location}_{self.local_rank}.pth"
+        checkpoint = torch.load(path, map_location="cpu", weights_only=False)
+        for key, value in checkpoint.items():
+            if key in ("optimizer", "model") or "train_dataloader" in key:
+                state[key].load_state_dict(value)
+            elif key not in ("tokenizer", "val_dataloader"):
+                state[key] = value
+
+    @contextmanager
+    def init_module(self, empty_init: bool = False):
+        yield None
 
     # -- gradient synchronisation ----------------------------------------------------------
     @property

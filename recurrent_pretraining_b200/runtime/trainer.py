@@ -299,6 +299,7 @@ def train(cfg, fabric, state) -> None:
     engine: TrainEngine = state["engine"]
     model, mc = state["model"], cfg.model_config
     loggers = make_loggers(cfg.logger_name, cfg.out_dir, cfg.run_name, cfg.logger_project, fabric.global_rank)
+    fabric._loggers = loggers                     # fabric.log_dict / log_to_summary reach the same sinks
     warmup_or_early_fail_allreduce(fabric)
     loss_mean, timer = RunningMean(32), StepTimer()
     total_tokens = 0

@@ -398,3 +398,60 @@ def test_schedules_take_the_reference_call_forms():
     assert abs(get_lr(55, 100, cfg) - (3e-3 - 0.5 * (3e-3 - 1e-4))) < 1e-15
     assert [get_batch_size(s, cfg) for s in (1, 15, 30, 31, 500)] == [1, math.ceil(0.5 * 12.5), 13, 12, 12]
     assert [get_batch_size(s, 30, 12) for s in (0, 15, 30, 31)] == [1, 6, 12, 12]
+
+
+def test_fabric_offers_the_hand_written_loop_interface(tmp_path, capsys):
+    """A loop written against the reference's fabric (setup / backward / clip_gradients / save / load / log_dict / ...,
+    recpre/utils.py:1072-1289) runs on ours: here one process on the CPU with a torch optimizer."""
+    from recurrent_pretraining_b200.parallel.fabric import Fabric
+
+    fabric = Fabric.single("cpu")
+    fabric.launch()
+    assert fabric.seed_everything(7, workers=True) == 7 and fabric.rank == 0 and fabric.local_device.type == "cpu"
+    assert fabric.strategy == "SimpleDDP" and fabric.get_prefix_for_checkpoint() == "checkpoints-sane-ddp"
+    with fabric.init_module(empty_init=False):
+        model = torch.nn.Linear(4, 3)
+    model = fabric.setup(model, compile=False)
+    opt = fabric.setup_optimizers(torch.optim.SGD(model.parameters(), lr=0.1))
+    train, val = fabric.setup_dataloaders([1, 2], [3])
+    assert train == [1, 2] and val == [3]
+    x = torch.randn(5, 4)
+    with fabric.no_backward_sync(model, enabled=True):
+        fabric.backward(model(x).pow(2).mean(), model=model)
+        assert fabric.no_sync
+    assert not fabric.no_sync
+    fabric.backward(model(x).pow(2).mean(), model=model)
+    norm = fabric.clip_gradients(model, opt, max_norm=1e-3)
+    total = torch.sqrt(sum(p.grad.pow(2).sum() for p in model.parameters()))
+    assert float(norm) > 1e-3 and abs(float(total) - 1e-3) < 1e-6
+    opt.step()
+    assert float(fabric.all_reduce(3.0)) == 3.0 and fabric.broadcast({"a": 1}) == {"a": 1}
+    fabric.barrier()
+    # save / load in the reference layout: <location>_<local rank>.pth, state_dict() of model / optimizer
+    state = {"model": model, "optimizer": opt, "microbatch_step": 12, "tokenizer": "kept out on load"}
+    fabric.save(str(tmp_path / "ckpt" / "step-00000012-run"), state)
+    assert (tmp_path / "ckpt" / "step-00000012-run_0.pth").is_file()
+    with pytest.raises(ValueError):
+        fabric.save(str(tmp_path / "ckpt" / "step-00000012-run"), state, overwrite=False)
+    fresh = torch.nn.Linear(4, 3)
+    state2 = {"model": fresh, "optimizer": torch.optim.SGD(fresh.parameters(), lr=0.1), "microbatch_step": 0,
+              "tokenizer": "mine"}
+    fabric.load(str(tmp_path / "ckpt" / "step-00000012-run"), state2)
+    assert torch.equal(fresh.weight, model.weight) and state2["microbatch_step"] == 12 and state2["tokenizer"] == "mine"
+
+    class Sink:
+        def __init__(self):
+            self.rows = []
+
+        def log_metrics(self, metrics, step=None):
+            self.rows.append((metrics, step))
+
+    sink = Sink()
+    fabric._loggers = [sink]
+    fabric.log_dict({"loss": torch.tensor(1.5), "lr": 0.1}, step=3)
+    fabric.log_to_summary({"best": 1.0})
+    fabric.log_chart({"ignored": 1})
+    assert sink.rows[0] == ({"loss": 1.5, "lr": 0.1}, 3) and sink.rows[1][0] == {"summary/best": 1.0}
+    fabric.print("hello", ranks=[0])
+    fabric.print("silent", ranks=[1])
+    assert capsys.readouterr().out.strip() == "hello"
