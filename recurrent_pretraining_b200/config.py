@@ -69,7 +69,7 @@ class ModelConfig:
     center_attention: bool = False
     clip_qkv: Optional[float] = None
     qk_norm: bool = False
-    activation_checkpoint_impl: str = "per-block"
+    activation_checkpoint_impl: Optional[str] = None   # default: per-iteration (recurrent) / per-block (GPT)
     simple_ops: bool = False
     strategy: str = "single"
     # GPT only
@@ -108,6 +108,9 @@ class ModelConfig:
             self.padded_vocab_size = _round_up(self.vocab_size, self.padding_multiple)
         else:
             self.vocab_size = min(self.vocab_size, self.padded_vocab_size)
+        if self.activation_checkpoint_impl is None:    # the two config classes of the reference differ here
+            self.activation_checkpoint_impl = "per-iteration" if self.architecture_class_name == "RecurrentGPT" \
+                else "per-block"
         if self.num_key_value_heads is None:
             self.num_key_value_heads = self.num_attention_heads
         if self.num_attention_heads % self.num_key_value_heads:
@@ -198,6 +201,111 @@ class ModelConfig:
         out["intermediate_size"] = self.intermediate_size // mu
         out["num_key_value_heads"] = self.num_key_value_heads // mu
         return out
+
+    @classmethod
+    def from_json(cls, path, **overrides: Any) -> "ModelConfig":
+        """A config stored as JSON (``lit_config.json`` / ``model_config.json``), keyword overrides applied on top."""
+        import json
+
+        with open(path, encoding="utf-8") as fp:
+            d = json.load(fp)
+        d.update(overrides)
+        d.pop("init", None)
+        return cls.from_dict(d)
+
+    @classmethod
+    def from_checkpoint(cls, path, **overrides: Any) -> "ModelConfig":
+        """``<path>/lit_config.json`` if it exists, else the registry entry named like the directory
+        (recpre/config_dynamic.py:168-174)."""
+        from pathlib import Path
+
+        path = Path(path)
+        if (path / "lit_config.json").is_file():
+            return cls.from_json(path / "lit_config.json", **overrides)
+        if path.name in registry.name_to_config:
+            return cls.from_name(path.name, **overrides)
+        raise FileNotFoundError(f"For {str(path)!r} neither 'lit_config.json' nor matching config exists.")
+
+    # class lookups by the names stored in the config (recpre/config_dynamic.py:176-251) -------------------------------
+    @property
+    def MLP(self):
+        from .models.blocks import MLP_CLASSES
+
+        return MLP_CLASSES[self.mlp_class_name]
+
+    @property
+    def Block(self):
+        from .models.blocks import BLOCK_CLASSES
+
+        return BLOCK_CLASSES[self.block_class_name]
+
+    @property
+    def Linear(self):
+        from .models.blocks import Linear
+
+        return Linear
+
+    @property
+    def Nonlin(self):
+        import torch.nn as nn
+
+        from .models.blocks import Relu2
+
+        if hasattr(nn, self.nonlin_name):
+            return getattr(nn, self.nonlin_name)
+        if self.nonlin_name == "ReLU2":
+            return Relu2
+        raise ValueError(f"Could not identify nonlinearity {self.nonlin_name}")
+
+    @property
+    def Norm(self):
+        """``cfg.Norm(size, eps=...)`` builds the configured norm."""
+        from .models.blocks import make_norm
+
+        def build(size: int, eps: Optional[float] = None, **_):
+            if eps is None or eps == self.norm_eps:
+                return make_norm(self, size)
+            return make_norm(dataclasses.replace(self, norm_eps=eps), size)
+
+        return build
+
+    @property
+    def attn_nonlin_fn(self):
+        """Factory of the attention computation ``f(q, k, v, mask)`` on [B, S, H, D] tensors for the configured provider
+        options (centering, causal-mean debiasing, soft cap); the models' attention modules apply the same options
+        themselves."""
+        from .models.blocks import _center_debias, _dense_attention
+
+        softcap = 20.0 if self.attn_impl == "flex-attention-soft-cap" else 0.0
+        center, debias = bool(self.center_attention), bool(self.debias_attention)
+
+        def factory():
+            def attend(q, k, v, mask=None):
+                if self.attn_impl == "debug-skip":
+                    return v
+                y = _dense_attention(q, k, v, softcap)
+                return _center_debias(y, v, q.shape[2], center, debias) if (center or debias) else y
+
+            return attend
+
+        return factory
+
+    @property
+    def checkpoint(self):
+        """The activation-checkpoint callable of ``activation_checkpoint_impl`` (plain, ``sac``, ``sac-attn``,
+        ``sac%N``)."""
+        from .ops.sac import checkpoint_fn
+
+        return checkpoint_fn(self.activation_checkpoint_impl)
+
+    def __getstate__(self):
+        state = dict(self.__dict__)
+        state.pop("init", None)                        # rebuilt from the fields
+        return state
+
+    def __setstate__(self, state):
+        self.__dict__.update(state)
+        self.__post_init__()
 
     def construct_model(self, **kwargs):
         """recpre/config_dynamic.py:441-444: ``cfg.construct_model(objective=..., gradient_checkpointing=...)``."""

@@ -369,21 +369,47 @@ class RecurrentGPT(_LMBase):
         return {"loss": loss, "logits": logits if (return_logits or labels is None) else None, "log_ppl": log_ppl}
 
     @torch.no_grad()
-    def monitor_module(self, x_out, x_rec, xk, e, n, k):
-        """Model telemetry for one step (recpre/model_dynamic.py:1374-1405)."""
-        xf, rf, kf = x_out.float(), x_rec.float(), xk.float()
-        tok = torch.nn.functional.normalize(xf[0], dim=-1)
-        corr = (tok @ tok.T).mean()
+    def monitor_module(self, x_out, x_rec, xk, input_embeds, num_steps_no_grad, num_steps_with_grad):
+        """Model telemetry for one step, with the reference's metric names and formulas
+        (recpre/model_dynamic.py:1374-1405): mean cosine between the centred token vectors of a sequence (minus the
+        1/S of the diagonal) for the output and for the recurrent state, their norms, the distance of the state from
+        the embedded input and the last recurrence's residual."""
+        x_out, x_rec, xk, e = x_out.float(), x_rec.float(), xk.float(), input_embeds.float()
         self.latest_metrics = {
-            "last_hidden_token_corr": corr.item(),
-            "last_hidden_norm": xf.norm(dim=-1).mean().item(),
-            "rec_hidden_norm": rf.norm(dim=-1).mean().item(),
-            "embed_norm": e.float().norm(dim=-1).mean().item(),
-            "rec_residual": (rf - kf).norm(dim=-1).mean().item(),
-            "num_steps_no_grad": n,
-            "num_steps_with_grad": k,
+            "last_hidden_token_corr": _token_corr(x_out),
+            "recurrent_state_token_corr": _token_corr(x_rec),
+            "last_hidden_norm": x_out.norm(dim=-1).mean(),
+            "recurrent_state_norm": x_rec.norm(dim=-1).mean(),
+            "recurrent_diff": (x_rec - e).norm(dim=-1).mean(),
+            "num_steps_no_grad": num_steps_no_grad,
+            "num_steps_with_grad": num_steps_with_grad,
+            "recurrent_residual": (x_rec - xk).norm(dim=-1).mean(),
+            "rel_residual": ((x_rec - xk).norm(dim=-1) / x_rec.norm(dim=-1)).mean(),
         }
         self.latest_metrics.update(getattr(self, "head_metrics", {}))
+
+    def reset_parameters(self) -> None:
+        """Re-draw every weight with the config's initialiser (embedding, blocks, adapter, head; norms to one)."""
+        _reinitialize(self)
+
+
+def _token_corr(x: torch.Tensor) -> torch.Tensor:
+    c = x - x.mean(dim=-1, keepdim=True)
+    c = c / c.norm(dim=-1, keepdim=True)
+    return (c @ c.transpose(1, 2)).mean() - 1 / x.shape[1]
+
+
+def _reinitialize(model: nn.Module) -> None:
+    init = model.config.init
+    init.init_weight_(model.transformer.wte.weight, "embedding")
+    for m in model.modules():
+        if m is not model and hasattr(m, "reset_parameters") and not isinstance(m, (RecurrentGPT, GPT)):
+            m.reset_parameters()
+    init.init_weight_(model.transformer.wte.weight, "embedding")      # nn.Embedding's own reset ran in the loop
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("qk_bias"):
+                p.zero_()
 
 
 class GPT(_LMBase):
@@ -428,5 +454,17 @@ class GPT(_LMBase):
             else:
                 x = block(x, rope, attention_mask)
         x = self.transformer.ln_f(x)
+        if self.monitoring:
+            self.monitor_module(x)
         loss, logits, log_ppl = self._loss(x, labels, return_logits or labels is None)
         return {"loss": loss, "logits": logits if (return_logits or labels is None) else None, "log_ppl": log_ppl}
+
+    @torch.no_grad()
+    def monitor_module(self, x: torch.Tensor) -> None:
+        """Telemetry of the baseline model (recpre/model_dynamic.py:139-144)."""
+        x = x.float()
+        self.latest_metrics = {"last_hidden_token_corr": _token_corr(x), "last_hidden_norm": x.norm(dim=-1).mean()}
+        self.latest_metrics.update(getattr(self, "head_metrics", {}))
+
+    def reset_parameters(self) -> None:
+        _reinitialize(self)

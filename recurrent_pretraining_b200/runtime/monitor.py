@@ -295,12 +295,16 @@ def enable_monitoring(model, on: bool = True) -> None:
             m.monitoring = on
 
 
-def harvest_metrics(model) -> dict:
-    out = {}
+def harvest_metrics(model, metrics: dict | None = None) -> dict:
+    """Collect (and clear) the ``latest_metrics`` of every module; one-element tensors become numbers.  With a
+    ``metrics`` dict the values are merged into it, as ``disable_monitoring_and_retrieve_metrics(module, metrics)`` of
+    the reference does (recpre/monitor.py:16-21)."""
+    out = {} if metrics is None else metrics
     for m in model.modules():
         lm = getattr(m, "latest_metrics", None)
         if lm:
-            out.update(lm)
+            out.update({k: (v.item() if torch.is_tensor(v) and v.numel() == 1 else v) for k, v in lm.items()})
+            m.latest_metrics = {}
     return out
 
 

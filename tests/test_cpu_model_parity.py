@@ -391,3 +391,68 @@ def test_every_init_strategy_matches_the_reference_initialiser():
                     assert torch.equal(a, b), (st, mu, orth, role, li)
                     checked += 1
     assert checked > 1500
+
+
+@needs_ref
+def test_monitoring_metrics_and_config_lookups_match_reference(tmp_path):
+    """Model telemetry (names and values), the config's class lookups, JSON / checkpoint-directory loaders, pickling,
+    the per-architecture default of the checkpoint placement, and ``reset_parameters``."""
+    import pickle
+
+    from recurrent_pretraining_b200.runtime.monitor import enable_monitoring, harvest_metrics
+
+    torch.manual_seed(0)
+    ref_model, ref_cfg = refload.build_train_model("nebel-raven-3.5b", **TINY)
+    cfg = ModelConfig.from_name("nebel-raven-3.5b", **TINY)
+    model = cfg.construct_model()
+    model.load_state_dict(ref_model.state_dict())
+    ref_model.config.state_init = model.config.state_init = "zero"
+    ids = torch.randint(0, 512, (2, 64))
+    ref_model.monitoring = True
+    enable_monitoring(model, True)
+    ref_model(ids, labels=ids, num_steps_pair=torch.tensor([2, 1]))
+    model(ids, labels=ids, num_steps_pair=torch.tensor([2, 1]))
+    want = {k: float(v) for k, v in ref_model.latest_metrics.items()}
+    got = harvest_metrics(model)
+    for key, value in want.items():
+        assert key in got and abs(float(got[key]) - value) < 1e-4 * max(1.0, abs(value)), (key, got.get(key), value)
+    assert model.latest_metrics == {}                              # harvested metrics are cleared
+    # class lookups by name
+    assert cfg.MLP.__name__ == ref_cfg.MLP.__name__ == "GatedMLP" and cfg.Block.__name__ == ref_cfg.Block.__name__
+    assert cfg.Linear.__name__ == "Linear" and isinstance(cfg.Nonlin(), torch.nn.SiLU)
+    norm = cfg.Norm(96, eps=cfg.norm_eps)
+    assert tuple(norm.weight.shape) == (96,)
+    q, k, v = (torch.randn(1, 8, 4, 24) for _ in range(3))
+    assert cfg.attn_nonlin_fn()(q, k, v, None).shape == (1, 8, 4, 24)
+    y = cfg.checkpoint(lambda t: t * 2, torch.ones(3, requires_grad=True))
+    assert torch.equal(y.detach(), torch.full((3,), 2.0))
+    assert cfg.activation_checkpoint_impl == ref_cfg.activation_checkpoint_impl
+    assert ModelConfig.from_name("gpt2-124m").activation_checkpoint_impl == "per-block"
+    assert ModelConfig.from_name("magpie-150m").activation_checkpoint_impl == \
+        refload.module("config_dynamic").Config.from_name("magpie-150m").activation_checkpoint_impl
+    # JSON / directory loaders and pickling
+    import json
+
+    (tmp_path / "nebel-raven-3.5b").mkdir()
+    assert ModelConfig.from_checkpoint(tmp_path / "nebel-raven-3.5b").n_embd == 5280      # by directory name
+    (tmp_path / "nebel-raven-3.5b" / "lit_config.json").write_text(json.dumps(cfg.to_dict()))
+    again = ModelConfig.from_checkpoint(tmp_path / "nebel-raven-3.5b", mean_recurrence=7)
+    assert again.n_embd == 96 and again.mean_recurrence == 7
+    with pytest.raises(FileNotFoundError):
+        ModelConfig.from_checkpoint(tmp_path / "nothing-here")
+    clone = pickle.loads(pickle.dumps(cfg))
+    assert clone.to_dict() == cfg.to_dict() and clone.init.get_std("embedding") == cfg.init.get_std("embedding")
+    # a full re-draw: every matrix changes, norms and the q/k bias go back to their start values
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("qk_bias") or "norm" in n:
+                p.add_(1.0)
+    model.reset_parameters()
+    for n, p in model.named_parameters():
+        if n.endswith("qk_bias"):
+            assert float(p.abs().max()) == 0.0
+        elif p.dim() == 1:
+            assert torch.equal(p, torch.ones_like(p)), n
+        else:
+            assert not torch.equal(p, before[n]), n
