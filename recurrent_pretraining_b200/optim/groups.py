@@ -18,11 +18,14 @@ def classify(name: str, ndim: int) -> str:
 
 
 def get_param_groups(named_parameters, no_weight_decay_for_bias_and_norm_params: bool = True,
-                     weight_lr_scale: float = 1.0, no_wd_on_embedding: bool = False, with_names: bool = False):
+                     weight_lr_scale: float = 1.0, no_wd_on_embedding: bool = False, verbose: bool = False,
+                     with_names: bool = False):
     buckets = {"weight": [], "embedding": [], "norm": []}
     names = {"weight": [], "embedding": [], "norm": []}
     for name, p in named_parameters:
         kind = classify(name, p.ndim)
+        if verbose:
+            print(f"Matched {name} to the {kind} group")
         buckets[kind].append(p)
         names[kind].append(name)
     groups = [
