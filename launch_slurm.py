@@ -102,10 +102,13 @@ class SlurmJob:
     rebuild_kernels: bool = True
     archives: list = field(default_factory=list)     # .tar.gz files staged to node-local storage before the run
     run_from_snapshot: str | None = None             # top-level folder of the staged code snapshot to cd into
+    environment: str | None = None                   # python environment: a directory, or a packed .tar.gz to stage
+    sub_dir: str | None = None                       # folder under output_dir for logs and sbatch files (run name)
+    proxy: str | None = None                         # http(s) proxy exported to the job (compute nodes without a route out)
 
     @property
     def log_dir(self) -> str:
-        return os.path.join(self.output_dir, self.run_name, "slurm")
+        return os.path.join(self.output_dir, self.sub_dir or self.run_name, "slurm")
 
     def time_string(self) -> str:
         d, rem = divmod(self.minutes, 24 * 60)
@@ -140,12 +143,23 @@ class SlurmJob:
         exports = "\n".join(f"export {k}={shlex.quote(str(v))}" for k, v in self.env.items())
         build = (f"srun --nodes=1 --ntasks=1 python -c 'import __graft_entry__ as g; g.build()'\n"
                  if self.rebuild_kernels else "")
-        stage = stage_archives_script(self.archives)
+        archives, activate = list(self.archives), ""
+        if self.environment:
+            env_path = self.environment
+            if env_path.endswith(".tar.gz"):                 # packed environment: unpack on every node, use it there
+                archives.append(env_path)
+                env_path = '"$STAGE_DIR"/' + os.path.basename(env_path)[: -len(".tar.gz")]
+            activate = (f'source {env_path}/bin/activate\n'
+                        f'echo "$(date -u) activated {os.path.basename(self.environment)}"\n')
+        if self.proxy:
+            activate += "".join(f"export {v}={shlex.quote(self.proxy)}\n"
+                                for v in ("http_proxy", "https_proxy", "HTTP_PROXY", "HTTPS_PROXY", "all_proxy"))
+        stage = stage_archives_script(archives)
         workdir = f'"$STAGE_DIR/{self.run_from_snapshot}"' if (stage and self.run_from_snapshot) else shlex.quote(HERE)
         body = f"""
 set -euo pipefail
 {stage}cd {workdir}
-{exports}
+{activate}{exports}
 export MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)
 export MASTER_PORT=$((20000 + SLURM_JOB_ID % 20000))
 echo "nodes: $SLURM_JOB_NODELIST  master: $MASTER_ADDR:$MASTER_PORT  started $(date)"
@@ -236,7 +250,20 @@ def parse_and_execute(argv=None):
     ap.add_argument("--snapshot", action="store_true",
                     help="freeze the working tree into a tar.gz, stage it to node-local storage and run from there")
     ap.add_argument("--archives", nargs="*", default=[], help="further .tar.gz files to stage on every node")
+    ap.add_argument("--cast_working_dirs", action="store_true", help="the reference launcher's name for --snapshot")
+    ap.add_argument("--environment", default=None,
+                    help="python environment to activate in the job: a directory with bin/activate, or a packed "
+                         ".tar.gz that is unpacked to node-local storage first")
+    ap.add_argument("--enable_internet", action="store_true",
+                    help="export the proxy given by --proxy (or $CLUSTER_PROXY) to the job")
+    ap.add_argument("--proxy", default=None, help="http(s) proxy URL for --enable_internet")
+    ap.add_argument("--sub_output_dir_name", default=None, help="folder under --output_dir for this run's files "
+                                                                 "(default: the run name)")
+    ap.add_argument("--extended_partition", action="store_true", help="submit to the 'extended' partition")
     args = ap.parse_args(argv)
+    args.snapshot = args.snapshot or args.cast_working_dirs
+    if args.extended_partition and not args.partition:
+        args.partition = "extended"
 
     name = args.run_name + (f"_{secrets.token_hex(3)}" if args.uuid else "")
     total = args.budget_minutes + 60 * args.budget_hours + 24 * 60 * args.budget_days
@@ -248,7 +275,9 @@ def parse_and_execute(argv=None):
                    partition=args.partition, account=args.account, qos="debug" if args.debug_qos else args.qos,
                    email=args.email, output_dir=args.output_dir or os.path.join(HERE, "outputs"), env=env,
                    custom_invocation=args.custom_invocation, dependency=args.dependency,
-                   rebuild_kernels=not args.no_rebuild, archives=list(args.archives))
+                   rebuild_kernels=not args.no_rebuild, archives=list(args.archives), environment=args.environment,
+                   proxy=(args.proxy or os.environ.get("CLUSTER_PROXY")) if args.enable_internet else None,
+                   sub_dir=args.sub_output_dir_name)
     if args.snapshot:
         snap = f"{name}_code"
         path = snapshot_working_tree(os.path.join(job.output_dir, name), snap) if not args.dryrun else \

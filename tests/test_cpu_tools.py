@@ -337,6 +337,17 @@ def test_launcher_snapshot_and_staging(tmp_path):
                                "--output_dir", str(tmp_path / "out"), "--run_name", "t"])
     text = job.sbatch_text()
     assert 'cd "$STAGE_DIR/t_code"' in text and "sbcast" in text
+    # the reference launcher's remaining options: packed environment, proxy, output sub-folder, partition, its flag names
+    job = L.parse_and_execute(["--nodes", "1", "--cast_working_dirs", "--dryrun", "--output_dir", str(tmp_path / "out"),
+                               "--run_name", "u", "--environment", "/scratch/envs/torch_env.tar.gz", "--enable_internet",
+                               "--proxy", "http://proxy:3128/", "--sub_output_dir_name", "runs_u", "--extended_partition"])
+    text = job.sbatch_text()
+    assert job.run_from_snapshot == "u_code" and job.log_dir.endswith(os.path.join("out", "runs_u", "slurm"))
+    assert "torch_env.tar.gz" in text and 'source "$STAGE_DIR"/torch_env/bin/activate' in text
+    assert "export https_proxy=http://proxy:3128/" in text and "#SBATCH --partition=extended" in text
+    plain = L.parse_and_execute(["--dryrun", "--output_dir", str(tmp_path / "out"), "--run_name", "v",
+                                 "--environment", "/opt/venv"]).sbatch_text()
+    assert "source /opt/venv/bin/activate" in plain and "proxy" not in plain
 
 
 def test_every_listed_reference_symbol_resolves_to_an_object_of_this_package():
