@@ -7,6 +7,8 @@ package can be imported.
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional, Tuple
 
 import torch
@@ -34,7 +36,14 @@ class RecurrentLM(_Base):
 
     @classmethod
     def from_checkpoint(cls, ckpt_path: str, tokenizer, device="cpu", **kw):
+        """A raw training checkpoint (this framework's or the reference's) plus a tokenizer object or the folder of a
+        Hugging Face tokenizer (evaluate_raven/quick_checkpoint_eval.py:53-79)."""
         from .convert_to_hf import load_training_checkpoint
+
+        if isinstance(tokenizer, (str, os.PathLike)):
+            from transformers import AutoTokenizer
+
+            tokenizer = AutoTokenizer.from_pretrained(str(tokenizer))
 
         cfg, sd = load_training_checkpoint(ckpt_path)
         model = cfg.construct_model()

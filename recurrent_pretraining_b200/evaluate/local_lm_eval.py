@@ -98,5 +98,58 @@ def main(argv=None) -> dict:
     return results
 
 
+def prepare_results(results: dict, save_filepath, print_results: bool = True) -> None:
+    """Print the result tables (when lm-eval's table formatter is importable) and store the results as JSON
+    (evaluate_raven/quick_checkpoint_eval.py:314-324)."""
+    from pathlib import Path
+
+    if print_results:
+        try:
+            from lm_eval.utils import make_table  # type: ignore
+
+            print(make_table(results))
+            if "groups" in results:
+                print(make_table(results, "groups"))
+        except ImportError:
+            print(json.dumps(results.get("results", results), indent=2, default=str))
+    Path(save_filepath).write_text(json.dumps(results, indent=2, ensure_ascii=False, default=str), encoding="utf-8")
+
+
+def quick_eval_check(checkpoint_name: str, tokenizer_path: str, device="cuda", out_dir: str = "outputs/eval",
+                     tasks: Optional[str] = "arc_easy,tinyHellaswag,tinyMMLU,piqa,openbookqa", num_fewshot: int = 0,
+                     batch_size: int = 16, limit=None, seed: int = 233, recurrence: int = 32,
+                     simple_evaluate=None) -> Optional[dict]:
+    """Benchmark a raw TRAINING checkpoint (no conversion) at a fixed recurrence and store
+    ``results_<tasks>_<checkpoint>_<recurrence>.json`` under ``out_dir``
+    (evaluate_raven/quick_checkpoint_eval.py:327-390).  ``simple_evaluate`` defaults to lm-eval's; tests and callers
+    without that package pass their own ``f(model=..., tasks=[...], ...) -> dict``."""
+    from pathlib import Path
+
+    from .lm_eval_wrapper import RecurrentLM
+
+    if simple_evaluate is None:
+        try:
+            from lm_eval import evaluator  # type: ignore
+
+            simple_evaluate = evaluator.simple_evaluate
+        except ImportError as exc:
+            raise SystemExit("lm-eval is not installed; pass simple_evaluate= or drive RecurrentLM directly") from exc
+    if tasks is None:
+        from lm_eval.tasks import TaskManager  # type: ignore
+
+        print("\n".join(TaskManager().task_index.keys()))
+        return None
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    model_name = str(checkpoint_name).split("/")[-1].split(".")[0]
+    lm = RecurrentLM.from_checkpoint(checkpoint_name, tokenizer_path, device=device, batch_size=batch_size,
+                                     recurrence=recurrence)
+    results = simple_evaluate(model=lm, tasks=tasks.split(","), num_fewshot=num_fewshot, batch_size=batch_size,
+                              device=str(device), limit=limit, random_seed=seed, numpy_random_seed=seed,
+                              torch_random_seed=seed)
+    prepare_results(results, out / f"results_{tasks}_{model_name}_{recurrence}.json")
+    return results
+
+
 if __name__ == "__main__":
     main()

@@ -209,7 +209,8 @@ REFERENCE_NAMES: dict[str, str] = {
     "recpre.utils.choose_logger": "runtime.monitor:make_loggers",
     # ---- evaluation, conversion, serving, launch ----------------------------------------------------------------------------------
     "evaluate_raven.quick_checkpoint_eval.RecurrentGPTWrapper": "evaluate.lm_eval_wrapper:RecurrentLM",
-    "evaluate_raven.quick_checkpoint_eval.quick_eval_check": "evaluate.local_lm_eval:main",
+    "evaluate_raven.quick_checkpoint_eval.quick_eval_check": "evaluate.local_lm_eval:quick_eval_check",
+    "evaluate_raven.quick_checkpoint_eval.prepare_results": "evaluate.local_lm_eval:prepare_results",
     "evaluate_raven.local_lm_eval.cli_evaluate": "evaluate.local_lm_eval:main",
     "evaluate_raven.checkpoint_to_hf_converter.hf_implementation_test_and_upload": "evaluate.convert_to_hf:convert",
     "evaluate_raven.checkpoint_to_hf_converter.mini_generate": "evaluate.convert_to_hf:greedy",

@@ -158,3 +158,29 @@ def test_adaptive_compute_wrapper_with_a_scripted_depth_schedule():
                            max_steps=6, max_gen_toks=4, device="cpu")
     lm.generate_until([("hello", {"max_gen_toks": 4})])
     assert lm.step_log and lm.step_log[0][:4] == [2, 4, 2, 4][:len(lm.step_log[0])], lm.step_log
+
+
+def test_quick_eval_check_scores_a_training_checkpoint_and_stores_results(tmp_path, monkeypatch):
+    """The reference's one-call benchmark of a raw training checkpoint (quick_checkpoint_eval.py:327-390) with a
+    stand-in for lm-eval's ``simple_evaluate`` that drives the wrapper's scoring interface."""
+    import json
+
+    from recurrent_pretraining_b200.evaluate import lm_eval_wrapper, local_lm_eval
+
+    cfg, model, path = _checkpoint(str(tmp_path))
+    calls = {}
+
+    def fake_simple_evaluate(model, tasks, num_fewshot, batch_size, device, limit, random_seed, numpy_random_seed,
+                             torch_random_seed):
+        calls.update(tasks=tasks, seed=(random_seed, numpy_random_seed, torch_random_seed), fewshot=num_fewshot)
+        ll = model.loglikelihood([("the cat", " sat")])
+        return {"results": {t: {"acc": 0.5, "ll": ll[0][0]} for t in tasks}, "n": len(tasks)}
+
+    monkeypatch.setattr(lm_eval_wrapper.RecurrentLM, "from_checkpoint",
+                        classmethod(lambda cls, p, tok, **kw: cls(model, ByteTok(), **{k: v for k, v in kw.items()})))
+    res = local_lm_eval.quick_eval_check(path, "unused-tokenizer-folder", device="cpu", out_dir=str(tmp_path / "eval"),
+                                         tasks="arc_easy,piqa", num_fewshot=0, batch_size=2, seed=233, recurrence=3,
+                                         simple_evaluate=fake_simple_evaluate)
+    assert calls == {"tasks": ["arc_easy", "piqa"], "seed": (233, 233, 233), "fewshot": 0}
+    stored = json.loads((tmp_path / "eval" / "results_arc_easy,piqa_step-00000008-run_0_3.json").read_text())
+    assert stored["n"] == 2 and stored["results"]["piqa"]["acc"] == 0.5 and res["results"]["arc_easy"]["ll"] < 0
