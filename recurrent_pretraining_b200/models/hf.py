@@ -79,6 +79,15 @@ class RavenForCausalLM(RavenPreTrainedModel, RavenGenerationMixin, GenerationMix
             coda=nn.ModuleList(make_block(mc, i + off) for i in range(C)),
             ln_f=make_norm(mc)))
         init.init_weight_(self.transformer.wte.weight, "embedding")
+        # The reference's inference model draws the up half of every gated-MLP input projection with the (smaller)
+        # output-projection deviation, unlike its training model (recpre/raven_modeling_minimal.py:103-104); a freshly
+        # constructed model follows it.  Loaded checkpoints overwrite all of this.
+        with torch.no_grad():
+            for name, module in self.transformer.named_modules():
+                if name.endswith("mlp.fc") and getattr(module, "weight", None) is not None \
+                        and not mc.skip_initialization:
+                    half = module.weight.shape[0] // 2
+                    init.normal_(module.weight[half:], std=float(config.init_values["out_proj"]))
         self.emb_scale = config.init_values["embed_scale"]
         self.lm_head = nn.Linear(E, config.padded_vocab_size, bias=False)
         if config.tie_embeddings:

@@ -318,3 +318,28 @@ def test_diffusion_style_sampler_strategies_statistics_and_analysis_tablets():
     assert bool((tab["token_tablet"][:used, :10] == ids[0]).all())             # every sweep starts from the prompt
     assert int(tab["token_tablet"][used:].abs().sum()) == 0                      # rows past the last sweep stay empty
     assert int(tab["counter_tablet"][used - 1].max()) >= 4
+
+
+@needs_ref
+def test_fresh_inference_model_is_initialised_like_the_reference():
+    """A newly constructed HF-style model: same parameter names and per-tensor deviations as the reference's
+    ``_init_weights`` gives -- in particular the up half of every gated-MLP input projection is drawn with the
+    output-projection deviation (the training model uses the input deviation for both halves)."""
+    mod = refload.module("raven_modeling_minimal")
+    cfgmod = refload.module("raven_config_minimal")
+    mod.RavenForCausalLM._tied_weights_keys = {"lm_head.weight": "transformer.wte.weight"}
+    torch.manual_seed(0)
+    theirs = dict(mod.RavenForCausalLM(cfgmod.RavenConfig(**SMALL)).named_parameters())
+    torch.manual_seed(0)
+    ours = dict(RavenForCausalLM(RavenConfig(**SMALL)).named_parameters())
+    assert set(theirs) == set(ours)
+    for name, want in theirs.items():
+        got = ours[name]
+        assert got.shape == want.shape
+        parts = [slice(None)]
+        if name.endswith("mlp.fc.weight"):
+            half = want.shape[0] // 2
+            parts = [slice(0, half), slice(half, None)]
+        for part in parts:
+            a, b = float(want[part].float().std()), float(got[part].float().std())
+            assert abs(a - b) <= 0.06 * max(a, 1e-9), (name, a, b)
