@@ -98,6 +98,11 @@ class _LMBase(nn.Module):
         return fc[..., 0].contiguous(), fc[..., 1].contiguous()
 
     def _loss(self, x, labels, return_logits: bool):
+        """Head and loss.  Every value of ``use_fused_head`` takes this one path: the loss is the mean cross entropy
+        over ALL labelled positions (ignore value -100) of the scaled logits, plus the optional z-loss.  The
+        reference's ``hhe`` head averages per-chunk means over chunks of 1024 rows instead (recpre/utils.py:1629-1668),
+        which is the same number only when every chunk carries the same count of labelled positions; its ``cce`` and
+        ``full-triton`` heads compute the global mean, as here."""
         cfg = self.config
         scale = cfg.init.logit_scale
         logits = None
