@@ -42,19 +42,23 @@ class CLISettings:
     model_name: str = "tiny"                 # "tiny" | a registry shape name | a local HF folder
     tokenizer_path: Optional[str] = None     # local tokenizer folder; None = byte-level fallback
     dataset_args: dict[str, Any] = field(default_factory=lambda: dict(q_col="question", a_col="answer"))
+    dataset_config: str = "main"             # configuration / sub-folder of a dataset saved with the `datasets` package
     max_seq_length: int = 128
     max_samples: Optional[int] = None
     micro_batch_size: int = 2
+    compile: bool = False                    # accepted for command-line compatibility: the kernels are built ahead of time
     max_steps: int = 0
     epochs: int = 1
     batch_size: int = 32
     optim_config: dict[str, Any] = field(default_factory=lambda: dict(lr=5e-7, weight_decay=0.0, betas=(0.9, 0.95),
                                                                        eps=1e-8))
     scheduler_args: dict[str, Any] = field(default_factory=lambda: dict(warmup=0.1, cooldown=0.1, min_lr_ratio=0.001))
+    eval_interval: int = 1_000_000_000       # optimizer steps between validations on the held-out rows
     seed: int = 74
     take_loss_over_all_tokens: bool = False
     max_grad_norm: float = 1_000_000.0
     precision: str = "bf16-true"
+    gradient_checkpointing: bool = False
     num_steps: Optional[int] = None          # fixed recurrence for training; None = sampled (n, k) as in pretraining
     save_final_checkpoint: bool = False
 
@@ -111,8 +115,16 @@ def load_rows(cfg: CLISettings) -> list[tuple[str, str]]:
 
         t = pq.read_table(loc, columns=[q, a]).to_pydict()
         rows = list(zip(t[q], t[a]))
+    elif os.path.isdir(loc):                 # a dataset written by `datasets.save_to_disk` (optionally per config)
+        from datasets import load_from_disk
+
+        sub = os.path.join(loc, cfg.dataset_config)
+        ds = load_from_disk(sub if os.path.isdir(sub) else loc)
+        ds = ds["train"] if hasattr(ds, "keys") and "train" in ds.keys() else ds
+        rows = list(zip(ds[q], ds[a]))
     else:
-        raise ValueError(f"dataset_location must be 'synthetic', a .jsonl or a .parquet file, got {loc!r}")
+        raise ValueError(f"dataset_location must be 'synthetic', a .jsonl / .parquet file or a saved dataset folder, "
+                         f"got {loc!r}")
     return rows[: cfg.max_samples] if cfg.max_samples else rows
 
 
@@ -158,6 +170,28 @@ def wsd_lr(step: int, total: int, base_lr: float, warmup: float, cooldown: float
 
 
 # ---------------------------------------------------------------------------------------------- training
+@torch.no_grad()
+def validate(model, ids, mask, cfg: CLISettings, device) -> dict:
+    """Held-out loss and perplexity over the supervised positions (the reference runs an lm-eval task here,
+    finetuning_simple_example.py:398-428; that package is optional, the loss is always available)."""
+    was_training = model.training
+    model.eval()
+    total, count = 0.0, 0
+    for b in range(0, len(ids), cfg.micro_batch_size):
+        x = ids[b:b + cfg.micro_batch_size].to(device)
+        m = mask[b:b + cfg.micro_batch_size]
+        labels = torch.where(m, ids[b:b + cfg.micro_batch_size], torch.full_like(m, -100, dtype=torch.long))[:, 1:]
+        n = int((labels != -100).sum())
+        if n == 0:
+            continue
+        out = model(x[:, :-1], labels=labels.contiguous().to(device), num_steps=cfg.num_steps)
+        total += float(out.loss) * n
+        count += n
+    model.train(was_training)
+    loss = total / max(count, 1)
+    return {"val_loss": loss, "val_ppl": math.exp(min(loss, 30.0)), "val_tokens": count}
+
+
 def train(cfg: CLISettings) -> dict:
     fabric = Fabric.from_env(grad_sync="flat") if "RANK" in os.environ else Fabric.single(
         torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu"))
@@ -165,9 +199,20 @@ def train(cfg: CLISettings) -> dict:
     dtype = torch.bfloat16 if cfg.precision == "bf16-true" and device.type == "cuda" else torch.float32
     tok = HFChatTokenizer(cfg.tokenizer_path) if cfg.tokenizer_path else ByteTokenizer()
     ids, mask = tokenize(load_rows(cfg), tok, cfg)
+    held = max(1, len(ids) // 20) if cfg.eval_interval < 1_000_000_000 else 0       # last 5 % of the rows
+    val_ids, val_mask = ids[len(ids) - held:], mask[len(mask) - held:]
+    ids, mask = ids[: len(ids) - held], mask[: len(mask) - held]
     ids, mask = ids[fabric.global_rank::fabric.world_size], mask[fabric.global_rank::fabric.world_size]
     model = build_model(cfg, tok.vocab_size, device, dtype)
     model.train()
+    if cfg.gradient_checkpointing:
+        model.gradient_checkpointing = True
+        if hasattr(model, "gradient_checkpointing_enable"):
+            try:
+                model.gradient_checkpointing_enable()
+            except Exception:
+                pass
+    validations = []
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.AdamW(params, **{k: (tuple(v) if isinstance(v, list) else v) for k, v in cfg.optim_config.items()})
     accumulation = max(1, cfg.batch_size // (cfg.micro_batch_size * fabric.world_size))
@@ -198,6 +243,10 @@ def train(cfg: CLISettings) -> dict:
             fabric.print(f"step {step:5d} | loss {loss:7.4f} | grad norm {float(norm):8.3f} | lr {lr:.3e} | "
                          f"{time.time() - t0:6.1f}s")
             step += 1
+            if held and step % cfg.eval_interval == 0:
+                vm = validate(model, val_ids, val_mask, cfg, device)
+                validations.append(dict(step=step, **vm))
+                fabric.print(f"step {step:5d} | validation loss {vm['val_loss']:.4f} | ppl {vm['val_ppl']:.2f}")
             if step >= total_steps:
                 break
     if cfg.save_final_checkpoint and fabric.global_rank == 0:
@@ -206,7 +255,7 @@ def train(cfg: CLISettings) -> dict:
         fabric.print(f"saved {path}")
     fabric.barrier()
     fabric.shutdown()
-    return {"losses": losses, "steps": step}
+    return {"losses": losses, "steps": step, "validations": validations}
 
 
 def parse(argv=None) -> CLISettings:

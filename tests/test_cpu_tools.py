@@ -31,7 +31,17 @@ def test_finetuning_example_learns():
     cfg = F.CLISettings(model_name="tiny", dataset_location="synthetic", max_steps=6, batch_size=4, micro_batch_size=2,
                         max_samples=32, max_seq_length=256, optim_config=dict(lr=3e-3, weight_decay=0.0))
     res = F.train(cfg)
-    assert res["steps"] == 6 and res["losses"][-1] < 0.7 * res["losses"][0]
+    assert res["steps"] == 6 and res["losses"][-1] < 0.7 * res["losses"][0] and res["validations"] == []
+    # periodic validation on held-out rows and activation checkpointing, from the command line
+    cfg2 = F.parse(["--model_name", "tiny", "--dataset_location", "synthetic", "--max_steps", "4", "--batch_size", "4",
+                    "--micro_batch_size", "2", "--max_samples", "40", "--eval_interval", "2", "--compile", "true",
+                    "--gradient_checkpointing", "true", "--dataset_config", "main",
+                    "--optim_config", '{"lr": 3e-3, "weight_decay": 0.0}'])
+    assert cfg2.gradient_checkpointing and cfg2.compile and cfg2.eval_interval == 2
+    res2 = F.train(cfg2)
+    assert [v["step"] for v in res2["validations"]] == [2, 4]
+    assert res2["validations"][-1]["val_loss"] < res2["validations"][0]["val_loss"] and \
+        res2["validations"][0]["val_tokens"] > 0
     assert abs(F.wsd_lr(0, 100, 1.0, 0.1, 0.1, 0.001) - 0.1) < 1e-9
     assert F.wsd_lr(50, 100, 1.0, 0.1, 0.1, 0.001) == 1.0 and F.wsd_lr(99, 100, 1.0, 0.1, 0.1, 0.001) < 0.2
     ids, mask = F.tokenize([("a?", "b")], F.ByteTokenizer(), cfg)
