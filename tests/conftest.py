@@ -22,3 +22,21 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _torch_checkpoint_stays_torchs():
+    """The reference package replaces a private function of ``torch.utils.checkpoint`` when its config module is
+    imported (a work-around written for an older torch).  Tests that import it as an oracle must not change how
+    activation checkpointing behaves in the tests that follow: put torch's own function back after every test."""
+    import torch.utils.checkpoint as ck
+
+    original = _TORCH_CHECKPOINT_GENERATOR
+    yield
+    if ck._checkpoint_without_reentrant_generator is not original:
+        ck._checkpoint_without_reentrant_generator = original
+
+
+import torch.utils.checkpoint as _ck  # noqa: E402
+
+_TORCH_CHECKPOINT_GENERATOR = _ck._checkpoint_without_reentrant_generator
