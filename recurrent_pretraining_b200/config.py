@@ -305,7 +305,11 @@ class ModelConfig:
 
     def __setstate__(self, state):
         self.__dict__.update(state)
-        self.__post_init__()
+        from .models.init import Init
+
+        depth = self.effective_expected_depth if self.is_recurrent else self.n_layer
+        self.init = Init(self.init_strategy, self.n_embd, self.intermediate_size, self.head_size, depth,
+                         self.mup_model_scaling_factor, orthogonal=self.init_orthogonal, skip=self.skip_initialization)
 
     def construct_model(self, **kwargs):
         """recpre/config_dynamic.py:441-444: ``cfg.construct_model(objective=..., gradient_checkpointing=...)``."""
