@@ -7,6 +7,7 @@ actual modules lives in ``models``; this module only validates and derives shape
 """
 from __future__ import annotations
 
+import copy
 import dataclasses
 import math
 from dataclasses import dataclass, field
@@ -265,7 +266,9 @@ class ModelConfig:
         def build(size: int, eps: Optional[float] = None, **_):
             if eps is None or eps == self.norm_eps:
                 return make_norm(self, size)
-            return make_norm(dataclasses.replace(self, norm_eps=eps), size)
+            other = copy.copy(self)                   # a shallow copy: the constructor would apply the muP widths again
+            other.norm_eps = eps
+            return make_norm(other, size)
 
         return build
 
