@@ -24,6 +24,9 @@ class Tokenizer:
         self.processor = None
         self.backend = None
         self.bos_id, self.eos_id, self.pad_id = HUGINN_IDS["bos"], HUGINN_IDS["eos"], HUGINN_IDS["pad"]
+        # ids that the cache-attention / document-block options would need; no tokenizer of the reference defines them
+        # (recpre/tokenizer.py:33-34), so those options stay off
+        self.cache_token_id = self.eod_token_id = None
         if self.checkpoint_dir is None or not self.checkpoint_dir.exists():
             if not allow_missing:
                 raise NotADirectoryError(f"Tokenizer checkpoint {checkpoint_dir} cannot be loaded.")

@@ -507,3 +507,42 @@ def test_derived_settings_match_the_reference_settings_class(name, monkeypatch):
                 "injection_type", "block_class_name", "norm_class_name", "init_strategy", "padded_vocab_size"):
         if hasattr(a.model_config, key):
             assert getattr(b.model_config, key) == getattr(a.model_config, key), key
+
+
+def test_tokenizer_wrapper_matches_the_reference_wrapper(tmp_path):
+    """A small BPE tokenizer trained on the spot, loaded through the reference's wrapper and through ours: special ids,
+    vocabulary size, encodings with every bos / eos / max_length combination, decoding, pickling."""
+    import json
+    import pickle
+
+    import refload
+    from tokenizers import Tokenizer as RawTokenizer
+    from tokenizers import models, pre_tokenizers, trainers
+
+    from recurrent_pretraining_b200.data.tokenizer import Tokenizer
+
+    raw = RawTokenizer(models.BPE(unk_token="<unk>"))
+    raw.pre_tokenizer = pre_tokenizers.Whitespace()
+    trainer = trainers.BpeTrainer(vocab_size=200, special_tokens=["<unk>", "<|begin_text|>", "<|end_text|>", "<|pad|>"])
+    raw.train_from_iterator(["hello world this is a test of the tokenizer", "another line of text for training"] * 20,
+                            trainer)
+    raw.save(str(tmp_path / "tokenizer.json"))
+    special = {"bos_token": "<|begin_text|>", "eos_token": "<|end_text|>", "pad_token": "<|pad|>"}
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(dict(special, tokenizer_class="PreTrainedTokenizerFast")))
+    (tmp_path / "special_tokens_map.json").write_text(json.dumps(special))
+    ours = Tokenizer(tmp_path)
+    assert (ours.bos_id, ours.eos_id, ours.pad_id) == (1, 2, 3) and ours.cache_token_id is None
+    text = "hello world this is a test"
+    if refload.available():
+        theirs = refload.module("tokenizer").Tokenizer(tmp_path)
+        assert (theirs.bos_id, theirs.eos_id, theirs.pad_id, theirs.vocab_size) == (1, 2, 3, ours.vocab_size)
+        for kw in (dict(), dict(bos=True), dict(eos=True), dict(bos=True, eos=True, max_length=5),
+                   dict(bos=False, eos=True, max_length=3)):
+            a, b = theirs.encode(text, **kw), ours.encode(text, **kw)
+            assert a.dtype == b.dtype and torch.equal(a, b), kw
+        ids = theirs.encode("hello world", bos=True, eos=True)
+        assert theirs.decode(ids) == ours.decode(ids)
+    ids = ours.encode(text, bos=True, eos=True)
+    assert int(ids[0]) == 1 and int(ids[-1]) == 2 and "hello" in ours.decode(ids)
+    again = pickle.loads(pickle.dumps(ours))
+    assert torch.equal(again.encode(text), ours.encode(text))
