@@ -267,6 +267,44 @@ def validate(cfg, fabric, state) -> dict:
     return {f"val_loss_depth_{d}": float(v) for d, v in zip(depths, means)}
 
 
+def _reference_metric_names(cfg, fabric, state, metrics: dict, running_loss: float, total_flops: float, t_start: float,
+                            initial_step: int) -> dict:
+    """The same quantities under the names the reference logs (train.py:566-636), so that dashboards built on its runs
+    keep working: whole-job throughput, time bookkeeping, utilisation, memory, and the data-mixture state."""
+    step = state["microbatch_step"]
+    sps = max(metrics.get("steps_per_second", 0.0), 1e-12)
+    elapsed = time.time() - t_start
+    done = max(step - initial_step, 1)
+    out = {
+        "local_loss": running_loss, "local_ppl": math.exp(min(running_loss, 30.0)), "microbatch_step": step,
+        "steps/second": sps, "seconds/step": 1.0 / sps,
+        "tokens/second": metrics.get("tokens_per_second", 0.0) * fabric.world_size,
+        "remaining_time": elapsed / done * max((cfg.max_steps or step) - step, 0), "total_time": elapsed,
+        "global_grad_norm": metrics.get("grad_norm"), "global_train_ppl": math.exp(min(metrics["global_loss"], 30.0)),
+    }
+    if cfg.measure_utilization:
+        out.update({"total_FLOPs": total_flops, "FLOP/S": metrics.get("tflops", 0.0) * fabric.world_size,
+                    "model_flop_utilization": metrics.get("mfu", 0.0)})
+        if fabric.device.type == "cuda":
+            out["max_mem_per_gpu"] = torch.cuda.max_memory_allocated(fabric.device) / 1024 ** 3
+            out["max_mem_reserved_per_gpu"] = torch.cuda.max_memory_reserved(fabric.device) / 1024 ** 3
+            torch.cuda.reset_peak_memory_stats(fabric.device)
+    sched = state.get("data_scheduler")
+    if sched is not None and len(cfg.dataset_names) > 1:
+        weights = list(sched.get_data_weights())
+        samples = fabric.all_reduce(torch.tensor(sched.get_sample_count(), dtype=torch.float32, device=fabric.device),
+                                    "sum").tolist()
+        epochs = fabric.all_reduce(torch.tensor(sched.get_epoch_count(), dtype=torch.float32, device=fabric.device),
+                                   "mean").tolist()
+        total = sum(weights) or 1.0
+        for i, name in enumerate(cfg.dataset_names):
+            out[f"data_scheduler_weight/{name}"] = weights[i]
+            out[f"data_scheduler_norm_weight/{name}"] = weights[i] / total
+            out[f"data_scheduler_sample_count/{name}"] = samples[i]
+            out[f"data_scheduler_epoch_count/{name}"] = epochs[i]
+    return out
+
+
 def check_device_waits(fabric, state) -> None:
     """Raise when a kernel of this rank timed out on a wait (a peer's flag, a pipeline barrier).  A timed-out wait in the
     gradient reduction already poisons that step's norm, so the update is skipped; the run still must not go on, because
@@ -302,7 +340,7 @@ def train(cfg, fabric, state) -> None:
     fabric._loggers = loggers                     # fabric.log_dict / log_to_summary reach the same sinks
     warmup_or_early_fail_allreduce(fabric)
     loss_mean, timer = RunningMean(32), StepTimer()
-    total_tokens = 0
+    total_tokens, total_flops, t_start, initial_step = 0, 0.0, time.time(), state["microbatch_step"]
     tokens_per_mb = cfg.micro_batch_size * cfg.block_size
     for x, y, _meta in state["train_dataloader"]:
         if state["microbatch_step"] >= cfg.max_steps:
@@ -327,6 +365,7 @@ def train(cfg, fabric, state) -> None:
             mc.flops_per_token(cfg.block_size, 0, 0) * tokens_per_mb
         timer.add(tokens_per_mb, flops)
         total_tokens += tokens_per_mb * fabric.world_size
+        total_flops += flops * fabric.world_size
         if state["microbatch_step"] % max(cfg.log_step_interval, 1) == 0:
             loss = float(out["loss"])  # host sync only at log points
             check_device_waits(fabric, state)
@@ -350,6 +389,8 @@ def train(cfg, fabric, state) -> None:
                 metrics.update(harvest_metrics(model))
                 metrics.update(optimizer_telemetry(model, engine.optimizer))
                 enable_monitoring(model, False)
+            metrics.update(_reference_metric_names(cfg, fabric, state, metrics, loss_mean.compute(), total_flops, t_start,
+                                                   initial_step))
             state["metrics"] = metrics
             for lg in loggers:
                 lg.log_metrics(metrics, step=state["microbatch_step"])

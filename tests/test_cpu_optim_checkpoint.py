@@ -369,3 +369,26 @@ def test_lion_update_matches_its_definition_and_reports_update_alignment():
         assert torch.allclose(p.detach(), w, atol=1e-6)
     cos = opt.get_post_step_metrics()["update_cos_sim"]
     assert abs(float(cos) - float((u * u.sign()).sum() / (u.norm() * u.sign().norm()))) < 1e-5
+
+
+def test_trainer_logs_the_reference_metric_names(tmp_path):
+    """One short CPU run through ``trainer.main``: the JSONL log carries this framework's keys and the reference's names
+    for the same quantities (train.py:566-636), per-source mixture state included when there are two sources."""
+    import json
+
+    from recurrent_pretraining_b200.runtime import trainer
+    from recurrent_pretraining_b200.settings import parse_cli
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = parse_cli([f"--config={root}/launch_configs/tiny_cpu_gloo.yaml", f"--out_dir={tmp_path}", "--max_steps=4",
+                     "--save_step_interval=0", "--save_last_step=false", "--world_batch_size=2", "--block_size=64",
+                     "--log_step_interval=2", "--run_name=names"])
+    trainer.main(cfg)
+    rows = [json.loads(line) for line in open(tmp_path / "logs" / "names.jsonl")]
+    last = rows[-1]
+    for key in ("local_loss", "local_ppl", "microbatch_step", "optimizer_step", "steps/second", "seconds/step",
+                "tokens/second", "remaining_time", "total_tokens", "total_time", "global_loss", "global_train_ppl",
+                "global_grad_norm", "total_FLOPs", "FLOP/S", "model_flop_utilization", "lr"):
+        assert key in last, key
+    assert last["microbatch_step"] == 4 and last["remaining_time"] == 0 and last["tokens/second"] > 0
+    assert abs(last["steps/second"] * last["seconds/step"] - 1) < 1e-9 and last["total_FLOPs"] > 0
