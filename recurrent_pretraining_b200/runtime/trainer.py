@@ -189,8 +189,10 @@ def startup(cfg, fabric: Fabric) -> dict:
     mc = cfg.model_config
     if cfg.block_size != mc.block_size and not cfg.ignore_block_size_mismatch:
         mc.block_size = cfg.block_size
-    objective = {"ignore_index": -100, "z_regularization": cfg.z_regularization,
-                 "label_smoothing": cfg.label_smoothing}
+    # as in the reference (train.py:248-253) the objective names the tokenizer's pad id; the training loss ignores only
+    # -100 (recpre/model_dynamic.py:1133-1134), the validation loss skips the pad id as well
+    objective = {"ignore_index": tokenizer.pad_id if tokenizer.pad_id is not None else -1,
+                 "z_regularization": cfg.z_regularization, "label_smoothing": cfg.label_smoothing}
     with torch.device(fabric.device):
         model = mc.construct_model(objective=objective, gradient_checkpointing=cfg.gradient_checkpointing)
     if cfg.model_checkpoint:
@@ -254,17 +256,27 @@ def validate(cfg, fabric, state) -> dict:
     model.eval()
     sums = torch.zeros(len(depths), device=fabric.device)
     n = 0
+    ignore = (getattr(model, "objective", None) or {}).get("ignore_index", -100)
     for i, (x, y, _) in enumerate(state["val_dataloader"]):
         if i >= cfg.eval_iters:
             break
         x, y = x.to(fabric.device, non_blocking=True), y.to(fabric.device, non_blocking=True)
+        if ignore not in (None, -100):             # the validation loss of the reference skips the pad id (train.py:351-354)
+            y = torch.where(y == ignore, torch.full_like(y, -100), y)
         for j, d in enumerate(depths):
             pair = torch.tensor([d, 0]) if mc.is_recurrent else None
             sums[j] += model(x, labels=y, num_steps_pair=pair)["loss"].float()
         n += 1
     model.train()
     means = fabric.all_reduce(sums / max(n, 1), "mean")
-    return {f"val_loss_depth_{d}": float(v) for d, v in zip(depths, means)}
+    out = {f"val_loss_depth_{d}": float(v) for d, v in zip(depths, means)}
+    # the reference's names: the full-depth value twice, and one pair per evaluated depth (train.py:377-383)
+    out["val_loss"] = float(means[-1])
+    out["val_ppl"] = math.exp(min(out["val_loss"], 30.0))
+    for d, v in zip(depths, means):
+        out[f"val_loss_{d}"] = float(v)
+        out[f"val_ppl_{d}"] = math.exp(min(float(v), 30.0))
+    return out
 
 
 def _reference_metric_names(cfg, fabric, state, metrics: dict, running_loss: float, total_flops: float, t_start: float,
