@@ -215,7 +215,9 @@ REFERENCE_NAMES: dict[str, str] = {
     "evaluate_raven.checkpoint_to_hf_converter.hf_implementation_test_and_upload": "evaluate.convert_to_hf:convert",
     "evaluate_raven.checkpoint_to_hf_converter.mini_generate": "evaluate.convert_to_hf:greedy",
     "evaluate_raven.quick_chat_rec_compare.quick_chat_interface": "evaluate.chat_compare:main",
-    "evaluate_raven.record_steps_in_bench.evaluate_with_steps": "evaluate.record_steps:record_steps",
+    "evaluate_raven.record_steps_in_bench.evaluate_with_steps": "evaluate.record_steps:evaluate_with_steps",
+    "evaluate_raven.record_steps_in_bench.save_step_histogram": "evaluate.record_steps:save_step_histogram",
+    "evaluate_raven.record_steps_in_bench.parse_gen_kwargs": "evaluate.record_steps:parse_gen_kwargs",
     "evaluate_raven.saturation_eval_dist.saturation_eval": "evaluate.saturation_eval:saturation_eval",
     "evaluate_raven.misc_benchmark_variants.hf_eval_adaptive_compute.HuginnWrapper": "evaluate.adaptive_eval:AdaptiveComputeLM",
     "vllm.raven_vllm.RavenForvLLM": "engine.decode:DecodeEngine",

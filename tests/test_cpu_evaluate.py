@@ -1,6 +1,7 @@
 """Evaluation helpers on CPU: checkpoint conversion, lm-eval style scoring, depth comparison, step recording."""
 import os
 
+import pytest
 import torch
 
 from recurrent_pretraining_b200.config import ModelConfig
@@ -85,6 +86,29 @@ def test_chat_compare_and_step_recorder():
     s = rec.summary()
     assert s["calls"] == 1 and s["tokens"] >= 5 and 1 <= s["mean_steps"] <= 6
     assert model.generate.__name__ != "patched"
+    # one-pass benchmark + step statistics, with a stand-in for the harness (record_steps_in_bench.py:30-78)
+    from types import SimpleNamespace
+
+    from recurrent_pretraining_b200.evaluate import record_steps as R
+
+    def harness(wrapper, model_args=None, tasks=None, **kw):
+        wrapper.model.generate(torch.tensor([tok.encode("abc")]), max_new_tokens=4, num_steps=6, criterion="kl",
+                               exit_threshold=1e-2)
+        return {"results": {t: {"acc": 1.0} for t in tasks}}
+
+    results, counts = R.evaluate_with_steps(SimpleNamespace(model=model), ["gsm8k"], model_args="x", simple_evaluate=harness)
+    entry = results["results"]["gsm8k"]
+    assert entry["adaptive_total_tokens"] == len(counts) >= 4 and 1 <= entry["adaptive_avg_steps"] <= 6
+    assert entry["adaptive_min_steps"] <= entry["adaptive_max_steps"] and entry["acc"] == 1.0
+    import json
+    import tempfile
+
+    path = R.save_step_histogram(counts, os.path.join(tempfile.mkdtemp(), "steps.json"))
+    assert sum(json.load(open(path)).values()) == len(counts)
+    assert R.parse_gen_kwargs("criterion=kl,exit_threshold=5e-4,continuous_compute=true,num_steps=64") == \
+        {"criterion": "kl", "exit_threshold": 5e-4, "continuous_compute": True, "num_steps": 64}
+    with pytest.raises(ValueError):
+        R.step_statistics([0, 0])
 
 
 def test_adaptive_compute_wrapper_records_steps(tmp_path):
