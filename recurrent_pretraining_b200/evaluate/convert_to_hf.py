@@ -91,6 +91,30 @@ def convert(checkpoint: str, out_dir: str, compare_to_pretrain_implementation: b
     return report
 
 
+def hf_implementation_test_and_upload(checkpoint_name: str, tokenizer_path: str | None = None, device="cpu",
+                                      out_dir: str = "outputs/eval", upload: bool = False,
+                                      compare_to_pretrain_implementation: bool = False,
+                                      hf_gen_crosscheck: bool = False) -> dict:
+    """The reference's entry point (evaluate_raven/checkpoint_to_hf_converter.py:85-193): convert
+    ``checkpoint_name`` into ``<out_dir>/<checkpoint stem>``, copy the tokenizer files beside the weights when a local
+    tokenizer folder is given, optionally compare against the training implementation; ``hf_gen_crosscheck`` is always
+    done (cached against uncached greedy decoding).  ``upload`` pushes to a Hub repository named like the checkpoint
+    and needs network access."""
+    import os
+    import shutil
+
+    model_name = str(checkpoint_name).split("/")[-1].split(".")[0]
+    target = os.path.join(out_dir, model_name)
+    report = convert(checkpoint_name, target, compare_to_pretrain_implementation, dtype=torch.bfloat16
+                     if str(device).startswith("cuda") else torch.float32, device=str(device),
+                     upload_repo=model_name if upload else None)
+    if tokenizer_path and os.path.isdir(tokenizer_path):
+        for name in os.listdir(tokenizer_path):
+            if name.startswith(("tokenizer", "special_tokens", "added_tokens", "vocab", "merges")):
+                shutil.copy(os.path.join(tokenizer_path, name), target)
+    return report
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("checkpoint")

@@ -212,7 +212,8 @@ REFERENCE_NAMES: dict[str, str] = {
     "evaluate_raven.quick_checkpoint_eval.quick_eval_check": "evaluate.local_lm_eval:quick_eval_check",
     "evaluate_raven.quick_checkpoint_eval.prepare_results": "evaluate.local_lm_eval:prepare_results",
     "evaluate_raven.local_lm_eval.cli_evaluate": "evaluate.local_lm_eval:main",
-    "evaluate_raven.checkpoint_to_hf_converter.hf_implementation_test_and_upload": "evaluate.convert_to_hf:convert",
+    "evaluate_raven.checkpoint_to_hf_converter.hf_implementation_test_and_upload":
+        "evaluate.convert_to_hf:hf_implementation_test_and_upload",
     "evaluate_raven.checkpoint_to_hf_converter.mini_generate": "evaluate.convert_to_hf:greedy",
     "evaluate_raven.quick_chat_rec_compare.quick_chat_interface": "evaluate.chat_compare:main",
     "evaluate_raven.record_steps_in_bench.evaluate_with_steps": "evaluate.record_steps:evaluate_with_steps",

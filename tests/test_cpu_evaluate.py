@@ -45,6 +45,17 @@ def test_checkpoint_converts_to_hf_folder_with_parity(tmp_path):
     a = dict(model.named_parameters())["transformer.core_block.0.attn.Wqkv.weight"]
     b = dict(again.named_parameters())["transformer.core_block.0.attn.Wqkv.weight"]
     assert torch.allclose(a, b)
+    # the reference's entry point: output folder named like the checkpoint, tokenizer files copied beside the weights
+    from recurrent_pretraining_b200.evaluate.convert_to_hf import hf_implementation_test_and_upload
+
+    tok_dir = os.path.join(tmp_path, "tok")
+    os.makedirs(tok_dir)
+    open(os.path.join(tok_dir, "tokenizer.json"), "w").write("{}")
+    rep2 = hf_implementation_test_and_upload(path, tok_dir, device="cpu", out_dir=os.path.join(tmp_path, "eval"),
+                                             upload=False, compare_to_pretrain_implementation=True)
+    target = os.path.join(tmp_path, "eval", "step-00000008-run_0")
+    assert rep2["cache_consistent"] and os.path.exists(os.path.join(target, "config.json"))
+    assert os.path.exists(os.path.join(target, "tokenizer.json"))
 
 
 def test_lm_eval_style_scoring(tmp_path):
