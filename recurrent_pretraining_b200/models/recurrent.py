@@ -429,6 +429,10 @@ class GPT(_LMBase):
             wte=nn.Embedding(config.padded_vocab_size, config.n_embd),
             h=nn.ModuleList(make_block(config, i) for i in range(config.n_layer)),
             ln_f=make_norm(config)))
+        if config.use_abacus:
+            # the reference creates this positional table for its baseline model and never reads it
+            # (recpre/model_dynamic.py:36-40); it exists here so that such checkpoints load key for key
+            self.transformer["abacus"] = nn.Embedding(config.block_size, config.n_embd)
         self.lm_head = Linear(config.n_embd, config.padded_vocab_size, bias=config.lm_head_bias,
                               init=lambda w: init.init_weight_(w, "head"))
         _accept_transposed_head(self)
