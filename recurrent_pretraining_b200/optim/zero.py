@@ -15,6 +15,9 @@ from torch.optim import Optimizer
 
 
 class SimpleZeroRedundancyOptimizer(Optimizer):
+    verbose = False
+    single_rank_return = False       # True: ``state_dict`` gathers every local rank's state on the node's first rank
+
     def __init__(self, params, optimizer_class, **kwargs):
         params = list(params)
         self.arg_lr = kwargs.get("lr")
@@ -76,8 +79,36 @@ class SimpleZeroRedundancyOptimizer(Optimizer):
             for p in weights[i:: self.local_devices - 1]:
                 dist.broadcast(p.data, src=self.node_root + i + 1, group=self.local_pg)
 
-    def state_dict(self):
-        return [self.local_optim_group.state_dict()]
+    @staticmethod
+    def _cpu_state_dict(state_dict: dict) -> dict:
+        out = {}
+        for k, v in state_dict.items():
+            if k == "state":
+                out[k] = {pid: {n: (t.cpu() if torch.is_tensor(t) else t) for n, t in st.items()} for pid, st in v.items()}
+            else:
+                out[k] = v
+        return out
+
+    def state_dict(self, cpu_before_gather: bool = True):
+        """``[local state]`` on every rank; with ``single_rank_return`` the node's first rank gets the list of all local
+        states and the others an empty one (recpre/optim.py:212-236)."""
+        local = self.local_optim_group.state_dict()
+        if self.local_pg is None:
+            return [self._cpu_state_dict(local)]
+        if not self.single_rank_return:
+            return [local]
+        local = self._cpu_state_dict(local) if cpu_before_gather else local
+        states = [None] * self.local_devices if self.local_rank == 0 else None
+        dist.gather_object(local, states, dst=self.node_root, group=self.local_pg)
+        if self.local_rank == 0:
+            return states if cpu_before_gather else [self._cpu_state_dict(s) for s in states]
+        return [{"state": {}, "param_groups": []}]
 
     def load_state_dict(self, state_dict):
-        self.local_optim_group.load_state_dict(state_dict[0] if isinstance(state_dict, list) else state_dict)
+        if isinstance(state_dict, list):
+            state_dict = state_dict[self.local_rank] if (self.single_rank_return and len(state_dict) > 1) \
+                else state_dict[0]
+        self.local_optim_group.load_state_dict(state_dict)
+
+    def __repr__(self) -> str:
+        return type(self).__name__ + repr(self.local_optim_group)
