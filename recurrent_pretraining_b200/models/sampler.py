@@ -28,11 +28,34 @@ def _gen(seed: int) -> torch.Generator:
     return g
 
 
-def _negative_binomial(r: float, mean: float) -> float:
-    """Gamma-Poisson mixture with dispersion r and the given mean (global RNG, as in the reference)."""
-    p = r / (r + mean)
-    lam = torch.distributions.Gamma(torch.tensor(float(r)), torch.tensor(p / (1 - p))).sample()
-    return float(torch.poisson(lam))
+def sample_gamma(alpha, beta):
+    """Gamma(alpha, rate beta) by the Marsaglia-Tsang squeeze on the global generator (alpha < 1 through the
+    alpha + 1 boost), drawing the same random numbers in the same order as recpre/model_dynamic.py:1465-1482."""
+    if alpha < 1:
+        return sample_gamma(alpha + 1, beta) * torch.rand(1).pow(1 / alpha)
+    d = alpha - 1 / 3
+    c = 1 / math.sqrt(9 * d)
+    while True:
+        x = torch.randn(1)
+        v = (1 + c * x) ** 3
+        u = torch.rand(1)
+        if u < 1 - 0.0331 * x ** 4:
+            return d * v / beta
+        if torch.log(u) < 0.5 * x * x + d * (1 - v + torch.log(v)):
+            return d * v / beta
+
+
+def sample_negative_binomial(t, target_mean):
+    """Gamma-Poisson mixture whose mean is ``target_mean``: success probability p = mean / (t / 2 + mean), dispersion
+    r = mean p / (1 - p) (recpre/model_dynamic.py:1485-1492)."""
+    p = target_mean / (t / 2 + target_mean)
+    r = target_mean * p / (1 - p)
+    beta = (1 - p) / p
+    return torch.poisson(sample_gamma(r, beta))
+
+
+def _negative_binomial(t: float, mean: float) -> float:
+    return float(sample_negative_binomial(t, mean))
 
 
 def depth_targets(scheme: str, mean_recurrence: int, mean_backprop_depth: int, step: int) -> tuple[int, int]:

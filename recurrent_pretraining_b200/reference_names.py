@@ -87,6 +87,8 @@ REFERENCE_NAMES: dict[str, str] = {
     "recpre.model_dynamic.precompute_freqs_cis": "ops.reference:freqs_cis_buffer",
     "recpre.model_dynamic.apply_rotary_emb_complex_like": "ops.reference:rope_interleaved",
     "recpre.model_dynamic.RecurrentGPT.randomized_iteration_sampler": "models.sampler:sample_recurrence",
+    "recpre.model_dynamic.sample_gamma": "models.sampler:sample_gamma",
+    "recpre.model_dynamic.sample_negative_binomial": "models.sampler:sample_negative_binomial",
     # ---- recpre/norms.py, init.py, misc.py, ops.py ----------------------------------------------------------------------
     "recpre.norms.RMSNorm": "models.blocks:RMSNorm",
     "recpre.norms.RMSNorm_llama": "models.blocks:RMSNorm",
