@@ -46,6 +46,9 @@ def chat_supervise_assistant(row, tok, add_bos, add_eos):
     return ids, labels
 
 
+apply_chat_template_supervise_all = chat_supervise_all                 # the reference's function names
+apply_chat_template_supervise_assistant = chat_supervise_assistant
+
 FORMAT_FNS = {
     "pass_text": pass_text,
     "concat_input_target": concat_input_target,

@@ -154,6 +154,11 @@ REFERENCE_NAMES: dict[str, str] = {
     "recpre.data_loading_utils.pass_text": "data.collate:pass_text",
     "recpre.data_loading_utils.concat_input_target": "data.collate:concat_input_target",
     "recpre.data_loading_utils.condition_input_supervise_target": "data.collate:condition_input_supervise_target",
+    "recpre.data_loading_utils.apply_chat_template_supervise_all": "data.collate:apply_chat_template_supervise_all",
+    "recpre.data_loading_utils.apply_chat_template_supervise_assistant":
+        "data.collate:apply_chat_template_supervise_assistant",
+    "recpre.data_loading_utils.apply_formatting": "data.collate:apply_formatting",
+    "recpre.data_loading_utils.shift_inputs_and_labels": "data.collate:shift_inputs_and_labels",
     "recpre.data_scheduler_utils.DataScheduler": "data.scheduler:DataScheduler",
     "recpre.data_scheduler_utils.DataSchedulerTracker": "data.scheduler:DataSchedulerTracker",
     "recpre.data_scheduler_utils.GetScheduler": "data.scheduler:GetScheduler",
